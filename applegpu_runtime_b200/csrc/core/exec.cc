@@ -1,0 +1,360 @@
+// Node executor: turns one graph node plus materialised inputs into kernel launches.
+//
+// Plays the role of LazyRuntime::execute_node_nb (lazy.rs:1571-2429) and of the per-op bodies
+// of EagerRuntime (eager.rs:246-1172). Layout-only ops (transpose, slice, reshape) return
+// views that share the input buffer whenever the strides allow it — upstream materialises each
+// of them with a copy kernel (lazy.rs:1891-1917, :2246-2262) — and consumers either read the
+// strided view directly (matmul, element-wise, copy) or make it contiguous first.
+#include "runtime.h"
+#include <atomic>
+#include <cmath>
+
+namespace ag {
+
+std::atomic<uint64_t> g_launch_count{0};
+uint64_t launch_count() { return g_launch_count.load(); }
+#define AG_LAUNCH(expr) do { AG_RETURN_IF_ERROR(expr); g_launch_count.fetch_add(1, std::memory_order_relaxed); } while (0)
+
+static Status alloc_out(const Dims& shape, DType dt, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
+  out->shape = shape; out->strides = contiguous_strides(shape); out->dtype = dt; out->byte_offset = 0; out->has_meta = true;
+  size_t nbytes = (size_t)numel_of(shape) * dtype_size(dt);
+  if (out_buf) {
+    if (out_buf->capacity < nbytes) return Status::compute("pre-allocated output is too small");
+    out->buf = out_buf;
+    return Status::OK();
+  }
+  return Shared::get().pool.acquire(nbytes == 0 ? 4 : nbytes, &out->buf);
+}
+
+Status make_contiguous(const TensorRec& in, TensorRec* out) {
+  if (in.contiguous()) { *out = in; return Status::OK(); }
+  AG_RETURN_IF_ERROR(alloc_out(in.shape, in.dtype, out, nullptr));
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.dry) return Status::OK();
+  AG_LAUNCH(k::copy_strided(ctx.stream, in.view(), out->view()));
+  return Status::OK();
+}
+
+Status upload(const TensorRec& t, const void* host, size_t nbytes) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.dry) return Status::compute("no CUDA device (dry-run mode)");
+  if (!t.contiguous()) return Status::invalid("upload needs a contiguous tensor");
+  if (nbytes > t.nbytes()) return Status::invalid("upload of " + std::to_string(nbytes) + " bytes exceeds tensor size " + std::to_string(t.nbytes()));
+  if (nbytes == 0) return Status::OK();
+  cudaError_t e = cudaMemcpyAsync(t.data(), host, nbytes, cudaMemcpyHostToDevice, ctx.stream);
+  if (e != cudaSuccess) return Status::compute(std::string("upload: ") + cudaGetErrorString(e));
+  return Status::OK();
+}
+
+Status download(const TensorRec& t, void* host, size_t nbytes) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.dry) return Status::compute("no CUDA device (dry-run mode)");
+  TensorRec c;
+  AG_RETURN_IF_ERROR(make_contiguous(t, &c));
+  if (nbytes > c.nbytes()) nbytes = c.nbytes();
+  if (nbytes) {
+    cudaError_t e = cudaMemcpyAsync(host, c.data(), nbytes, cudaMemcpyDeviceToHost, ctx.stream);
+    if (e != cudaSuccess) return Status::compute(std::string("download: ") + cudaGetErrorString(e));
+  }
+  cudaError_t e = cudaStreamSynchronize(ctx.stream);
+  if (e != cudaSuccess) return Status::compute(std::string("synchronize: ") + cudaGetErrorString(e));
+  return Status::OK();
+}
+
+// Strides that present `old` (shape, strides) as `new_shape` without moving data, if any.
+static bool view_strides(const Dims& old_shape, const Dims& old_strides, const Dims& new_shape, Dims* out) {
+  int64_t numel = numel_of(old_shape);
+  out->assign(new_shape.size(), 0);
+  if (numel == 0) { *out = contiguous_strides(new_shape); return true; }
+  int vd = (int)new_shape.size() - 1;
+  if (old_shape.empty()) { for (auto& s : *out) s = 1; return true; }
+  int64_t chunk_base = old_strides.back();
+  int64_t t_numel = 1, v_numel = 1;
+  for (int td = (int)old_shape.size() - 1; td >= 0; td--) {
+    t_numel *= old_shape[td];
+    if (td == 0 || (old_shape[td - 1] != 1 && old_strides[td - 1] != t_numel * chunk_base)) {
+      while (vd >= 0 && (v_numel < t_numel || new_shape[vd] == 1)) {
+        (*out)[vd] = v_numel * chunk_base;
+        v_numel *= new_shape[vd];
+        vd--;
+      }
+      if (v_numel != t_numel) return false;
+      if (td > 0) { chunk_base = old_strides[td - 1]; t_numel = 1; v_numel = 1; }
+    }
+  }
+  return vd == -1;
+}
+
+// Describe a (possibly strided, possibly broadcast) batched matmul for the GEMM launchers.
+static Status build_gemm(const TensorRec& a, const TensorRec& b, const TensorRec& c, k::GemmDesc* d,
+                         std::vector<TensorRec>* keep_alive) {
+  TensorRec A = a, B = b;
+  auto fill = [&](const TensorRec& A2, const TensorRec& B2) -> bool {
+    int an = (int)A2.shape.size(), bn = (int)B2.shape.size(), cn = (int)c.shape.size();
+    d->m = A2.shape[an - 2]; d->k = A2.shape[an - 1]; d->n = B2.shape[bn - 1];
+    d->a_row = A2.strides[an - 2]; d->a_col = A2.strides[an - 1];
+    d->b_row = B2.strides[bn - 2]; d->b_col = B2.strides[bn - 1];
+    d->c_row = c.strides[cn - 2];
+    // batch dims of C with per-operand strides (0 where the operand broadcasts)
+    int nb = cn - 2;
+    std::vector<int64_t> bs(nb), sa(nb, 0), sb(nb, 0), sc(nb);
+    for (int i = 0; i < nb; i++) {
+      bs[i] = c.shape[i]; sc[i] = c.strides[i];
+      int ai = i - (nb - (an - 2)), bi = i - (nb - (bn - 2));
+      if (ai >= 0 && A2.shape[ai] != 1) sa[i] = A2.strides[ai];
+      if (bi >= 0 && B2.shape[bi] != 1) sb[i] = B2.strides[bi];
+    }
+    // drop size-1 dims, merge neighbours that are jointly collapsible
+    std::vector<int64_t> ms, ma, mb, mc;
+    for (int i = 0; i < nb; i++) {
+      if (bs[i] == 1) continue;
+      if (!ms.empty() && ma.back() == sa[i] * bs[i] && mb.back() == sb[i] * bs[i] && mc.back() == sc[i] * bs[i]) {
+        ms.back() *= bs[i]; ma.back() = sa[i]; mb.back() = sb[i]; mc.back() = sc[i];
+      } else { ms.push_back(bs[i]); ma.push_back(sa[i]); mb.push_back(sb[i]); mc.push_back(sc[i]); }
+    }
+    if (ms.size() > 2) return false;
+    d->batch = 1; d->batch_inner = 1;
+    d->a_batch = d->b_batch = d->c_batch = 0; d->a_batch_inner = d->b_batch_inner = d->c_batch_inner = 0;
+    if (ms.size() == 1) { d->batch = ms[0]; d->a_batch = ma[0]; d->b_batch = mb[0]; d->c_batch = mc[0]; }
+    if (ms.size() == 2) {
+      d->batch = ms[0]; d->a_batch = ma[0]; d->b_batch = mb[0]; d->c_batch = mc[0];
+      d->batch_inner = ms[1]; d->a_batch_inner = ma[1]; d->b_batch_inner = mb[1]; d->c_batch_inner = mc[1];
+    }
+    return true;
+  };
+  if (!fill(A, B)) {
+    TensorRec Ac, Bc;
+    AG_RETURN_IF_ERROR(make_contiguous(A, &Ac));
+    AG_RETURN_IF_ERROR(make_contiguous(B, &Bc));
+    keep_alive->push_back(Ac); keep_alive->push_back(Bc);
+    A = Ac; B = Bc;
+    if (!fill(A, B)) return Status::compute("matmul batch layout cannot be expressed in two stride levels");
+  }
+  d->a = A.data(); d->b = B.data(); d->c = c.data();
+  d->dtype = A.dtype; d->b_dtype = B.dtype;
+  return Status::OK();
+}
+
+static k::UnOp unop_of(Op op) {
+  switch (op) {
+    case Op::Neg: return k::UnOp::Neg; case Op::Relu: return k::UnOp::Relu; case Op::Exp: return k::UnOp::Exp;
+    case Op::Log: return k::UnOp::Log; case Op::Sqrt: return k::UnOp::Sqrt; case Op::Tanh: return k::UnOp::Tanh;
+    case Op::Sin: return k::UnOp::Sin; case Op::Cos: return k::UnOp::Cos; case Op::Gelu: return k::UnOp::Gelu;
+    case Op::GeluExact: return k::UnOp::GeluExact; case Op::Sigmoid: return k::UnOp::Sigmoid; case Op::Abs: return k::UnOp::Abs;
+    case Op::Sign: return k::UnOp::Sign; default: return k::UnOp::Copy;
+  }
+}
+
+static Status attention_exec(const TensorRec& q, const TensorRec& kk, const TensorRec& v, bool causal, TensorRec* out,
+                             std::shared_ptr<Buffer> out_buf, const Dims& out_shape) {
+  // softmax[_causal]((Q K^T) * 1/sqrt(d_k)) V with the score matrix materialised in the storage
+  // dtype, as ops.rs:1559-1569 / :1605-1615 compose it; the scale rides in the first GEMM's epilogue.
+  DeviceCtx& ctx = DeviceCtx::get();
+  int qn = (int)q.shape.size(), kn = (int)kk.shape.size();
+  int64_t tq = q.shape[qn - 2], dk = q.shape[qn - 1], tk = kk.shape[kn - 2];
+  Dims sshape(out_shape.begin(), out_shape.end() - 1);
+  sshape.push_back(tk);
+  TensorRec scores;
+  AG_RETURN_IF_ERROR(alloc_out(sshape, q.dtype, &scores, nullptr));
+  AG_RETURN_IF_ERROR(alloc_out(out_shape, q.dtype, out, out_buf));
+  if (ctx.dry) return Status::OK();
+  (void)tq;
+  TensorRec kt = kk;  // K^T as a view
+  std::swap(kt.shape[kn - 1], kt.shape[kn - 2]);
+  std::swap(kt.strides[kn - 1], kt.strides[kn - 2]);
+  std::vector<TensorRec> keep;
+  k::GemmDesc g1;
+  AG_RETURN_IF_ERROR(build_gemm(q, kt, scores, &g1, &keep));
+  g1.ep.alpha = 1.0f / std::sqrt((float)dk);
+  AG_LAUNCH(k::matmul(ctx.stream, g1));
+  AG_LAUNCH(k::softmax(ctx.stream, scores.view(), causal, scores.view()));
+  k::GemmDesc g2;
+  AG_RETURN_IF_ERROR(build_gemm(scores, v, *out, &g2, &keep));
+  AG_LAUNCH(k::matmul(ctx.stream, g2));
+  return Status::OK();
+}
+
+Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  AG_RETURN_IF_ERROR(ctx.make_current());
+  const OpKind& kd = node.op;
+  cudaStream_t s = ctx.stream;
+  const bool dry = ctx.dry;
+
+  // layout-only ops first: they may return views
+  switch (kd.op) {
+    case Op::Transpose: {
+      TensorRec v = *in[0];
+      std::swap(v.shape[kd.i0], v.shape[kd.i1]);
+      std::swap(v.strides[kd.i0], v.strides[kd.i1]);
+      if (!out_buf) { *out = v; out->has_meta = true; return Status::OK(); }
+      AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
+      if (!dry) AG_LAUNCH(k::copy_strided(s, v.view(), out->view()));
+      return Status::OK();
+    }
+    case Op::Slice: {
+      TensorRec v = *in[0];
+      v.byte_offset += (size_t)(kd.i1 * v.strides[kd.i0]) * dtype_size(v.dtype);
+      v.shape[kd.i0] = kd.i2 - kd.i1;
+      if (!out_buf) { *out = v; out->has_meta = true; return Status::OK(); }
+      AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
+      if (!dry) AG_LAUNCH(k::copy_strided(s, v.view(), out->view()));
+      return Status::OK();
+    }
+    case Op::Reshape: {
+      Dims ns;
+      if (!out_buf && view_strides(in[0]->shape, in[0]->strides, node.out_shape, &ns)) {
+        *out = *in[0]; out->shape = node.out_shape; out->strides = ns; out->has_meta = true;
+        return Status::OK();
+      }
+      // gather into a contiguous buffer of the old shape, then relabel
+      AG_RETURN_IF_ERROR(alloc_out(in[0]->shape, node.out_dtype, out, out_buf));
+      if (!dry) AG_LAUNCH(k::copy_strided(s, in[0]->view(), out->view()));
+      out->shape = node.out_shape; out->strides = contiguous_strides(node.out_shape);
+      return Status::OK();
+    }
+    default: break;
+  }
+
+  if (kd.op == Op::FusedAttention) return attention_exec(*in[0], *in[1], *in[2], kd.causal, out, out_buf, node.out_shape);
+
+  AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
+  if (dry) return Status::OK();
+  TView ov = out->view();
+
+  switch (kd.op) {
+    case Op::Add: case Op::Sub: case Op::Mul: case Op::Div: {
+      k::BinOp bop = kd.op == Op::Add ? k::BinOp::Add : kd.op == Op::Sub ? k::BinOp::Sub : kd.op == Op::Mul ? k::BinOp::Mul : k::BinOp::Div;
+      AG_LAUNCH(k::binary(s, bop, in[0]->view(), in[1]->view(), ov));
+      return Status::OK();
+    }
+    case Op::Neg: case Op::Relu: case Op::Exp: case Op::Log: case Op::Sqrt: case Op::Tanh: case Op::Sin: case Op::Cos:
+    case Op::Gelu: case Op::GeluExact: case Op::Sigmoid: case Op::Abs: case Op::Sign:
+      AG_LAUNCH(k::unary(s, unop_of(kd.op), in[0]->view(), ov));
+      return Status::OK();
+    case Op::ScalarMul:
+      AG_LAUNCH(k::scalar_mul(s, in[0]->view(), kd.f0, ov));
+      return Status::OK();
+    case Op::FusedElementwise: {
+      std::vector<TView> views;
+      for (auto* t : in) views.push_back(t->view());
+      AG_LAUNCH(k::fused_elementwise(s, kd.prog, views.data(), ov));
+      return Status::OK();
+    }
+    case Op::Matmul: case Op::FusedLinear: {
+      std::vector<TensorRec> keep;
+      k::GemmDesc g;
+      AG_RETURN_IF_ERROR(build_gemm(*in[0], *in[1], *out, &g, &keep));
+      if (kd.op == Op::FusedLinear) {
+        size_t idx = 2;
+        g.ep.alpha = kd.f0;
+        g.ep.act = kd.act;
+        TensorRec tmp;
+        if (kd.has_bias) { AG_RETURN_IF_ERROR(make_contiguous(*in[idx++], &tmp)); keep.push_back(tmp); g.ep.bias = keep.back().data(); }
+        if (kd.has_residual) {
+          AG_RETURN_IF_ERROR(make_contiguous(*in[idx++], &tmp)); keep.push_back(tmp);
+          if (keep.back().shape != out->shape) return Status::compute("fused residual shape mismatch");
+          g.ep.residual = keep.back().data();
+        }
+      }
+      AG_LAUNCH(k::matmul(s, g));
+      return Status::OK();
+    }
+    case Op::MatmulInt8: {
+      // x [..,M,K] @ (w_q [N,K] * scales[N])^T ; B is K-major int8, scales applied in the epilogue.
+      TensorRec x, w;
+      AG_RETURN_IF_ERROR(make_contiguous(*in[0], &x));
+      AG_RETURN_IF_ERROR(make_contiguous(*in[1], &w));
+      k::GemmDesc g;
+      g.dtype = x.dtype; g.b_dtype = DType::I8;
+      g.a = x.data(); g.b = w.data(); g.c = out->data();
+      g.k = x.shape.back(); g.m = numel_of(x.shape) / (g.k ? g.k : 1); g.n = w.shape[0];
+      g.batch = 1; g.batch_inner = 1;
+      g.a_row = g.k; g.a_col = 1; g.a_batch = 0;
+      g.b_row = 1; g.b_col = g.k; g.b_batch = 0;
+      g.c_row = g.n; g.c_batch = 0;
+      g.ep.b_scales = (const float*)in[2]->data();
+      AG_LAUNCH(k::matmul(s, g));
+      return Status::OK();
+    }
+    case Op::Softmax: case Op::SoftmaxCausal: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::softmax(s, c.view(), kd.op == Op::SoftmaxCausal, ov));
+      return Status::OK();
+    }
+    case Op::LayerNorm: {
+      TensorRec c, g, b;
+      AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &g)); AG_RETURN_IF_ERROR(make_contiguous(*in[2], &b));
+      AG_LAUNCH(k::layer_norm(s, c.view(), g.view(), b.view(), kd.f0, ov));
+      return Status::OK();
+    }
+    case Op::Embedding: {
+      TensorRec w, ix; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &w)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &ix));
+      AG_LAUNCH(k::embedding(s, w.view(), ix.view(), ov));
+      return Status::OK();
+    }
+    case Op::FusedEmbedAdd: {
+      TensorRec w0, i0, w1, i1;
+      AG_RETURN_IF_ERROR(make_contiguous(*in[0], &w0)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &i0));
+      AG_RETURN_IF_ERROR(make_contiguous(*in[2], &w1)); AG_RETURN_IF_ERROR(make_contiguous(*in[3], &i1));
+      AG_LAUNCH(k::embedding_add(s, w0.view(), i0.view(), w1.view(), i1.view(), ov));
+      return Status::OK();
+    }
+    case Op::AddBias: {
+      TensorRec c, b; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &b));
+      AG_LAUNCH(k::add_bias(s, c.view(), b.view(), kd.act, ov));
+      return Status::OK();
+    }
+    case Op::Argmax: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::argmax(s, c.view(), ov));
+      return Status::OK();
+    }
+    case Op::Sum: case Op::Mean: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::sum_last(s, c.view(), ov, kd.op == Op::Mean));
+      return Status::OK();
+    }
+    case Op::Concat: {
+      // two strided copies into disjoint slices of the output
+      int64_t dim = kd.i0;
+      TensorRec lo = *out, hi = *out;
+      lo.shape[dim] = in[0]->shape[dim];
+      hi.shape[dim] = in[1]->shape[dim];
+      hi.byte_offset += (size_t)(in[0]->shape[dim] * out->strides[dim]) * dtype_size(out->dtype);
+      AG_LAUNCH(k::copy_strided(s, in[0]->view(), lo.view()));
+      AG_LAUNCH(k::copy_strided(s, in[1]->view(), hi.view()));
+      return Status::OK();
+    }
+    case Op::Gather: case Op::IndexSelect: {
+      TensorRec c, ix; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &ix));
+      if (kd.op == Op::Gather) AG_LAUNCH(k::gather2d(s, c.view(), (int)kd.i0, ix.view(), ov));
+      else AG_LAUNCH(k::index_select2d(s, c.view(), (int)kd.i0, ix.view(), ov));
+      return Status::OK();
+    }
+    case Op::ThresholdBackward: {
+      TensorRec g, x; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &g)); AG_RETURN_IF_ERROR(make_contiguous(*in[1], &x));
+      AG_LAUNCH(k::threshold_backward(s, g.view(), x.view(), kd.f0, ov));
+      return Status::OK();
+    }
+    case Op::Cast: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::cast(s, c.view(), ov));
+      return Status::OK();
+    }
+    case Op::Quantize: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::quantize(s, c.view(), kd.f0, (int)kd.i0, ov));
+      return Status::OK();
+    }
+    case Op::Dequantize: {
+      TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
+      AG_LAUNCH(k::dequantize(s, c.view(), kd.f0, (int)kd.i0, ov));
+      return Status::OK();
+    }
+    default:
+      return Status::compute(std::string(op_debug_name(kd.op)) + " is unsupported on this backend");
+  }
+}
+
+}  // namespace ag

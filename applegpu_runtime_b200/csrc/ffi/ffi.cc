@@ -1,0 +1,866 @@
+// extern "C" surface: include/applegpu_b200_ffi.h (the reference's symbols) and
+// include/applegpu_b200_ext.h (additive). Mirrors backend_ffi.rs and eager_ffi.rs: one global
+// runtime per flavour behind a mutex, idempotent init, thread-local last-error strings, no
+// exceptions across the boundary.
+#include "../../../include/applegpu_b200_ffi.h"
+#include "../../../include/applegpu_b200_ext.h"
+#include "../core/runtime.h"
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+namespace ag {
+uint64_t launch_count();
+namespace k {
+void set_matmul_path(int mode);
+int matmul_take_status(cudaStream_t s);
+}
+}
+using namespace ag;
+
+namespace {
+
+struct LazyState { std::mutex mu; LazyRuntime rt; bool ready = false; };
+struct EagerState { std::mutex mu; EagerRuntime rt; bool ready = false; };
+LazyState& lazy_state() { static LazyState s; return s; }
+EagerState& eager_state() { static EagerState s; return s; }
+
+thread_local std::string t_ffi_error; thread_local bool t_ffi_has_error = false;
+thread_local std::string t_eager_error; thread_local bool t_eager_has_error = false;
+void set_ffi_error(const std::string& m) { t_ffi_error = m; t_ffi_has_error = true; }
+void set_eager_error(const std::string& m) { t_eager_error = m; t_eager_has_error = true; }
+
+Dims to_dims(const uint64_t* d, uint32_t n) { Dims v(n); for (uint32_t i = 0; i < n; i++) v[i] = (int64_t)d[i]; return v; }
+
+struct LazyMetaSrc : MetaSource {
+  const LazyRuntime* rt;
+  explicit LazyMetaSrc(const LazyRuntime* r) : rt(r) {}
+  Status shape(uint64_t id, Dims* out) const override { return rt->shape(id, out); }
+  Status dtype(uint64_t id, DType* out) const override { return rt->dtype(id, out); }
+};
+
+bool ffi_ready(const char* what) {
+  if (lazy_state().ready) return true;
+  set_ffi_error(std::string(what) + " failed: applegpu FFI not initialized - call applegpu_ffi_init() first");
+  return false;
+}
+bool eager_ready() {
+  if (eager_state().ready) return true;
+  set_eager_error("applegpu eager FFI not initialized - call applegpu_eager_init() first");
+  return false;
+}
+
+// Validate + record one node; returns its id or 0 (message prefixed "<name> failed: ").
+uint64_t record(const char* name, OpKind kind, std::vector<uint64_t> inputs) {
+  if (!ffi_ready(name)) return 0;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  OpNode node;
+  node.op = std::move(kind);
+  node.inputs = std::move(inputs);
+  LazyMetaSrc src(&st.rt);
+  Status s = infer_node(src, &node);
+  if (!s.ok()) { set_ffi_error(std::string(name) + " failed: " + s.to_string()); return 0; }
+  node.id = next_op_id();
+  uint64_t id = node.id;
+  st.rt.record_op(std::move(node));
+  return id;
+}
+OpKind mk(Op op) { OpKind k; k.op = op; return k; }
+
+uint8_t* record_out(const char* name, OpKind kind, std::vector<uint64_t> inputs, uint64_t* out_id) {
+  uint64_t id = record(name, std::move(kind), std::move(inputs));
+  if (!id) return nullptr;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  void* ptr = nullptr;
+  Status s = st.rt.preallocate_output(id, &ptr);
+  if (!s.ok()) { set_ffi_error("alloc output failed: " + s.to_string()); return nullptr; }
+  if (out_id) *out_id = id;
+  return static_cast<uint8_t*>(ptr);
+}
+
+uint8_t* eager_run(OpKind kind, std::vector<uint64_t> inputs, uint64_t* out_id) {
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  uint64_t id = 0; void* ptr = nullptr;
+  Status s = st.rt.run(std::move(kind), inputs, &id, &ptr);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  if (out_id) *out_id = id;
+  return static_cast<uint8_t*>(ptr);
+}
+
+Status init_device(bool dry) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.ready) return Status::OK();
+  if (dry) { ctx.dry = true; ctx.ready = true; ctx.name = "dry-run (no device)"; return Status::OK(); }
+  return ctx.init(true);
+}
+
+cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+void* g_flush_buf = nullptr;
+constexpr size_t kFlushBytes = (size_t)256 << 20;  // 2x the 126 MB L2
+
+}  // namespace
+
+extern "C" {
+
+// ── graph flavour ───────────────────────────────────────────────────────────
+bool applegpu_ffi_init(void) {
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.ready) return true;
+  Status s = init_device(false);
+  if (!s.ok()) { set_ffi_error(s.to_string()); return false; }
+  Shared::get();
+  st.ready = true;
+  return true;
+}
+bool applegpu_ffi_init_dry(void) {
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.ready) return DeviceCtx::get().dry;
+  Status s = init_device(true);
+  if (!s.ok()) { set_ffi_error(s.to_string()); return false; }
+  Shared::get();
+  st.ready = true;
+  return DeviceCtx::get().dry;
+}
+const char* applegpu_ffi_last_error(void) { return t_ffi_has_error ? t_ffi_error.c_str() : nullptr; }
+
+uint8_t* applegpu_ffi_alloc(uint64_t size_bytes, int8_t, uint64_t* out_tensor_id) {
+  if (!ffi_ready("alloc")) return nullptr;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  uint64_t id = 0; void* ptr = nullptr;
+  Status s = st.rt.alloc_raw((size_t)size_bytes, &id, &ptr);
+  if (!s.ok()) { set_ffi_error("alloc failed: " + s.to_string()); return nullptr; }
+  if (out_tensor_id) *out_tensor_id = id;
+  return static_cast<uint8_t*>(ptr);
+}
+void applegpu_ffi_free(uint64_t tensor_id) {
+  if (!lazy_state().ready) return;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  st.rt.free_tensor(tensor_id);
+}
+int32_t applegpu_ffi_register_tensor(uint64_t tensor_id, const uint64_t* dims, uint32_t ndim, int8_t dtype_i8) {
+  if (!ffi_ready("register_tensor")) return -1;
+  DType dt;
+  if (!dtype_from_wire(dtype_i8, &dt)) { set_ffi_error("Invalid dtype wire value: " + std::to_string((int)dtype_i8)); return -1; }
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.register_tensor(tensor_id, to_dims(dims, ndim), dt);
+  if (!s.ok()) { set_ffi_error("register_tensor failed: " + s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_ffi_shape(uint64_t tensor_id, uint64_t* out_dims, uint32_t* out_ndim) {
+  if (!ffi_ready("shape")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Dims d;
+  Status s = st.rt.shape(tensor_id, &d);
+  if (!s.ok()) { set_ffi_error("shape failed: " + s.to_string()); return -1; }
+  *out_ndim = (uint32_t)d.size();
+  for (size_t i = 0; i < d.size(); i++) out_dims[i] = (uint64_t)d[i];
+  return 0;
+}
+int8_t applegpu_ffi_dtype(uint64_t tensor_id) {
+  if (!lazy_state().ready) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  DType dt;
+  if (!st.rt.dtype(tensor_id, &dt).ok()) return -1;
+  return (int8_t)dt;
+}
+
+uint64_t applegpu_ffi_add(uint64_t a, uint64_t b) { return record("add", mk(Op::Add), {a, b}); }
+uint64_t applegpu_ffi_sub(uint64_t a, uint64_t b) { return record("sub", mk(Op::Sub), {a, b}); }
+uint64_t applegpu_ffi_mul(uint64_t a, uint64_t b) { return record("mul", mk(Op::Mul), {a, b}); }
+uint64_t applegpu_ffi_div(uint64_t a, uint64_t b) { return record("div", mk(Op::Div), {a, b}); }
+uint64_t applegpu_ffi_matmul(uint64_t a, uint64_t b) { return record("matmul", mk(Op::Matmul), {a, b}); }
+uint64_t applegpu_ffi_relu(uint64_t x) { return record("relu", mk(Op::Relu), {x}); }
+uint64_t applegpu_ffi_neg(uint64_t x) { return record("neg", mk(Op::Neg), {x}); }
+uint64_t applegpu_ffi_exp(uint64_t x) { return record("exp", mk(Op::Exp), {x}); }
+uint64_t applegpu_ffi_log(uint64_t x) { return record("log", mk(Op::Log), {x}); }
+uint64_t applegpu_ffi_sqrt(uint64_t x) { return record("sqrt", mk(Op::Sqrt), {x}); }
+uint64_t applegpu_ffi_tanh(uint64_t x) { return record("tanh", mk(Op::Tanh), {x}); }
+uint64_t applegpu_ffi_sin(uint64_t x) { return record("sin", mk(Op::Sin), {x}); }
+uint64_t applegpu_ffi_cos(uint64_t x) { return record("cos", mk(Op::Cos), {x}); }
+uint64_t applegpu_ffi_abs(uint64_t x) { return record("abs", mk(Op::Abs), {x}); }
+uint64_t applegpu_ffi_sign(uint64_t x) { return record("sign", mk(Op::Sign), {x}); }
+uint64_t applegpu_ffi_sigmoid(uint64_t x) { return record("sigmoid", mk(Op::Sigmoid), {x}); }
+uint64_t applegpu_ffi_gelu(uint64_t x) { return record("gelu", mk(Op::Gelu), {x}); }
+uint64_t applegpu_ffi_gelu_exact(uint64_t x) { return record("gelu_exact", mk(Op::GeluExact), {x}); }
+uint64_t applegpu_ffi_softmax(uint64_t x) { return record("softmax", mk(Op::Softmax), {x}); }
+uint64_t applegpu_ffi_softmax_causal(uint64_t x) { return record("softmax_causal", mk(Op::SoftmaxCausal), {x}); }
+uint64_t applegpu_ffi_layer_norm(uint64_t x, uint64_t gamma, uint64_t beta, float eps) {
+  OpKind k = mk(Op::LayerNorm); k.f0 = eps;
+  return record("layer_norm", k, {x, gamma, beta});
+}
+uint64_t applegpu_ffi_embedding(uint64_t w, uint64_t idx) { return record("embedding", mk(Op::Embedding), {w, idx}); }
+uint64_t applegpu_ffi_add_bias(uint64_t x, uint64_t b) { return record("add_bias", mk(Op::AddBias), {x, b}); }
+uint64_t applegpu_ffi_scalar_mul(uint64_t x, float scale) { OpKind k = mk(Op::ScalarMul); k.f0 = scale; return record("scalar_mul", k, {x}); }
+uint64_t applegpu_ffi_argmax(uint64_t x) { return record("argmax", mk(Op::Argmax), {x}); }
+uint64_t applegpu_ffi_sum(uint64_t x) { return record("sum", mk(Op::Sum), {x}); }
+uint64_t applegpu_ffi_mean(uint64_t x) { return record("mean", mk(Op::Mean), {x}); }
+uint64_t applegpu_ffi_transpose_dims(uint64_t x, uint32_t d0, uint32_t d1) {
+  if (d0 == d1) {
+    // the reference returns the input id itself for a no-op transpose (ops.rs:522-524), after range checks
+    if (!ffi_ready("transpose")) return 0;
+    LazyState& st = lazy_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    Dims s;
+    Status r = st.rt.shape(x, &s);
+    if (!r.ok()) { set_ffi_error("transpose failed: " + r.to_string()); return 0; }
+    if (d0 >= s.size()) {
+      set_ffi_error("transpose failed: Invalid tensor: transpose dims (" + std::to_string(d0) + ", " + std::to_string(d1) + ") out of range for " + std::to_string(s.size()) + "D tensor");
+      return 0;
+    }
+    return x;
+  }
+  OpKind k = mk(Op::Transpose); k.i0 = d0; k.i1 = d1;
+  return record("transpose", k, {x});
+}
+uint64_t applegpu_ffi_transpose(uint64_t x) {
+  if (!ffi_ready("transpose")) return 0;
+  Dims s;
+  {
+    LazyState& st = lazy_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    Status r = st.rt.shape(x, &s);
+    if (!r.ok()) { set_ffi_error("transpose failed: " + r.to_string()); return 0; }
+  }
+  if (s.size() < 2) { set_ffi_error("transpose failed: Invalid tensor: transpose requires at least 2D tensor, got " + dims_str(s)); return 0; }
+  return applegpu_ffi_transpose_dims(x, (uint32_t)s.size() - 2, (uint32_t)s.size() - 1);
+}
+uint64_t applegpu_ffi_reshape(uint64_t x, const uint64_t* dims, uint32_t ndim) {
+  OpKind k = mk(Op::Reshape); k.shape = to_dims(dims, ndim);
+  return record("reshape", k, {x});
+}
+uint64_t applegpu_ffi_slice(uint64_t x, uint32_t dim, uint64_t start, uint64_t end) {
+  OpKind k = mk(Op::Slice); k.i0 = dim; k.i1 = (int64_t)start; k.i2 = (int64_t)end;
+  return record("slice", k, {x});
+}
+uint64_t applegpu_ffi_concat(uint64_t a, uint64_t b, uint32_t dim) { OpKind k = mk(Op::Concat); k.i0 = dim; return record("concat", k, {a, b}); }
+uint64_t applegpu_ffi_gather(uint64_t x, uint32_t dim, uint64_t idx) { OpKind k = mk(Op::Gather); k.i0 = dim; return record("gather", k, {x, idx}); }
+uint64_t applegpu_ffi_index_select(uint64_t x, uint32_t dim, uint64_t idx) { OpKind k = mk(Op::IndexSelect); k.i0 = dim; return record("index_select", k, {x, idx}); }
+uint64_t applegpu_ffi_cast(uint64_t x, int8_t target) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_ffi_error("cast failed: Invalid dtype wire value: " + std::to_string((int)target)); return 0; }
+  if (!ffi_ready("cast")) return 0;
+  {
+    LazyState& st = lazy_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    DType cur;
+    if (st.rt.dtype(x, &cur).ok() && cur == dt && cur != DType::F64) return x;  // no-op cast returns its input (ops.rs:2304-2307)
+  }
+  OpKind k = mk(Op::Cast); k.dt = dt;
+  return record("cast", k, {x});
+}
+uint64_t applegpu_ffi_quantize(uint64_t x, int8_t target, float scale, int32_t zp) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_ffi_error("quantize failed: Invalid dtype wire value: " + std::to_string((int)target)); return 0; }
+  OpKind k = mk(Op::Quantize); k.dt = dt; k.f0 = scale; k.i0 = zp;
+  return record("quantize", k, {x});
+}
+uint64_t applegpu_ffi_dequantize(uint64_t x, int8_t target, float scale, int32_t zp) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_ffi_error("dequantize failed: Invalid dtype wire value: " + std::to_string((int)target)); return 0; }
+  OpKind k = mk(Op::Dequantize); k.dt = dt; k.f0 = scale; k.i0 = zp;
+  return record("dequantize", k, {x});
+}
+
+static uint64_t attention_impl(const char* name, uint64_t q, uint64_t kk, uint64_t v, bool causal) {
+  // The 5-op composition of ops.rs:1531-1618; the fusion pass may later collapse it.
+  if (!ffi_ready(name)) return 0;
+  Dims qs, ks, vs;
+  {
+    LazyState& st = lazy_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    Status s = st.rt.shape(q, &qs);
+    if (s.ok()) s = st.rt.shape(kk, &ks);
+    if (s.ok()) s = st.rt.shape(v, &vs);
+    if (!s.ok()) { set_ffi_error(std::string(name) + " failed: " + s.to_string()); return 0; }
+  }
+  if (qs.size() < 2 || ks.size() < 2 || vs.size() < 2) {
+    set_ffi_error(std::string(name) + (causal ? " failed: Invalid tensor: attention_causal requires at least 2D tensors"
+                                              : " failed: Invalid tensor: attention requires at least 2D tensors for Q, K, V"));
+    return 0;
+  }
+  int64_t dk = qs.back();
+  if (ks.back() != dk) { set_ffi_error(std::string(name) + " failed: Invalid tensor: Q and K must have same d_k: " + std::to_string(dk) + " vs " + std::to_string(ks.back())); return 0; }
+  int64_t kv = ks[ks.size() - 2];
+  if (vs[vs.size() - 2] != kv) { set_ffi_error(std::string(name) + " failed: Invalid tensor: K and V must have same kv_len: " + std::to_string(kv) + " vs " + std::to_string(vs[vs.size() - 2])); return 0; }
+  uint64_t kt = applegpu_ffi_transpose(kk);
+  if (!kt) return 0;
+  uint64_t scores = applegpu_ffi_matmul(q, kt);
+  if (!scores) return 0;
+  uint64_t scaled = applegpu_ffi_scalar_mul(scores, 1.0f / std::sqrt((float)dk));
+  if (!scaled) return 0;
+  uint64_t w = causal ? applegpu_ffi_softmax_causal(scaled) : applegpu_ffi_softmax(scaled);
+  if (!w) return 0;
+  uint64_t out = applegpu_ffi_matmul(w, v);
+  // The intermediates belong to this call: release them so only the graph holds them.
+  applegpu_ffi_free(kt); applegpu_ffi_free(scores); applegpu_ffi_free(scaled); applegpu_ffi_free(w);
+  return out;
+}
+uint64_t applegpu_ffi_attention(uint64_t q, uint64_t k, uint64_t v) { return attention_impl("attention", q, k, v, false); }
+uint64_t applegpu_ffi_attention_causal(uint64_t q, uint64_t k, uint64_t v) { return attention_impl("attention_causal", q, k, v, true); }
+
+uint64_t applegpu_ffi_matmul_int8(uint64_t x, uint64_t q, uint64_t scales) { return record("matmul_int8", mk(Op::MatmulInt8), {x, q, scales}); }
+
+int32_t applegpu_ffi_quantize_weight(uint64_t weight_id, uint64_t* out_q_id, uint64_t* out_scales_id) {
+  if (!ffi_ready("quantize_weight")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.rt.is_pending(weight_id)) { Status s = st.rt.eval(weight_id); if (!s.ok()) { set_ffi_error("quantize_weight failed: " + s.to_string()); return -1; } }
+  const TensorRec* w = st.rt.tensor(weight_id);
+  if (!w || !w->has_meta) { set_ffi_error("quantize_weight failed: Invalid tensor: Tensor " + std::to_string(weight_id) + " not found"); return -1; }
+  if (w->shape.size() != 2 || !dtype_is_float(w->dtype) || w->dtype == DType::F64) { set_ffi_error("quantize_weight failed: Invalid tensor: weight must be a 2D float tensor [N,K]"); return -1; }
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.dry) { set_ffi_error("quantize_weight failed: no CUDA device (dry-run mode)"); return -1; }
+  TensorRec wc, q, sc;
+  Status s = make_contiguous(*w, &wc);
+  if (s.ok()) { q.shape = w->shape; q.strides = contiguous_strides(q.shape); q.dtype = DType::I8; q.has_meta = true; s = Shared::get().pool.acquire(q.nbytes() ? q.nbytes() : 4, &q.buf); }
+  if (s.ok()) { sc.shape = {w->shape[0]}; sc.strides = {1}; sc.dtype = DType::F32; sc.has_meta = true; s = Shared::get().pool.acquire(sc.nbytes() ? sc.nbytes() : 4, &sc.buf); }
+  if (s.ok()) s = ctx.make_current();
+  if (s.ok()) s = k::quantize_rows(ctx.stream, wc.view(), q.view(), sc.view());
+  if (!s.ok()) { set_ffi_error("quantize_weight failed: " + s.to_string()); return -1; }
+  uint64_t qid = next_tensor_id(), sid = next_tensor_id();
+  st.rt.insert_tensor(qid, q); st.rt.insert_tensor(sid, sc);
+  *out_q_id = qid; *out_scales_id = sid;
+  return 0;
+}
+
+int32_t applegpu_ffi_copy(uint64_t src_id, uint64_t dst_id) {
+  if (!ffi_ready("copy")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.rt.is_pending(src_id)) { Status s = st.rt.eval(src_id); if (!s.ok()) { set_ffi_error("copy: eval src failed: " + s.to_string()); return -1; } }
+  const TensorRec* src = st.rt.tensor(src_id);
+  if (!src || !src->has_meta) { set_ffi_error("copy failed: Invalid tensor: Tensor " + std::to_string(src_id) + " not found"); return -1; }
+  const TensorRec* dst = st.rt.tensor(dst_id);
+  if (!dst || !dst->buf) { set_ffi_error("copy: dst tensor " + std::to_string(dst_id) + " not found"); return -1; }
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.dry) { set_ffi_error("copy failed: no CUDA device (dry-run mode)"); return -1; }
+  TensorRec c;
+  Status s = make_contiguous(*src, &c);
+  if (!s.ok()) { set_ffi_error("copy failed: " + s.to_string()); return -1; }
+  size_t n = c.nbytes();
+  if (n > dst->buf->capacity - dst->byte_offset) { set_ffi_error("copy failed: destination buffer is smaller than the source"); return -1; }
+  if (n) {
+    cudaError_t e = cudaMemcpyAsync(dst->data(), c.data(), n, cudaMemcpyDeviceToDevice, ctx.stream);
+    if (e != cudaSuccess) { set_ffi_error(std::string("copy failed: ") + cudaGetErrorString(e)); return -1; }
+  }
+  return 0;
+}
+
+uint8_t* applegpu_ffi_add_out(uint64_t a, uint64_t b, uint64_t* o) { return record_out("add", mk(Op::Add), {a, b}, o); }
+uint8_t* applegpu_ffi_mul_out(uint64_t a, uint64_t b, uint64_t* o) { return record_out("mul", mk(Op::Mul), {a, b}, o); }
+uint8_t* applegpu_ffi_sub_out(uint64_t a, uint64_t b, uint64_t* o) { return record_out("sub", mk(Op::Sub), {a, b}, o); }
+uint8_t* applegpu_ffi_div_out(uint64_t a, uint64_t b, uint64_t* o) { return record_out("div", mk(Op::Div), {a, b}, o); }
+uint8_t* applegpu_ffi_matmul_out(uint64_t a, uint64_t b, uint64_t* o) { return record_out("matmul", mk(Op::Matmul), {a, b}, o); }
+uint8_t* applegpu_ffi_relu_out(uint64_t x, uint64_t* o) { return record_out("relu", mk(Op::Relu), {x}, o); }
+uint8_t* applegpu_ffi_neg_out(uint64_t x, uint64_t* o) { return record_out("neg", mk(Op::Neg), {x}, o); }
+uint8_t* applegpu_ffi_threshold_backward_out(uint64_t grad, uint64_t x, float thr, uint64_t* o) {
+  OpKind k = mk(Op::ThresholdBackward); k.f0 = thr;
+  return record_out("threshold_backward", k, {grad, x}, o);
+}
+uint8_t* applegpu_ffi_scalar_mul_out(uint64_t x, float scale, uint64_t* o) { OpKind k = mk(Op::ScalarMul); k.f0 = scale; return record_out("scalar_mul", k, {x}, o); }
+uint8_t* applegpu_ffi_mean_all_out(uint64_t x, uint64_t* o) {
+  // mean_all = reshape to [1, numel] then mean over the last dim -> [1] (ops.rs mean_all composition).
+  if (!ffi_ready("mean_all")) return nullptr;
+  Dims s;
+  {
+    LazyState& st = lazy_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    Status r = st.rt.shape(x, &s);
+    if (!r.ok()) { set_ffi_error("mean_all failed: " + r.to_string()); return nullptr; }
+  }
+  uint64_t n = (uint64_t)numel_of(s);
+  uint64_t flat = applegpu_ffi_reshape(x, &n, 1);
+  if (!flat) return nullptr;
+  uint8_t* p = record_out("mean_all", mk(Op::Mean), {flat}, o);
+  applegpu_ffi_free(flat);
+  return p;
+}
+
+int32_t applegpu_ffi_eval(uint64_t tensor_id) {
+  if (!ffi_ready("eval")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.eval(tensor_id);
+  if (!s.ok()) { set_ffi_error("eval failed: " + s.to_string()); return -1; }
+  return 0;
+}
+void applegpu_ffi_synchronize(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.ready && !ctx.dry) cudaStreamSynchronize(ctx.stream);
+}
+int32_t applegpu_ffi_read_f32(uint64_t tensor_id, float* out_ptr, uint64_t max_elements) {
+  if (!ffi_ready("read_f32")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.read_f32(tensor_id, out_ptr, max_elements);
+  if (!s.ok()) { set_ffi_error("read_f32 failed: " + s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_ffi_upload(uint64_t tensor_id, const void* host_ptr, uint64_t nbytes) {
+  if (!ffi_ready("upload")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.write_bytes(tensor_id, host_ptr, (size_t)nbytes);
+  if (!s.ok()) { set_ffi_error("upload failed: " + s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nbytes) {
+  if (!ffi_ready("read_bytes")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.read_bytes(tensor_id, host_ptr, (size_t)nbytes);
+  if (!s.ok()) { set_ffi_error("read_bytes failed: " + s.to_string()); return -1; }
+  return 0;
+}
+uint64_t applegpu_ffi_from_host(const void* host_ptr, const uint64_t* dims, uint32_t ndim, int8_t dtype) {
+  DType dt;
+  if (!dtype_from_wire(dtype, &dt)) { set_ffi_error("Invalid dtype wire value: " + std::to_string((int)dtype)); return 0; }
+  Dims d = to_dims(dims, ndim);
+  uint64_t bytes = (uint64_t)numel_of(d) * dtype_size(dt);
+  uint64_t id = 0;
+  uint8_t* p = applegpu_ffi_alloc(bytes == 0 ? 4 : bytes, dtype, &id);
+  if (!p && !DeviceCtx::get().dry) return 0;
+  if (!id) return 0;
+  if (applegpu_ffi_register_tensor(id, dims, ndim, dtype) != 0) { applegpu_ffi_free(id); return 0; }
+  if (host_ptr && bytes && !DeviceCtx::get().dry) {
+    if (applegpu_ffi_upload(id, host_ptr, bytes) != 0) { applegpu_ffi_free(id); return 0; }
+  }
+  return id;
+}
+int64_t applegpu_ffi_plan(uint64_t tensor_id, char* buf, uint64_t cap) {
+  if (!ffi_ready("plan")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  std::string out;
+  Status s = st.rt.plan(tensor_id, &out);
+  if (!s.ok()) { set_ffi_error("plan failed: " + s.to_string()); return -1; }
+  if (buf && cap) { size_t n = out.size() < cap - 1 ? out.size() : (size_t)cap - 1; std::memcpy(buf, out.data(), n); buf[n] = 0; }
+  return (int64_t)out.size();
+}
+int32_t applegpu_ffi_is_pending(uint64_t tensor_id) {
+  if (!lazy_state().ready) return 0;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  return st.rt.is_pending(tensor_id) ? 1 : 0;
+}
+void applegpu_ffi_set_fusion(bool elementwise_chains, bool patterns) { fusion::set_enabled(elementwise_chains, patterns); }
+
+// ── eager flavour ───────────────────────────────────────────────────────────
+bool applegpu_eager_init(void) {
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.ready) return true;
+  Status s = init_device(false);
+  if (!s.ok()) { set_eager_error(s.to_string()); return false; }
+  Shared::get();
+  st.ready = true;
+  return true;
+}
+const char* applegpu_eager_last_error(void) { return t_eager_has_error ? t_eager_error.c_str() : nullptr; }
+
+uint8_t* applegpu_eager_alloc(const uint64_t* dims, uint32_t ndim, int8_t dtype, uint64_t* out_id) {
+  if (!eager_ready()) return nullptr;
+  DType dt;
+  if (!dtype_from_wire(dtype, &dt)) { set_eager_error("invalid dtype wire value: " + std::to_string((int)dtype)); return nullptr; }
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  uint64_t id = 0; void* ptr = nullptr;
+  Status s = st.rt.alloc(to_dims(dims, ndim), dt, &id, &ptr);
+  if (!s.ok()) { set_eager_error("alloc failed: " + s.to_string()); return nullptr; }
+  if (out_id) *out_id = id;
+  return static_cast<uint8_t*>(ptr);
+}
+void applegpu_eager_free(uint64_t id) {
+  if (!eager_state().ready) return;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  st.rt.free_tensor(id);
+}
+int32_t applegpu_eager_register_shape(uint64_t id, const uint64_t* dims, uint32_t ndim) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.register_shape(id, to_dims(dims, ndim));
+  if (!s.ok()) { set_eager_error(s.kind == ErrKind::InvalidTensor && s.msg.rfind("tensor ", 0) == 0 ? s.msg : s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_eager_shape(uint64_t id, uint64_t* out_dims, uint32_t* out_ndim) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Dims d;
+  Status s = st.rt.shape(id, &d);
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  *out_ndim = (uint32_t)d.size();
+  for (size_t i = 0; i < d.size(); i++) out_dims[i] = (uint64_t)d[i];
+  return 0;
+}
+int8_t applegpu_eager_dtype(uint64_t id) {
+  if (!eager_state().ready) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  DType dt;
+  if (!st.rt.dtype(id, &dt).ok()) return -1;
+  return (int8_t)dt;
+}
+
+uint8_t* applegpu_eager_add(uint64_t a, uint64_t b, uint64_t* o) { return eager_run(mk(Op::Add), {a, b}, o); }
+uint8_t* applegpu_eager_sub(uint64_t a, uint64_t b, uint64_t* o) { return eager_run(mk(Op::Sub), {a, b}, o); }
+uint8_t* applegpu_eager_mul(uint64_t a, uint64_t b, uint64_t* o) { return eager_run(mk(Op::Mul), {a, b}, o); }
+uint8_t* applegpu_eager_div(uint64_t a, uint64_t b, uint64_t* o) { return eager_run(mk(Op::Div), {a, b}, o); }
+uint8_t* applegpu_eager_relu(uint64_t x, uint64_t* o) { return eager_run(mk(Op::Relu), {x}, o); }
+uint8_t* applegpu_eager_neg(uint64_t x, uint64_t* o) { return eager_run(mk(Op::Neg), {x}, o); }
+
+uint8_t* applegpu_eager_matmul(uint64_t a, uint64_t b, uint64_t* o) {
+  if (!eager_ready()) return nullptr;
+  {
+    EagerState& st = eager_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    const TensorRec *ta, *tb;
+    Status s = st.rt.get(a, &ta);
+    if (s.ok()) s = st.rt.get(b, &tb);
+    if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+    if (!ta->contiguous() || !tb->contiguous()) { set_eager_error("Invalid tensor: matmul requires contiguous inputs"); return nullptr; }
+  }
+  return eager_run(mk(Op::Matmul), {a, b}, o);
+}
+
+uint8_t* applegpu_eager_matmul_ex(uint64_t a, uint64_t b, bool ta, bool tb, uint64_t* o) {
+  // Transposes are stride swaps on temporary views of the base tensors; the GEMM reads them in place.
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  uint64_t va = a, vb = b;
+  auto make_t = [&](uint64_t id, uint64_t* out) -> bool {
+    std::lock_guard<std::mutex> g(st.mu);
+    const TensorRec* t;
+    Status s = st.rt.get(id, &t);
+    if (!s.ok()) { set_eager_error(s.to_string()); return false; }
+    if (t->shape.size() < 2) { set_eager_error("Invalid tensor: matmul requires 2D+ tensors"); return false; }
+    Dims sh = t->shape, stv = t->strides;
+    size_t n = sh.size();
+    std::swap(sh[n - 1], sh[n - 2]); std::swap(stv[n - 1], stv[n - 2]);
+    void* p;
+    s = st.rt.create_view(id, sh, stv, 0, out, &p);
+    if (!s.ok()) { set_eager_error(s.to_string()); return false; }
+    return true;
+  };
+  if (ta && !make_t(a, &va)) return nullptr;
+  if (tb && !make_t(b, &vb)) { if (ta) applegpu_eager_free(va); return nullptr; }
+  uint8_t* r = eager_run(mk(Op::Matmul), {va, vb}, o);
+  if (ta) applegpu_eager_free(va);
+  if (tb) applegpu_eager_free(vb);
+  return r;
+}
+
+uint8_t* applegpu_eager_threshold_backward(uint64_t grad, uint64_t x, float thr, uint64_t* o) {
+  OpKind k = mk(Op::ThresholdBackward); k.f0 = thr;
+  return eager_run(k, {grad, x}, o);
+}
+uint8_t* applegpu_eager_scalar_mul(uint64_t x, float scale, uint64_t* o) { OpKind k = mk(Op::ScalarMul); k.f0 = scale; return eager_run(k, {x}, o); }
+
+static uint8_t* eager_reduce(uint64_t x, int mode, int64_t dim, bool keepdim, uint64_t* o) {
+  // mode 0: mean over all elements -> [1]; mode 1: sum over `dim`.
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec* t;
+  Status s = st.rt.get(x, &t);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  if (!dtype_is_float(t->dtype) || t->dtype == DType::F64) { set_eager_error(std::string("Unsupported dtype: reduction requires a float dtype, got ") + dtype_name(t->dtype)); return nullptr; }
+  Dims out_shape;
+  int64_t nd = (int64_t)t->shape.size();
+  if (mode == 1) {
+    if (dim < 0) dim += nd;
+    if (dim < 0 || dim >= nd) { set_eager_error("Invalid tensor: sum_dim: dim out of range for " + std::to_string(nd) + "D tensor"); return nullptr; }
+    for (int64_t i = 0; i < nd; i++) { if (i == dim) { if (keepdim) out_shape.push_back(1); } else out_shape.push_back(t->shape[i]); }
+  } else out_shape = {1};
+  DeviceCtx& ctx = DeviceCtx::get();
+  TensorRec c, out;
+  s = make_contiguous(*t, &c);
+  if (s.ok()) {
+    out.shape = out_shape; out.strides = contiguous_strides(out_shape); out.dtype = t->dtype; out.has_meta = true;
+    s = Shared::get().pool.acquire(out.nbytes() ? out.nbytes() : 4, &out.buf);
+  }
+  if (s.ok()) s = ctx.make_current();
+  if (s.ok() && ctx.dry) s = Status::compute("no CUDA device (dry-run mode)");
+  if (s.ok()) s = mode == 1 ? k::sum_dim(ctx.stream, c.view(), (int)dim, out.view()) : k::mean_all(ctx.stream, c.view(), out.view());
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  uint64_t id = st.rt.adopt(out);
+  if (o) *o = id;
+  return static_cast<uint8_t*>(out.data());
+}
+uint8_t* applegpu_eager_mean_all(uint64_t x, uint64_t* o) { return eager_reduce(x, 0, 0, false, o); }
+uint8_t* applegpu_eager_sum_dim(uint64_t x, int64_t dim, bool keepdim, uint64_t* o) { return eager_reduce(x, 1, dim, keepdim, o); }
+
+uint8_t* applegpu_eager_create_view(uint64_t base, const uint64_t* shape, const uint64_t* strides, uint32_t ndim, uint64_t offset, uint64_t* out_id) {
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  uint64_t id = 0; void* p = nullptr;
+  Status s = st.rt.create_view(base, to_dims(shape, ndim), to_dims(strides, ndim), offset, &id, &p);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  if (out_id) *out_id = id;
+  return static_cast<uint8_t*>(p);
+}
+int32_t applegpu_eager_add_scaled_inplace(uint64_t self, uint64_t other, float alpha) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.add_scaled_inplace(self, other, alpha);
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_eager_add_inplace(uint64_t self, uint64_t other) { return applegpu_eager_add_scaled_inplace(self, other, 1.0f); }
+void applegpu_eager_flush_and_wait(void) { applegpu_ffi_synchronize(); }
+void applegpu_eager_synchronize(void) { applegpu_ffi_synchronize(); }
+
+uint8_t* applegpu_eager_embedding(uint64_t w, uint64_t idx, uint64_t* o) { return eager_run(mk(Op::Embedding), {w, idx}, o); }
+uint8_t* applegpu_eager_layer_norm(uint64_t x, uint64_t gamma, uint64_t beta, float eps, uint64_t* o) {
+  OpKind k = mk(Op::LayerNorm); k.f0 = eps;
+  return eager_run(k, {x, gamma, beta}, o);
+}
+uint8_t* applegpu_eager_gelu(uint64_t x, uint64_t* o) { return eager_run(mk(Op::Gelu), {x}, o); }
+uint8_t* applegpu_eager_softmax(uint64_t x, uint64_t* o) { return eager_run(mk(Op::Softmax), {x}, o); }
+uint64_t applegpu_eager_find_by_data_ptr(const uint8_t* ptr) {
+  if (!eager_state().ready) return 0;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  return st.rt.find_by_data_ptr(ptr);
+}
+
+uint8_t* applegpu_eager_gelu_exact(uint64_t x, uint64_t* o) { return eager_run(mk(Op::GeluExact), {x}, o); }
+uint8_t* applegpu_eager_softmax_causal(uint64_t x, uint64_t* o) { return eager_run(mk(Op::SoftmaxCausal), {x}, o); }
+uint8_t* applegpu_eager_add_bias(uint64_t x, uint64_t b, uint64_t* o) { return eager_run(mk(Op::AddBias), {x, b}, o); }
+uint8_t* applegpu_eager_argmax(uint64_t x, uint64_t* o) { return eager_run(mk(Op::Argmax), {x}, o); }
+uint8_t* applegpu_eager_gather(uint64_t x, uint32_t dim, uint64_t idx, uint64_t* o) { OpKind k = mk(Op::Gather); k.i0 = dim; return eager_run(k, {x, idx}, o); }
+uint8_t* applegpu_eager_index_select(uint64_t x, uint32_t dim, uint64_t idx, uint64_t* o) { OpKind k = mk(Op::IndexSelect); k.i0 = dim; return eager_run(k, {x, idx}, o); }
+uint8_t* applegpu_eager_cast(uint64_t x, int8_t target, uint64_t* o) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_eager_error("invalid dtype wire value: " + std::to_string((int)target)); return nullptr; }
+  OpKind k = mk(Op::Cast); k.dt = dt;
+  return eager_run(k, {x}, o);
+}
+uint8_t* applegpu_eager_quantize(uint64_t x, int8_t target, float scale, int32_t zp, uint64_t* o) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_eager_error("invalid dtype wire value: " + std::to_string((int)target)); return nullptr; }
+  OpKind k = mk(Op::Quantize); k.dt = dt; k.f0 = scale; k.i0 = zp;
+  return eager_run(k, {x}, o);
+}
+uint8_t* applegpu_eager_dequantize(uint64_t x, int8_t target, float scale, int32_t zp, uint64_t* o) {
+  DType dt;
+  if (!dtype_from_wire(target, &dt)) { set_eager_error("invalid dtype wire value: " + std::to_string((int)target)); return nullptr; }
+  OpKind k = mk(Op::Dequantize); k.dt = dt; k.f0 = scale; k.i0 = zp;
+  return eager_run(k, {x}, o);
+}
+uint8_t* applegpu_eager_unary(uint64_t x, const char* name, uint64_t* o) {
+  struct E { const char* n; Op op; };
+  static const E table[] = {{"neg", Op::Neg}, {"relu", Op::Relu}, {"exp", Op::Exp}, {"log", Op::Log}, {"sqrt", Op::Sqrt}, {"tanh", Op::Tanh},
+                            {"sin", Op::Sin}, {"cos", Op::Cos}, {"gelu", Op::Gelu}, {"gelu_exact", Op::GeluExact}, {"sigmoid", Op::Sigmoid},
+                            {"abs", Op::Abs}, {"sign", Op::Sign}};
+  for (auto& e : table) if (name && std::strcmp(name, e.n) == 0) return eager_run(mk(e.op), {x}, o);
+  set_eager_error(std::string("unknown unary op: ") + (name ? name : "(null)"));
+  return nullptr;
+}
+
+// Shape inference for the two ops below reuses matmul's rules through a scratch node.
+uint8_t* applegpu_eager_linear(uint64_t x, uint64_t w, uint64_t bias, uint64_t residual, int32_t act, bool transpose_w, uint64_t* o) {
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec *tx, *tw, *tb = nullptr, *tr = nullptr;
+  Status s = st.rt.get(x, &tx);
+  if (s.ok()) s = st.rt.get(w, &tw);
+  if (s.ok() && bias) s = st.rt.get(bias, &tb);
+  if (s.ok() && residual) s = st.rt.get(residual, &tr);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  if (tx->shape.size() < 2 || tw->shape.size() != 2) { set_eager_error("Invalid tensor: linear requires x >= 2D and a 2D weight"); return nullptr; }
+  if (tx->dtype != tw->dtype) { set_eager_error(std::string("Invalid tensor: dtype mismatch: ") + dtype_debug(tx->dtype) + " vs " + dtype_debug(tw->dtype)); return nullptr; }
+  TensorRec wv = *tw;
+  if (transpose_w) { std::swap(wv.shape[0], wv.shape[1]); std::swap(wv.strides[0], wv.strides[1]); }
+  if (tx->shape.back() != wv.shape[0]) {
+    set_eager_error("Invalid tensor: matmul inner dim mismatch: " + std::to_string(tx->shape.back()) + " vs " + std::to_string(wv.shape[0]));
+    return nullptr;
+  }
+  OpNode node;
+  node.op.op = Op::FusedLinear; node.op.f0 = 1.0f;
+  node.op.act = act == 1 ? k::Act::GeluTanh : act == 2 ? k::Act::GeluErf : act == 3 ? k::Act::Relu : k::Act::None;
+  node.out_shape = tx->shape; node.out_shape.back() = wv.shape[1]; node.out_dtype = tx->dtype;
+  // collapse x to 2-D so the bias lands on the last dim
+  TensorRec xc;
+  s = make_contiguous(*tx, &xc);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  Dims full = node.out_shape;
+  int64_t rows = numel_of(xc.shape) / (xc.shape.back() ? xc.shape.back() : 1);
+  xc.shape = {rows, xc.shape.back()}; xc.strides = contiguous_strides(xc.shape);
+  node.out_shape = {rows, wv.shape[1]};
+  std::vector<const TensorRec*> ins{&xc, &wv};
+  TensorRec rc;
+  if (tb) {
+    if (!(tb->shape.size() == 1 && tb->shape[0] == wv.shape[1])) { set_eager_error("Invalid tensor: linear bias must be [" + std::to_string(wv.shape[1]) + "]"); return nullptr; }
+    node.op.has_bias = true; ins.push_back(tb);
+  }
+  if (tr) {
+    if (tr->shape != full) { set_eager_error("Invalid tensor: linear residual shape " + dims_str(tr->shape) + " must be " + dims_str(full)); return nullptr; }
+    s = make_contiguous(*tr, &rc);
+    if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+    rc.shape = node.out_shape; rc.strides = contiguous_strides(rc.shape);
+    node.op.has_residual = true; ins.push_back(&rc);
+  }
+  TensorRec out;
+  s = execute_node(node, ins, &out, nullptr);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  out.shape = full; out.strides = contiguous_strides(full);
+  uint64_t id = st.rt.adopt(out);
+  if (o) *o = id;
+  return static_cast<uint8_t*>(out.data());
+}
+
+uint8_t* applegpu_eager_attention(uint64_t q, uint64_t kk, uint64_t v, bool causal, uint64_t* o) {
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec *tq, *tk, *tv;
+  Status s = st.rt.get(q, &tq);
+  if (s.ok()) s = st.rt.get(kk, &tk);
+  if (s.ok()) s = st.rt.get(v, &tv);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  if (tq->shape.size() < 2 || tk->shape.size() < 2 || tv->shape.size() < 2) { set_eager_error("Invalid tensor: attention requires at least 2D tensors for Q, K, V"); return nullptr; }
+  if (!(tq->dtype == tk->dtype && tk->dtype == tv->dtype) || !dtype_is_float(tq->dtype) || tq->dtype == DType::F64) { set_eager_error("Invalid tensor: attention requires Q, K, V of one float dtype"); return nullptr; }
+  if (tk->shape.back() != tq->shape.back()) { set_eager_error("Invalid tensor: Q and K must have same d_k: " + std::to_string(tq->shape.back()) + " vs " + std::to_string(tk->shape.back())); return nullptr; }
+  if (tk->shape[tk->shape.size() - 2] != tv->shape[tv->shape.size() - 2]) { set_eager_error("Invalid tensor: K and V must have same kv_len: " + std::to_string(tk->shape[tk->shape.size() - 2]) + " vs " + std::to_string(tv->shape[tv->shape.size() - 2])); return nullptr; }
+  if (tq->shape.size() != tk->shape.size() || tq->shape.size() != tv->shape.size() ||
+      !std::equal(tq->shape.begin(), tq->shape.end() - 2, tk->shape.begin()) || !std::equal(tq->shape.begin(), tq->shape.end() - 2, tv->shape.begin())) {
+    set_eager_error("Invalid tensor: attention requires matching leading dims on Q, K, V"); return nullptr;
+  }
+  OpNode node;
+  node.op.op = Op::FusedAttention; node.op.causal = causal;
+  node.out_shape = tq->shape; node.out_shape.back() = tv->shape.back(); node.out_dtype = tq->dtype;
+  TensorRec out;
+  s = execute_node(node, {tq, tk, tv}, &out, nullptr);
+  if (!s.ok()) { set_eager_error(s.to_string()); return nullptr; }
+  uint64_t id = st.rt.adopt(out);
+  if (o) *o = id;
+  return static_cast<uint8_t*>(out.data());
+}
+
+int32_t applegpu_eager_upload(uint64_t id, const void* host_ptr, uint64_t nbytes) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec* t;
+  Status s = st.rt.get(id, &t);
+  if (s.ok()) s = upload(*t, host_ptr, (size_t)nbytes);
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_eager_download(uint64_t id, void* host_ptr, uint64_t nbytes) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec* t;
+  Status s = st.rt.get(id, &t);
+  if (s.ok()) s = download(*t, host_ptr, (size_t)nbytes);
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  return 0;
+}
+
+// ── runtime services ────────────────────────────────────────────────────────
+void applegpu_pool_stats(uint64_t* out7) {
+  PoolStats s = Shared::get().pool.stats();
+  out7[0] = s.hits; out7[1] = s.misses; out7[2] = s.pooled_bytes; out7[3] = s.bucket_count;
+  out7[4] = s.live_bytes; out7[5] = s.peak_live_bytes; out7[6] = s.live_buffers;
+}
+void applegpu_pool_drain(void) { Shared::get().pool.drain(); }
+void applegpu_pool_set_watermark(uint64_t n) { Shared::get().pool.set_max_pooled_bytes((size_t)n); }
+int32_t applegpu_pool_prewarm(const uint64_t* sizes, uint32_t n) {
+  std::vector<size_t> v(sizes, sizes + n);
+  Status s = Shared::get().pool.prewarm(v);
+  if (!s.ok()) { set_ffi_error(s.to_string()); return -1; }
+  return 0;
+}
+void applegpu_pool_fail_next(int32_t n) { Shared::get().pool.fail_next_allocs(n); }
+uint64_t applegpu_memory_usage(void) { return Shared::get().pool.stats().live_bytes; }
+uint64_t applegpu_tensor_count(void) {
+  uint64_t n = 0;
+  { LazyState& st = lazy_state(); std::lock_guard<std::mutex> g(st.mu); n += st.rt.tensor_count(); }
+  { EagerState& st = eager_state(); std::lock_guard<std::mutex> g(st.mu); n += st.rt.tensor_count(); }
+  return n;
+}
+void* applegpu_stream(void) { return (void*)DeviceCtx::get().stream; }
+int32_t applegpu_device(void) { return DeviceCtx::get().device; }
+const char* applegpu_device_name(void) { return DeviceCtx::get().name.c_str(); }
+uint64_t applegpu_launch_count(void) { return ag::launch_count(); }
+void applegpu_set_matmul_path(int32_t mode) { k::set_matmul_path(mode); }
+int32_t applegpu_pipeline_status(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry) return 0;
+  return k::matmul_take_status(ctx.stream);
+}
+const char* applegpu_matmul_path(uint64_t a, uint64_t b, bool eager) {
+  TensorRec ta, tb;
+  if (eager) {
+    EagerState& st = eager_state(); std::lock_guard<std::mutex> g(st.mu);
+    const TensorRec *pa, *pb;
+    if (!st.rt.get(a, &pa).ok() || !st.rt.get(b, &pb).ok()) return nullptr;
+    ta = *pa; tb = *pb;
+  } else {
+    LazyState& st = lazy_state(); std::lock_guard<std::mutex> g(st.mu);
+    const TensorRec *pa = st.rt.tensor(a), *pb = st.rt.tensor(b);
+    if (!pa || !pb || !pa->has_meta || !pb->has_meta) return nullptr;
+    ta = *pa; tb = *pb;
+  }
+  if (ta.shape.size() < 2 || tb.shape.size() < 2) return nullptr;
+  k::GemmDesc d;
+  size_t an = ta.shape.size(), bn = tb.shape.size();
+  d.dtype = ta.dtype; d.b_dtype = tb.dtype; d.a = ta.data(); d.b = tb.data(); d.c = nullptr;
+  d.m = ta.shape[an - 2]; d.k = ta.shape[an - 1]; d.n = tb.shape[bn - 1];
+  d.a_row = ta.strides[an - 2]; d.a_col = ta.strides[an - 1]; d.b_row = tb.strides[bn - 2]; d.b_col = tb.strides[bn - 1];
+  d.batch = 1; d.a_batch = d.b_batch = d.c_batch = 0; d.c_row = d.n;
+  return k::matmul_path(d);
+}
+int32_t applegpu_timer_start(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry) return -1;
+  if (!g_ev0) { cudaEventCreate(&g_ev0); cudaEventCreate(&g_ev1); }
+  return cudaEventRecord(g_ev0, ctx.stream) == cudaSuccess ? 0 : -1;
+}
+float applegpu_timer_stop_ms(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry || !g_ev0) return -1.f;
+  if (cudaEventRecord(g_ev1, ctx.stream) != cudaSuccess) return -1.f;
+  if (cudaEventSynchronize(g_ev1) != cudaSuccess) return -1.f;
+  float ms = -1.f;
+  cudaEventElapsedTime(&ms, g_ev0, g_ev1);
+  return ms;
+}
+int32_t applegpu_flush_l2(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry) return -1;
+  if (!g_flush_buf && cudaMalloc(&g_flush_buf, kFlushBytes) != cudaSuccess) { g_flush_buf = nullptr; return -1; }
+  return k::flush_l2(ctx.stream, g_flush_buf, kFlushBytes).ok() ? 0 : -1;
+}
+const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype) {
+  thread_local std::string out;
+  DType dt;
+  if (!base_name || !dtype_from_wire(dtype, &dt) || dt == DType::F64) return nullptr;
+  std::string b(base_name);
+  static const char* float_only[] = {"matmul", "softmax", "softmax_causal", "layer_norm", "gelu", "gelu_exact", "add_bias", "embedding",
+                                     "elementwise_exp", "elementwise_log", "elementwise_sqrt", "elementwise_tanh", "elementwise_relu", "sigmoid"};
+  for (const char* f : float_only) if (b == f && !dtype_is_float(dt)) return nullptr;
+  out = b + dtype_suffix(dt);
+  return out.c_str();
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+// Device helpers shared by the bandwidth-bound kernels: 16-byte vector access,
+// storage<->float conversion (half types compute in float and round once on store,
+// as kernel_templates.rs:171-191 `needs_float_acc` does), warp/block reductions.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "kernels.h"
+
+namespace ag { namespace k {
+
+template <typename T> struct Cvt;
+template <> struct Cvt<float> {
+  static __device__ __forceinline__ float to(float v) { return v; }
+  static __device__ __forceinline__ float from(float v) { return v; }
+};
+template <> struct Cvt<__half> {
+  static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from(float v) { return __float2half_rn(v); }
+};
+template <> struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from(float v) { return __float2bfloat16_rn(v); }
+};
+
+// A 16-byte pack of T.
+template <typename T> struct alignas(16) Pack {
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Pack<T> ld16(const T* p) {
+  Pack<T> r;
+  *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+// Streaming variants: data touched once should not displace reusable lines.
+template <typename T>
+__device__ __forceinline__ Pack<T> ld16_stream(const T* p) {
+  Pack<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void st16(T* p, const Pack<T>& v) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&v);
+}
+template <typename T>
+__device__ __forceinline__ void st16_stream(T* p, const Pack<T>& v) {
+  __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&v));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide reductions over up to 32 warps; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* smem /* >=33 floats */) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? smem[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+__device__ __forceinline__ float block_max(float v, float* smem) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) smem[w] = v;
+  __syncthreads();
+  float r = (lane < nw) ? smem[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+// tanh-GELU with the reference's clamp (kernel_templates.rs:299-302).
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  float inner = 0.7978845608f * (x + 0.044715f * x * x * x);
+  inner = fminf(fmaxf(inner, -10.0f), 10.0f);
+  return x * 0.5f * (1.0f + tanhf(inner));
+}
+// erf-GELU. The reference evaluates erf with the Abramowitz-Stegun 7.1.26 polynomial
+// (kernel_templates.rs:312-323, max error 1.5e-7); erff is at least as close to the
+// exact function, and both sit inside the 1e-5 tolerance of the reference's tests.
+__device__ __forceinline__ float gelu_erf_f(float x) {
+  return x * 0.5f * (1.0f + erff(x * 0.70710678118f));
+}
+__device__ __forceinline__ float apply_act(float x, Act a) {
+  switch (a) {
+    case Act::GeluTanh: return gelu_tanh_f(x);
+    case Act::GeluErf: return gelu_erf_f(x);
+    case Act::Relu: return fmaxf(x, 0.f);
+    default: return x;
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline Status cuda_status(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return Status::OK();
+  return Status::compute(std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define AG_CHECK_LAUNCH(what) do { cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) return cuda_status(_e, what); } while (0)
+
+// Grid sizing: a multiple of the SM count, capped by the work available.
+int sm_count();
+inline int grid_for(int64_t work_items, int per_block, int blocks_per_sm = 8) {
+  int64_t need = (work_items + per_block - 1) / per_block;
+  int64_t cap = (int64_t)sm_count() * blocks_per_sm;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+#define AG_DISPATCH_FLOAT(dt, T, ...)                                              \
+  switch (dt) {                                                                    \
+    case DType::F32: { using T = float; __VA_ARGS__; break; }                      \
+    case DType::F16: { using T = __half; __VA_ARGS__; break; }                     \
+    case DType::BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
+    default: return Status::unsupported(std::string("kernel has no ") + dtype_name(dt) + " variant"); \
+  }
+
+}}  // namespace ag::k

@@ -1,0 +1,427 @@
+// Batched matmul on the 5th-generation tensor cores: TMA -> shared-memory ring -> tcgen05.mma
+// with fp32 accumulators in TMEM -> fused epilogue (alpha, per-channel scale, bias, activation,
+// residual) -> global memory.
+//
+// Replaces the reference's 32x32 threadgroup-tile `matmul{s}` kernel (kernel_templates.rs:987-1072)
+// and its MPSMatrixMultiplication call (swift/.../compute.swift:1584-1598) for f16/bf16 operands;
+// the arithmetic contract is unchanged: C[b,i,j] = sum_k A[b,i,k] * B[b,k,j] with float
+// accumulation and one rounding on store.
+//
+// One persistent CTA per SM walks output tiles of 128 x BN. Warp roles:
+//   warp 0      TMA producer: fills a STAGES-deep ring of {A 128x64, B BNx64} tiles (128B swizzle)
+//   warp 1      MMA issuer: one elected thread issues 4 x (128 x BN x 16) tcgen05.mma per stage,
+//               commits the stage back to the producer, and owns the TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator (two TMEM buffers, so the next
+//               tile's main loop overlaps this tile's epilogue), epilogue math, stores
+// B is taken either K-major ([N,K] rows, e.g. a tied embedding or K in Q.K^T) or N-major
+// ([K,N] rows, the layout of every GPT-2 Conv1D weight and of V in P.V) through the
+// descriptor's major bit, so no operand is ever transposed in memory.
+#include "common.cuh"
+#include "sm100.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+#include <type_traits>
+
+namespace ag { namespace k {
+
+using namespace ag::sm100;
+
+constexpr int BM = 128;          // UMMA M (cta_group::1)
+constexpr int BK = 64;           // 64 x 2 B = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kTcThreads = 192;
+
+struct TcParams {
+  void* c;
+  const void* bias;
+  const void* residual;
+  const float* b_scales;
+  float alpha;
+  int act;
+  int m, n, k, batch;          // batch = outer * inner
+  int batch_inner;
+  long long c_row, c_batch, c_batch_inner;
+  int a_bcast, b_bcast;        // bit 0: outer index pinned to 0, bit 1: inner index pinned to 0
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+template <int BN> struct TcCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kTmemCols = 2 * BN;                         // two accumulator buffers
+};
+
+template <typename T>
+__device__ __forceinline__ void epilogue_store_chunk(const TcParams& p, const uint32_t (&acc)[32], long long gm, int col0, long long c_off) {
+  // One thread owns row gm, columns col0 .. col0+31.
+  T* C = reinterpret_cast<T*>(p.c) + c_off + gm * p.c_row;
+  const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off + gm * p.c_row : nullptr;
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  const bool full = col0 + 32 <= p.n;
+  const bool vec = full && ((reinterpret_cast<uintptr_t>(C + col0) & 15u) == 0) && (!R || (reinterpret_cast<uintptr_t>(R + col0) & 15u) == 0);
+  if (vec) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      Pack<T> o;
+      Pack<T> r;
+      if (R) r = ld16(R + col0 + g * 8);
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        int cidx = col0 + g * 8 + e;
+        float v = __uint_as_float(acc[g * 8 + e]) * p.alpha;
+        if (p.b_scales) v *= __ldg(p.b_scales + cidx);
+        if (bias) v += Cvt<T>::to(__ldg(bias + cidx));
+        v = apply_act(v, (Act)p.act);
+        if (R) v += Cvt<T>::to(r.v[e]);
+        o.v[e] = Cvt<T>::from(v);
+      }
+      st16(C + col0 + g * 8, o);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+      int cidx = col0 + e;
+      if (cidx < p.n) {
+        float v = __uint_as_float(acc[e]) * p.alpha;
+        if (p.b_scales) v *= __ldg(p.b_scales + cidx);
+        if (bias) v += Cvt<T>::to(__ldg(bias + cidx));
+        v = apply_act(v, (Act)p.act);
+        if (R) v += Cvt<T>::to(R[cidx]);
+        C[cidx] = Cvt<T>::from(v);
+      }
+    }
+  }
+}
+
+template <int BN, bool B_MN, typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
+  using Cfg = TcCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (p.k + BK - 1) / BK;
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;
+  const long long num_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 4); }
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ── TMA producer ──
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int batch = (int)(t / tiles_per_batch);
+        int rem = (int)(t % tiles_per_batch);
+        int m0 = (rem % p.tiles_m) * BM;
+        int n0 = (rem / p.tiles_m) * BN;
+        int bo = batch / p.batch_inner, bi = batch % p.batch_inner;
+        int a_bo = (p.a_bcast & 1) ? 0 : bo, a_bi = (p.a_bcast & 2) ? 0 : bi;
+        int b_bo = (p.b_bcast & 1) ? 0 : bo, b_bi = (p.b_bcast & 2) ? 0 : bi;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_4d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, a_bi, a_bo);
+          if (B_MN) {
+            // [K,N] rows: one 64(n) x 64(k) box per 64-wide slice of the tile's N extent.
+#pragma unroll
+            for (int j = 0; j < BN / 64; j++)
+              tma_load_4d(sb + j * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + j * 64, kb * BK, b_bi, b_bo);
+          } else {
+            tma_load_4d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, b_bi, b_bo);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ── MMA issuer ──
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, 0, B_MN ? 1 : 0, BM, BN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, p.status, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; kk++) {
+            // A, K-major: 8-row groups 1024 B apart; a K step of 16 elements is 32 B inside the swizzle row.
+            uint64_t da = make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+            uint64_t db;
+            if (B_MN) {
+              // B, N-major: rows are k (128 B = 64 n); 8-k groups 1024 B apart (SBO); 64-n slices
+              // 64*128 B apart (LBO); a K step of 16 rows is 2048 B.
+              db = make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 64 * 128, 1024);
+            } else {
+              db = make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+            }
+            mma_f16_ss(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&tmem_full_bar[acc]);  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ── epilogue warps ──
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int batch = (int)(t / tiles_per_batch);
+      int rem = (int)(t % tiles_per_batch);
+      int m0 = (rem % p.tiles_m) * BM;
+      int n0 = (rem / p.tiles_m) * BN;
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      long long gm = (long long)m0 + quarter * 32 + lane;
+      long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        if (n0 + c * 32 >= p.n) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        if (gm < p.m) epilogue_store_chunk<T>(p, r, gm, n0 + c * 32, c_off);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+// ── host side ───────────────────────────────────────────────────────────────
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; uint64_t d[4]; uint64_t s[3]; uint32_t b0, b1; int dt; int pad;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; i++) { h ^= w[i]; h *= 1099511628211ull; }
+    return (size_t)h;
+  }
+};
+static std::mutex g_map_mu;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+// 4-D map over (inner, rows, batch_inner, batch_outer) of 2-byte elements with a 128B-swizzled
+// box {b0, b1, 1, 1}. Strides are in elements; a dimension of extent 1 may carry any stride.
+static Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uint64_t rows, uint64_t nbi, uint64_t nbo,
+                       uint64_t row_stride, uint64_t bi_stride, uint64_t bo_stride, uint32_t b0, uint32_t b1) {
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = ptr; key.d[0] = inner; key.d[1] = rows; key.d[2] = nbi; key.d[3] = nbo;
+  key.s[0] = row_stride; key.s[1] = bi_stride; key.s[2] = bo_stride; key.b0 = b0; key.b1 = b1; key.dt = (int)dt;
+  {
+    std::lock_guard<std::mutex> g(g_map_mu);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) { *out = it->second; return Status::OK(); }
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return Status::compute("cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[4] = {inner, rows, nbi, nbo};
+  uint64_t s1 = row_stride * 2;
+  uint64_t s2 = (nbi > 1 ? bi_stride : rows * row_stride) * 2;
+  uint64_t s3 = (nbo > 1 ? bo_stride : (nbi > 1 ? nbi * bi_stride : rows * row_stride)) * 2;
+  cuuint64_t gstride[3] = {s1, s2, s3};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMapDataType cdt = dt == DType::BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(out, cdt, 4, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::compute("cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  {
+    std::lock_guard<std::mutex> g(g_map_mu);
+    if (g_map_cache.size() > 4096) g_map_cache.clear();
+    g_map_cache.emplace(key, *out);
+  }
+  return Status::OK();
+}
+
+// 0 = not expressible, 1 = K-major ([N,K] rows), 2 = N-major ([K,N] rows).
+static int classify_b(const GemmDesc& d) {
+  if (d.b_row == 1 && d.b_col % 8 == 0 && d.b_col >= d.k) return 1;
+  if (d.b_col == 1 && d.b_row % 8 == 0 && d.b_row >= d.n) return 2;
+  return 0;
+}
+
+static bool tc_eligible(const GemmDesc& d) {
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
+  if (d.m < 1 || d.n < 1 || d.k < 1 || d.batch < 1 || d.batch_inner < 1) return false;
+  if (d.m > 0x7fffffff || d.n > 0x7fffffff || d.k > 0x7fffffff || d.batch * d.batch_inner > 0x7fffffff) return false;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(d.a) || !al16(d.b)) return false;
+  // A must be K-major with 16-byte aligned rows; batch strides 16-byte aligned (0 = broadcast).
+  if (d.a_col != 1 || d.a_row % 8 != 0 || d.a_row < d.k) return false;
+  if (d.batch > 1 && d.a_batch % 8 != 0) return false;
+  if (d.batch_inner > 1 && d.a_batch_inner % 8 != 0) return false;
+  if (classify_b(d) == 0) return false;
+  if (d.batch > 1 && d.b_batch % 8 != 0) return false;
+  if (d.batch_inner > 1 && d.b_batch_inner % 8 != 0) return false;
+  return true;
+}
+
+Status matmul_simt(cudaStream_t s, const GemmDesc& d);
+
+static int* g_status_word = nullptr;   // device int, lazily allocated once per process
+static int* g_status_host = nullptr;   // pinned mirror
+
+template <int BN, bool B_MN, typename T>
+static Status launch_tc(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, long long num_tiles) {
+  using Cfg = TcCfg<BN>;
+  static bool attr_set = false;
+  auto kern = gemm_tc_kernel<BN, B_MN, T>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return cuda_status(e, "matmul (tcgen05) smem attribute");
+    attr_set = true;
+  }
+  int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
+  kern<<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(ma, mb, p);
+  AG_CHECK_LAUNCH("matmul (tcgen05)");
+  return Status::OK();
+}
+
+Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
+  const bool b_mn = classify_b(d) == 2;
+  const long long nb = d.batch * d.batch_inner;
+  // Tile width: 256 when the problem has enough tiles to fill the machine, else 128.
+  long long tiles_m = (d.m + BM - 1) / BM;
+  int bn = 256;
+  if (d.n <= 128 || tiles_m * ((d.n + 255) / 256) * nb < (long long)sm_count()) bn = 128;
+  long long tiles_n = (d.n + bn - 1) / bn;
+  CUtensorMap ma, mb;
+  // A broadcast (stride-0) batch level is mapped as extent 1 and its coordinate pinned to 0.
+  int a_bcast = ((d.batch > 1 && d.a_batch == 0) ? 1 : 0) | ((d.batch_inner > 1 && d.a_batch_inner == 0) ? 2 : 0);
+  int b_bcast = ((d.batch > 1 && d.b_batch == 0) ? 1 : 0) | ((d.batch_inner > 1 && d.b_batch_inner == 0) ? 2 : 0);
+  uint64_t a_nbo = (a_bcast & 1) ? 1 : (uint64_t)d.batch, a_nbi = (a_bcast & 2) ? 1 : (uint64_t)d.batch_inner;
+  uint64_t b_nbo = (b_bcast & 1) ? 1 : (uint64_t)d.batch, b_nbi = (b_bcast & 2) ? 1 : (uint64_t)d.batch_inner;
+  AG_RETURN_IF_ERROR(make_map(&ma, d.dtype, d.a, (uint64_t)d.k, (uint64_t)d.m, a_nbi, a_nbo, (uint64_t)d.a_row,
+                              (uint64_t)d.a_batch_inner, (uint64_t)d.a_batch, BK, BM));
+  if (!b_mn) {
+    AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.k, (uint64_t)d.n, b_nbi, b_nbo, (uint64_t)d.b_col,
+                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)bn));
+  } else {
+    AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.n, (uint64_t)d.k, b_nbi, b_nbo, (uint64_t)d.b_row,
+                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, 64, BK));
+  }
+  TcParams p;
+  p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.b_scales = d.ep.b_scales; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
+  p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.batch = (int)nb; p.batch_inner = (int)d.batch_inner;
+  p.c_row = d.c_row; p.c_batch = d.c_batch; p.c_batch_inner = d.c_batch_inner; p.a_bcast = a_bcast; p.b_bcast = b_bcast;
+  p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
+  long long num_tiles = tiles_m * tiles_n * nb;
+#define AG_TC(BNV, MN) \
+  (d.dtype == DType::BF16 ? launch_tc<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc<BNV, MN, __half>(s, ma, mb, p, num_tiles))
+  if (bn == 256) return b_mn ? AG_TC(256, true) : AG_TC(256, false);
+  return b_mn ? AG_TC(128, true) : AG_TC(128, false);
+#undef AG_TC
+}
+
+static int g_force_path = 0;  // 0 auto, 1 simt, 2 tcgen05 (error if not eligible)
+void set_matmul_path(int mode) { g_force_path = mode; }
+
+const char* matmul_path(const GemmDesc& d) {
+  if (g_force_path == 1) return "simt";
+  return tc_eligible(d) ? "tcgen05" : "simt";
+}
+
+int* matmul_status_word() {
+  if (!g_status_word) {
+    if (cudaMalloc(&g_status_word, sizeof(int)) != cudaSuccess) { g_status_word = nullptr; return nullptr; }
+    cudaMemset(g_status_word, 0, sizeof(int));
+    cudaMallocHost(&g_status_host, sizeof(int));
+    if (g_status_host) *g_status_host = 0;
+  }
+  return g_status_word;
+}
+
+// Reads and clears the pipeline status word; non-zero means a bounded wait gave up.
+int matmul_take_status(cudaStream_t s) {
+  if (!g_status_word || !g_status_host) return 0;
+  if (cudaMemcpyAsync(g_status_host, g_status_word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+  int v = *g_status_host;
+  if (v != 0) cudaMemsetAsync(g_status_word, 0, sizeof(int), s);
+  return v;
+}
+
+Status matmul(cudaStream_t s, const GemmDesc& d) {
+  if (d.m == 0 || d.n == 0 || d.batch == 0) return Status::OK();
+  bool elig = tc_eligible(d);
+  if (g_force_path == 2 && !elig) return Status::compute("matmul: tcgen05 path forced but operands are not TMA-compatible");
+  if (elig && g_force_path != 1) {
+    int* st = matmul_status_word();
+    if (!st) return Status::compute("matmul: cannot allocate status word");
+    return matmul_tc(s, d, st);
+  }
+  return matmul_simt(s, d);
+}
+
+}}  // namespace ag::k

@@ -1,0 +1,102 @@
+// Host-side launchers for the sm_100a kernels. One entry per kernel family of the
+// reference's crates/core/src/kernel_templates.rs; each launcher validates what the
+// kernel needs (alignment, dtype) and enqueues on the given stream. Nothing here
+// allocates or synchronises.
+#pragma once
+#include <cuda_runtime.h>
+#include "../core/types.h"
+
+namespace ag { namespace k {
+
+enum class BinOp : int { Add = 0, Sub, Mul, Div };
+enum class UnOp : int {
+  Neg = 0, Relu, Exp, Log, Sqrt, Tanh, Sin, Cos, Gelu, GeluExact, Sigmoid, Abs, Sign, Copy
+};
+enum class Act : int { None = 0, GeluTanh = 1, GeluErf = 2, Relu = 3 };
+
+// Fused element-wise chain (reference: fusion.rs:167-238 emits MSL text; here the chain
+// is a register program interpreted per element). Registers 0..n_inputs-1 hold the loaded
+// leaf inputs; instruction i writes register n_inputs+i; the last register is stored.
+struct FusedInstr { int8_t op; int8_t is_binary; int8_t a; int8_t b; };
+constexpr int kFusedMaxInputs = 8;
+constexpr int kFusedMaxInstrs = 24;
+struct FusedProgram {
+  int n_inputs = 0;
+  int n_instrs = 0;
+  FusedInstr instrs[kFusedMaxInstrs];
+};
+
+Status binary(cudaStream_t s, BinOp op, const TView& a, const TView& b, const TView& out);
+Status unary(cudaStream_t s, UnOp op, const TView& in, const TView& out);
+Status scalar_mul(cudaStream_t s, const TView& in, float scale, const TView& out);
+Status fused_elementwise(cudaStream_t s, const FusedProgram& prog, const TView* ins, const TView& out);
+// out[i] = act(in[i] + bias[(i / inner) % channels]); channels = dims[1], inner = prod(dims[2:]).
+Status add_bias(cudaStream_t s, const TView& in, const TView& bias, Act act, const TView& out);
+Status threshold_backward(cudaStream_t s, const TView& grad, const TView& in, float threshold, const TView& out);
+// self += alpha * other (both contiguous or same-strided views).
+Status add_scaled_inplace(cudaStream_t s, const TView& self, const TView& other, float alpha);
+
+Status layer_norm(cudaStream_t s, const TView& in, const TView& gamma, const TView& beta, float eps, const TView& out);
+// Row softmax over the last dim. causal: rows are the second-to-last dim, mask col > row.
+Status softmax(cudaStream_t s, const TView& in, bool causal, const TView& out);
+Status argmax(cudaStream_t s, const TView& in, const TView& out_i32);
+Status sum_last(cudaStream_t s, const TView& in, const TView& out, bool mean);
+Status sum_dim(cudaStream_t s, const TView& in, int dim, const TView& out);
+Status mean_all(cudaStream_t s, const TView& in, const TView& out);
+
+Status embedding(cudaStream_t s, const TView& weight, const TView& idx, const TView& out);
+// out[i,:] = wte[tok[i],:] + wpe[pos[i],:] in one pass (token + position embedding).
+Status embedding_add(cudaStream_t s, const TView& wte, const TView& tok, const TView& wpe, const TView& pos, const TView& out);
+Status gather2d(cudaStream_t s, const TView& in, int dim, const TView& idx, const TView& out);
+Status index_select2d(cudaStream_t s, const TView& in, int dim, const TView& idx, const TView& out);
+
+Status quantize(cudaStream_t s, const TView& in, float scale, int zero_point, const TView& out);
+Status dequantize(cudaStream_t s, const TView& in, float scale, int zero_point, const TView& out);
+// Per-output-channel symmetric int8: w [N,K] float -> q [N,K] int8, scale[n] = max|w[n,:]|/127.
+Status quantize_rows(cudaStream_t s, const TView& w, const TView& q, const TView& scales);
+Status cast(cudaStream_t s, const TView& in, const TView& out);
+// Strided gather-copy: dst (any strides) <- src (any strides), same shape and dtype size.
+Status copy_strided(cudaStream_t s, const TView& src, const TView& dst);
+
+struct GemmEpilogue {
+  const void* bias = nullptr;      // [N], same dtype as C
+  const void* residual = nullptr;  // same layout as C
+  Act act = Act::None;
+  float alpha = 1.0f;              // applied to the accumulator before bias
+  const float* b_scales = nullptr; // int8-weight path: per-output-channel scales [N]
+};
+struct GemmDesc {
+  DType dtype;            // dtype of A and C (f32/f16/bf16)
+  DType b_dtype;          // = dtype, or I8 for the weight-quantised path
+  const void* a; const void* b; void* c;
+  int64_t m, n, k;
+  // Batch index = (outer, inner): `batch` outer entries, each with `batch_inner` inner entries,
+  // so that a [B, heads, T, d] view with unrelated B and head strides needs no copy.
+  int64_t batch, batch_inner = 1;
+  // Element strides. a: [batch, m, k]; b: logical [batch, k, n]; c: [batch, m, n] with ldc.
+  int64_t a_row, a_col, a_batch, a_batch_inner = 0;
+  int64_t b_row, b_col, b_batch, b_batch_inner = 0;  // b_row = stride along k, b_col = stride along n
+  int64_t c_row, c_batch, c_batch_inner = 0;
+  GemmEpilogue ep;
+};
+Status matmul(cudaStream_t s, const GemmDesc& d);
+// Reports which kernel family `matmul` would choose: "tcgen05" or "simt".
+const char* matmul_path(const GemmDesc& d);
+
+struct AttnDesc {
+  DType dtype;
+  const void* q; const void* k; const void* v; void* o;
+  int64_t batch, heads, tq, tk, d;     // flattened leading dims = batch*heads
+  int64_t q_b, q_h, q_t;               // element strides (last dim contiguous)
+  int64_t k_b, k_h, k_t;
+  int64_t v_b, v_h, v_t;
+  int64_t o_b, o_h, o_t;
+  float scale;
+  bool causal;
+};
+Status attention(cudaStream_t s, const AttnDesc& d);
+
+// Writes more than the L2 capacity so the next timed kernel starts cold.
+Status flush_l2(cudaStream_t s, void* scratch, size_t bytes);
+
+}}  // namespace ag::k

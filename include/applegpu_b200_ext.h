@@ -1,0 +1,148 @@
+/*
+ * Additive entry points of the B200 build. None of these exist in the reference's
+ * backend_cpp/applegpu_ffi.h: upstream reaches the same operations only through in-process Rust
+ * calls from its PyO3 module (crates/python/src/metal_backend.rs -> crates/core/src/ops.rs), so
+ * a C caller had no way to record them. Each function follows the conventions of
+ * applegpu_b200_ffi.h and cites the Rust function whose behaviour it exposes.
+ */
+#ifndef APPLEGPU_B200_EXT_H
+#define APPLEGPU_B200_EXT_H
+
+#include <stdint.h>
+#include <stdbool.h>
+#include <stddef.h>
+
+#ifndef APPLEGPU_API
+#  if defined(__GNUC__)
+#    define APPLEGPU_API __attribute__((visibility("default")))
+#  else
+#    define APPLEGPU_API
+#  endif
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ── host <-> device bytes (device pointers are not host-dereferenceable) ───── */
+/* Stream-ordered copy into a tensor; the host buffer may be reused when the call returns
+ * only if it is pageable (pinned buffers must outlive the next synchronize). */
+APPLEGPU_API int32_t applegpu_ffi_upload(uint64_t tensor_id, const void* host_ptr, uint64_t nbytes);
+/* Evaluates if pending, copies out, and waits. Reference: LazyRuntime::read_bytes, lazy.rs:2554-2560. */
+APPLEGPU_API int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nbytes);
+/* alloc + register_tensor + upload in one call; returns the id, 0 on failure. */
+APPLEGPU_API uint64_t applegpu_ffi_from_host(const void* host_ptr, const uint64_t* dims, uint32_t ndim, int8_t dtype);
+APPLEGPU_API int32_t applegpu_eager_upload(uint64_t id, const void* host_ptr, uint64_t nbytes);
+APPLEGPU_API int32_t applegpu_eager_download(uint64_t id, void* host_ptr, uint64_t nbytes);
+
+/* ── graph flavour: the rest of the transformer-forward op set ─────────────── */
+/* Reference recorders: ops.rs div :364, unary ops :594-615, softmax :487-506, softmax_causal
+ * :1367-1386, layer_norm :618-651, embedding :1194-1230, add_bias :1322-1361, scalar_mul :554-568,
+ * argmax :1390-1413, sum / mean :1417-1470, transpose :540-552, transpose_dims :510-538, reshape
+ * :570-592, slice :1234-1268, concat :1271-1316, gather :1729-1780, index_select :1784-1829, cast
+ * :2299-2320, quantize :2250-2273, dequantize :2276-2296, attention :1531-1572, attention_causal
+ * :1577-1618. All return the output id, 0 on failure. */
+APPLEGPU_API uint64_t applegpu_ffi_div(uint64_t a_id, uint64_t b_id);
+APPLEGPU_API uint64_t applegpu_ffi_exp(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_log(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_sqrt(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_tanh(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_sin(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_cos(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_abs(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_sign(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_sigmoid(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_gelu(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_gelu_exact(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_softmax(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_softmax_causal(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_layer_norm(uint64_t input_id, uint64_t gamma_id, uint64_t beta_id, float eps);
+APPLEGPU_API uint64_t applegpu_ffi_embedding(uint64_t weight_id, uint64_t indices_id);
+APPLEGPU_API uint64_t applegpu_ffi_add_bias(uint64_t input_id, uint64_t bias_id);
+APPLEGPU_API uint64_t applegpu_ffi_scalar_mul(uint64_t input_id, float scale);
+APPLEGPU_API uint64_t applegpu_ffi_argmax(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_sum(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_mean(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_transpose(uint64_t input_id);
+APPLEGPU_API uint64_t applegpu_ffi_transpose_dims(uint64_t input_id, uint32_t dim0, uint32_t dim1);
+APPLEGPU_API uint64_t applegpu_ffi_reshape(uint64_t input_id, const uint64_t* dims, uint32_t ndim);
+APPLEGPU_API uint64_t applegpu_ffi_slice(uint64_t input_id, uint32_t dim, uint64_t start, uint64_t end);
+APPLEGPU_API uint64_t applegpu_ffi_concat(uint64_t a_id, uint64_t b_id, uint32_t dim);
+APPLEGPU_API uint64_t applegpu_ffi_gather(uint64_t input_id, uint32_t dim, uint64_t index_id);
+APPLEGPU_API uint64_t applegpu_ffi_index_select(uint64_t input_id, uint32_t dim, uint64_t index_id);
+APPLEGPU_API uint64_t applegpu_ffi_cast(uint64_t input_id, int8_t target_dtype);
+APPLEGPU_API uint64_t applegpu_ffi_quantize(uint64_t input_id, int8_t target_dtype, float scale, int32_t zero_point);
+APPLEGPU_API uint64_t applegpu_ffi_dequantize(uint64_t input_id, int8_t target_dtype, float scale, int32_t zero_point);
+APPLEGPU_API uint64_t applegpu_ffi_attention(uint64_t q_id, uint64_t k_id, uint64_t v_id);
+APPLEGPU_API uint64_t applegpu_ffi_attention_causal(uint64_t q_id, uint64_t k_id, uint64_t v_id);
+
+/* Per-output-channel symmetric int8 weights (no upstream counterpart; upstream lists
+ * int8-weight matmul as backlog). quantize_weight: w [N,K] float -> *out_q [N,K] int8 and
+ * *out_scales [N] f32 with scale[n] = max|w[n,:]|/127, evaluated immediately.
+ * matmul_int8: x [..,M,K] @ (q * scale)^T -> [..,M,N], dequantisation fused into the GEMM. */
+APPLEGPU_API int32_t applegpu_ffi_quantize_weight(uint64_t weight_id, uint64_t* out_q_id, uint64_t* out_scales_id);
+APPLEGPU_API uint64_t applegpu_ffi_matmul_int8(uint64_t x_id, uint64_t q_id, uint64_t scales_id);
+
+/* ── eager flavour: the same ops, executed immediately ─────────────────────── */
+APPLEGPU_API uint8_t* applegpu_eager_gelu_exact(uint64_t input_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_softmax_causal(uint64_t input_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_add_bias(uint64_t input_id, uint64_t bias_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_argmax(uint64_t input_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_gather(uint64_t input_id, uint32_t dim, uint64_t index_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_index_select(uint64_t input_id, uint32_t dim, uint64_t index_id, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_cast(uint64_t input_id, int8_t target_dtype, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_quantize(uint64_t input_id, int8_t target_dtype, float scale, int32_t zero_point, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_dequantize(uint64_t input_id, int8_t target_dtype, float scale, int32_t zero_point, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_attention(uint64_t q_id, uint64_t k_id, uint64_t v_id, bool causal, uint64_t* out_id);
+APPLEGPU_API uint8_t* applegpu_eager_unary(uint64_t input_id, const char* op_name, uint64_t* out_id);
+/* Linear layer with its epilogue in the GEMM kernel: act(x @ w * 1 + bias) + residual.
+ * bias_id / residual_id may be 0; act: 0 none, 1 tanh-GELU, 2 erf-GELU, 3 ReLU. w is [K,N], or
+ * [N,K] when transpose_w. */
+APPLEGPU_API uint8_t* applegpu_eager_linear(uint64_t x_id, uint64_t w_id, uint64_t bias_id, uint64_t residual_id, int32_t act, bool transpose_w, uint64_t* out_id);
+
+/* ── runtime services ──────────────────────────────────────────────────────── */
+/* Metadata-only mode for hosts without a GPU: ids, shapes, validation, the fusion pass and
+ * applegpu_ffi_plan work; anything that would launch a kernel fails. Must be the first init call. */
+APPLEGPU_API bool applegpu_ffi_init_dry(void);
+/* Writes the launch plan of eval(tensor_id) after the fusion pass, one kernel per line, without
+ * running it. Returns the full length (may exceed cap), -1 on failure. */
+APPLEGPU_API int64_t applegpu_ffi_plan(uint64_t tensor_id, char* buf, uint64_t cap);
+APPLEGPU_API int32_t applegpu_ffi_is_pending(uint64_t tensor_id);
+/* Toggle the reference's element-wise chain rule and this build's graph-level rewrites. */
+APPLEGPU_API void applegpu_ffi_set_fusion(bool elementwise_chains, bool patterns);
+/* out[0..6] = hits, misses, pooled_bytes, bucket_count, live_bytes, peak_live_bytes, live_buffers.
+ * Reference: BufferPool::stats, pool.rs:100-108 (first four). */
+APPLEGPU_API void applegpu_pool_stats(uint64_t* out7);
+APPLEGPU_API void applegpu_pool_drain(void);
+APPLEGPU_API void applegpu_pool_set_watermark(uint64_t max_pooled_bytes);
+APPLEGPU_API int32_t applegpu_pool_prewarm(const uint64_t* sizes, uint32_t n);
+/* Host-side fault injection for tests: the next n device allocations report failure. */
+APPLEGPU_API void applegpu_pool_fail_next(int32_t n);
+APPLEGPU_API uint64_t applegpu_memory_usage(void);
+APPLEGPU_API uint64_t applegpu_tensor_count(void);
+/* The CUDA stream (cudaStream_t) all work is enqueued on, and the device ordinal. */
+APPLEGPU_API void* applegpu_stream(void);
+APPLEGPU_API int32_t applegpu_device(void);
+APPLEGPU_API const char* applegpu_device_name(void);
+/* Kernel launches issued since process start. */
+APPLEGPU_API uint64_t applegpu_launch_count(void);
+/* Which kernel family a matmul of these tensors would take: "tcgen05", "simt", or NULL on error. */
+APPLEGPU_API const char* applegpu_matmul_path(uint64_t a_id, uint64_t b_id, bool eager);
+/* 0 auto, 1 force the CUDA-core kernel, 2 require the tcgen05 kernel. */
+APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
+/* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
+APPLEGPU_API int32_t applegpu_pipeline_status(void);
+/* CUDA-event stopwatch on the runtime stream. */
+APPLEGPU_API int32_t applegpu_timer_start(void);
+APPLEGPU_API float applegpu_timer_stop_ms(void);
+/* Evicts the L2 by streaming writes over a scratch buffer larger than the cache. */
+APPLEGPU_API int32_t applegpu_flush_l2(void);
+/* Kernel name the registry resolves for (base name, dtype), e.g. ("matmul", 10) -> "matmul_bf16".
+ * Reference: KernelRegistry::resolve_kernel, compute.rs:1478-1567. Returns NULL if unsupported. */
+APPLEGPU_API const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* APPLEGPU_B200_EXT_H */
