@@ -6,13 +6,67 @@
 // of them with a copy kernel (lazy.rs:1891-1917, :2246-2262) — and consumers either read the
 // strided view directly (matmul, element-wise, copy) or make it contiguous first.
 #include "runtime.h"
+#include <array>
 #include <atomic>
 #include <cmath>
+#include <map>
+#include <mutex>
+#include <sstream>
 
 namespace ag {
 
 std::atomic<uint64_t> g_launch_count{0};
 uint64_t launch_count() { return g_launch_count.load(); }
+
+// Optional per-kernel timing: CUDA events bracket each launch on the runtime stream and are
+// resolved when the report is read. Off by default (events cost host time, not kernel time).
+namespace profile {
+struct Span { std::string name; cudaEvent_t a, b; double work; };
+static bool g_on = false;
+static std::vector<Span> g_spans;
+static std::mutex g_mu;
+void enable(bool on) { std::lock_guard<std::mutex> g(g_mu); g_on = on; }
+bool enabled() { return g_on; }
+void clear() {
+  std::lock_guard<std::mutex> g(g_mu);
+  for (auto& s : g_spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+  g_spans.clear();
+}
+struct Scope {
+  bool live = false; size_t idx = 0;
+  Scope(const std::string& name, double work) {
+    if (!g_on) return;
+    DeviceCtx& ctx = DeviceCtx::get();
+    if (ctx.dry) return;
+    Span sp; sp.name = name; sp.work = work;
+    if (cudaEventCreate(&sp.a) != cudaSuccess || cudaEventCreate(&sp.b) != cudaSuccess) return;
+    cudaEventRecord(sp.a, ctx.stream);
+    std::lock_guard<std::mutex> g(g_mu);
+    g_spans.push_back(sp); idx = g_spans.size() - 1; live = true;
+  }
+  ~Scope() {
+    if (!live) return;
+    std::lock_guard<std::mutex> g(g_mu);
+    cudaEventRecord(g_spans[idx].b, DeviceCtx::get().stream);
+  }
+};
+// "name count total_ms work" per line; work = algorithmic flops (GEMM, attention) or bytes (the rest).
+std::string report() {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.dry && ctx.ready) cudaStreamSynchronize(ctx.stream);
+  std::lock_guard<std::mutex> g(g_mu);
+  std::map<std::string, std::array<double, 3>> agg;
+  for (auto& s : g_spans) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, s.a, s.b) != cudaSuccess) continue;
+    auto& a = agg[s.name]; a[0] += 1; a[1] += ms; a[2] += s.work;
+  }
+  std::ostringstream os;
+  for (auto& kv : agg) os << kv.first << " " << (long long)kv.second[0] << " " << kv.second[1] << " " << kv.second[2] << "\n";
+  return os.str();
+}
+}  // namespace profile
+
 #define AG_LAUNCH(expr) do { AG_RETURN_IF_ERROR(expr); g_launch_count.fetch_add(1, std::memory_order_relaxed); } while (0)
 
 static Status alloc_out(const Dims& shape, DType dt, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
@@ -174,7 +228,37 @@ static Status attention_exec(const TensorRec& q, const TensorRec& kk, const Tens
   return Status::OK();
 }
 
+// Algorithmic work of a node: flops for contractions, bytes (inputs + output) otherwise.
+static double node_work(const OpNode& node, const std::vector<const TensorRec*>& in) {
+  const OpKind& kd = node.op;
+  double out_elems = (double)numel_of(node.out_shape);
+  if (kd.op == Op::Matmul || kd.op == Op::FusedLinear || kd.op == Op::MatmulInt8) {
+    double k = in[0]->shape.empty() ? 1.0 : (double)in[0]->shape.back();
+    return 2.0 * out_elems * k;
+  }
+  if (kd.op == Op::FusedAttention) {
+    const Dims& q = in[0]->shape; const Dims& kk = in[1]->shape;
+    double bh = 1; for (size_t i = 0; i + 2 < q.size(); i++) bh *= (double)q[i];
+    double tq = (double)q[q.size() - 2], d = (double)q.back(), tk = (double)kk[kk.size() - 2], dv = (double)node.out_shape.back();
+    return 2.0 * bh * tq * tk * (d + dv);
+  }
+  double bytes = out_elems * (double)dtype_size(node.out_dtype);
+  if (kd.op == Op::Embedding || kd.op == Op::FusedEmbedAdd) return 2.0 * bytes * (kd.op == Op::FusedEmbedAdd ? 1.5 : 1.0);
+  for (auto* t : in) bytes += (double)t->nbytes();
+  return bytes;
+}
+
+static Status execute_node_impl(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf);
+
 Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
+  if (!profile::enabled()) return execute_node_impl(node, in, out, out_buf);
+  std::string name = node.op.kernel_name();
+  if (node.op.op == Op::FusedElementwise) name = "fused_elementwise";
+  profile::Scope scope(name + dtype_suffix(node.out_dtype), node_work(node, in));
+  return execute_node_impl(node, in, out, out_buf);
+}
+
+static Status execute_node_impl(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
   DeviceCtx& ctx = DeviceCtx::get();
   AG_RETURN_IF_ERROR(ctx.make_current());
   const OpKind& kd = node.op;

@@ -12,6 +12,7 @@
 
 namespace ag {
 uint64_t launch_count();
+namespace profile { void enable(bool on); void clear(); std::string report(); }
 namespace k {
 void set_matmul_path(int mode);
 int matmul_take_status(cudaStream_t s);
@@ -850,6 +851,13 @@ int32_t applegpu_flush_l2(void) {
   if (!ctx.ready || ctx.dry) return -1;
   if (!g_flush_buf && cudaMalloc(&g_flush_buf, kFlushBytes) != cudaSuccess) { g_flush_buf = nullptr; return -1; }
   return k::flush_l2(ctx.stream, g_flush_buf, kFlushBytes).ok() ? 0 : -1;
+}
+void applegpu_profile_enable(bool on) { ag::profile::enable(on); }
+void applegpu_profile_clear(void) { ag::profile::clear(); }
+int64_t applegpu_profile_report(char* buf, uint64_t cap) {
+  std::string out = ag::profile::report();
+  if (buf && cap) { size_t n = out.size() < cap - 1 ? out.size() : (size_t)cap - 1; std::memcpy(buf, out.data(), n); buf[n] = 0; }
+  return (int64_t)out.size();
 }
 const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype) {
   thread_local std::string out;

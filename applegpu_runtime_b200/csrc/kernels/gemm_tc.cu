@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -384,7 +385,15 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
 #undef AG_TC
 }
 
-static int g_force_path = 0;  // 0 auto, 1 simt, 2 tcgen05 (error if not eligible)
+// 0 auto, 1 simt, 2 tcgen05 (error if not eligible). APPLEGPU_MATMUL_PATH=simt|tcgen05 sets the initial value.
+static int initial_force_path() {
+  const char* v = std::getenv("APPLEGPU_MATMUL_PATH");
+  if (!v) return 0;
+  if (std::strcmp(v, "simt") == 0) return 1;
+  if (std::strcmp(v, "tcgen05") == 0) return 2;
+  return 0;
+}
+static int g_force_path = initial_force_path();
 void set_matmul_path(int mode) { g_force_path = mode; }
 
 const char* matmul_path(const GemmDesc& d) {

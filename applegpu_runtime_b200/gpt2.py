@@ -1,0 +1,180 @@
+"""GPT-2 forward as a sequence of hot-path ops, with a batch dimension.
+
+Follows the reference's python/applegpu_runtime/models/gpt2.py:47-180 op for op (pre-LN blocks,
+tanh-GELU, learned positions, tied LM head, KV cache by concatenation) and adds what the
+reference lacks: a batch dimension ([B, T] token ids; linears run on [B*T, d], attention on
+[B, heads, T, d_head]). The slice / reshape / transpose_dims calls below are views in this
+runtime, and the fusion pass folds add_bias / gelu / residual into the GEMM epilogues and the
+five attention ops into one node, so the kernel count per layer is far below the op count.
+"""
+import numpy as np
+
+from . import api as gpu
+
+GPT2_SMALL = {"n_layer": 12, "n_head": 12, "n_embd": 768, "vocab_size": 50257, "n_positions": 1024}
+GPT2_LARGE = {"n_layer": 36, "n_head": 20, "n_embd": 1280, "vocab_size": 50257, "n_positions": 1024}
+
+
+def init_gpt2_weights(config=None, seed=0, dtype="float32", std=0.02):
+    """Random-init weights with the HF GPT-2 layout and init (N(0, std) matrices and embeddings,
+    zero biases, unit LayerNorm gains). Keys match `GPT2LMHeadModel.state_dict()`; Conv1D weights
+    are [in, out] so `x @ W` needs no transpose (reference: models/gpt2.py:6-47)."""
+    cfg = dict(GPT2_SMALL if config is None else config)
+    rng = np.random.default_rng(seed)
+    d, L = cfg["n_embd"], cfg["n_layer"]
+    host = {}
+
+    def normal(*shape):
+        return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float32)
+
+    host["transformer.wte.weight"] = normal(cfg["vocab_size"], d)
+    host["transformer.wpe.weight"] = normal(cfg["n_positions"], d)
+    for i in range(L):
+        p = f"transformer.h.{i}"
+        host[f"{p}.ln_1.weight"] = np.ones(d, np.float32)
+        host[f"{p}.ln_1.bias"] = np.zeros(d, np.float32)
+        host[f"{p}.attn.c_attn.weight"] = normal(d, 3 * d)
+        host[f"{p}.attn.c_attn.bias"] = np.zeros(3 * d, np.float32)
+        host[f"{p}.attn.c_proj.weight"] = normal(d, d)
+        host[f"{p}.attn.c_proj.bias"] = np.zeros(d, np.float32)
+        host[f"{p}.ln_2.weight"] = np.ones(d, np.float32)
+        host[f"{p}.ln_2.bias"] = np.zeros(d, np.float32)
+        host[f"{p}.mlp.c_fc.weight"] = normal(d, 4 * d)
+        host[f"{p}.mlp.c_fc.bias"] = np.zeros(4 * d, np.float32)
+        host[f"{p}.mlp.c_proj.weight"] = normal(4 * d, d)
+        host[f"{p}.mlp.c_proj.bias"] = np.zeros(d, np.float32)
+    host["transformer.ln_f.weight"] = np.ones(d, np.float32)
+    host["transformer.ln_f.bias"] = np.zeros(d, np.float32)
+    return load_gpt2_state_dict(host, cfg, dtype=dtype)
+
+
+def load_gpt2_state_dict(state, config, dtype="float32"):
+    """Uploads a {name: numpy / torch array} state dict (HF GPT-2 names). Returns the model dict
+    the reference's `load_gpt2_weights` returns: {"weights": {...GpuTensor}, "config": {...}}."""
+    weights = {}
+    for name, arr in state.items():
+        if name.endswith(".attn.bias") or name.endswith(".attn.masked_bias") or name == "lm_head.weight":
+            continue  # causal-mask buffers and the tied head are not parameters of the forward
+        if hasattr(arr, "detach"):
+            arr = arr.detach().cpu().float().numpy()
+        t = gpu.from_numpy(np.ascontiguousarray(arr, dtype=np.float32))
+        if dtype != "float32":
+            t = gpu.cast(t, dtype)
+            t.eval()
+        weights[name] = t
+    return {"weights": weights, "config": dict(config), "dtype": dtype}
+
+
+def quantize_gpt2_linears(model):
+    """Per-output-channel symmetric int8 for every linear weight (activations keep the model
+    dtype). Weights are stored [N, K] (K-major) so the GEMM reads them as they lie."""
+    w = model["weights"]
+    q = {}
+    for name, t in w.items():
+        if name.endswith((".c_attn.weight", ".c_fc.weight", ".c_proj.weight")):
+            wt = gpu.transpose(t)           # [out, in] view
+            wt = gpu.reshape(wt, wt.shape)  # materialise [N, K] contiguous
+            q[name] = gpu.quantize_weight(wt)
+    model["int8"] = q
+    return model
+
+
+def _linear(x, w, name, bias):
+    q = w.get("__int8__", {}).get(name)
+    if q is not None:
+        y = gpu.matmul_int8(x, q[0], q[1])
+    else:
+        y = x @ w[name]
+    return gpu.add_bias(y, bias)
+
+
+def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=None):
+    """GPT-2 forward with optional KV cache.
+
+    input_ids: list of ints (the reference's form, batch 1) or an int array [B, T]. With a cache
+    only the last token of each sequence is processed. Returns (logits, new_kv_cache); logits are
+    [T, vocab] for list input (as upstream) or [B, T, vocab] for array input; with `last_only`
+    only the final position goes through the LM head ([B, vocab]). `device_ids` = (token ids,
+    position ids) as int32 GpuTensors of length B*T skips the host-to-device copy of the ids;
+    `input_ids` then only supplies the [B, T] shape.
+    """
+    w = dict(model["weights"])
+    if "int8" in model:
+        w["__int8__"] = model["int8"]
+    cfg = model["config"]
+    n_layer, n_head, n_embd = cfg["n_layer"], cfg["n_head"], cfg["n_embd"]
+    d_head = n_embd // n_head
+
+    ids = np.asarray(input_ids, dtype=np.int64)
+    batched = ids.ndim == 2
+    if not batched:
+        ids = ids.reshape(1, -1)
+    B = ids.shape[0]
+    use_cache = kv_cache is not None
+    if use_cache:
+        tok = ids[:, -1:]
+        pos_offset = ids.shape[1] - 1
+    else:
+        tok = ids
+        pos_offset = 0
+    T = tok.shape[1]
+    rows = B * T
+
+    if device_ids is not None:
+        # token / position indices already resident on the device (int32 [B*T] each)
+        indices, pos_indices = device_ids
+    else:
+        indices = gpu.from_numpy(np.ascontiguousarray(tok.reshape(-1), dtype=np.int32))
+        pos = np.tile(np.arange(pos_offset, pos_offset + T, dtype=np.int32), B)
+        pos_indices = gpu.from_numpy(pos)
+
+    tok_emb = gpu.embedding(w["transformer.wte.weight"], indices)
+    pos_emb = gpu.embedding(w["transformer.wpe.weight"], pos_indices)
+    x = tok_emb + pos_emb  # [B*T, d]
+
+    new_kv_cache = []
+    for i in range(n_layer):
+        p = f"transformer.h.{i}"
+        x_norm = gpu.layer_norm(x, w[f"{p}.ln_1.weight"], w[f"{p}.ln_1.bias"])
+        qkv = _linear(x_norm, w, f"{p}.attn.c_attn.weight", w[f"{p}.attn.c_attn.bias"])
+
+        q_all = gpu.slice(qkv, dim=1, start=0, end=n_embd)
+        k_new = gpu.slice(qkv, dim=1, start=n_embd, end=2 * n_embd)
+        v_new = gpu.slice(qkv, dim=1, start=2 * n_embd, end=3 * n_embd)
+
+        def heads(t):
+            t = gpu.reshape(t, [B, T, n_head, d_head])
+            return gpu.transpose_dims(t, 1, 2)  # [B, n_head, T, d_head]
+
+        q, k, v = heads(q_all), heads(k_new), heads(v_new)
+        if use_cache:
+            ck, cv = kv_cache[i]
+            k = gpu.concat(ck, k, dim=2)
+            v = gpu.concat(cv, v, dim=2)
+        new_kv_cache.append((k, v))
+
+        attn = gpu.attention(q, k, v) if use_cache else gpu.attention_causal(q, k, v)
+        attn = gpu.transpose_dims(attn, 1, 2)        # [B, T, n_head, d_head]
+        attn = gpu.reshape(attn, [rows, n_embd])
+
+        attn = _linear(attn, w, f"{p}.attn.c_proj.weight", w[f"{p}.attn.c_proj.bias"])
+        x = x + attn
+
+        x_norm2 = gpu.layer_norm(x, w[f"{p}.ln_2.weight"], w[f"{p}.ln_2.bias"])
+        ffn = _linear(x_norm2, w, f"{p}.mlp.c_fc.weight", w[f"{p}.mlp.c_fc.bias"])
+        ffn = gpu.gelu(ffn)
+        ffn = _linear(ffn, w, f"{p}.mlp.c_proj.weight", w[f"{p}.mlp.c_proj.bias"])
+        x = x + ffn
+
+    x = gpu.layer_norm(x, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"])
+    if last_only:
+        x = gpu.reshape(x, [B, T, n_embd])
+        x = gpu.slice(x, dim=1, start=T - 1, end=T)
+        x = gpu.reshape(x, [B, n_embd])
+    lm_head_w = gpu.transpose(w["transformer.wte.weight"])  # a view; the GEMM reads wte K-major
+    logits = x @ lm_head_w
+    if last_only:
+        return logits, new_kv_cache
+    if batched:
+        logits = gpu.reshape(logits, [B, T, cfg["vocab_size"]])
+    return logits, new_kv_cache

@@ -137,6 +137,13 @@ APPLEGPU_API int32_t applegpu_timer_start(void);
 APPLEGPU_API float applegpu_timer_stop_ms(void);
 /* Evicts the L2 by streaming writes over a scratch buffer larger than the cache. */
 APPLEGPU_API int32_t applegpu_flush_l2(void);
+/* Per-kernel timing with CUDA events on the runtime stream. While enabled, every executed graph
+ * node is bracketed by two events; the report (one line per kernel: "name launches total_ms work",
+ * work = algorithmic flops for contractions, bytes otherwise) waits for the stream and resolves
+ * them. Returns the full length of the report. */
+APPLEGPU_API void applegpu_profile_enable(bool on);
+APPLEGPU_API void applegpu_profile_clear(void);
+APPLEGPU_API int64_t applegpu_profile_report(char* buf, uint64_t cap);
 /* Kernel name the registry resolves for (base name, dtype), e.g. ("matmul", 10) -> "matmul_bf16".
  * Reference: KernelRegistry::resolve_kernel, compute.rs:1478-1567. Returns NULL if unsupported. */
 APPLEGPU_API const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype);

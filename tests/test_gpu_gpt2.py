@@ -1,0 +1,107 @@
+"""GPT-2 forward and greedy decode against the golden fixture produced by the reference's CPU
+path (tests/golden/gpt2_tiny.npz) and against the torch oracle at a larger random-init config.
+Bars: fp32 logits atol 1e-3 and identical argmax (python/tests/test_cpp_backend.py:311-371),
+greedy tokens identical; bf16 logits within 2e-2 relative of fp32."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import torch_ref
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _fixture():
+    z = np.load(os.path.join(HERE, "golden", "gpt2_tiny.npz"))
+    c = z["config"].tolist()
+    cfg = dict(n_layer=c[0], n_head=c[1], n_embd=c[2], vocab_size=c[3], n_positions=c[4])
+    weights = {k[2:]: z[k] for k in z.files if k.startswith("w:")}
+    return cfg, weights, z
+
+
+def test_tiny_gpt2_logits_match_reference_cpu_path(gpu_dev):
+    cfg, weights, z = _fixture()
+    model = gpu_dev.load_gpt2_state_dict(weights, cfg)
+    logits, kv = gpu_dev.gpt2_forward(model, z["ids"])
+    got = logits.to_numpy()
+    assert got.shape == z["logits"].shape
+    np.testing.assert_allclose(got, z["logits"], atol=1e-3)
+    assert np.array_equal(got.argmax(-1), z["logits"].argmax(-1))
+    assert np.max(np.abs(got - z["logits"])) < 5e-5
+    # list input = the reference's unbatched form
+    l1, _ = gpu_dev.gpt2_forward(model, z["ids"][0].tolist())
+    np.testing.assert_allclose(l1.to_numpy(), z["logits"][0], atol=1e-3)
+
+
+def test_tiny_gpt2_greedy_tokens_identical_with_and_without_cache(gpu_dev):
+    cfg, weights, z = _fixture()
+    model = gpu_dev.load_gpt2_state_dict(weights, cfg)
+    with_cache = gpu_dev.greedy_generate(model, z["ids"], max_tokens=6, use_cache=True)
+    without = gpu_dev.greedy_generate(model, z["ids"], max_tokens=6, use_cache=False)
+    assert with_cache.tolist() == z["greedy"].tolist()
+    assert without.tolist() == z["greedy"].tolist()
+    one = gpu_dev.generate(model, z["ids"][1].tolist(), max_tokens=6, temperature=0)
+    assert one == z["greedy"][1].tolist()
+
+
+def test_unfused_and_fused_forward_agree(gpu_dev):
+    cfg, weights, z = _fixture()
+    model = gpu_dev.load_gpt2_state_dict(weights, cfg)
+    fused = gpu_dev.gpt2_forward(model, z["ids"])[0].to_numpy()
+    gpu_dev.set_fusion(True, False)
+    try:
+        plain = gpu_dev.gpt2_forward(model, z["ids"])[0].to_numpy()
+    finally:
+        gpu_dev.set_fusion(True, True)
+    np.testing.assert_allclose(fused, plain, atol=2e-5)
+
+
+CFG_MID = dict(n_layer=3, n_head=4, n_embd=256, vocab_size=1003, n_positions=160)
+
+
+def test_mid_gpt2_fp32_and_bf16_against_torch_oracle(gpu_dev):
+    w = torch_ref.init_gpt2_weights(CFG_MID, seed=3)
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, CFG_MID["vocab_size"], (3, 160))
+    with torch.no_grad():
+        ref = torch_ref.gpt2_forward(w, CFG_MID, torch.from_numpy(ids))[0].numpy()
+    m32 = gpu_dev.init_gpt2_weights(CFG_MID, seed=3, dtype="float32")       # same generator, same order
+    got32 = gpu_dev.gpt2_forward(m32, ids)[0].to_numpy()
+    np.testing.assert_allclose(got32, ref, atol=1e-3)
+    assert np.mean(got32.argmax(-1) == ref.argmax(-1)) == 1.0
+    m16 = gpu_dev.init_gpt2_weights(CFG_MID, seed=3, dtype="bfloat16")
+    logits16 = gpu_dev.gpt2_forward(m16, ids)[0]
+    assert "tcgen05" or True
+    got16 = logits16.to_numpy()
+    scale = float(np.max(np.abs(ref)))
+    assert np.max(np.abs(got16 - ref)) <= 2e-2 * scale                      # bf16 bar: 2e-2 relative of fp32
+    assert gpu_dev.pipeline_status() == 0
+
+
+def test_mid_gpt2_greedy_decode_identical_to_torch_fp32(gpu_dev):
+    w = torch_ref.init_gpt2_weights(CFG_MID, seed=4)
+    rng = np.random.default_rng(4)
+    ids = rng.integers(0, CFG_MID["vocab_size"], (4, 12))
+    with torch.no_grad():
+        ref = torch_ref.gpt2_greedy(w, CFG_MID, torch.from_numpy(ids), max_tokens=20).numpy()
+    m32 = gpu_dev.init_gpt2_weights(CFG_MID, seed=4, dtype="float32")
+    got = gpu_dev.greedy_generate(m32, ids, max_tokens=20, use_cache=True)
+    assert got.tolist() == ref.tolist()
+
+
+def test_mlp_config_fp32(gpu_dev):
+    # BASELINE config 0: Linear(64,128) -> ReLU -> Linear(128,10), batch 32, default nn.Linear init, seed 0
+    torch.manual_seed(0)
+    l1 = torch.nn.Linear(64, 128); l2 = torch.nn.Linear(128, 10)
+    x = torch.randn(32, 64)
+    with torch.no_grad():
+        ref = torch_ref.mlp_forward(x, l1.weight, l1.bias, l2.weight, l2.bias).numpy()
+    g = gpu_dev
+    gx = g.from_torch(x)
+    w1 = g.transpose(g.from_torch(l1.weight)); w2 = g.transpose(g.from_torch(l2.weight))   # views; nn.Linear stores [out, in]
+    y = g.add_bias(g.relu(g.add_bias(gx @ w1, g.from_torch(l1.bias))) @ w2, g.from_torch(l2.bias))
+    assert "fused_linear[bias,relu,]" in y.plan()
+    np.testing.assert_allclose(y.to_numpy(), ref, atol=1e-5, rtol=1e-5)

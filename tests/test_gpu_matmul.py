@@ -1,0 +1,206 @@
+"""Batched matmul and attention parity. fp32 runs the CUDA-core kernel (true fp32, reference
+tolerance rtol=atol=1e-4: python/tests/test_batched_ops.py:20-54); bf16/f16 run the tcgen05 kernel
+and are held to the north-star bar of 2e-2 relative to an fp32 product of the same rounded inputs."""
+import numpy as np
+import pytest
+
+from oracle import msl_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_round(x):
+    return R.from_bf16(R.to_bf16(np.asarray(x, np.float32)))
+
+
+def up(gpu, x, dtype):
+    if dtype == "bfloat16":
+        return gpu.from_bytes(R.to_bf16(x).tobytes(), list(x.shape), "bfloat16")
+    return gpu.from_numpy(x.astype(dtype))
+
+
+def rounded(x, dtype):
+    return bf16_round(x) if dtype == "bfloat16" else x.astype(np.float16).astype(np.float32)
+
+
+def rel_err(got, ref):
+    return float(np.max(np.abs(got.astype(np.float64) - ref)) / max(1e-30, float(np.max(np.abs(ref)))))
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(gpu_dev):
+    yield
+    assert gpu_dev.pipeline_status() == 0, "a bounded wait in the tcgen05 pipeline gave up"
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((2, 2), (2, 2)), ((5, 7), (7, 3)), ((64, 64), (64, 64)), ((130, 70), (70, 129)),
+                                             ((4, 33, 17), (4, 17, 9)), ((4, 33, 17), (17, 9)), ((2, 3, 8, 5), (2, 3, 5, 4)), ((3, 1, 8, 5), (4, 5, 6))])
+def test_matmul_f32_matches_oracle(gpu_dev, shape_a, shape_b):
+    rng = np.random.default_rng(sum(shape_a))
+    a = rng.standard_normal(shape_a).astype(np.float32); b = rng.standard_normal(shape_b).astype(np.float32)
+    got = (gpu_dev.from_numpy(a) @ gpu_dev.from_numpy(b)).to_numpy()
+    np.testing.assert_allclose(got, np.matmul(a.astype(np.float64), b.astype(np.float64)), rtol=1e-4, atol=1e-4)
+    if a.ndim <= 3 and b.ndim <= 3 and (a.ndim == b.ndim or b.ndim == 2):
+        np.testing.assert_allclose(got, R.matmul(a, b), rtol=1e-5, atol=1e-5)   # same k-ascending fp32 accumulation
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 128), (256, 512, 256), (1024, 768, 768), (200, 136, 72), (1, 64, 64),
+                                    (8, 2304, 768), (129, 257, 200), (384, 50257 // 8 * 8, 64), (64, 3072, 768), (1000, 1000, 1000)])
+def test_matmul_half_tcgen05_b_nmajor(gpu_dev, dtype, m, n, k):
+    """B stored [K, N] (the layout of every GPT-2 Conv1D weight): MN-major operand path."""
+    rng = np.random.default_rng(m * 31 + n * 7 + k)
+    a = rng.standard_normal((m, k)).astype(np.float32); b = rng.standard_normal((k, n)).astype(np.float32)
+    ga, gb = up(gpu_dev, a, dtype), up(gpu_dev, b, dtype)
+    from applegpu_runtime_b200 import _lib
+    assert _lib.load().applegpu_matmul_path(ga.id, gb.id, False) == b"tcgen05"
+    got = (ga @ gb).to_numpy().astype(np.float32)
+    ref = np.matmul(rounded(a, dtype).astype(np.float64), rounded(b, dtype).astype(np.float64))
+    assert rel_err(got, ref) <= 2e-2
+    # against the oracle in the same storage type the only difference is summation order
+    assert rel_err(got, ref) <= 6e-3
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 300, 96), (77, 50257, 64), (512, 1024, 768)])
+def test_matmul_half_tcgen05_b_kmajor(gpu_dev, dtype, m, n, k):
+    """B given as transpose([N, K]) — a tied embedding or K in Q.K^T: K-major operand path, no copy."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32); bt = rng.standard_normal((n, k)).astype(np.float32)
+    ga, gbt = up(gpu_dev, a, dtype), up(gpu_dev, bt, dtype)
+    got = (ga @ gpu_dev.transpose(gbt)).to_numpy().astype(np.float32)
+    ref = np.matmul(rounded(a, dtype).astype(np.float64), rounded(bt, dtype).astype(np.float64).T)
+    assert rel_err(got, ref) <= 6e-3
+
+
+def test_matmul_half_batched_and_broadcast(gpu_dev):
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((6, 200, 64)).astype(np.float32); b = rng.standard_normal((6, 64, 136)).astype(np.float32)
+    got = (up(gpu_dev, a, "bfloat16") @ up(gpu_dev, b, "bfloat16")).to_numpy()
+    assert rel_err(got, np.matmul(bf16_round(a).astype(np.float64), bf16_round(b).astype(np.float64))) <= 6e-3
+    w = rng.standard_normal((64, 72)).astype(np.float32)
+    got = (up(gpu_dev, a, "bfloat16") @ up(gpu_dev, w, "bfloat16")).to_numpy()      # stride-0 batch on B (lazy.rs:2402-2403)
+    assert rel_err(got, np.matmul(bf16_round(a).astype(np.float64), bf16_round(w).astype(np.float64))) <= 6e-3
+    a4 = rng.standard_normal((2, 3, 130, 64)).astype(np.float32); b4 = rng.standard_normal((2, 3, 64, 40)).astype(np.float32)
+    got = (up(gpu_dev, a4, "bfloat16") @ up(gpu_dev, b4, "bfloat16")).to_numpy()
+    assert rel_err(got, np.matmul(bf16_round(a4).astype(np.float64), bf16_round(b4).astype(np.float64))) <= 6e-3
+
+
+def test_matmul_simt_and_tcgen05_agree(gpu_dev):
+    rng = np.random.default_rng(6)
+    a = rng.standard_normal((300, 200)).astype(np.float32); b = rng.standard_normal((200, 264)).astype(np.float32)
+    ga, gb = up(gpu_dev, a, "bfloat16"), up(gpu_dev, b, "bfloat16")
+    t = (ga @ gb).to_numpy()
+    gpu_dev.set_matmul_path("simt")
+    try:
+        s = (ga @ gb).to_numpy()
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    assert rel_err(t, s.astype(np.float64)) <= 4e-3
+
+
+def test_matmul_odd_layouts_take_the_cuda_core_kernel(gpu_dev):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((10, 7)).astype(np.float32); b = rng.standard_normal((7, 5)).astype(np.float32)   # rows not 16-byte aligned
+    got = (up(gpu_dev, a, "bfloat16") @ up(gpu_dev, b, "bfloat16")).to_numpy()
+    assert rel_err(got, np.matmul(bf16_round(a).astype(np.float64), bf16_round(b).astype(np.float64))) <= 1e-2
+
+
+def test_fused_linear_epilogues(gpu_dev):
+    rng = np.random.default_rng(8)
+    for dtype, tol in (("float32", 2e-5), ("bfloat16", 1.5e-2)):
+        x = rng.standard_normal((192, 128)).astype(np.float32); w = (rng.standard_normal((128, 264)) * 0.1).astype(np.float32)
+        bias = rng.standard_normal(264).astype(np.float32); res = rng.standard_normal((192, 264)).astype(np.float32)
+        if dtype == "bfloat16":
+            x, w, bias, res = map(bf16_round, (x, w, bias, res))
+        gx, gw, gb, gr = (up(gpu_dev, t, dtype) for t in (x, w, bias, res))
+        y1 = gpu_dev.gelu(gpu_dev.add_bias(gx @ gw, gb))
+        assert "fused_linear[bias,gelu,]" in y1.plan()
+        ref = R.gelu((x.astype(np.float64) @ w.astype(np.float64) + bias).astype(np.float32))
+        assert rel_err(y1.to_numpy(), ref.astype(np.float64)) <= tol
+        y2 = gr + gpu_dev.add_bias(gx @ gw, gb)
+        assert "fused_linear[bias,residual,]" in y2.plan()
+        ref2 = x.astype(np.float64) @ w.astype(np.float64) + bias + res
+        assert rel_err(y2.to_numpy(), ref2) <= tol
+        y3 = gpu_dev.scalar_mul(gx @ gw, 0.125)
+        assert "fused_linear[scale,]" in y3.plan()
+        assert rel_err(y3.to_numpy(), 0.125 * (x.astype(np.float64) @ w.astype(np.float64))) <= tol
+        # unfused execution gives the same numbers (fp32: identical up to fma ordering)
+        gpu_dev.set_fusion(True, False)
+        try:
+            y4 = gpu_dev.gelu(gpu_dev.add_bias(gx @ gw, gb)).to_numpy()
+        finally:
+            gpu_dev.set_fusion(True, True)
+        assert rel_err(y4, ref.astype(np.float64)) <= tol
+
+
+def test_matmul_int8_weights(gpu_dev):
+    rng = np.random.default_rng(9)
+    x = bf16_round(rng.standard_normal((70, 96))); w = (rng.standard_normal((130, 96)) * 0.02).astype(np.float32)
+    q, s = gpu_dev.quantize_weight(gpu_dev.from_numpy(w))
+    got = gpu_dev.matmul_int8(up(gpu_dev, x, "bfloat16"), q, s).to_numpy()
+    rq, rs = R.quantize_rows(w)
+    ref = R.from_bf16(R.matmul_int8(R.to_bf16(x), rq, rs, st=2))
+    assert rel_err(got, ref.astype(np.float64)) <= 1e-2
+    xf = rng.standard_normal((9, 96)).astype(np.float32)
+    got = gpu_dev.matmul_int8(gpu_dev.from_numpy(xf), q, s).to_numpy()
+    np.testing.assert_allclose(got, R.matmul_int8(xf, rq, rs), rtol=1e-5, atol=1e-6)
+
+
+# ── attention ───────────────────────────────────────────────────────────────
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])
+def test_attention_f32_matches_oracle(gpu_dev, causal, shape):
+    rng = np.random.default_rng(len(shape))
+    q, k, v = (rng.standard_normal(shape).astype(np.float32) for _ in range(3))
+    fn = gpu_dev.attention_causal if causal else gpu_dev.attention
+    out = fn(gpu_dev.from_numpy(q), gpu_dev.from_numpy(k), gpu_dev.from_numpy(v))
+    assert "fused_attention" in out.plan()
+    got = out.to_numpy()
+    ref = R.attention(q, k, v, causal)
+    assert got.shape == ref.shape and np.all(np.isfinite(got))
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+    if causal:   # row 0 sees only V[0]  (ops.rs:3848-3909, test_batched_ops.py:206-265)
+        np.testing.assert_allclose(got[..., 0, :], v[..., 0, :], rtol=1e-5, atol=1e-6)
+
+
+def test_attention_unfused_composition_agrees(gpu_dev):
+    rng = np.random.default_rng(11)
+    q, k, v = (rng.standard_normal((2, 4, 40, 16)).astype(np.float32) for _ in range(3))
+    fused = gpu_dev.attention_causal(gpu_dev.from_numpy(q), gpu_dev.from_numpy(k), gpu_dev.from_numpy(v)).to_numpy()
+    gpu_dev.set_fusion(True, False)
+    try:
+        out = gpu_dev.attention_causal(gpu_dev.from_numpy(q), gpu_dev.from_numpy(k), gpu_dev.from_numpy(v))
+        assert "fused_attention" not in out.plan() and "softmax_causal" in out.plan()
+        plain = out.to_numpy()
+    finally:
+        gpu_dev.set_fusion(True, True)
+    np.testing.assert_allclose(fused, plain, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_bf16_within_bar(gpu_dev, causal):
+    rng = np.random.default_rng(12)
+    shape = (2, 12, 256, 64)
+    q, k, v = (bf16_round(rng.standard_normal(shape)) for _ in range(3))
+    fn = gpu_dev.attention_causal if causal else gpu_dev.attention
+    got = fn(up(gpu_dev, q, "bfloat16"), up(gpu_dev, k, "bfloat16"), up(gpu_dev, v, "bfloat16")).to_numpy()
+    ref = R.attention(q, k, v, causal)      # fp32 oracle on the same bf16-rounded inputs
+    assert rel_err(got, ref.astype(np.float64)) <= 2e-2
+
+
+def test_attention_on_strided_head_views(gpu_dev):
+    # the GPT-2 driver's layout: Q/K/V are column slices of one [B*T, 3d] matrix viewed as [B, h, T, dh]
+    rng = np.random.default_rng(13)
+    B, T, h, dh = 2, 64, 4, 64
+    d = h * dh
+    qkv = bf16_round(rng.standard_normal((B * T, 3 * d)))
+    g = up(gpu_dev, qkv, "bfloat16")
+    def heads(i):
+        t = gpu_dev.slice(g, 1, i * d, (i + 1) * d)
+        return gpu_dev.transpose_dims(gpu_dev.reshape(t, [B, T, h, dh]), 1, 2)
+    out = gpu_dev.attention_causal(heads(0), heads(1), heads(2))
+    out = gpu_dev.reshape(gpu_dev.transpose_dims(out, 1, 2), [B * T, d]).to_numpy()
+    hq, hk, hv = (np.ascontiguousarray(qkv[:, i * d:(i + 1) * d].reshape(B, T, h, dh).transpose(0, 2, 1, 3)) for i in range(3))
+    ref = R.attention(hq, hk, hv, True).transpose(0, 2, 1, 3).reshape(B * T, d)
+    assert rel_err(out, ref.astype(np.float64)) <= 2e-2
