@@ -21,8 +21,8 @@ uint64_t next_op_id() { return g_op_id.fetch_add(1, std::memory_order_relaxed); 
 uint64_t next_fused_id() { return g_fused_id.fetch_add(1, std::memory_order_relaxed); }
 
 DeviceCtx& DeviceCtx::get() {
-  static DeviceCtx ctx;
-  return ctx;
+  static DeviceCtx* ctx = new DeviceCtx();  // never destroyed: outlives every buffer deleter
+  return *ctx;
 }
 
 static int env_int(const char* name, int dflt) {
@@ -86,8 +86,8 @@ Shared::Shared() : pool(0) {
   if (lim > 0) pool.set_memory_limit((size_t)lim << 20);
 }
 Shared& Shared::get() {
-  static Shared s;
-  return s;
+  static Shared* s = new Shared();  // never destroyed (see DeviceCtx::get)
+  return *s;
 }
 
 BufferPool::BufferPool(size_t max_pooled_bytes) : max_pooled_(max_pooled_bytes) {}

@@ -24,8 +24,10 @@ namespace {
 
 struct LazyState { std::mutex mu; LazyRuntime rt; bool ready = false; };
 struct EagerState { std::mutex mu; EagerRuntime rt; bool ready = false; };
-LazyState& lazy_state() { static LazyState s; return s; }
-EagerState& eager_state() { static EagerState s; return s; }
+// Leaked on purpose: buffers held by the runtimes return to the pool from their deleters, so
+// neither may be destroyed before the other at process exit; the CUDA context reclaims the memory.
+LazyState& lazy_state() { static LazyState* s = new LazyState(); return *s; }
+EagerState& eager_state() { static EagerState* s = new EagerState(); return *s; }
 
 thread_local std::string t_ffi_error; thread_local bool t_ffi_has_error = false;
 thread_local std::string t_eager_error; thread_local bool t_eager_has_error = false;
