@@ -163,6 +163,7 @@ EXT_SYMBOLS = {
     "applegpu_profile_clear": (None, []),
     "applegpu_profile_report": (i64, [ctypes.c_char_p, u64]),
     "applegpu_resolve_kernel": (cstr, [cstr, i8]),
+    "applegpu_attention_noalloc": (i32, [vp, vp, vp, vp, i8, u64, u64, u64, u64, u64, cbool, vp]),
 }
 
 _lib = None

@@ -33,6 +33,12 @@ thread_local std::string t_ffi_error; thread_local bool t_ffi_has_error = false;
 thread_local std::string t_eager_error; thread_local bool t_eager_has_error = false;
 void set_ffi_error(const std::string& m) { t_ffi_error = m; t_ffi_has_error = true; }
 void set_eager_error(const std::string& m) { t_eager_error = m; t_eager_has_error = true; }
+}  // namespace
+namespace ag {
+// Lets entry points defined in other translation units report through applegpu_ffi_last_error().
+void set_ffi_error_text(const std::string& m) { set_ffi_error(m); }
+}
+namespace {
 
 Dims to_dims(const uint64_t* d, uint32_t n) { Dims v(n); for (uint32_t i = 0; i < n; i++) v[i] = (int64_t)d[i]; return v; }
 

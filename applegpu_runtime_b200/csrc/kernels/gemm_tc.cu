@@ -433,4 +433,13 @@ Status matmul(cudaStream_t s, const GemmDesc& d) {
   return matmul_simt(s, d);
 }
 
+// Same dispatch with a caller-provided status word: performs no device allocation.
+Status matmul_with_status(cudaStream_t s, const GemmDesc& d, int* status_word) {
+  if (d.m == 0 || d.n == 0 || d.batch == 0) return Status::OK();
+  bool elig = tc_eligible(d);
+  if (g_force_path == 2 && !elig) return Status::compute("matmul: tcgen05 path forced but operands are not TMA-compatible");
+  if (elig && g_force_path != 1) return matmul_tc(s, d, status_word);
+  return matmul_simt(s, d);
+}
+
 }}  // namespace ag::k

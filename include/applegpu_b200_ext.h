@@ -148,6 +148,32 @@ APPLEGPU_API int64_t applegpu_profile_report(char* buf, uint64_t cap);
  * Reference: KernelRegistry::resolve_kernel, compute.rs:1478-1567. Returns NULL if unsupported. */
 APPLEGPU_API const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype);
 
+/* ── attention without device allocation ───────────────────────────────────────
+ * No counterpart in the reference.
+ *
+ * Every other attention entry point takes its score matrix from the buffer pool, which may call
+ * cudaMallocAsync. This one is for callers that are not allowed to allocate device memory when
+ * they need attention: a serving loop with a fixed memory budget, a plugin whose host
+ * application owns every device buffer, code running between another framework's allocator
+ * checkpoints. It computes softmax[_causal](Q K^T / sqrt(d_k)) V on caller-owned DEVICE pointers
+ * and calls no cudaMalloc / cudaFree / pool routine; its scratch is a fixed array of
+ * APPLEGPU_NOALLOC_SCRATCH_BYTES that is part of the library image (each GPU that loads the
+ * library holds it until the process exits).
+ *
+ *   q [batch_heads, q_len, d_k], k [batch_heads, kv_len, d_k], v [batch_heads, kv_len, d_v],
+ *   out [batch_heads, q_len, d_v]; all contiguous, all of `dtype` (0 f32, 1 f16, 10 bf16).
+ *   cuda_stream: a cudaStream_t (NULL = the legacy default stream). Work is enqueued, not awaited.
+ *
+ * Limit: batch_heads * q_len * kv_len * sizeof(dtype) must not exceed
+ * APPLEGPU_NOALLOC_SCRATCH_BYTES; larger problems are rejected with -1 and a message in
+ * applegpu_ffi_last_error(). The first call on a device looks up the scratch address for that
+ * device (with that device current); make that first call before any stream capture. All calls
+ * share the one scratch array, which keeps the previous call's contents: calls whose GPU work
+ * overlaps (different streams, different threads) race on it and must be serialised by the caller.
+ * Returns 0 on success. */
+#define APPLEGPU_NOALLOC_SCRATCH_BYTES (64ull << 20)
+APPLEGPU_API int32_t applegpu_attention_noalloc(const void* q, const void* k, const void* v, void* out, int8_t dtype, uint64_t batch_heads, uint64_t q_len, uint64_t kv_len, uint64_t d_k, uint64_t d_v, bool causal, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
