@@ -11,7 +11,7 @@
 //   warp 0      TMA producer: fills a STAGES-deep ring of {A 128x64, B BNx64} tiles (128B swizzle)
 //   warp 1      MMA issuer: one elected thread issues 4 x (128 x BN x 16) tcgen05.mma per stage,
 //               commits the stage back to the producer, and owns the TMEM allocation
-//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator (two TMEM buffers, so the next
+//   warps 2..9  epilogue: tcgen05.ld of the finished accumulator (two TMEM buffers, so the next
 //               tile's main loop overlaps this tile's epilogue), epilogue math, stores
 // B is taken either K-major ([N,K] rows, e.g. a tied embedding or K in Q.K^T) or N-major
 // ([K,N] rows, the layout of every GPT-2 Conv1D weight and of V in P.V) through the
@@ -32,7 +32,7 @@ using namespace ag::sm100;
 constexpr int BM = 128;          // UMMA M (cta_group::1)
 constexpr int BK = 64;           // 64 x 2 B = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 64 + 8 * 32;   // TMA warp, MMA warp, eight epilogue warps
 
 struct TcParams {
   void* c;
@@ -46,58 +46,168 @@ struct TcParams {
   long long c_row, c_batch, c_batch_inner;
   int a_bcast, b_bcast;        // bit 0: outer index pinned to 0, bit 1: inner index pinned to 0
   int tiles_m, tiles_n;
+  int vec_ok;                  // C (and residual) rows are 16-byte aligned: 16-byte global accesses
+  int bias_vec;                // bias pointer is 16-byte aligned
   int* status;
 };
+
+constexpr int kEpiWarps = 8;                       // two warps per TMEM lane quarter, alternating column groups
+constexpr int kStgPitch = 80;
+constexpr int kStgBytesPerWarp = 32 * kStgPitch;   // 2560
+constexpr int kStgBytes = kEpiWarps * kStgBytesPerWarp;
 
 template <int BN> struct TcCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + 1024;  // ring + epilogue staging + alignment slack
   static constexpr int kTmemCols = 2 * BN;                         // two accumulator buffers
 };
 
+// Epilogue staging: each epilogue warp owns a [32 rows x 32 cols] 2-byte tile in shared memory with an
+// 80-byte row pitch (64 B of data + 16 B pad: the row-per-lane accesses of the math phase are
+// bank-conflict free, the 4-lanes-per-row accesses of the global phase at most 2-way).
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One 32-column group of one warp's 32 rows: TMEM -> registers -> epilogue math -> shared -> global.
+// Every epilogue option is tested once per group (uniform branches around 32-element loops), and
+// global traffic is issued with 4 lanes per row (64 contiguous bytes per row per instruction) when
+// rows are 16-byte aligned, or 32 consecutive 2-byte elements per instruction otherwise (e.g. the
+// 50257-wide LM head), instead of one row per lane.
 template <typename T>
-__device__ __forceinline__ void epilogue_store_chunk(const TcParams& p, const uint32_t (&acc)[32], long long gm, int col0, long long c_off) {
-  // One thread owns row gm, columns col0 .. col0+31.
-  T* C = reinterpret_cast<T*>(p.c) + c_off + gm * p.c_row;
-  const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off + gm * p.c_row : nullptr;
-  const T* bias = reinterpret_cast<const T*>(p.bias);
-  const bool full = col0 + 32 <= p.n;
-  const bool vec = full && ((reinterpret_cast<uintptr_t>(C + col0) & 15u) == 0) && (!R || (reinterpret_cast<uintptr_t>(R + col0) & 15u) == 0);
-  if (vec) {
+__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, long long row0, int col0,
+                                               long long c_off, int lane) {
+  T* C = reinterpret_cast<T*>(p.c) + c_off;
+  const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
+  const int sub_row = lane >> 2, sub_chunk = lane & 3;
+  const bool full_cols = col0 + 32 <= p.n;
+
+  // 1. residual tile -> shared (coalesced)
+  if (R) {
+    if (p.vec_ok) {
 #pragma unroll
-    for (int g = 0; g < 4; g++) {
-      Pack<T> o;
-      Pack<T> r;
-      if (R) r = ld16(R + col0 + g * 8);
+      for (int it = 0; it < 4; it++) {
+        int r = it * 8 + sub_row;
+        long long gm = row0 + r;
+        int gc = col0 + sub_chunk * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (gm < p.m && gc + 8 <= p.n) v = *reinterpret_cast<const uint4*>(R + gm * p.c_row + gc);
+        else if (gm < p.m && gc < p.n) {
+          alignas(16) T tmp[8];
 #pragma unroll
-      for (int e = 0; e < 8; e++) {
-        int cidx = col0 + g * 8 + e;
-        float v = __uint_as_float(acc[g * 8 + e]) * p.alpha;
-        if (p.b_scales) v *= __ldg(p.b_scales + cidx);
-        if (bias) v += Cvt<T>::to(__ldg(bias + cidx));
-        v = apply_act(v, (Act)p.act);
-        if (R) v += Cvt<T>::to(r.v[e]);
-        o.v[e] = Cvt<T>::from(v);
+          for (int e = 0; e < 8; e++) tmp[e] = gc + e < p.n ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
+          v = *reinterpret_cast<uint4*>(tmp);
+        }
+        *reinterpret_cast<uint4*>(stg + r * kStgPitch + sub_chunk * 16) = v;
       }
-      st16(C + col0 + g * 8, o);
+    } else {
+      for (int r = 0; r < 32; r++) {
+        long long gm = row0 + r;
+        T v = (gm < p.m && col0 + lane < p.n) ? R[gm * p.c_row + col0 + lane] : Cvt<T>::from(0.f);
+        *reinterpret_cast<T*>(stg + r * kStgPitch + lane * 2) = v;
+      }
     }
-  } else {
+    __syncwarp();
+  }
+
+  // 2. accumulators -> registers
+  uint32_t acc[32];
+  tmem_ld_32x32(taddr, acc);
+  tmem_ld_wait();
+  float v[32];
 #pragma unroll
-    for (int e = 0; e < 32; e++) {
-      int cidx = col0 + e;
-      if (cidx < p.n) {
-        float v = __uint_as_float(acc[e]) * p.alpha;
-        if (p.b_scales) v *= __ldg(p.b_scales + cidx);
-        if (bias) v += Cvt<T>::to(__ldg(bias + cidx));
-        v = apply_act(v, (Act)p.act);
-        if (R) v += Cvt<T>::to(R[cidx]);
-        C[cidx] = Cvt<T>::from(v);
+  for (int e = 0; e < 32; e++) v[e] = __uint_as_float(acc[e]);
+
+  // 3. epilogue math: one uniform test per option, then a straight 32-element loop
+  if (p.alpha != 1.0f) {
+#pragma unroll
+    for (int e = 0; e < 32; e++) v[e] *= p.alpha;
+  }
+  if (p.b_scales) {
+#pragma unroll
+    for (int e = 0; e < 32; e++) { int ci = col0 + e; v[e] *= __ldg(p.b_scales + (ci < p.n ? ci : p.n - 1)); }
+  }
+  if (p.bias) {
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    if (full_cols && p.bias_vec) {
+#pragma unroll
+      for (int g = 0; g < 4; g++) {
+        Pack<T> b = ld16(bias + col0 + g * 8);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(b.v[e]);
       }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; e++) { int ci = col0 + e; v[e] += Cvt<T>::to(__ldg(bias + (ci < p.n ? ci : p.n - 1))); }
     }
   }
+  switch ((Act)p.act) {
+    case Act::GeluTanh:
+#pragma unroll
+      for (int e = 0; e < 32; e++) v[e] = gelu_tanh_f(v[e]);
+      break;
+    case Act::GeluErf:
+#pragma unroll
+      for (int e = 0; e < 32; e++) v[e] = gelu_erf_f(v[e]);
+      break;
+    case Act::Relu:
+#pragma unroll
+      for (int e = 0; e < 32; e++) v[e] = fmaxf(v[e], 0.f);
+      break;
+    default: break;
+  }
+  uint8_t* my_row = stg + lane * kStgPitch;
+  if (R) {
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      Pack<T> r = *reinterpret_cast<const Pack<T>*>(my_row + g * 16);
+#pragma unroll
+      for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(r.v[e]);
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    uint4 o;
+    o.x = pack2<T>(v[g * 8 + 0], v[g * 8 + 1]); o.y = pack2<T>(v[g * 8 + 2], v[g * 8 + 3]);
+    o.z = pack2<T>(v[g * 8 + 4], v[g * 8 + 5]); o.w = pack2<T>(v[g * 8 + 6], v[g * 8 + 7]);
+    *reinterpret_cast<uint4*>(my_row + g * 16) = o;
+  }
+  __syncwarp();
+
+  // 4. shared -> global (coalesced)
+  if (p.vec_ok) {
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+      int r = it * 8 + sub_row;
+      long long gm = row0 + r;
+      int gc = col0 + sub_chunk * 8;
+      if (gm < p.m && gc < p.n) {
+        uint4 o = *reinterpret_cast<const uint4*>(stg + r * kStgPitch + sub_chunk * 16);
+        if (gc + 8 <= p.n) *reinterpret_cast<uint4*>(C + gm * p.c_row + gc) = o;
+        else {
+          const T* tv = reinterpret_cast<const T*>(&o);
+          for (int e = 0; e < 8 && gc + e < p.n; e++) C[gm * p.c_row + gc + e] = tv[e];
+        }
+      }
+    }
+  } else if (col0 + lane < p.n) {
+    for (int r = 0; r < 32; r++) {
+      long long gm = row0 + r;
+      if (gm >= p.m) break;
+      C[gm * p.c_row + col0 + lane] = *reinterpret_cast<const T*>(stg + r * kStgPitch + lane * 2);
+    }
+  }
+  __syncwarp();
 }
 
 template <int BN, bool B_MN, typename T>
@@ -121,7 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 4); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], kEpiWarps); }
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -216,16 +326,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int n0 = (rem / p.tiles_m) * BN;
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4)) { ok = false; break; }
       tc_fence_after_sync();
-      long long gm = (long long)m0 + quarter * 32 + lane;
+      long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      const int pair = (warp - 2) >> 2;  // the two warps of a lane quarter alternate 32-column groups
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c++) {
-        if (n0 + c * 32 >= p.n) break;  // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + (uint32_t)(c * 32), r);
-        tmem_ld_wait();
-        if (gm < p.m) epilogue_store_chunk<T>(p, r, gm, n0 + c * 32, c_off);
+      for (int g = pair; g < BN / 32; g += 2) {
+        if (n0 + g * 32 >= p.n) break;  // uniform across the warp
+        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, row0, n0 + g * 32, c_off, lane);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -377,6 +486,10 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.batch = (int)nb; p.batch_inner = (int)d.batch_inner;
   p.c_row = d.c_row; p.c_batch = d.c_batch; p.c_batch_inner = d.c_batch_inner; p.a_bcast = a_bcast; p.b_bcast = b_bcast;
   p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
+  auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  p.vec_ok = (al16p(d.c) && d.c_row % 8 == 0 && d.c_batch % 8 == 0 && d.c_batch_inner % 8 == 0 &&
+              (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
+  p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
   long long num_tiles = tiles_m * tiles_n * nb;
 #define AG_TC(BNV, MN) \
   (d.dtype == DType::BF16 ? launch_tc<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc<BNV, MN, __half>(s, ma, mb, p, num_tiles))
