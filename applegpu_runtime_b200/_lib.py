@@ -155,6 +155,7 @@ EXT_SYMBOLS = {
     "applegpu_launch_count": (u64, []),
     "applegpu_matmul_path": (cstr, [u64, u64, cbool]),
     "applegpu_set_matmul_path": (None, [i32]),
+    "applegpu_set_attention_path": (None, [i32]),
     "applegpu_pipeline_status": (i32, []),
     "applegpu_timer_start": (i32, []),
     "applegpu_timer_stop_ms": (f32, []),

@@ -475,6 +475,11 @@ def set_matmul_path(mode):
     _L().applegpu_set_matmul_path({"auto": 0, "simt": 1, "tcgen05": 2}[mode])
 
 
+def set_attention_path(mode):
+    """'auto' (single-kernel attention when eligible) or 'composed' (GEMM + softmax + GEMM)."""
+    _L().applegpu_set_attention_path({"auto": 0, "composed": 1}[mode])
+
+
 def pipeline_status():
     return int(_L().applegpu_pipeline_status())
 

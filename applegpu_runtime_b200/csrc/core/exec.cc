@@ -6,6 +6,7 @@
 // of them with a copy kernel (lazy.rs:1891-1917, :2246-2262) — and consumers either read the
 // strided view directly (matmul, element-wise, copy) or make it contiguous first.
 #include "runtime.h"
+#include <algorithm>
 #include <array>
 #include <atomic>
 #include <cmath>
@@ -199,6 +200,8 @@ static k::UnOp unop_of(Op op) {
   }
 }
 
+bool g_fused_attention = true;  // false: always compose attention from GEMM + softmax + GEMM
+
 static Status attention_exec(const TensorRec& q, const TensorRec& kk, const TensorRec& v, bool causal, TensorRec* out,
                              std::shared_ptr<Buffer> out_buf, const Dims& out_shape) {
   // softmax[_causal]((Q K^T) * 1/sqrt(d_k)) V with the score matrix materialised in the storage
@@ -208,6 +211,30 @@ static Status attention_exec(const TensorRec& q, const TensorRec& kk, const Tens
   int64_t tq = q.shape[qn - 2], dk = q.shape[qn - 1], tk = kk.shape[kn - 2];
   Dims sshape(out_shape.begin(), out_shape.end() - 1);
   sshape.push_back(tk);
+  // Single-kernel form when the shapes allow it: leading dims (batch, heads) equal on Q, K, V.
+  if (!ctx.dry && qn <= 4 && qn >= 2 && kn == qn && (int)v.shape.size() == qn && q.strides.back() == 1 && kk.strides.back() == 1 &&
+      v.strides.back() == 1 && std::equal(q.shape.begin(), q.shape.end() - 2, kk.shape.begin()) &&
+      std::equal(q.shape.begin(), q.shape.end() - 2, v.shape.begin()) && g_fused_attention) {
+    k::AttnDesc ad;
+    ad.dtype = q.dtype; ad.q = q.data(); ad.k = kk.data(); ad.v = v.data();
+    ad.batch = qn == 4 ? q.shape[0] : 1; ad.heads = qn >= 3 ? q.shape[qn - 3] : 1;
+    ad.tq = tq; ad.tk = tk; ad.d = dk; ad.dv = v.shape.back();
+    auto lead = [&](const TensorRec& t, int64_t* sb, int64_t* sh, int64_t* st) {
+      int n = (int)t.shape.size();
+      *st = t.strides[n - 2];
+      *sh = n >= 3 ? t.strides[n - 3] : 0;
+      *sb = n == 4 ? t.strides[0] : 0;
+    };
+    lead(q, &ad.q_b, &ad.q_h, &ad.q_t); lead(kk, &ad.k_b, &ad.k_h, &ad.k_t); lead(v, &ad.v_b, &ad.v_h, &ad.v_t);
+    ad.scale = 1.0f / std::sqrt((float)dk); ad.causal = causal;
+    if (q.dtype == kk.dtype && q.dtype == v.dtype && k::attention_fused_eligible(ad)) {
+      AG_RETURN_IF_ERROR(alloc_out(out_shape, q.dtype, out, out_buf));
+      ad.o = out->data();
+      lead(*out, &ad.o_b, &ad.o_h, &ad.o_t);
+      AG_LAUNCH(k::attention(ctx.stream, ad));
+      return Status::OK();
+    }
+  }
   TensorRec scores;
   AG_RETURN_IF_ERROR(alloc_out(sshape, q.dtype, &scores, nullptr));
   AG_RETURN_IF_ERROR(alloc_out(out_shape, q.dtype, out, out_buf));

@@ -11,6 +11,7 @@
 #include <mutex>
 
 namespace ag {
+extern bool g_fused_attention;
 uint64_t launch_count();
 namespace profile { void enable(bool on); void clear(); std::string report(); }
 namespace k {
@@ -812,6 +813,7 @@ int32_t applegpu_device(void) { return DeviceCtx::get().device; }
 const char* applegpu_device_name(void) { return DeviceCtx::get().name.c_str(); }
 uint64_t applegpu_launch_count(void) { return ag::launch_count(); }
 void applegpu_set_matmul_path(int32_t mode) { k::set_matmul_path(mode); }
+void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return 0;

@@ -1,0 +1,316 @@
+// Fused scaled-dot-product attention for head dimension 64 (bf16 / f16): softmax[_causal](Q K^T /
+// sqrt(d)) V in one kernel, scores never leave the SM.
+//
+// Replaces the reference's 5-launch composition (ops.rs:1531-1618: transpose(K), matmul,
+// scalar_mul, softmax[_causal], matmul, with [.., Tq, Tk] score tensors materialised three times)
+// for the shapes every model on the path uses (GPT-2 small / large and BERT-base all have
+// d_head = 64). Semantics kept: mask is `col > row` with rows counted from 0, probabilities are
+// rounded to the storage type before the P.V product (the reference stores softmax output in
+// the storage type), the row sum is accumulated unrounded in float.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in blocks of
+// 128:  S = Q K_j^T (tcgen05, fp32 in TMEM) -> online softmax by 128 threads, one query row each
+// (running max / sum in registers, exp2 with the 1/sqrt(d) scale folded in) -> P_j as bf16 into
+// shared memory in the 128B-swizzled K-major layout the tensor core reads -> O_j = P_j V_j
+// (tcgen05, V read N-major in place) -> O = O * alpha + O_j in registers. Warp roles: warp 0
+// TMA producer (Q once, K double-buffered, V single-buffered), warp 1 MMA issuer and TMEM owner,
+// warps 2..5 softmax / output. Two CTAs fit per SM (96 KB shared memory, 256 TMEM columns each),
+// so one CTA's softmax overlaps the other's MMAs. All waits are bounded.
+#include "common.cuh"
+#include "sm100.cuh"
+#include <cuda.h>
+#include <type_traits>
+
+namespace ag { namespace k {
+
+using namespace ag::sm100;
+
+Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uint64_t rows, uint64_t nbi, uint64_t nbo,
+                uint64_t row_stride, uint64_t bi_stride, uint64_t bo_stride, uint32_t b0, uint32_t b1);
+int* matmul_status_word();
+
+constexpr int kAttnThreads = 192;
+constexpr int kQ = 128;    // query rows per CTA
+constexpr int kKV = 128;   // keys per block
+constexpr int kD = 64;     // head dimension
+constexpr int kTileBytes = 128 * kD * 2;                 // 16 KB: Q, K or V tile
+constexpr int kPBytes = kQ * kKV * 2;                    // 32 KB
+constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * kTileBytes /*K*/ + kTileBytes /*V*/ + kPBytes + 1024;
+constexpr int kAttnTmemCols = 256;                       // S: 128, O block: 64
+
+struct AttnParams {
+  void* o;
+  long long o_b, o_h, o_t;   // element strides of the output
+  int heads, tq, tk;
+  int causal;
+  int o_vec;                 // output rows are 16-byte aligned
+  float scale_log2;          // (1/sqrt(d)) * log2(e)
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full, s_empty, p_full, p_empty, o_full, o_empty;
+  __shared__ uint32_t tmem_base_slot;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTileBytes;       // two stages
+  uint8_t* sV = sK + 2 * kTileBytes;
+  uint8_t* sP = sV + kTileBytes;       // two 64-wide k-blocks of 16 KB
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_tiles = (p.tq + kQ - 1) / kQ;
+  const int qt = q_tiles - 1 - (int)blockIdx.x;   // heaviest (longest causal prefix) tiles first
+  const int bh = (int)blockIdx.y;
+  const int b = bh / p.heads, h = bh % p.heads;
+  const int q0 = qt * kQ;
+  int n_blocks = (p.tk + kKV - 1) / kKV;
+  if (p.causal) {
+    int last_col = q0 + kQ - 1;  // the largest column any row of this tile may see
+    int nb = last_col / kKV + 1;
+    if (nb < n_blocks) n_blocks = nb;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    mbar_init(&v_full, 1); mbar_init(&v_empty, 1);
+    mbar_init(&s_full, 1); mbar_init(&s_empty, 4);
+    mbar_init(&p_full, 4); mbar_init(&p_empty, 1);
+    mbar_init(&o_full, 1); mbar_init(&o_empty, 4);
+    mbar_fence_init();
+    prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+  }
+  if (warp == 1) { tmem_alloc(&tmem_base_slot, kAttnTmemCols); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&q_full, kTileBytes);
+      tma_load_4d(sQ, &tmap_q, &q_full, 0, q0, h, b);
+      bool ok = true;
+      for (int j = 0; j < n_blocks && ok; j++) {
+        int st = j & 1;
+        if (!mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1, p.status, 11)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &tmap_k, &k_full[st], 0, j * kKV, h, b);
+        if (!mbar_wait(&v_empty, (j & 1) ^ 1, p.status, 12)) { ok = false; break; }
+        mbar_expect_tx(&v_full, kTileBytes);
+        tma_load_4d(sV, &tmap_v, &v_full, 0, j * kKV, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, kQ, kKV);   // S = Q K^T: both K-major, N = 128
+      constexpr uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, kQ, kD);    // O = P V: V is N-major, N = 64
+      bool ok = mbar_wait(&q_full, 0, p.status, 13);
+      auto issue_s = [&](int j) -> bool {
+        int st = j & 1;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1, p.status, 14)) return false;
+        if (!mbar_wait(&s_empty, (j & 1) ^ 1, p.status, 15)) return false;
+        tc_fence_after_sync();
+        uint32_t a = smem_u32(sQ), bb = smem_u32(sK + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; kk++)
+          mma_f16_ss(tmem_s, make_smem_desc_sw128(a + kk * 32, 16, 1024), make_smem_desc_sw128(bb + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(&k_empty[st]);
+        mma_commit(&s_full);
+        return true;
+      };
+      if (ok && n_blocks > 0) ok = issue_s(0);
+      for (int j = 0; j < n_blocks && ok; j++) {
+        if (j + 1 < n_blocks) { if (!issue_s(j + 1)) { ok = false; break; } }
+        if (!mbar_wait(&v_full, j & 1, p.status, 16)) { ok = false; break; }
+        if (!mbar_wait(&p_full, j & 1, p.status, 17)) { ok = false; break; }
+        if (!mbar_wait(&o_empty, (j & 1) ^ 1, p.status, 18)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t a = smem_u32(sP), bb = smem_u32(sV);
+#pragma unroll
+        for (int kk = 0; kk < kKV / 16; kk++) {
+          // P: two 64-wide k-blocks of 16 KB, 32 B per K step inside a block.
+          uint64_t da = make_smem_desc_sw128(a + (kk >> 2) * (kQ * 128) + (kk & 3) * 32, 16, 1024);
+          // V: rows are keys (128 B = 64 head dims); a K step of 16 keys is 2048 B.
+          uint64_t db = make_smem_desc_sw128(bb + kk * 2048, 64 * 128, 1024);
+          mma_f16_ss(tmem_o, da, db, idesc_o, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(&v_empty);
+        mma_commit(&p_empty);
+        mma_commit(&o_full);
+      }
+    }
+  } else {
+    // ── softmax / output: thread = query row ──
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;          // row inside the tile = TMEM lane
+    const int row = q0 + r;                     // row inside the sequence
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o_acc[kD];
+#pragma unroll
+    for (int e = 0; e < kD; e++) o_acc[e] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks && ok; j++) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full, j & 1, p.status, 19))) { ok = false; break; }  // warp-uniform exits
+      tc_fence_after_sync();
+      const int col_base = j * kKV;
+      // columns this row may see inside the block: [0, lim)
+      int lim = p.tk - col_base;
+      if (p.causal) { int c = row - col_base + 1; if (c < lim) lim = c; }
+      if (lim > kKV) lim = kKV;
+      const bool full = lim >= kKV;
+      // pass 1: row maximum
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kKV / 32; c++) {
+        uint32_t s[32];
+        tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
+        tmem_ld_wait();
+        if (full) {
+#pragma unroll
+          for (int e = 0; e < 32; e++) m_blk = fmaxf(m_blk, __uint_as_float(s[e]));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e++) if (c * 32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s[e]));
+        }
+      }
+      float m_new = fmaxf(m_run, m_blk * p.scale_log2);
+      // a row with nothing visible in this block (only rows past the sequence end) keeps its state
+      float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      float alpha = exp2f(m_run - m_use);
+      // P overwrites the buffer the previous P.V product read
+      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty, (j & 1) ^ 1, p.status, 20))) { ok = false; break; }
+      // pass 2: probabilities
+      float l_blk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kKV / 32; c++) {
+        uint32_t s[32];
+        tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          float x = exp2f(__uint_as_float(s[e]) * p.scale_log2 - m_use);
+          if (!full && c * 32 + e >= lim) x = 0.f;
+          pv[e] = x;
+          l_blk += x;
+        }
+        uint8_t* dst = sP + (c >> 1) * (kQ * 128) + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+          Pack<T> o;
+#pragma unroll
+          for (int e = 0; e < 8; e++) o.v[e] = Cvt<T>::from(pv[g * 8 + e]);
+          int chunk = ((c & 1) * 4 + g) ^ (r & 7);   // 128B swizzle: 16-byte chunk index XOR row % 8
+          *reinterpret_cast<Pack<T>*>(dst + chunk * 16) = o;
+        }
+      }
+      // S has been read twice: the next Q K^T may overwrite it
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty);
+      // P is complete for this warp's 32 rows: publish to the tensor core (async proxy)
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      // O = O * alpha + P V
+      if (!__all_sync(0xffffffffu, mbar_wait(&o_full, j & 1, p.status, 21))) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < kD / 32; c++) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), ov);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e++) o_acc[c * 32 + e] = o_acc[c * 32 + e] * alpha + __uint_as_float(ov[e]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty);
+    }
+    if (ok && row < p.tq) {
+      float inv = 1.0f / l_run;
+      T* dst = reinterpret_cast<T*>(p.o) + (long long)b * p.o_b + (long long)h * p.o_h + (long long)row * p.o_t;
+      if (p.o_vec) {
+#pragma unroll
+        for (int g = 0; g < kD / 8; g++) {
+          Pack<T> o;
+#pragma unroll
+          for (int e = 0; e < 8; e++) o.v[e] = Cvt<T>::from(o_acc[g * 8 + e] * inv);
+          st16(dst + g * 8, o);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < kD; e++) dst[e] = Cvt<T>::from(o_acc[e] * inv);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kAttnTmemCols);
+}
+
+static bool attn_view_ok(const void* ptr, int64_t sb, int64_t sh, int64_t st, int64_t batch, int64_t heads) {
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return false;
+  if (st % 8 != 0 || st < kD) return false;
+  if (heads > 1 && sh % 8 != 0) return false;
+  if (batch > 1 && sb % 8 != 0) return false;
+  return true;
+}
+
+bool attention_fused_eligible(const AttnDesc& d) {
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16)) return false;
+  if (d.d != kD || d.dv != kD) return false;
+  if (d.tq < 1 || d.tk < 1 || d.batch < 1 || d.heads < 1) return false;
+  if (d.tq > 0x3fffffff || d.tk > 0x3fffffff || d.batch * d.heads > 65535) return false;
+  return attn_view_ok(d.q, d.q_b, d.q_h, d.q_t, d.batch, d.heads) && attn_view_ok(d.k, d.k_b, d.k_h, d.k_t, d.batch, d.heads) &&
+         attn_view_ok(d.v, d.v_b, d.v_h, d.v_t, d.batch, d.heads);
+}
+
+template <typename T>
+static Status launch_attention(cudaStream_t s, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p,
+                               dim3 grid) {
+  static bool attr_set = false;
+  auto kern = attention_tc_kernel<T>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    if (e != cudaSuccess) return cuda_status(e, "attention smem attribute");
+    attr_set = true;
+  }
+  kern<<<grid, kAttnThreads, kAttnSmem, s>>>(mq, mk, mv, p);
+  AG_CHECK_LAUNCH("attention (tcgen05)");
+  return Status::OK();
+}
+
+Status attention(cudaStream_t s, const AttnDesc& d) {
+  if (!attention_fused_eligible(d)) return Status::compute("attention: operands are not eligible for the fused kernel");
+  int* st = matmul_status_word();
+  if (!st) return Status::compute("attention: cannot allocate status word");
+  CUtensorMap mq, mk, mv;
+  AG_RETURN_IF_ERROR(make_map(&mq, d.dtype, d.q, kD, (uint64_t)d.tq, (uint64_t)d.heads, (uint64_t)d.batch, (uint64_t)d.q_t, (uint64_t)d.q_h, (uint64_t)d.q_b, kD, kQ));
+  AG_RETURN_IF_ERROR(make_map(&mk, d.dtype, d.k, kD, (uint64_t)d.tk, (uint64_t)d.heads, (uint64_t)d.batch, (uint64_t)d.k_t, (uint64_t)d.k_h, (uint64_t)d.k_b, kD, kKV));
+  AG_RETURN_IF_ERROR(make_map(&mv, d.dtype, d.v, kD, (uint64_t)d.tk, (uint64_t)d.heads, (uint64_t)d.batch, (uint64_t)d.v_t, (uint64_t)d.v_h, (uint64_t)d.v_b, kD, kKV));
+  AttnParams p;
+  p.o = d.o; p.o_b = d.o_b; p.o_h = d.o_h; p.o_t = d.o_t;
+  p.heads = (int)d.heads; p.tq = (int)d.tq; p.tk = (int)d.tk; p.causal = d.causal ? 1 : 0;
+  p.o_vec = ((reinterpret_cast<uintptr_t>(d.o) & 15u) == 0 && d.o_t % 8 == 0 && d.o_h % 8 == 0 && d.o_b % 8 == 0) ? 1 : 0;
+  p.scale_log2 = d.scale * 1.4426950408889634f;
+  p.status = st;
+  dim3 grid((unsigned)((d.tq + kQ - 1) / kQ), (unsigned)(d.batch * d.heads), 1);
+  if (d.dtype == DType::BF16) return launch_attention<__nv_bfloat16>(s, mq, mk, mv, p, grid);
+  return launch_attention<__half>(s, mq, mk, mv, p, grid);
+}
+
+}}  // namespace ag::k

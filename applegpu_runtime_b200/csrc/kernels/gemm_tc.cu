@@ -324,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int rem = (int)(t % tiles_per_batch);
       int m0 = (rem % p.tiles_m) * BM;
       int n0 = (rem / p.tiles_m) * BN;
-      if (!mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
       tc_fence_after_sync();
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
@@ -382,7 +382,7 @@ static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
 
 // 4-D map over (inner, rows, batch_inner, batch_outer) of 2-byte elements with a 128B-swizzled
 // box {b0, b1, 1, 1}. Strides are in elements; a dimension of extent 1 may carry any stride.
-static Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uint64_t rows, uint64_t nbi, uint64_t nbo,
+Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uint64_t rows, uint64_t nbi, uint64_t nbo,
                        uint64_t row_stride, uint64_t bi_stride, uint64_t bo_stride, uint32_t b0, uint32_t b1) {
   MapKey key;
   std::memset(&key, 0, sizeof(key));

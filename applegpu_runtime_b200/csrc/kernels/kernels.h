@@ -86,7 +86,7 @@ const char* matmul_path(const GemmDesc& d);
 struct AttnDesc {
   DType dtype;
   const void* q; const void* k; const void* v; void* o;
-  int64_t batch, heads, tq, tk, d;     // flattened leading dims = batch*heads
+  int64_t batch, heads, tq, tk, d, dv; // leading dims = (batch, heads)
   int64_t q_b, q_h, q_t;               // element strides (last dim contiguous)
   int64_t k_b, k_h, k_t;
   int64_t v_b, v_h, v_t;
@@ -94,6 +94,9 @@ struct AttnDesc {
   float scale;
   bool causal;
 };
+// Single-kernel attention (tcgen05, d = dv = 64, f16/bf16, TMA-compatible views); `attention_fused_eligible`
+// tells whether `attention` accepts the problem, otherwise the caller composes it from GEMMs.
+bool attention_fused_eligible(const AttnDesc& d);
 Status attention(cudaStream_t s, const AttnDesc& d);
 
 // Writes more than the L2 capacity so the next timed kernel starts cold.

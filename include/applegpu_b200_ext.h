@@ -130,6 +130,9 @@ APPLEGPU_API uint64_t applegpu_launch_count(void);
 APPLEGPU_API const char* applegpu_matmul_path(uint64_t a_id, uint64_t b_id, bool eager);
 /* 0 auto, 1 force the CUDA-core kernel, 2 require the tcgen05 kernel. */
 APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
+/* 0 auto (single-kernel attention when head dim is 64 and dtype is f16/bf16), 1 always compose
+ * attention from GEMM + softmax + GEMM with materialised scores. */
+APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
 /* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
 /* CUDA-event stopwatch on the runtime stream. */

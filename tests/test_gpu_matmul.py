@@ -189,6 +189,35 @@ def test_attention_bf16_within_bar(gpu_dev, causal):
     assert rel_err(got, ref.astype(np.float64)) <= 2e-2
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("causal,shape_q,tk", [(True, (2, 3, 128, 64), 128), (True, (1, 2, 200, 64), 200), (True, (2, 12, 1024, 64), 1024),
+                                               (False, (1, 4, 130, 64), 130), (False, (3, 2, 1, 64), 300), (False, (1, 1, 77, 64), 513),
+                                               (True, (4, 384, 64), 384), (False, (256, 64), 256), (True, (1, 1, 300, 64), 140)])
+def test_attention_single_kernel_matches_oracle_and_composition(gpu_dev, dtype, causal, shape_q, tk):
+    """Head dim 64 in f16/bf16 takes the single-kernel path: ragged query / key tails, Tq != Tk,
+    a decode-shaped call (Tq = 1), 2-D / 3-D / 4-D leading dims."""
+    rng = np.random.default_rng(tk + len(shape_q))
+    shape_kv = shape_q[:-2] + (tk, 64)
+    q = rounded(rng.standard_normal(shape_q).astype(np.float32), dtype)
+    k = rounded(rng.standard_normal(shape_kv).astype(np.float32), dtype)
+    v = rounded(rng.standard_normal(shape_kv).astype(np.float32), dtype)
+    fn = gpu_dev.attention_causal if causal else gpu_dev.attention
+    fused = fn(up(gpu_dev, q, dtype), up(gpu_dev, k, dtype), up(gpu_dev, v, dtype)).to_numpy().astype(np.float32)
+    ref = R.attention(q, k, v, causal).astype(np.float64)          # fp32 oracle on the same rounded inputs
+    assert np.all(np.isfinite(fused))
+    assert rel_err(fused, ref) <= 2e-2
+    gpu_dev.set_attention_path("composed")
+    try:
+        composed = fn(up(gpu_dev, q, dtype), up(gpu_dev, k, dtype), up(gpu_dev, v, dtype)).to_numpy().astype(np.float32)
+    finally:
+        gpu_dev.set_attention_path("auto")
+    assert rel_err(composed, ref) <= 2e-2
+    assert rel_err(fused, composed.astype(np.float64)) <= 2e-2
+    # the single-kernel form keeps scores in fp32, so it is the closer of the two to the fp32 oracle
+    assert rel_err(fused, ref) <= rel_err(composed, ref) + 2e-3
+    assert gpu_dev.pipeline_status() == 0
+
+
 def test_attention_on_strided_head_views(gpu_dev):
     # the GPT-2 driver's layout: Q/K/V are column slices of one [B*T, 3d] matrix viewed as [B, h, T, dh]
     rng = np.random.default_rng(13)
