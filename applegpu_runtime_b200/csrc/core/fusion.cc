@@ -266,6 +266,19 @@ static void rewrite_attention(Rewriter& rw, uint64_t id) {
   rw.replace({kt->id, mm1->id, sc->id, sm->id, mm2->id}, std::move(fused));
 }
 
+// add_bias -> gelu | gelu_exact | relu outside a linear layer: one pass over the tensor instead of two.
+static void rewrite_bias_act(Rewriter& rw, uint64_t id) {
+  const OpNode* ab = rw.g.get_node(id);
+  if (!ab || ab->op.op != Op::AddBias || ab->op.act != k::Act::None) return;
+  const OpNode* c = rw.sole_consumer(id);
+  if (!c || !(c->op.op == Op::Gelu || c->op.op == Op::GeluExact || c->op.op == Op::Relu)) return;
+  if (c->out_shape != ab->out_shape || c->out_dtype != ab->out_dtype) return;
+  OpNode fused = *ab;
+  fused.id = c->id;
+  fused.op.act = c->op.op == Op::Gelu ? k::Act::GeluTanh : c->op.op == Op::GeluExact ? k::Act::GeluErf : k::Act::Relu;
+  rw.replace({ab->id, c->id}, std::move(fused));
+}
+
 static void rewrite_embed_add(Rewriter& rw, uint64_t id) {
   const OpNode* add = rw.g.get_node(id);
   if (!add || add->op.op != Op::Add || add->inputs.size() != 2 || add->inputs[0] == add->inputs[1]) return;
@@ -292,6 +305,7 @@ std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, con
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_linear(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_embed_add(rw, id); }
+    for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_bias_act(rw, id); }
     std::vector<uint64_t> next;
     for (uint64_t id : cur) if (!rw.removed.count(id) && g.has_node(id)) next.push_back(id);
     cur.swap(next);

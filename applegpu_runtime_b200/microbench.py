@@ -1,0 +1,146 @@
+"""Per-op microbenchmarks (the op microbench config of the headline benchmark, and the tool the
+ncu captures under profiles/ are taken with).
+
+Counterpart of the reference's benchmarks/bench_ops.py:23-39,122-142 (median of repeated launches
+per op). Shapes default to the benchmark config: batched matmul B=8 with M=N=K in {1024, 2048, 4096};
+layer_norm [8192, 768]; softmax_causal [96, 1024, 1024]; gelu+add_bias [8192, 3072]; plus the GEMM
+and attention shapes of a GPT-2-small forward. Each line reports the CUDA-event time per launch,
+the algorithmic work (flops for contractions, bytes otherwise) and the achieved rate.
+
+  python -m applegpu_runtime_b200.microbench                      all ops, bf16 and fp32
+  python -m applegpu_runtime_b200.microbench --op matmul --shape 8,4096,4096,4096 --dtype bfloat16 --iters 3
+"""
+import argparse
+import ctypes
+import json
+import sys
+
+import numpy as np
+
+from . import _lib
+from . import api as gpu
+
+
+def _tensor(rng, shape, dtype, scale=1.0):
+    t = gpu.from_numpy((rng.standard_normal(shape) * scale).astype(np.float32))
+    if dtype != "float32":
+        t = gpu.cast(t, dtype)
+        t.eval()
+    return t
+
+
+def _time(fn, iters, warmup=3, flush=False):
+    lib = _lib.load()
+    for _ in range(warmup):
+        fn().eval()
+    gpu.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            lib.applegpu_flush_l2()
+        lib.applegpu_timer_start()
+        fn().eval()
+        times.append(float(lib.applegpu_timer_stop_ms()))
+    return float(np.median(times))
+
+
+def bench_matmul(rng, dtype, b, m, n, k, iters, flush):
+    a = _tensor(rng, (b, m, k) if b > 1 else (m, k), dtype)
+    w = _tensor(rng, (b, k, n) if b > 1 else (k, n), dtype)
+    ms = _time(lambda: a @ w, iters, flush=flush)
+    flops = 2.0 * b * m * n * k
+    return {"op": "matmul", "dtype": dtype, "shape": [b, m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s"}
+
+
+def bench_lm_head(rng, dtype, m, vocab, k, iters, flush):
+    a = _tensor(rng, (m, k), dtype)
+    wte = _tensor(rng, (vocab, k), dtype, 0.02)
+    ms = _time(lambda: a @ gpu.transpose(wte), iters, flush=flush)
+    flops = 2.0 * m * vocab * k
+    return {"op": "matmul_kmajor_b", "dtype": dtype, "shape": [m, vocab, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s"}
+
+
+def bench_layer_norm(rng, dtype, rows, cols, iters, flush):
+    x = _tensor(rng, (rows, cols), dtype)
+    g = _tensor(rng, (cols,), dtype); b = _tensor(rng, (cols,), dtype)
+    ms = _time(lambda: gpu.layer_norm(x, g, b, 1e-5), iters, flush=flush)
+    e = gpu.dtype_size(dtype)
+    nbytes = 2.0 * rows * cols * e + 2 * cols * e
+    return {"op": "layer_norm", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+
+
+def bench_softmax_causal(rng, dtype, b, rows, cols, iters, flush):
+    x = _tensor(rng, (b, rows, cols), dtype)
+    ms = _time(lambda: gpu.softmax_causal(x), iters, flush=flush)
+    e = gpu.dtype_size(dtype)
+    tri = sum(min(r + 1, cols) for r in range(rows))
+    nbytes = (b * tri + b * rows * cols) * float(e)   # lower-triangle read + full write
+    return {"op": "softmax_causal", "dtype": dtype, "shape": [b, rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+
+
+def bench_gelu_add_bias(rng, dtype, rows, cols, iters, flush):
+    x = _tensor(rng, (rows, cols), dtype); bias = _tensor(rng, (cols,), dtype)
+
+    def fn():
+        return gpu.gelu(gpu.add_bias(x, bias))   # the fusion pass turns the pair into one add_bias[gelu] kernel
+    ms = _time(fn, iters, flush=flush)
+    e = gpu.dtype_size(dtype)
+    nbytes = 2.0 * rows * cols * e + cols * e
+    return {"op": "gelu+add_bias", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+
+
+def bench_attention(rng, dtype, b, h, t, d, causal, iters, flush):
+    q = _tensor(rng, (b, h, t, d), dtype); k = _tensor(rng, (b, h, t, d), dtype); v = _tensor(rng, (b, h, t, d), dtype)
+    fn = gpu.attention_causal if causal else gpu.attention
+    ms = _time(lambda: fn(q, k, v), iters, flush=flush)
+    flops = 4.0 * b * h * t * t * d * (0.5 if causal else 1.0)
+    return {"op": "attention_causal" if causal else "attention", "dtype": dtype, "shape": [b, h, t, d], "ms": ms, "work": flops,
+            "rate": flops / ms / 1e9, "unit": "TFLOP/s (causal-minimal flops)" if causal else "TFLOP/s"}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="all")
+    ap.add_argument("--shape", default="")
+    ap.add_argument("--dtype", default="")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--flush-l2", action="store_true", help="evict L2 before every timed launch")
+    args = ap.parse_args(argv)
+    gpu.init_backend()
+    rng = np.random.default_rng(0)
+    dtypes = [args.dtype] if args.dtype else ["bfloat16", "float32"]
+    shape = [int(x) for x in args.shape.split(",")] if args.shape else None
+    out = []
+    for dt in dtypes:
+        if args.op in ("all", "matmul"):
+            for s in ([shape] if shape else [[8, 1024, 1024, 1024], [8, 2048, 2048, 2048], [8, 4096, 4096, 4096]]):
+                if dt == "float32" and s[1] >= 4096 and not shape:
+                    continue  # 1.1 TFLOP on the CUDA-core kernel: run explicitly with --shape
+                out.append(bench_matmul(rng, dt, *s, args.iters, args.flush_l2))
+        if args.op in ("all", "gpt2_gemms") and dt != "float32":
+            for (m, n, k) in [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072)]:
+                out.append(bench_matmul(rng, dt, 1, m, n, k, args.iters, args.flush_l2))
+            out.append(bench_lm_head(rng, dt, 8192, 50257, 768, args.iters, args.flush_l2))
+        if args.op == "lm_head":
+            out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args.flush_l2))
+        if args.op in ("all", "layer_norm"):
+            out.append(bench_layer_norm(rng, dt, *(shape or [8192, 768]), args.iters, args.flush_l2))
+        if args.op in ("all", "softmax_causal"):
+            out.append(bench_softmax_causal(rng, dt, *(shape or [96, 1024, 1024]), args.iters, args.flush_l2))
+        if args.op in ("all", "gelu_add_bias"):
+            out.append(bench_gelu_add_bias(rng, dt, *(shape or [8192, 3072]), args.iters, args.flush_l2))
+        if args.op in ("all", "attention") and dt != "float32":
+            out.append(bench_attention(rng, dt, *(shape or [8, 12, 1024, 64]), True, args.iters, args.flush_l2))
+        for r in out:
+            if not r.get("_printed"):
+                r["_printed"] = True
+                print(json.dumps({k: v for k, v in r.items() if k != "_printed"}), flush=True)
+    st = gpu.pipeline_status()
+    if st:
+        print(json.dumps({"pipeline_status": st}))
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -144,6 +144,14 @@ def test_add_bias_f32_exact(gpu_dev, shape, bias_n):
     assert np.array_equal(gpu_dev.add_bias(gpu_dev.from_numpy(x), gpu_dev.from_numpy(b)).to_numpy(), R.add_bias(x, b))
 
 
+def test_add_bias_then_gelu_is_one_kernel(gpu_dev):
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((64, 3072)).astype(np.float32); b = rng.standard_normal(3072).astype(np.float32)
+    y = gpu_dev.gelu(gpu_dev.add_bias(gpu_dev.from_numpy(x), gpu_dev.from_numpy(b)))
+    assert y.plan().strip() == "add_bias[gelu]_f32 [64, 3072]"
+    close(y.to_numpy(), R.gelu(R.add_bias(x, b)), rel=1e-5, abs_=1e-6)
+
+
 # ── reductions ──────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("rows,cols", [(8192, 768), (3, 4), (5, 1), (17, 1280), (9, 1001), (2, 5120), (4, 20000), (1, 50257)])
 def test_layer_norm_f32(gpu_dev, rows, cols):
