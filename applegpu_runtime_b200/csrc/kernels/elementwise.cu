@@ -88,6 +88,41 @@ __device__ __forceinline__ float apply_binary(int op, float a, float b) {
   }
 }
 
+// Block forms: the op is tested once, then a straight loop runs over the thread's elements.
+template <int M>
+__device__ __forceinline__ void unary_block(int op, const float (&x)[M], float (&y)[M]) {
+#define AG_UN(CASE, EXPR) case (int)UnOp::CASE: _Pragma("unroll") for (int i = 0; i < M; i++) { float v = x[i]; y[i] = (EXPR); } break;
+  switch (op) {
+    AG_UN(Neg, -v) AG_UN(Relu, fmaxf(v, 0.0f)) AG_UN(Exp, expf(v)) AG_UN(Log, logf(v)) AG_UN(Sqrt, sqrtf(v)) AG_UN(Tanh, tanhf(v))
+    AG_UN(Sin, sinf(v)) AG_UN(Cos, cosf(v)) AG_UN(Gelu, gelu_tanh_f(v)) AG_UN(GeluExact, gelu_erf_f(v))
+    AG_UN(Sigmoid, 1.0f / (1.0f + expf(-v))) AG_UN(Abs, fabsf(v)) AG_UN(Sign, (v > 0.f) ? 1.f : ((v < 0.f) ? -1.f : 0.f))
+    default:
+#pragma unroll
+      for (int i = 0; i < M; i++) y[i] = x[i];
+  }
+#undef AG_UN
+}
+template <int M>
+__device__ __forceinline__ void binary_block(int op, const float (&a)[M], const float (&b)[M], float (&y)[M]) {
+  switch (op) {
+    case (int)BinOp::Add:
+#pragma unroll
+      for (int i = 0; i < M; i++) y[i] = a[i] + b[i];
+      break;
+    case (int)BinOp::Sub:
+#pragma unroll
+      for (int i = 0; i < M; i++) y[i] = a[i] - b[i];
+      break;
+    case (int)BinOp::Mul:
+#pragma unroll
+      for (int i = 0; i < M; i++) y[i] = a[i] * b[i];
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < M; i++) y[i] = __fdiv_rn(a[i], b[i]);
+  }
+}
+
 struct ProgParams {
   FusedProgram prog;
   const void* in[kFusedMaxInputs];
@@ -99,59 +134,75 @@ struct ProgParams {
 template <typename T>
 __global__ void __launch_bounds__(256) program_vec_kernel(ProgParams p, uint32_t bcast_mask, T* __restrict__ out, int64_t n_packs, int64_t n) {
   constexpr int N = Pack<T>::N;
+  constexpr int U = 16 / N;  // 16 elements per thread per trip: 4 (fp32) or 2 (half types) independent 16-byte loads in flight per leaf
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t pk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pk < n_packs; pk += stride) {
-    float acc[N];
+  for (int64_t pk0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pk0 < n_packs; pk0 += stride * U) {
+    float acc[U * N];
     const int ni = p.prog.n_instrs;
     for (int it = 0; it < ni; it++) {
       FusedInstr ins = p.prog.instrs[it];
-      float a[N], b[N];
+      float a[U * N], b[U * N];
       if (ins.a < 0) {
 #pragma unroll
-        for (int e = 0; e < N; e++) a[e] = acc[e];
+        for (int u = 0; u < U; u++)
+#pragma unroll
+          for (int e = 0; e < N; e++) a[u * N + e] = acc[u * N + e];
       } else {
         const T* src = reinterpret_cast<const T*>(p.in[ins.a]);
         if (bcast_mask & (1u << ins.a)) {
           float s = Cvt<T>::to(src[0]);
 #pragma unroll
-          for (int e = 0; e < N; e++) a[e] = s;
-        } else {
-          Pack<T> v = ld16(src + pk * N);
+          for (int u = 0; u < U; u++)
 #pragma unroll
-          for (int e = 0; e < N; e++) a[e] = Cvt<T>::to(v.v[e]);
+            for (int e = 0; e < N; e++) a[u * N + e] = s;
+        } else {
+          Pack<T> v[U];
+#pragma unroll
+          for (int u = 0; u < U; u++) { int64_t pk = pk0 + u * stride; if (pk < n_packs) v[u] = ld16_stream(src + pk * N); }
+#pragma unroll
+          for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int e = 0; e < N; e++) a[u * N + e] = Cvt<T>::to(v[u].v[e]);
         }
       }
       if (ins.is_binary) {
         if (ins.b < 0) {
 #pragma unroll
-          for (int e = 0; e < N; e++) b[e] = acc[e];
+          for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int e = 0; e < N; e++) b[u * N + e] = acc[u * N + e];
         } else {
           const T* src = reinterpret_cast<const T*>(p.in[ins.b]);
           if (bcast_mask & (1u << ins.b)) {
             float s = Cvt<T>::to(src[0]);
 #pragma unroll
-            for (int e = 0; e < N; e++) b[e] = s;
-          } else {
-            Pack<T> v = ld16(src + pk * N);
+            for (int u = 0; u < U; u++)
 #pragma unroll
-            for (int e = 0; e < N; e++) b[e] = Cvt<T>::to(v.v[e]);
+              for (int e = 0; e < N; e++) b[u * N + e] = s;
+          } else {
+            Pack<T> v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) { int64_t pk = pk0 + u * stride; if (pk < n_packs) v[u] = ld16_stream(src + pk * N); }
+#pragma unroll
+            for (int u = 0; u < U; u++)
+#pragma unroll
+              for (int e = 0; e < N; e++) b[u * N + e] = Cvt<T>::to(v[u].v[e]);
           }
         }
-#pragma unroll
-        for (int e = 0; e < N; e++) acc[e] = apply_binary(ins.op, a[e], b[e]);
+        binary_block<U * N>(ins.op, a, b, acc);
       } else {
-#pragma unroll
-        for (int e = 0; e < N; e++) acc[e] = apply_unary(ins.op, a[e]);
+        unary_block<U * N>(ins.op, a, acc);
       }
     }
-    if (p.use_scalar) {
 #pragma unroll
-      for (int e = 0; e < N; e++) acc[e] *= p.scalar;
+    for (int u = 0; u < U; u++) {
+      int64_t pk = pk0 + u * stride;
+      if (pk >= n_packs) break;
+      Pack<T> o;
+#pragma unroll
+      for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(p.use_scalar ? acc[u * N + e] * p.scalar : acc[u * N + e]);
+      st16_stream(out + pk * N, o);
     }
-    Pack<T> o;
-#pragma unroll
-    for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(acc[e]);
-    st16(out + pk * N, o);
   }
   // tail (n not a multiple of the pack width)
   int64_t tail0 = n_packs * N;
@@ -326,20 +377,48 @@ template <typename T>
 __global__ void __launch_bounds__(256) add_bias_rows_kernel(const T* __restrict__ in, const T* __restrict__ bias, T* __restrict__ out,
                                                              int64_t n_packs, int packs_per_row, Act act) {
   constexpr int N = Pack<T>::N;
+  constexpr int U = 16 / N;  // 16 elements per thread per trip, independent 16-byte loads in flight
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t pk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pk < n_packs; pk += stride) {
-    int c = (int)(pk % packs_per_row) * N;
-    Pack<T> x = ld16_stream(in + pk * N);
-    Pack<T> b = ld16(bias + c);
-    Pack<T> o;
+  for (int64_t pk0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pk0 < n_packs; pk0 += stride * U) {
+    Pack<T> x[U], b[U];
 #pragma unroll
-    for (int e = 0; e < N; e++) {
-      // The sum is rounded to the storage type before the activation, as two separate
-      // reference kernels (add_bias then gelu) would do.
-      float v = Cvt<T>::to(Cvt<T>::from(Cvt<T>::to(x.v[e]) + Cvt<T>::to(b.v[e])));
-      o.v[e] = Cvt<T>::from(apply_act(v, act));
+    for (int u = 0; u < U; u++) {
+      int64_t pk = pk0 + u * stride;
+      if (pk < n_packs) { x[u] = ld16_stream(in + pk * N); b[u] = ld16(bias + (int)(pk % packs_per_row) * N); }
     }
-    st16_stream(out + pk * N, o);
+    float v[U * N];
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+      for (int e = 0; e < N; e++) {
+        // The sum is rounded to the storage type before the activation, as two separate
+        // reference kernels (add_bias then gelu) would do.
+        v[u * N + e] = Cvt<T>::to(Cvt<T>::from(Cvt<T>::to(x[u].v[e]) + Cvt<T>::to(b[u].v[e])));
+      }
+    switch (act) {  // tested once per trip, not per element
+      case Act::GeluTanh:
+#pragma unroll
+        for (int i = 0; i < U * N; i++) v[i] = gelu_tanh_f(v[i]);
+        break;
+      case Act::GeluErf:
+#pragma unroll
+        for (int i = 0; i < U * N; i++) v[i] = gelu_erf_f(v[i]);
+        break;
+      case Act::Relu:
+#pragma unroll
+        for (int i = 0; i < U * N; i++) v[i] = fmaxf(v[i], 0.f);
+        break;
+      default: break;
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      int64_t pk = pk0 + u * stride;
+      if (pk >= n_packs) break;
+      Pack<T> o;
+#pragma unroll
+      for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(v[u * N + e]);
+      st16_stream(out + pk * N, o);
+    }
   }
 }
 template <typename T>

@@ -153,16 +153,21 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
     float sum = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
+      // packs entirely right of the diagonal (or past the row) hold only masked slots: skip their math
+      if ((lane + it * 32) * N < valid) {
 #pragma unroll
-      for (int e = 0; e < N; e++) {
-        // Masked slots hold -inf and contribute exp(-inf) = 0.
-        float ex = expf(v[it][e] - m);
-        sum += ex;
-        // Half types: the reference stores exp() in the storage type and divides that value.
-        v[it][e] = Cvt<T>::to(Cvt<T>::from(ex));
+        for (int e = 0; e < N; e++) {
+          // Masked slots hold -inf and contribute exp(-inf) = 0. __expf (hardware exp2) is within
+          // 2 ulp plus the rounding of x*log2(e): well inside the 1e-5 bar.
+          float ex = __expf(v[it][e] - m);
+          sum += ex;
+          // Half types: the reference stores exp() in the storage type and divides that value.
+          v[it][e] = Cvt<T>::to(Cvt<T>::from(ex));
+        }
       }
     }
     sum = warp_sum(sum);
+    const float inv = __fdiv_rn(1.0f, sum);  // one division per row; e * (1/sum) is within 1 ulp of e / sum
     T* y = out + row * cols;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
@@ -170,10 +175,12 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
       int c0 = pk * N;
       if (pk < packs) {
         Pack<T> o;
+        if (c0 < valid) {
 #pragma unroll
-        for (int e = 0; e < N; e++) {
-          bool on = c0 + e < valid;
-          o.v[e] = on ? Cvt<T>::from(__fdiv_rn(v[it][e], sum)) : Cvt<T>::from(0.f);
+          for (int e = 0; e < N; e++) o.v[e] = (c0 + e < valid) ? Cvt<T>::from(v[it][e] * inv) : Cvt<T>::from(0.f);
+        } else {
+#pragma unroll
+          for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(0.f);
         }
         st16_stream(y + c0, o);
       }

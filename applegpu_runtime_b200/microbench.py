@@ -5,7 +5,8 @@ Counterpart of the reference's benchmarks/bench_ops.py:23-39,122-142 (median of 
 per op). Shapes default to the benchmark config: batched matmul B=8 with M=N=K in {1024, 2048, 4096};
 layer_norm [8192, 768]; softmax_causal [96, 1024, 1024]; gelu+add_bias [8192, 3072]; plus the GEMM
 and attention shapes of a GPT-2-small forward. Each line reports the CUDA-event time per launch,
-the algorithmic work (flops for contractions, bytes otherwise) and the achieved rate.
+the algorithmic work (flops for contractions, bytes otherwise) and the achieved rate. By default launches run back to back inside one event pair and cycle through
+enough buffer sets (inputs and outputs) that no launch finds its data in the 126 MB L2.
 
   python -m applegpu_runtime_b200.microbench                      all ops, bf16 and fp32
   python -m applegpu_runtime_b200.microbench --op matmul --shape 8,4096,4096,4096 --dtype bfloat16 --iters 3
@@ -29,73 +30,98 @@ def _tensor(rng, shape, dtype, scale=1.0):
     return t
 
 
-def _time(fn, iters, warmup=3, flush=False):
+L2_BYTES = 126 << 20
+
+
+def _nsets(footprint_bytes, rotate):
+    """Buffer sets to cycle through so that consecutive launches never find their data in L2."""
+    if not rotate:
+        return 1
+    return int(max(1, min(8, -(-2 * L2_BYTES // max(1, int(footprint_bytes))))))
+
+
+def _time(fns, iters, warmup=3, single=False):
+    """CUDA-event time per launch on the runtime stream. Default: one event pair around `iters`
+    back-to-back launches cycling through the buffer sets in `fns` (outputs of the last len(fns)
+    launches are kept alive so the pool rotates output buffers too). `single`: median of
+    individually timed launches (includes launch latency)."""
+    import collections
     lib = _lib.load()
-    for _ in range(warmup):
-        fn().eval()
+    keep = collections.deque(maxlen=len(fns))
+    for i in range(max(warmup, 2 * len(fns) + 2)):  # long enough for the pool to reach its steady set of buffers
+        o = fns[i % len(fns)](); o.eval(); keep.append(o)
     gpu.synchronize()
-    times = []
-    for _ in range(iters):
-        if flush:
-            lib.applegpu_flush_l2()
-        lib.applegpu_timer_start()
-        fn().eval()
-        times.append(float(lib.applegpu_timer_stop_ms()))
-    return float(np.median(times))
+    if single:
+        times = []
+        for i in range(iters):
+            lib.applegpu_timer_start()
+            o = fns[i % len(fns)](); o.eval(); keep.append(o)
+            times.append(float(lib.applegpu_timer_stop_ms()))
+        return float(np.median(times))
+    lib.applegpu_timer_start()
+    for i in range(iters):
+        o = fns[i % len(fns)](); o.eval(); keep.append(o)
+    return float(lib.applegpu_timer_stop_ms()) / iters
 
 
-def bench_matmul(rng, dtype, b, m, n, k, iters, flush):
-    a = _tensor(rng, (b, m, k) if b > 1 else (m, k), dtype)
-    w = _tensor(rng, (b, k, n) if b > 1 else (k, n), dtype)
-    ms = _time(lambda: a @ w, iters, flush=flush)
+def bench_matmul(rng, dtype, b, m, n, k, iters, opt):
+    e = gpu.dtype_size(dtype)
+    sets = []
+    for _ in range(_nsets((b * m * k + b * k * n + b * m * n) * e, opt.rotate)):
+        a = _tensor(rng, (b, m, k) if b > 1 else (m, k), dtype)
+        w = _tensor(rng, (b, k, n) if b > 1 else (k, n), dtype)
+        sets.append((a, w))
+    ms = _time([lambda a=a, w=w: a @ w for a, w in sets], iters, single=opt.single)
     flops = 2.0 * b * m * n * k
-    return {"op": "matmul", "dtype": dtype, "shape": [b, m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s"}
+    return {"op": "matmul", "dtype": dtype, "shape": [b, m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
-def bench_lm_head(rng, dtype, m, vocab, k, iters, flush):
+def bench_lm_head(rng, dtype, m, vocab, k, iters, opt):
     a = _tensor(rng, (m, k), dtype)
     wte = _tensor(rng, (vocab, k), dtype, 0.02)
-    ms = _time(lambda: a @ gpu.transpose(wte), iters, flush=flush)
+    ms = _time([lambda: a @ gpu.transpose(wte)], iters, single=opt.single)
     flops = 2.0 * m * vocab * k
-    return {"op": "matmul_kmajor_b", "dtype": dtype, "shape": [m, vocab, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s"}
+    return {"op": "matmul_kmajor_b", "dtype": dtype, "shape": [m, vocab, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": 1}
 
 
-def bench_layer_norm(rng, dtype, rows, cols, iters, flush):
-    x = _tensor(rng, (rows, cols), dtype)
+def bench_layer_norm(rng, dtype, rows, cols, iters, opt):
+    e = gpu.dtype_size(dtype)
     g = _tensor(rng, (cols,), dtype); b = _tensor(rng, (cols,), dtype)
-    ms = _time(lambda: gpu.layer_norm(x, g, b, 1e-5), iters, flush=flush)
-    e = gpu.dtype_size(dtype)
+    xs = [_tensor(rng, (rows, cols), dtype) for _ in range(_nsets(2 * rows * cols * e, opt.rotate))]
+    ms = _time([lambda x=x: gpu.layer_norm(x, g, b, 1e-5) for x in xs], iters, single=opt.single)
     nbytes = 2.0 * rows * cols * e + 2 * cols * e
-    return {"op": "layer_norm", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+    return {"op": "layer_norm", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s", "sets": len(xs)}
 
 
-def bench_softmax_causal(rng, dtype, b, rows, cols, iters, flush):
-    x = _tensor(rng, (b, rows, cols), dtype)
-    ms = _time(lambda: gpu.softmax_causal(x), iters, flush=flush)
+def bench_softmax_causal(rng, dtype, b, rows, cols, iters, opt):
     e = gpu.dtype_size(dtype)
+    xs = [_tensor(rng, (b, rows, cols), dtype) for _ in range(_nsets(2 * b * rows * cols * e, opt.rotate))]
+    ms = _time([lambda x=x: gpu.softmax_causal(x) for x in xs], iters, single=opt.single)
     tri = sum(min(r + 1, cols) for r in range(rows))
     nbytes = (b * tri + b * rows * cols) * float(e)   # lower-triangle read + full write
-    return {"op": "softmax_causal", "dtype": dtype, "shape": [b, rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+    return {"op": "softmax_causal", "dtype": dtype, "shape": [b, rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s", "sets": len(xs)}
 
 
-def bench_gelu_add_bias(rng, dtype, rows, cols, iters, flush):
-    x = _tensor(rng, (rows, cols), dtype); bias = _tensor(rng, (cols,), dtype)
-
-    def fn():
-        return gpu.gelu(gpu.add_bias(x, bias))   # the fusion pass turns the pair into one add_bias[gelu] kernel
-    ms = _time(fn, iters, flush=flush)
+def bench_gelu_add_bias(rng, dtype, rows, cols, iters, opt):
     e = gpu.dtype_size(dtype)
+    bias = _tensor(rng, (cols,), dtype)
+    xs = [_tensor(rng, (rows, cols), dtype) for _ in range(_nsets(2 * rows * cols * e, opt.rotate))]
+    # the fusion pass turns add_bias -> gelu into one add_bias[gelu] kernel
+    ms = _time([lambda x=x: gpu.gelu(gpu.add_bias(x, bias)) for x in xs], iters, single=opt.single)
     nbytes = 2.0 * rows * cols * e + cols * e
-    return {"op": "gelu+add_bias", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s"}
+    return {"op": "gelu+add_bias", "dtype": dtype, "shape": [rows, cols], "ms": ms, "work": nbytes, "rate": nbytes / ms / 1e6, "unit": "GB/s", "sets": len(xs)}
 
 
-def bench_attention(rng, dtype, b, h, t, d, causal, iters, flush):
-    q = _tensor(rng, (b, h, t, d), dtype); k = _tensor(rng, (b, h, t, d), dtype); v = _tensor(rng, (b, h, t, d), dtype)
+def bench_attention(rng, dtype, b, h, t, d, causal, iters, opt):
+    e = gpu.dtype_size(dtype)
+    sets = []
+    for _ in range(_nsets(4 * b * h * t * d * e, opt.rotate)):
+        sets.append(tuple(_tensor(rng, (b, h, t, d), dtype) for _ in range(3)))
     fn = gpu.attention_causal if causal else gpu.attention
-    ms = _time(lambda: fn(q, k, v), iters, flush=flush)
+    ms = _time([lambda q=q, k=k, v=v: fn(q, k, v) for q, k, v in sets], iters, single=opt.single)
     flops = 4.0 * b * h * t * t * d * (0.5 if causal else 1.0)
     return {"op": "attention_causal" if causal else "attention", "dtype": dtype, "shape": [b, h, t, d], "ms": ms, "work": flops,
-            "rate": flops / ms / 1e9, "unit": "TFLOP/s (causal-minimal flops)" if causal else "TFLOP/s"}
+            "rate": flops / ms / 1e9, "unit": "TFLOP/s (causal-minimal flops)" if causal else "TFLOP/s", "sets": len(sets)}
 
 
 def main(argv=None):
@@ -104,7 +130,8 @@ def main(argv=None):
     ap.add_argument("--shape", default="")
     ap.add_argument("--dtype", default="")
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--flush-l2", action="store_true", help="evict L2 before every timed launch")
+    ap.add_argument("--single", action="store_true", help="time every launch with its own event pair (includes launch latency)")
+    ap.add_argument("--no-rotate", dest="rotate", action="store_false", help="one buffer set: inputs stay L2-warm between launches")
     args = ap.parse_args(argv)
     gpu.init_backend()
     rng = np.random.default_rng(0)
@@ -116,21 +143,21 @@ def main(argv=None):
             for s in ([shape] if shape else [[8, 1024, 1024, 1024], [8, 2048, 2048, 2048], [8, 4096, 4096, 4096]]):
                 if dt == "float32" and s[1] >= 4096 and not shape:
                     continue  # 1.1 TFLOP on the CUDA-core kernel: run explicitly with --shape
-                out.append(bench_matmul(rng, dt, *s, args.iters, args.flush_l2))
+                out.append(bench_matmul(rng, dt, *s, args.iters, args))
         if args.op in ("all", "gpt2_gemms") and dt != "float32":
             for (m, n, k) in [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072)]:
-                out.append(bench_matmul(rng, dt, 1, m, n, k, args.iters, args.flush_l2))
-            out.append(bench_lm_head(rng, dt, 8192, 50257, 768, args.iters, args.flush_l2))
+                out.append(bench_matmul(rng, dt, 1, m, n, k, args.iters, args))
+            out.append(bench_lm_head(rng, dt, 8192, 50257, 768, args.iters, args))
         if args.op == "lm_head":
-            out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args.flush_l2))
+            out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args))
         if args.op in ("all", "layer_norm"):
-            out.append(bench_layer_norm(rng, dt, *(shape or [8192, 768]), args.iters, args.flush_l2))
+            out.append(bench_layer_norm(rng, dt, *(shape or [8192, 768]), args.iters, args))
         if args.op in ("all", "softmax_causal"):
-            out.append(bench_softmax_causal(rng, dt, *(shape or [96, 1024, 1024]), args.iters, args.flush_l2))
+            out.append(bench_softmax_causal(rng, dt, *(shape or [96, 1024, 1024]), args.iters, args))
         if args.op in ("all", "gelu_add_bias"):
-            out.append(bench_gelu_add_bias(rng, dt, *(shape or [8192, 3072]), args.iters, args.flush_l2))
+            out.append(bench_gelu_add_bias(rng, dt, *(shape or [8192, 3072]), args.iters, args))
         if args.op in ("all", "attention") and dt != "float32":
-            out.append(bench_attention(rng, dt, *(shape or [8, 12, 1024, 64]), True, args.iters, args.flush_l2))
+            out.append(bench_attention(rng, dt, *(shape or [8, 12, 1024, 64]), True, args.iters, args))
         for r in out:
             if not r.get("_printed"):
                 r["_printed"] = True

