@@ -202,8 +202,10 @@ static k::UnOp unop_of(Op op) {
 
 bool g_fused_attention = true;  // false: always compose attention from GEMM + softmax + GEMM
 
-static Status attention_exec(const TensorRec& q, const TensorRec& kk, const TensorRec& v, bool causal, TensorRec* out,
-                             std::shared_ptr<Buffer> out_buf, const Dims& out_shape) {
+// `dst` is the already allocated destination, shaped [.., Tq, dv] with any leading strides (the
+// merge-heads form passes a [B, h, T, dv] view of a [B, T, h*dv] buffer).
+static Status attention_exec(const TensorRec& q, const TensorRec& kk, const TensorRec& v, bool causal, const TensorRec& dst) {
+  const Dims& out_shape = dst.shape;
   // softmax[_causal]((Q K^T) * 1/sqrt(d_k)) V with the score matrix materialised in the storage
   // dtype, as ops.rs:1559-1569 / :1605-1615 compose it; the scale rides in the first GEMM's epilogue.
   DeviceCtx& ctx = DeviceCtx::get();
@@ -228,16 +230,14 @@ static Status attention_exec(const TensorRec& q, const TensorRec& kk, const Tens
     lead(q, &ad.q_b, &ad.q_h, &ad.q_t); lead(kk, &ad.k_b, &ad.k_h, &ad.k_t); lead(v, &ad.v_b, &ad.v_h, &ad.v_t);
     ad.scale = 1.0f / std::sqrt((float)dk); ad.causal = causal;
     if (q.dtype == kk.dtype && q.dtype == v.dtype && k::attention_fused_eligible(ad)) {
-      AG_RETURN_IF_ERROR(alloc_out(out_shape, q.dtype, out, out_buf));
-      ad.o = out->data();
-      lead(*out, &ad.o_b, &ad.o_h, &ad.o_t);
+      ad.o = dst.data();
+      lead(dst, &ad.o_b, &ad.o_h, &ad.o_t);
       AG_LAUNCH(k::attention(ctx.stream, ad));
       return Status::OK();
     }
   }
   TensorRec scores;
   AG_RETURN_IF_ERROR(alloc_out(sshape, q.dtype, &scores, nullptr));
-  AG_RETURN_IF_ERROR(alloc_out(out_shape, q.dtype, out, out_buf));
   if (ctx.dry) return Status::OK();
   (void)tq;
   TensorRec kt = kk;  // K^T as a view
@@ -250,7 +250,7 @@ static Status attention_exec(const TensorRec& q, const TensorRec& kk, const Tens
   AG_LAUNCH(k::matmul(ctx.stream, g1));
   AG_LAUNCH(k::softmax(ctx.stream, scores.view(), causal, scores.view()));
   k::GemmDesc g2;
-  AG_RETURN_IF_ERROR(build_gemm(scores, v, *out, &g2, &keep));
+  AG_RETURN_IF_ERROR(build_gemm(scores, v, dst, &g2, &keep));
   AG_LAUNCH(k::matmul(ctx.stream, g2));
   return Status::OK();
 }
@@ -327,7 +327,18 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
     default: break;
   }
 
-  if (kd.op == Op::FusedAttention) return attention_exec(*in[0], *in[1], *in[2], kd.causal, out, out_buf, node.out_shape);
+  if (kd.op == Op::FusedAttention) {
+    AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
+    TensorRec dst = *out;
+    if (kd.i0 == 1) {
+      // merge-heads form: the node's result is [B, T, h*dv] (or [B*T, h*dv]); attention writes it
+      // through a [B, h, T, dv] view, so no transpose copy follows.
+      const Dims& l = kd.shape;  // logical [B, h, T, dv]
+      dst.shape = l;
+      dst.strides = {l[2] * l[1] * l[3], l[3], l[1] * l[3], 1};
+    }
+    return attention_exec(*in[0], *in[1], *in[2], kd.causal, dst);
+  }
 
   AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
   if (dry) return Status::OK();

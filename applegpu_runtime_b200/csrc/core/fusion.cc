@@ -266,6 +266,30 @@ static void rewrite_attention(Rewriter& rw, uint64_t id) {
   rw.replace({kt->id, mm1->id, sc->id, sm->id, mm2->id}, std::move(fused));
 }
 
+// attention([B,h,T,d]) -> transpose_dims(1,2) -> reshape([B*T, h*d] or [B, T, h*d]): the head merge every
+// transformer block does. The attention node takes over the reshape's id and shape and writes its
+// output in [B, T, h, d] order directly (upstream: two materialising copies, lazy.rs:1891-1917, :2246-2262).
+static void rewrite_attention_merge(Rewriter& rw, uint64_t id) {
+  const OpNode* at = rw.g.get_node(id);
+  if (!at || at->op.op != Op::FusedAttention || at->op.i0 != 0 || at->out_shape.size() != 4) return;
+  const OpNode* tr = rw.sole_consumer(id);
+  if (!tr || tr->op.op != Op::Transpose) return;
+  if (!((tr->op.i0 == 1 && tr->op.i1 == 2) || (tr->op.i0 == 2 && tr->op.i1 == 1))) return;
+  const OpNode* rs = rw.sole_consumer(tr->id);
+  if (!rs || rs->op.op != Op::Reshape) return;
+  const Dims& l = at->out_shape;  // [B, h, T, dv]
+  const Dims& r = rs->out_shape;
+  bool ok = (r.size() == 2 && r[0] == l[0] * l[2] && r[1] == l[1] * l[3]) ||
+            (r.size() == 3 && r[0] == l[0] && r[1] == l[2] && r[2] == l[1] * l[3]);
+  if (!ok) return;
+  OpNode fused = *at;
+  fused.id = rs->id;
+  fused.op.i0 = 1;
+  fused.op.shape = l;
+  fused.out_shape = r;
+  rw.replace({at->id, tr->id, rs->id}, std::move(fused));
+}
+
 // add_bias -> gelu | gelu_exact | relu outside a linear layer: one pass over the tensor instead of two.
 static void rewrite_bias_act(Rewriter& rw, uint64_t id) {
   const OpNode* ab = rw.g.get_node(id);
@@ -303,6 +327,7 @@ std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, con
   if (g_patterns) {
     Rewriter rw(g, cur, keep);
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention(rw, id); }
+    for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention_merge(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_linear(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_embed_add(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_bias_act(rw, id); }

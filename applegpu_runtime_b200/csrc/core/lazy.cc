@@ -174,7 +174,7 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
       if (n->op.has_residual) os << "residual,";
       os << "]";
     }
-    if (n->op.op == Op::FusedAttention) os << (n->op.causal ? "[causal]" : "[full]");
+    if (n->op.op == Op::FusedAttention) os << (n->op.causal ? "[causal" : "[full") << (n->op.i0 == 1 ? ",merge_heads]" : "]");
     if (n->op.op == Op::AddBias && n->op.act != k::Act::None) os << (n->op.act == k::Act::GeluTanh ? "[gelu]" : n->op.act == k::Act::GeluErf ? "[gelu_exact]" : "[relu]");
     if (n->op.op == Op::FusedElementwise) os << "{" << n->op.expr << "}";
     os << dtype_suffix(n->out_dtype) << " " << dims_str(n->out_shape) << "\n";

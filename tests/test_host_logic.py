@@ -186,7 +186,7 @@ def test_graph_rewrites_collapse_the_gpt2_layer(gpu):
     assert logits.shape == [2, 8, 100]
     names = [l.split("_f32")[0] for l in logits.plan().strip().splitlines()]
     assert names[0] == "fused_embed_add"
-    assert names.count("fused_attention[causal]") == 2
+    assert names.count("fused_attention[causal,merge_heads]") == 2   # writes [B, T, h*d] directly: no head-merge copy
     assert names.count("fused_linear[bias,]") == 2                 # QKV projections
     assert names.count("fused_linear[bias,gelu,]") == 2            # FC1 + GELU
     assert names.count("fused_linear[bias,residual,]") == 4        # attention out-proj and FC2, with the residual add
@@ -205,7 +205,7 @@ def test_kv_cache_step_uses_full_attention(gpu):
     logits2, kv2 = gpu.gpt2_forward(m, ids2, kv_cache=kv, last_only=True)
     assert logits2.shape == [2, 100] and kv2[0][0].shape == [2, 4, 6, 16]
     names = [l.split("_f32")[0] for l in logits2.plan().strip().splitlines()]
-    assert names.count("fused_attention[full]") == 2 and names.count("concat_dim1") + names.count("concat_dim0") == 4
+    assert names.count("fused_attention[full,merge_heads]") == 2 and names.count("concat_dim1") + names.count("concat_dim0") == 4
 
 
 def test_free_is_deferred_while_pending_ops_use_a_tensor(gpu):
