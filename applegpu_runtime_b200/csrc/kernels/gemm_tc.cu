@@ -55,13 +55,15 @@ constexpr int kEpiWarps = 8;                       // two warps per TMEM lane qu
 constexpr int kStgPitch = 80;
 constexpr int kStgBytesPerWarp = 32 * kStgPitch;   // 2560
 constexpr int kStgBytes = kEpiWarps * kStgBytesPerWarp;
+constexpr int kBiasSlots = 128;                    // bias values one epilogue warp needs per tile (4 groups x 32 columns)
+constexpr int kBiasBytes = kEpiWarps * kBiasSlots * 2;
 
 template <int BN> struct TcCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + 1024;  // ring + epilogue staging + alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + kBiasBytes + 1024;  // ring + epilogue staging + bias slices + alignment slack
   static constexpr int kTmemCols = 2 * BN;                         // two accumulator buffers
 };
 
@@ -84,32 +86,42 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 // global traffic is issued with 4 lanes per row (64 contiguous bytes per row per instruction) when
 // rows are 16-byte aligned, or 32 consecutive 2-byte elements per instruction otherwise (e.g. the
 // 50257-wide LM head), instead of one row per lane.
+// Residual rows of one 32x32 group, 4 lanes per row, into registers (vector path only). Issued one
+// group ahead of its use so that the global-load latency overlaps the previous group's math and stores.
 template <typename T>
-__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, long long row0, int col0,
-                                               long long c_off, int lane) {
+__device__ __forceinline__ void load_residual_group(const TcParams& p, const T* R, long long row0, int col0, int lane, uint4 (&rpre)[4]) {
+  const int sub_row = lane >> 2, sub_chunk = lane & 3;
+  const int gc = col0 + sub_chunk * 8;
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    long long gm = row0 + it * 8 + sub_row;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (gm < p.m && gc + 8 <= p.n) v = *reinterpret_cast<const uint4*>(R + gm * p.c_row + gc);
+    else if (gm < p.m && gc < p.n) {
+      alignas(16) T tmp[8];
+#pragma unroll
+      for (int e = 0; e < 8; e++) tmp[e] = gc + e < p.n ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
+      v = *reinterpret_cast<uint4*>(tmp);
+    }
+    rpre[it] = v;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, uint4 (&rpre)[4],
+                                               long long row0, int col0, int next_col0, long long c_off, int lane) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
   const int sub_row = lane >> 2, sub_chunk = lane & 3;
-  const bool full_cols = col0 + 32 <= p.n;
 
-  // 1. residual tile -> shared (coalesced)
+  // 1. residual tile -> shared (coalesced). On the vector path the values were fetched one group
+  //    ahead; the next group's fetch is issued here and lands while this group is computed.
   if (R) {
     if (p.vec_ok) {
 #pragma unroll
-      for (int it = 0; it < 4; it++) {
-        int r = it * 8 + sub_row;
-        long long gm = row0 + r;
-        int gc = col0 + sub_chunk * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (gm < p.m && gc + 8 <= p.n) v = *reinterpret_cast<const uint4*>(R + gm * p.c_row + gc);
-        else if (gm < p.m && gc < p.n) {
-          alignas(16) T tmp[8];
-#pragma unroll
-          for (int e = 0; e < 8; e++) tmp[e] = gc + e < p.n ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
-          v = *reinterpret_cast<uint4*>(tmp);
-        }
-        *reinterpret_cast<uint4*>(stg + r * kStgPitch + sub_chunk * 16) = v;
-      }
+      for (int it = 0; it < 4; it++)
+        *reinterpret_cast<uint4*>(stg + (it * 8 + sub_row) * kStgPitch + sub_chunk * 16) = rpre[it];
+      if (next_col0 >= 0) load_residual_group<T>(p, R, row0, next_col0, lane, rpre);
     } else {
       for (int r = 0; r < 32; r++) {
         long long gm = row0 + r;
@@ -137,18 +149,14 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 #pragma unroll
     for (int e = 0; e < 32; e++) { int ci = col0 + e; v[e] *= __ldg(p.b_scales + (ci < p.n ? ci : p.n - 1)); }
   }
-  if (p.bias) {
-    const T* bias = reinterpret_cast<const T*>(p.bias);
-    if (full_cols && p.bias_vec) {
+  if (bias_s) {
+    // this group's 32 bias values were staged in shared memory before the accumulator wait:
+    // every lane reads the same 16 bytes (a broadcast)
 #pragma unroll
-      for (int g = 0; g < 4; g++) {
-        Pack<T> b = ld16(bias + col0 + g * 8);
+    for (int g = 0; g < 4; g++) {
+      Pack<T> b = *reinterpret_cast<const Pack<T>*>(bias_s + g * 8);
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(b.v[e]);
-      }
-    } else {
-#pragma unroll
-      for (int e = 0; e < 32; e++) { int ci = col0 + e; v[e] += Cvt<T>::to(__ldg(bias + (ci < p.n ? ci : p.n - 1))); }
+      for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(b.v[e]);
     }
   }
   switch ((Act)p.act) {
@@ -324,17 +332,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int rem = (int)(t % tiles_per_batch);
       int m0 = (rem % p.tiles_m) * BM;
       int n0 = (rem / p.tiles_m) * BN;
-      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
-      tc_fence_after_sync();
+      // Everything that does not depend on the accumulator is fetched before waiting for it: this
+      // warp's bias slice (into warp-private shared memory) and the first group's residual rows.
+      const int pair = (warp - 2) >> 2;  // the two warps of a lane quarter alternate 32-column groups
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
+      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * kBiasSlots;
+      if (p.bias) {
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          bias_s[gi * 32 + lane] = ci < p.n ? __ldg(bias + ci) : Cvt<T>::from(0.f);
+        }
+      }
+      uint4 rpre[4];
+      if (p.residual && p.vec_ok && n0 + pair * 32 < p.n)
+        load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
+      __syncwarp();
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
+      tc_fence_after_sync();
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
-      const int pair = (warp - 2) >> 2;  // the two warps of a lane quarter alternate 32-column groups
 #pragma unroll 1
-      for (int g = pair; g < BN / 32; g += 2) {
+      for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
-        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, row0, n0 + g * 32, c_off, lane);
+        int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
+        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+                          c_off, lane);
       }
       tc_fence_before_sync();
       __syncwarp();

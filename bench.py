@@ -89,36 +89,6 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def dist_setup(n_gpus):
-    """torch.distributed is plumbing only: a barrier and a max-reduce of the timings."""
-    if n_gpus <= 1 or "RANK" not in os.environ:
-        return None, 0, 1
-    import torch
-    import torch.distributed as dist
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    use_cuda = torch.cuda.is_available()
-    if use_cuda:
-        torch.cuda.set_device(local)
-    dist.init_process_group(backend="nccl" if use_cuda else "gloo")
-    return dist, rank, world
-
-
-def barrier(dist):
-    if dist is not None:
-        dist.barrier()
-
-
-def max_over_ranks(dist, value):
-    if dist is None:
-        return value
-    import torch
-    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
-    t = torch.tensor([value], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
 def cpu_reference_step(weights, cfg, ids_t):
     import torch
     from oracle import torch_ref
@@ -180,7 +150,9 @@ def run_reference(args):
 
 
 def run_b200(args):
-    dist, rank, world = dist_setup(args.gpus)
+    from applegpu_runtime_b200.sharding import RankGroup
+    group = RankGroup.from_env(args.gpus)  # bookkeeping only: barrier + MAX of the timings; no data-path collective
+    rank, world = group.rank, group.world
     import applegpu_runtime_b200 as gpu
     from applegpu_runtime_b200 import _lib
     from applegpu_runtime_b200.gpt2 import GPT2_SMALL
@@ -226,7 +198,7 @@ def run_b200(args):
     # ── value: device-resident ids, CUDA events on the runtime stream, max over ranks ──
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", 0)))
     launches0 = gpu.launch_count()
-    barrier(dist)
+    group.barrier()
     gpu.synchronize()
     sampler.start()
     lib.applegpu_timer_start()
@@ -235,16 +207,16 @@ def run_b200(args):
     ms = float(lib.applegpu_timer_stop_ms())
     gpu.synchronize()
     clocks = sampler.stop()
-    barrier(dist)
+    group.barrier()
     launches = gpu.launch_count() - launches0
-    ms = max_over_ranks(dist, ms)
+    ms = group.max(ms)
     tokens_total = n_tok * args.steps * world
     value = tokens_total / (ms / 1e3)
 
     # ── e2e: pinned host ids in, int32 next-token ids out, every step ──
     for i in range(3):
         step_e2e(i)
-    barrier(dist)
+    group.barrier()
     gpu.synchronize()
     t0 = time.perf_counter()
     lib.applegpu_timer_start()
@@ -252,7 +224,7 @@ def run_b200(args):
         step_e2e(i)
     ms_e2e_dev = float(lib.applegpu_timer_stop_ms())
     wall_e2e = (time.perf_counter() - t0) * 1e3
-    ms_e2e = max_over_ranks(dist, max(ms_e2e_dev, wall_e2e))
+    ms_e2e = group.max(max(ms_e2e_dev, wall_e2e))
     e2e = {"value": tokens_total / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * n_tok * 4, "d2h_bytes_per_step": n_tok * 4,
            "ms_per_step": ms_e2e / args.steps}
 
@@ -289,8 +261,7 @@ def run_b200(args):
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_batch=1)
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    group.close()
 
 
 def main():
