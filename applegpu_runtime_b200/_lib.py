@@ -88,6 +88,7 @@ REFERENCE_SYMBOLS = {
 EXT_SYMBOLS = {
     "applegpu_ffi_upload": (i32, [u64, vp, u64]),
     "applegpu_ffi_read_bytes": (i32, [u64, vp, u64]),
+    "applegpu_ffi_read_bytes_async": (i32, [u64, vp, u64]),
     "applegpu_ffi_from_host": (u64, [vp, u64p, u32, i8]),
     "applegpu_eager_upload": (i32, [u64, vp, u64]),
     "applegpu_eager_download": (i32, [u64, vp, u64]),
@@ -157,6 +158,8 @@ EXT_SYMBOLS = {
     "applegpu_set_matmul_path": (None, [i32]),
     "applegpu_set_attention_path": (None, [i32]),
     "applegpu_pipeline_status": (i32, []),
+    "applegpu_marker_record": (u64, []),
+    "applegpu_marker_wait": (i32, [u64]),
     "applegpu_timer_start": (i32, []),
     "applegpu_timer_stop_ms": (f32, []),
     "applegpu_flush_l2": (i32, []),

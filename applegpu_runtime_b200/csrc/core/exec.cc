@@ -101,7 +101,7 @@ Status upload(const TensorRec& t, const void* host, size_t nbytes) {
   return Status::OK();
 }
 
-Status download(const TensorRec& t, void* host, size_t nbytes) {
+Status download(const TensorRec& t, void* host, size_t nbytes, bool wait) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (ctx.dry) return Status::compute("no CUDA device (dry-run mode)");
   TensorRec c;
@@ -111,6 +111,7 @@ Status download(const TensorRec& t, void* host, size_t nbytes) {
     cudaError_t e = cudaMemcpyAsync(host, c.data(), nbytes, cudaMemcpyDeviceToHost, ctx.stream);
     if (e != cudaSuccess) return Status::compute(std::string("download: ") + cudaGetErrorString(e));
   }
+  if (!wait) return Status::OK();  // stream-ordered: the bytes are defined after the next synchronize
   cudaError_t e = cudaStreamSynchronize(ctx.stream);
   if (e != cudaSuccess) return Status::compute(std::string("synchronize: ") + cudaGetErrorString(e));
   return Status::OK();

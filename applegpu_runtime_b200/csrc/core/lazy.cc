@@ -190,11 +190,11 @@ Status LazyRuntime::get_ptr(uint64_t id, void** ptr) {
   return Status::OK();
 }
 
-Status LazyRuntime::read_bytes(uint64_t id, void* host, size_t nbytes) {
+Status LazyRuntime::read_bytes(uint64_t id, void* host, size_t nbytes, bool wait) {
   if (is_pending(id)) AG_RETURN_IF_ERROR(eval(id));
   const TensorRec* t = tensor(id);
   if (!t || !t->has_meta) return Status::invalid("Tensor " + std::to_string(id) + " not found");
-  return download(*t, host, nbytes);
+  return download(*t, host, nbytes, wait);
 }
 
 Status LazyRuntime::write_bytes(uint64_t id, const void* host, size_t nbytes) {

@@ -105,7 +105,7 @@ Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& inp
                     std::shared_ptr<Buffer> out_buf = nullptr);
 Status make_contiguous(const TensorRec& in, TensorRec* out);
 Status upload(const TensorRec& t, const void* host, size_t nbytes);
-Status download(const TensorRec& t, void* host, size_t nbytes);
+Status download(const TensorRec& t, void* host, size_t nbytes, bool wait = true);
 
 class LazyRuntime {
  public:
@@ -121,7 +121,7 @@ class LazyRuntime {
   Status preallocate_output(uint64_t node_id, void** ptr);
   Status insert_tensor(uint64_t id, TensorRec rec);
   void free_tensor(uint64_t id);  // deferred while pending nodes reference it (lazy.rs:118-144)
-  Status read_bytes(uint64_t id, void* host, size_t nbytes);
+  Status read_bytes(uint64_t id, void* host, size_t nbytes, bool wait = true);
   Status read_f32(uint64_t id, float* out, uint64_t max_elements);
   Status write_bytes(uint64_t id, const void* host, size_t nbytes);
   Status get_ptr(uint64_t id, void** ptr);

@@ -434,6 +434,14 @@ int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nby
   if (!s.ok()) { set_ffi_error("read_bytes failed: " + s.to_string()); return -1; }
   return 0;
 }
+int32_t applegpu_ffi_read_bytes_async(uint64_t tensor_id, void* host_ptr, uint64_t nbytes) {
+  if (!ffi_ready("read_bytes_async")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = st.rt.read_bytes(tensor_id, host_ptr, (size_t)nbytes, /*wait=*/false);
+  if (!s.ok()) { set_ffi_error("read_bytes_async failed: " + s.to_string()); return -1; }
+  return 0;
+}
 uint64_t applegpu_ffi_from_host(const void* host_ptr, const uint64_t* dims, uint32_t ndim, int8_t dtype) {
   DType dt;
   if (!dtype_from_wire(dtype, &dt)) { set_ffi_error("Invalid dtype wire value: " + std::to_string((int)dtype)); return 0; }
@@ -855,6 +863,35 @@ float applegpu_timer_stop_ms(void) {
   float ms = -1.f;
   cudaEventElapsedTime(&ms, g_ev0, g_ev1);
   return ms;
+}
+// Completion markers: a small ring of reusable events (timing disabled: cheaper to record).
+static constexpr int kMarkerSlots = 64;
+static cudaEvent_t g_markers[kMarkerSlots];
+static uint64_t g_marker_seq = 0;
+static std::mutex g_marker_mu;
+uint64_t applegpu_marker_record(void) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry) return 0;
+  std::lock_guard<std::mutex> g(g_marker_mu);
+  uint64_t seq = ++g_marker_seq;
+  cudaEvent_t& ev = g_markers[seq % kMarkerSlots];
+  if (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { ev = nullptr; return 0; }
+  if (cudaEventRecord(ev, ctx.stream) != cudaSuccess) return 0;
+  return seq;
+}
+int32_t applegpu_marker_wait(uint64_t marker) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry || marker == 0) return -1;
+  cudaEvent_t ev;
+  {
+    std::lock_guard<std::mutex> g(g_marker_mu);
+    if (marker > g_marker_seq) return -1;
+    // a slot that has been re-recorded since marks a later point of the same stream: waiting on it
+    // still implies that `marker` completed
+    ev = g_markers[marker % kMarkerSlots];
+  }
+  if (!ev) return -1;
+  return cudaEventSynchronize(ev) == cudaSuccess ? 0 : -1;
 }
 int32_t applegpu_flush_l2(void) {
   DeviceCtx& ctx = DeviceCtx::get();

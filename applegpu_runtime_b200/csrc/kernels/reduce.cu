@@ -261,9 +261,43 @@ __global__ void __launch_bounds__(256) argmax_kernel(const T* __restrict__ in, i
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const T* x = in + row * cols;
     ArgPair best{-INFINITY, 0x7fffffff};
-    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+    // Each thread visits its elements in ascending index order, so a strict '>' keeps the first
+    // maximum; NaNs never compare greater. Rows start on arbitrary element boundaries (a 50257-wide
+    // row is only 2-byte aligned): scalar head up to the first 16-byte boundary, 16-byte packs, scalar tail.
+    constexpr int N = Pack<T>::N;
+    int64_t head = (int64_t)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(x) & 15u)) & 15u) / sizeof(T));
+    if (head > cols) head = cols;
+    for (int64_t j = threadIdx.x; j < head; j += blockDim.x) {
       float f = Cvt<T>::to(x[j]);
-      if (f == f) best = arg_better(best, ArgPair{f, (int)j});
+      if (f > best.v) best = ArgPair{f, (int)j};
+    }
+    const int64_t npacks = (cols - head) / N;
+    const T* xv = x + head;
+    int64_t pk = threadIdx.x;
+    for (; pk + 3 * (int64_t)blockDim.x < npacks; pk += 4 * (int64_t)blockDim.x) {
+      Pack<T> q[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) q[u] = ld16_stream(xv + (pk + u * (int64_t)blockDim.x) * N);
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+#pragma unroll
+        for (int e = 0; e < N; e++) {
+          float f = Cvt<T>::to(q[u].v[e]);
+          if (f > best.v) best = ArgPair{f, (int)(head + (pk + u * (int64_t)blockDim.x) * N + e)};
+        }
+      }
+    }
+    for (; pk < npacks; pk += blockDim.x) {
+      Pack<T> q = ld16_stream(xv + pk * N);
+#pragma unroll
+      for (int e = 0; e < N; e++) {
+        float f = Cvt<T>::to(q.v[e]);
+        if (f > best.v) best = ArgPair{f, (int)(head + pk * N + e)};
+      }
+    }
+    for (int64_t j = head + npacks * N + threadIdx.x; j < cols; j += blockDim.x) {
+      float f = Cvt<T>::to(x[j]);
+      if (f > best.v) best = ArgPair{f, (int)j};
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -30,6 +30,12 @@ extern "C" {
 APPLEGPU_API int32_t applegpu_ffi_upload(uint64_t tensor_id, const void* host_ptr, uint64_t nbytes);
 /* Evaluates if pending, copies out, and waits. Reference: LazyRuntime::read_bytes, lazy.rs:2554-2560. */
 APPLEGPU_API int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nbytes);
+/* Same, but only enqueues the copy on the runtime stream: the bytes are defined after the next
+ * applegpu_ffi_synchronize (or any blocking read). `host_ptr` should be pinned memory (a pageable
+ * buffer makes the copy block) and must stay valid until then. Lets a caller issue the next forward
+ * while the previous result is still in flight. No counterpart in the reference (its buffers are
+ * host-visible unified memory, read in place). */
+APPLEGPU_API int32_t applegpu_ffi_read_bytes_async(uint64_t tensor_id, void* host_ptr, uint64_t nbytes);
 /* alloc + register_tensor + upload in one call; returns the id, 0 on failure. */
 APPLEGPU_API uint64_t applegpu_ffi_from_host(const void* host_ptr, const uint64_t* dims, uint32_t ndim, int8_t dtype);
 APPLEGPU_API int32_t applegpu_eager_upload(uint64_t id, const void* host_ptr, uint64_t nbytes);
@@ -136,6 +142,11 @@ APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
 /* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
 /* CUDA-event stopwatch on the runtime stream. */
+/* A marker is a point in the runtime stream; wait blocks the host until everything enqueued before
+ * the marker (kernels, copies of applegpu_ffi_read_bytes_async) has completed. 0 = failure. Lets a
+ * serving loop keep one step in flight: record after step i, build step i+1, then wait for i. */
+APPLEGPU_API uint64_t applegpu_marker_record(void);
+APPLEGPU_API int32_t applegpu_marker_wait(uint64_t marker);
 APPLEGPU_API int32_t applegpu_timer_start(void);
 APPLEGPU_API float applegpu_timer_stop_ms(void);
 /* Evicts the L2 by streaming writes over a scratch buffer larger than the cache. */
