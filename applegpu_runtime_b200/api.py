@@ -471,8 +471,9 @@ def set_fusion(elementwise_chains=True, patterns=True):
 
 
 def set_matmul_path(mode):
-    """'auto', 'simt' (CUDA-core kernel) or 'tcgen05' (error if operands are not TMA-compatible)."""
-    _L().applegpu_set_matmul_path({"auto": 0, "simt": 1, "tcgen05": 2}[mode])
+    """'auto', 'simt' (CUDA-core kernel), 'tcgen05' (error if operands are not TMA-compatible),
+    'tcgen05_1cta' (single-CTA tiles only) or 'tcgen05_pair' (256 x 256 CTA-pair tiles where the shape allows)."""
+    _L().applegpu_set_matmul_path({"auto": 0, "simt": 1, "tcgen05": 2, "tcgen05_1cta": 3, "tcgen05_pair": 4}[mode])
 
 
 def set_attention_path(mode):

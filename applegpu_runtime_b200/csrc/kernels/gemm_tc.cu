@@ -374,6 +374,187 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
+// ── CTA-pair variant ────────────────────────────────────────────────────────
+// Two CTAs of a cluster compute one 256 x 256 tile with cta_group::2 MMAs. Each CTA loads its own
+// 128 rows of A and only HALF of the B tile (128 of the 256 columns); the tensor cores of the pair
+// exchange the halves. Per CTA and 64-deep K step that is 32 KB written to and read from shared
+// memory instead of 48 KB, which is what bounds the single-CTA kernel (its MMAs wait on shared-
+// memory bandwidth, not on the tensor pipe).
+//   full barriers     live in the even CTA; both CTAs' TMA loads credit their bytes there
+//   empty/tmem_full   one copy per CTA; the even CTA's MMA thread commits to both
+//   tmem_empty        lives in the even CTA; the epilogue warps of both CTAs arrive there
+// Everything else (warp roles, epilogue, bounded waits) is as in the single-CTA kernel.
+constexpr int kPairBN = 256;
+struct PairCfg {
+  static constexpr int kABytes = BM * BK * 2;               // this CTA's 128 rows of A
+  static constexpr int kBBytes = (kPairBN / 2) * BK * 2;    // this CTA's half of B
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + kBiasBytes + 1024;
+  static constexpr int kTmemCols = 2 * kPairBN;
+};
+
+template <bool B_MN, typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
+  using Cfg = PairCfg;
+  constexpr int STAGES = Cfg::kStages;
+  constexpr int BN = kPairBN;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int num_kb = (p.k + BK - 1) / BK;
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;   // tiles of 256 x 256
+  const long long num_tiles = tiles_per_batch * p.batch;
+  const long long first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps); }
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is signalled on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ── TMA producer (both CTAs) ──
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
+        int batch = (int)(t / tiles_per_batch);
+        int rem = (int)(t % tiles_per_batch);
+        int m0 = (rem % p.tiles_m) * (2 * BM) + (int)rank * BM;
+        int n0 = (rem / p.tiles_m) * BN + (int)rank * (BN / 2);
+        int bo = batch / p.batch_inner, bi = batch % p.batch_inner;
+        int a_bo = (p.a_bcast & 1) ? 0 : bo, a_bi = (p.a_bcast & 2) ? 0 : bi;
+        int b_bo = (p.b_bcast & 1) ? 0 : bo, b_bi = (p.b_bcast & 2) ? 0 : bi;
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, 1)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);   // both CTAs' bytes
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+          tma_load_4d_pair(sa, &tmap_a, bar, kb * BK, m0, a_bi, a_bo);
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 128; j++)
+              tma_load_4d_pair(sb + j * (64 * BK * 2), &tmap_b, bar, n0 + j * 64, kb * BK, b_bi, b_bo);
+          } else {
+            tma_load_4d_pair(sb, &tmap_b, bar, kb * BK, n0, b_bi, b_bo);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ── MMA issuer (even CTA only) ──
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, 0, B_MN ? 1 : 0, 2 * BM, BN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, p.status, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; kb++) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; kk++) {
+            uint64_t da = make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+            uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 64 * 128, 1024)
+                               : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+            mma_f16_ss_pair(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          mma_commit_pair(mapa_u32(eb, 0));
+          mma_commit_pair(mapa_u32(eb, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+        mma_commit_pair(mapa_u32(fb, 0));
+        mma_commit_pair(mapa_u32(fb, 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ── epilogue warps (both CTAs; each reads its own 128 accumulator lanes) ──
+    const int quarter = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
+      int batch = (int)(t / tiles_per_batch);
+      int rem = (int)(t % tiles_per_batch);
+      int m0 = (rem % p.tiles_m) * (2 * BM) + (int)rank * BM;
+      int n0 = (rem / p.tiles_m) * BN;
+      const int pair = (warp - 2) >> 2;
+      long long row0 = (long long)m0 + quarter * 32;
+      long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
+      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * kBiasSlots;
+      if (p.bias) {
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          bias_s[gi * 32 + lane] = ci < p.n ? __ldg(bias + ci) : Cvt<T>::from(0.f);
+        }
+      }
+      uint4 rpre[4];
+      if (p.residual && p.vec_ok && n0 + pair * 32 < p.n)
+        load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
+      __syncwarp();
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      if (row0 < p.m) {   // a peer CTA whose rows lie past M has nothing to store
+#pragma unroll 1
+        for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
+          if (n0 + g * 32 >= p.n) break;
+          int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
+          epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+                            c_off, lane);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // Neither CTA may leave (or free TMEM) while its peer can still signal its barriers or run
+  // MMAs against its shared memory.
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+}
+
 // ── host side ───────────────────────────────────────────────────────────────
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -483,13 +664,50 @@ static Status launch_tc(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap
   return Status::OK();
 }
 
+// Clusters of two CTAs (one CTA per SM) that can be resident at once; 0 if the query fails.
+template <bool B_MN, typename T>
+static int pair_clusters() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  auto kern = gemm_tc_pair_kernel<B_MN, T>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes) != cudaSuccess) { cudaGetLastError(); return cached = 0; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * (sm_count() / 2)), 1, 1);
+  cfg.blockDim = dim3(kTcThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  if (n > sm_count() / 2) n = sm_count() / 2;
+  return cached = n;
+}
+
+template <bool B_MN, typename T>
+static Status launch_tc_pair(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, long long num_tiles) {
+  int clusters = pair_clusters<B_MN, T>();
+  if (clusters <= 0) return Status::compute("matmul (tcgen05, CTA pairs): no resident cluster available");
+  int grid = 2 * (int)(num_tiles < clusters ? num_tiles : clusters);
+  gemm_tc_pair_kernel<B_MN, T><<<grid, kTcThreads, PairCfg::kSmemBytes, s>>>(ma, mb, p);
+  AG_CHECK_LAUNCH("matmul (tcgen05, CTA pairs)");
+  return Status::OK();
+}
+
+static int g_force_path = 0;   // 0 auto, 1 simt, 2 tcgen05 (error if not eligible), 3 single-CTA tiles only, 4 CTA-pair tiles where they apply
+
 Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   const bool b_mn = classify_b(d) == 2;
   const long long nb = d.batch * d.batch_inner;
-  // Tile width: 256 when the problem has enough tiles to fill the machine, else 128.
-  long long tiles_m = (d.m + BM - 1) / BM;
+  // Single-CTA tiles, 256 wide when those fill the machine, else 128. The CTA-pair kernel (256 x 256
+  // tiles) is opt-in: on the transformer shapes measured here it runs within a few percent of the
+  // single-CTA kernel (slightly slower), so the simpler kernel stays the default.
+  const long long pair_tiles = ((d.m + 2 * BM - 1) / (2 * BM)) * ((d.n + kPairBN - 1) / kPairBN) * nb;
+  const bool use_pair = g_force_path == 4 && d.m > BM && d.n > 128 && pair_tiles >= sm_count() / 4;
+  long long tiles_m = use_pair ? (d.m + 2 * BM - 1) / (2 * BM) : (d.m + BM - 1) / BM;
   int bn = 256;
-  if (d.n <= 128 || tiles_m * ((d.n + 255) / 256) * nb < (long long)sm_count()) bn = 128;
+  if (!use_pair && (d.n <= 128 || tiles_m * ((d.n + 255) / 256) * nb < (long long)sm_count())) bn = 128;
   long long tiles_n = (d.n + bn - 1) / bn;
   CUtensorMap ma, mb;
   // A broadcast (stride-0) batch level is mapped as extent 1 and its coordinate pinned to 0.
@@ -501,7 +719,7 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
                               (uint64_t)d.a_batch_inner, (uint64_t)d.a_batch, BK, BM));
   if (!b_mn) {
     AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.k, (uint64_t)d.n, b_nbi, b_nbo, (uint64_t)d.b_col,
-                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)bn));
+                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)(use_pair ? kPairBN / 2 : bn)));
   } else {
     AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.n, (uint64_t)d.k, b_nbi, b_nbo, (uint64_t)d.b_row,
                                 (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, 64, BK));
@@ -516,6 +734,10 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
               (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
   p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
   long long num_tiles = tiles_m * tiles_n * nb;
+  if (use_pair) {
+    if (d.dtype == DType::BF16) return b_mn ? launch_tc_pair<true, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair<false, __nv_bfloat16>(s, ma, mb, p, num_tiles);
+    return b_mn ? launch_tc_pair<true, __half>(s, ma, mb, p, num_tiles) : launch_tc_pair<false, __half>(s, ma, mb, p, num_tiles);
+  }
 #define AG_TC(BNV, MN) \
   (d.dtype == DType::BF16 ? launch_tc<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (bn == 256) return b_mn ? AG_TC(256, true) : AG_TC(256, false);
@@ -523,15 +745,17 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
 #undef AG_TC
 }
 
-// 0 auto, 1 simt, 2 tcgen05 (error if not eligible). APPLEGPU_MATMUL_PATH=simt|tcgen05 sets the initial value.
+// APPLEGPU_MATMUL_PATH=simt|tcgen05|tcgen05_1cta|tcgen05_pair sets the initial value of the path switch.
 static int initial_force_path() {
   const char* v = std::getenv("APPLEGPU_MATMUL_PATH");
   if (!v) return 0;
   if (std::strcmp(v, "simt") == 0) return 1;
   if (std::strcmp(v, "tcgen05") == 0) return 2;
+  if (std::strcmp(v, "tcgen05_1cta") == 0) return 3;
+  if (std::strcmp(v, "tcgen05_pair") == 0) return 4;
   return 0;
 }
-static int g_force_path = initial_force_path();
+static const int g_force_path_init = (g_force_path = initial_force_path());
 void set_matmul_path(int mode) { g_force_path = mode; }
 
 const char* matmul_path(const GemmDesc& d) {

@@ -134,7 +134,8 @@ APPLEGPU_API const char* applegpu_device_name(void);
 APPLEGPU_API uint64_t applegpu_launch_count(void);
 /* Which kernel family a matmul of these tensors would take: "tcgen05", "simt", or NULL on error. */
 APPLEGPU_API const char* applegpu_matmul_path(uint64_t a_id, uint64_t b_id, bool eager);
-/* 0 auto, 1 force the CUDA-core kernel, 2 require the tcgen05 kernel. */
+/* 0 auto, 1 force the CUDA-core kernel, 2 require a tcgen05 kernel, 3 tcgen05 with single-CTA
+ * tiles only, 4 tcgen05 with CTA-pair 256 x 256 tiles (cta_group::2) where the shape is large enough. */
 APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
 /* 0 auto (single-kernel attention when head dim is 64 and dtype is f16/bf16), 1 always compose
  * attention from GEMM + softmax + GEMM with materialised scores. */

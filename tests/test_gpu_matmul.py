@@ -73,6 +73,54 @@ def test_matmul_half_tcgen05_b_kmajor(gpu_dev, dtype, m, n, k):
     assert rel_err(got, ref) <= 6e-3
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k,kmajor", [(4096, 768, 256, False), (2100, 2312, 136, False), (4224, 776, 64, False), (8192, 2304, 768, False),
+                                           (4096, 1000, 200, True), (2100, 50257, 64, True)])
+def test_matmul_cta_pair_tiles(gpu_dev, dtype, m, n, k, kmajor):
+    """Shapes large enough for the 256 x 256 CTA-pair kernel (cta_group::2): ragged M (a peer CTA partly or
+    wholly past the last row), ragged N, both B layouts; checked against fp64 and against the single-CTA kernel."""
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k) if kmajor else (k, n)).astype(np.float32)
+    ga, gb = up(gpu_dev, a, dtype), up(gpu_dev, b, dtype)
+    gpu_dev.set_matmul_path("tcgen05_pair")
+    try:
+        got = (ga @ (gpu_dev.transpose(gb) if kmajor else gb)).to_numpy().astype(np.float32)
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    bb = rounded(b, dtype).astype(np.float64)
+    ref = np.matmul(rounded(a, dtype).astype(np.float64), bb.T if kmajor else bb)
+    assert rel_err(got, ref) <= 6e-3
+    gpu_dev.set_matmul_path("tcgen05_1cta")
+    try:
+        one = (ga @ (gpu_dev.transpose(gb) if kmajor else gb)).to_numpy().astype(np.float32)
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    assert rel_err(got, one.astype(np.float64)) <= 1e-3
+
+
+@pytest.fixture
+def pair_path(gpu_dev):
+    gpu_dev.set_matmul_path("tcgen05_pair")
+    yield
+    gpu_dev.set_matmul_path("auto")
+
+
+def test_matmul_cta_pair_batched_and_epilogues(gpu_dev, pair_path):
+    rng = np.random.default_rng(77)
+    a = rng.standard_normal((12, 512, 64)).astype(np.float32); b = rng.standard_normal((12, 64, 520)).astype(np.float32)
+    got = (up(gpu_dev, a, "bfloat16") @ up(gpu_dev, b, "bfloat16")).to_numpy()
+    assert rel_err(got, np.matmul(bf16_round(a).astype(np.float64), bf16_round(b).astype(np.float64))) <= 6e-3
+    x = bf16_round(rng.standard_normal((4100, 128))); w = bf16_round(rng.standard_normal((128, 776)) * 0.1)
+    bias = bf16_round(rng.standard_normal(776)); res = bf16_round(rng.standard_normal((4100, 776)))
+    gx, gw, gb, gr = (up(gpu_dev, t, "bfloat16") for t in (x, w, bias, res))
+    y1 = gpu_dev.gelu(gpu_dev.add_bias(gx @ gw, gb)).to_numpy()
+    ref = R.gelu((x.astype(np.float64) @ w.astype(np.float64) + bias).astype(np.float32))
+    assert rel_err(y1, ref.astype(np.float64)) <= 1.5e-2
+    y2 = (gr + gpu_dev.add_bias(gx @ gw, gb)).to_numpy()
+    assert rel_err(y2, x.astype(np.float64) @ w.astype(np.float64) + bias + res) <= 1.5e-2
+
+
 def test_matmul_half_batched_and_broadcast(gpu_dev):
     rng = np.random.default_rng(5)
     a = rng.standard_normal((6, 200, 64)).astype(np.float32); b = rng.standard_normal((6, 64, 136)).astype(np.float32)
