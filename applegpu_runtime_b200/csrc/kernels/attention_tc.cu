@@ -91,6 +91,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  pdl_wait();      // the prologue above may overlap the tail of the kernel that produces Q, K and V
+  pdl_trigger();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -289,8 +291,8 @@ static Status launch_attention(cudaStream_t s, const CUtensorMap& mq, const CUte
     if (e != cudaSuccess) return cuda_status(e, "attention smem attribute");
     attr_set = true;
   }
-  kern<<<grid, kAttnThreads, kAttnSmem, s>>>(mq, mk, mv, p);
-  AG_CHECK_LAUNCH("attention (tcgen05)");
+  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kAttnThreads), kAttnSmem, s, mq, mk, mv, p);
+  if (le != cudaSuccess) return cuda_status(le, "attention (tcgen05)");
   return Status::OK();
 }
 

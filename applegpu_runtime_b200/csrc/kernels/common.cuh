@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
 #include <cstdint>
+#include <utility>
 #include "kernels.h"
 
 namespace ag { namespace k {
@@ -117,6 +118,29 @@ inline Status cuda_status(cudaError_t e, const char* what) {
   return Status::compute(std::string(what) + ": " + cudaGetErrorString(e));
 }
 #define AG_CHECK_LAUNCH(what) do { cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) return cuda_status(_e, what); } while (0)
+
+// ── programmatic dependent launch ───────────────────────────────────────────
+// Kernels of the forward path are launched so that kernel N+1 may be scheduled while kernel N is
+// still draining: its CTAs run their prologue (barrier init, TMEM allocation, descriptor prefetch)
+// and then block in pdl_wait() until kernel N has completed and its writes are visible. Rules kept
+// by every kernel launched through launch_pdl: all threads call pdl_wait() before the first access
+// to global memory (so completion stays transitive along the stream), and pdl_trigger() follows
+// it (the next kernel is released for scheduling once every CTA of this one has started).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();   // APPLEGPU_PDL=0 turns the launch attribute off (kernels then serialise as usual)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(std::forward<Args>(args))...);
+}
 
 // Grid sizing: a multiple of the SM count, capped by the work available.
 int sm_count();

@@ -8,6 +8,7 @@
 // moves as 16-byte packs through a grid sized from the SM count, and the strided form is
 // kept for views and broadcasts.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace ag { namespace k {
 
@@ -20,6 +21,11 @@ int sm_count() {
     else g_sm_count = 148;
   }
   return g_sm_count;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] { const char* v = std::getenv("APPLEGPU_PDL"); return !(v && v[0] == '0'); }();
+  return on;
 }
 
 // ── index helpers ───────────────────────────────────────────────────────────

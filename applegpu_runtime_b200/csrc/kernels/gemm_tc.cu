@@ -252,6 +252,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();      // everything above overlapped the previous kernel's tail; operands are final from here
+  pdl_trigger();
 
   if (warp == 0) {
     // ── TMA producer ──
@@ -659,8 +661,8 @@ static Status launch_tc(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap
     attr_set = true;
   }
   int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
-  kern<<<grid, kTcThreads, Cfg::kSmemBytes, s>>>(ma, mb, p);
-  AG_CHECK_LAUNCH("matmul (tcgen05)");
+  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kTcThreads), Cfg::kSmemBytes, s, ma, mb, p);
+  if (le != cudaSuccess) return cuda_status(le, "matmul (tcgen05)");
   return Status::OK();
 }
 

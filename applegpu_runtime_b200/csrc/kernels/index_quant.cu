@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(256) embedding_add_kernel(const T* __restrict_
   constexpr int N = Pack<T>::N;
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
+  pdl_wait();
+  pdl_trigger();
   for (int64_t i = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); i < n_idx; i += (int64_t)gridDim.x * wpb) {
     int64_t r = tok[i]; r = r < 0 ? 0 : (r >= vocab ? vocab - 1 : r);
     int64_t q = pos[i]; q = q < 0 ? 0 : (q >= n_pos ? n_pos - 1 : q);
@@ -81,9 +83,10 @@ Status embedding_add(cudaStream_t s, const TView& wte, const TView& tok, const T
   if ((dim * esz) % 16 != 0 || !aligned16(wte.ptr) || !aligned16(wpe.ptr) || !aligned16(out.ptr))
     return Status::compute("embedding_add needs 16-byte aligned rows");
   int grid = grid_for(n_idx, 8, 8);
-  AG_DISPATCH_FLOAT(wte.dtype, T, (embedding_add_kernel<T><<<grid, 256, 0, s>>>((const T*)wte.ptr, (const int32_t*)tok.ptr, (const T*)wpe.ptr,
-      (const int32_t*)pos.ptr, (T*)out.ptr, n_idx, (int)dim, wte.shape[0], wpe.shape[0])));
-  AG_CHECK_LAUNCH("embedding_add");
+  cudaError_t le = cudaSuccess;
+  AG_DISPATCH_FLOAT(wte.dtype, T, (le = launch_pdl(embedding_add_kernel<T>, dim3(grid), dim3(256), 0, s, (const T*)wte.ptr, (const int32_t*)tok.ptr,
+      (const T*)wpe.ptr, (const int32_t*)pos.ptr, (T*)out.ptr, n_idx, (int)dim, wte.shape[0], wpe.shape[0])));
+  if (le != cudaSuccess) return cuda_status(le, "embedding_add");
   return Status::OK();
 }
 

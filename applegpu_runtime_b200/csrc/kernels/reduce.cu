@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
   const int warps_per_block = blockDim.x >> 5;
   const int packs = cols / N;
   const float inv_cols = 1.0f / (float)cols;
+  pdl_wait();
+  pdl_trigger();
   for (int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * warps_per_block) {
     const T* x = in + row * cols;
     float v[ITERS][N];
@@ -97,10 +99,12 @@ static Status layer_norm_t(cudaStream_t s, const TView& in, const TView& gamma, 
     const int threads = 128, wpb = 4;
     int grid = grid_for(rows, wpb, 16);
     int iters = (int)((packs + 31) / 32);
-#define AG_LN(I) layer_norm_warp_kernel<T, I><<<grid, threads, 0, s>>>(x, g, b, y, rows, (int)cols, eps)
+    cudaError_t le = cudaSuccess;
+#define AG_LN(I) le = launch_pdl(layer_norm_warp_kernel<T, I>, dim3(grid), dim3(threads), 0, s, x, g, b, y, rows, (int)cols, eps)
     if (iters <= 1) AG_LN(1); else if (iters <= 2) AG_LN(2); else if (iters <= 3) AG_LN(3); else if (iters <= 4) AG_LN(4);
     else if (iters <= 6) AG_LN(6); else if (iters <= 8) AG_LN(8); else if (iters <= 12) AG_LN(12); else AG_LN(16);
 #undef AG_LN
+    if (le != cudaSuccess) return cuda_status(le, "layer_norm");
   } else {
     int grid = (int)(rows < (int64_t)sm_count() * 8 ? rows : (int64_t)sm_count() * 8);
     layer_norm_block_kernel<T><<<grid, 256, 0, s>>>(x, g, b, y, rows, cols, eps);
