@@ -38,6 +38,21 @@ constexpr int kPBytes = kQ * kKV * 2;                    // 32 KB
 constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * kTileBytes /*K*/ + kTileBytes /*V*/ + kPBytes + 1024;
 constexpr int kAttnTmemCols = 256;                       // S: 128, O block: 64
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2_t(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2_t<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2_t<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 struct AttnParams {
   void* o;
   long long o_b, o_h, o_t;   // element strides of the output
@@ -168,18 +183,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       int lim = p.tk - col_base;
       if (p.causal) { int c = row - col_base + 1; if (c < lim) lim = c; }
       if (lim > kKV) lim = kKV;
-      const bool full = lim >= kKV;
-      // pass 1: row maximum
+      // `full` must be warp-uniform: it selects between code paths that both contain warp-collective
+      // TMEM loads. Rows of one warp can differ (the causal diagonal crosses the warp's 32 rows).
+      const bool full = __all_sync(0xffffffffu, lim >= kKV);
+      // pass 1: row maximum (four independent running maxima keep the dependency chains short)
       float m_blk = -INFINITY;
+      if (full) {
 #pragma unroll 1
-      for (int c = 0; c < kKV / 32; c++) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
-        tmem_ld_wait();
-        if (full) {
+        for (int c = 0; c < kKV / 32; c++) {
+          uint32_t s[32];
+          tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
+          tmem_ld_wait();
+          float m0 = __uint_as_float(s[0]), m1 = __uint_as_float(s[1]), m2 = __uint_as_float(s[2]), m3 = __uint_as_float(s[3]);
 #pragma unroll
-          for (int e = 0; e < 32; e++) m_blk = fmaxf(m_blk, __uint_as_float(s[e]));
-        } else {
+          for (int e = 4; e < 32; e += 4) {
+            m0 = fmaxf(m0, __uint_as_float(s[e])); m1 = fmaxf(m1, __uint_as_float(s[e + 1]));
+            m2 = fmaxf(m2, __uint_as_float(s[e + 2])); m3 = fmaxf(m3, __uint_as_float(s[e + 3]));
+          }
+          m_blk = fmaxf(m_blk, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kKV / 32; c++) {
+          uint32_t s[32];
+          tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
+          tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; e++) if (c * 32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s[e]));
         }
@@ -187,34 +215,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       float m_new = fmaxf(m_run, m_blk * p.scale_log2);
       // a row with nothing visible in this block (only rows past the sequence end) keeps its state
       float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      float alpha = exp2f(m_run - m_use);
+      float alpha = ex2_approx(m_run - m_use);
       // P overwrites the buffer the previous P.V product read
       if (!__all_sync(0xffffffffu, mbar_wait(&p_empty, (j & 1) ^ 1, p.status, 20))) { ok = false; break; }
-      // pass 2: probabilities
-      float l_blk = 0.f;
+      // pass 2: probabilities = exp2(s * scale - m): one FFMA, one MUFU, one add per element; two
+      // elements per convert; 16-byte shared stores in the swizzled K-major layout
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      const float sc = p.scale_log2;
 #pragma unroll 1
       for (int c = 0; c < kKV / 32; c++) {
         uint32_t s[32];
         tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
         tmem_ld_wait();
         float pv[32];
+        if (full) {
 #pragma unroll
-        for (int e = 0; e < 32; e++) {
-          float x = exp2f(__uint_as_float(s[e]) * p.scale_log2 - m_use);
-          if (!full && c * 32 + e >= lim) x = 0.f;
-          pv[e] = x;
-          l_blk += x;
+          for (int e = 0; e < 32; e++) pv[e] = ex2_approx(fmaf(__uint_as_float(s[e]), sc, -m_use));
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e++) {
+            float x = ex2_approx(fmaf(__uint_as_float(s[e]), sc, -m_use));
+            pv[e] = (c * 32 + e < lim) ? x : 0.f;
+          }
         }
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) { l0 += pv[e]; l1 += pv[e + 1]; l2 += pv[e + 2]; l3 += pv[e + 3]; }
         uint8_t* dst = sP + (c >> 1) * (kQ * 128) + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; g++) {
-          Pack<T> o;
-#pragma unroll
-          for (int e = 0; e < 8; e++) o.v[e] = Cvt<T>::from(pv[g * 8 + e]);
+          uint4 o;
+          o.x = pack2_t<T>(pv[g * 8 + 0], pv[g * 8 + 1]); o.y = pack2_t<T>(pv[g * 8 + 2], pv[g * 8 + 3]);
+          o.z = pack2_t<T>(pv[g * 8 + 4], pv[g * 8 + 5]); o.w = pack2_t<T>(pv[g * 8 + 6], pv[g * 8 + 7]);
           int chunk = ((c & 1) * 4 + g) ^ (r & 7);   // 128B swizzle: 16-byte chunk index XOR row % 8
-          *reinterpret_cast<Pack<T>*>(dst + chunk * 16) = o;
+          *reinterpret_cast<uint4*>(dst + chunk * 16) = o;
         }
       }
+      const float l_blk = (l0 + l1) + (l2 + l3);
       // S has been read twice: the next Q K^T may overwrite it
       tc_fence_before_sync();
       __syncwarp();
