@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include <cuda.h>
+#include <cstdlib>
 #include <type_traits>
 
 namespace ag { namespace k {
@@ -31,12 +32,13 @@ int* matmul_status_word();
 
 constexpr int kAttnThreads = 192;
 constexpr int kQ = 128;    // query rows per CTA
-constexpr int kKV = 128;   // keys per block
+constexpr int kKV = 64;    // keys per block
 constexpr int kD = 64;     // head dimension
-constexpr int kTileBytes = 128 * kD * 2;                 // 16 KB: Q, K or V tile
-constexpr int kPBytes = kQ * kKV * 2;                    // 32 KB
-constexpr int kAttnSmem = kTileBytes /*Q*/ + 2 * kTileBytes /*K*/ + kTileBytes /*V*/ + kPBytes + 1024;
-constexpr int kAttnTmemCols = 256;                       // S: 128, O block: 64
+constexpr int kQBytes = kQ * kD * 2;                     // 16 KB
+constexpr int kKVBytes = kKV * kD * 2;                   // 8 KB: one K or V block
+constexpr int kPBytes = kQ * kKV * 2;                    // 16 KB: one P block
+constexpr int kAttnSmem = kQBytes + 2 * kKVBytes /*K*/ + 2 * kKVBytes /*V*/ + 2 * kPBytes + 1024;
+constexpr int kAttnTmemCols = 256;                       // S: 2 x 64, O block: 2 x 64
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -68,14 +70,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full, v_empty, s_full, s_empty, p_full, p_empty, o_full, o_empty;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
   __shared__ uint32_t tmem_base_slot;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + kTileBytes;       // two stages
-  uint8_t* sV = sK + 2 * kTileBytes;
-  uint8_t* sP = sV + kTileBytes;       // two 64-wide k-blocks of 16 KB
+  uint8_t* sK = sQ + kQBytes;            // two stages
+  uint8_t* sV = sK + 2 * kKVBytes;       // two stages
+  uint8_t* sP = sV + 2 * kKVBytes;       // two stages
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (p.tq + kQ - 1) / kQ;
@@ -92,11 +94,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < 2; s++) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    mbar_init(&v_full, 1); mbar_init(&v_empty, 1);
-    mbar_init(&s_full, 1); mbar_init(&s_empty, 4);
-    mbar_init(&p_full, 4); mbar_init(&p_empty, 1);
-    mbar_init(&o_full, 1); mbar_init(&o_empty, 4);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 4); mbar_init(&p_empty[s], 1);
+      mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 4);
+    }
     mbar_fence_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
   }
@@ -105,63 +109,71 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kKV;   // each: two buffers of 64 columns
   pdl_wait();      // the prologue above may overlap the tail of the kernel that produces Q, K and V
   pdl_trigger();
 
   if (warp == 0) {
+    // ── TMA producer: Q once, then K and V blocks through two-deep rings ──
     if (lane == 0) {
-      mbar_expect_tx(&q_full, kTileBytes);
+      mbar_expect_tx(&q_full, kQBytes);
       tma_load_4d(sQ, &tmap_q, &q_full, 0, q0, h, b);
       bool ok = true;
       for (int j = 0; j < n_blocks && ok; j++) {
-        int st = j & 1;
-        if (!mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1, p.status, 11)) { ok = false; break; }
-        mbar_expect_tx(&k_full[st], kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &tmap_k, &k_full[st], 0, j * kKV, h, b);
-        if (!mbar_wait(&v_empty, (j & 1) ^ 1, p.status, 12)) { ok = false; break; }
-        mbar_expect_tx(&v_full, kTileBytes);
-        tma_load_4d(sV, &tmap_v, &v_full, 0, j * kKV, h, b);
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, 11)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], kKVBytes);
+        tma_load_4d(sK + st * kKVBytes, &tmap_k, &k_full[st], 0, j * kKV, h, b);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, 12)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], kKVBytes);
+        tma_load_4d(sV + st * kKVBytes, &tmap_v, &v_full[st], 0, j * kKV, h, b);
       }
     }
   } else if (warp == 1) {
+    // ── MMA issuer. S_j = Q K_j^T runs two blocks ahead of the softmax (two S buffers), O_j = P_j V_j
+    //    is issued as soon as P_j is published and is read back one block later. ──
     if (lane == 0) {
       constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, kQ, kKV);   // S = Q K^T: both K-major, N = 128
+      constexpr uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, kQ, kKV);   // S = Q K^T: both K-major, N = 64
       constexpr uint32_t idesc_o = make_idesc_f16(fmt, 0, 1, kQ, kD);    // O = P V: V is N-major, N = 64
       bool ok = mbar_wait(&q_full, 0, p.status, 13);
       auto issue_s = [&](int j) -> bool {
-        int st = j & 1;
-        if (!mbar_wait(&k_full[st], (j >> 1) & 1, p.status, 14)) return false;
-        if (!mbar_wait(&s_empty, (j & 1) ^ 1, p.status, 15)) return false;
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(&k_full[st], ph, p.status, 14)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, 15)) return false;
         tc_fence_after_sync();
-        uint32_t a = smem_u32(sQ), bb = smem_u32(sK + st * kTileBytes);
+        const uint32_t a = smem_u32(sQ), bb = smem_u32(sK + st * kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < kD / 16; kk++)
-          mma_f16_ss(tmem_s, make_smem_desc_sw128(a + kk * 32, 16, 1024), make_smem_desc_sw128(bb + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          mma_f16_ss(tmem_s + (uint32_t)(st * kKV), make_smem_desc_sw128(a + kk * 32, 16, 1024), make_smem_desc_sw128(bb + kk * 32, 16, 1024),
+                     idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(&k_empty[st]);
-        mma_commit(&s_full);
+        mma_commit(&s_full[st]);
         return true;
       };
       if (ok && n_blocks > 0) ok = issue_s(0);
+      if (ok && n_blocks > 1) ok = issue_s(1);
       for (int j = 0; j < n_blocks && ok; j++) {
-        if (j + 1 < n_blocks) { if (!issue_s(j + 1)) { ok = false; break; } }
-        if (!mbar_wait(&v_full, j & 1, p.status, 16)) { ok = false; break; }
-        if (!mbar_wait(&p_full, j & 1, p.status, 17)) { ok = false; break; }
-        if (!mbar_wait(&o_empty, (j & 1) ^ 1, p.status, 18)) { ok = false; break; }
+        const int st = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (!mbar_wait(&v_full[st], ph, p.status, 16)) { ok = false; break; }
+        if (!mbar_wait(&p_full[st], ph, p.status, 17)) { ok = false; break; }
+        if (!mbar_wait(&o_empty[st], ph ^ 1, p.status, 18)) { ok = false; break; }
         tc_fence_after_sync();
-        uint32_t a = smem_u32(sP), bb = smem_u32(sV);
+        const uint32_t a = smem_u32(sP + st * kPBytes), bb = smem_u32(sV + st * kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < kKV / 16; kk++) {
-          // P: two 64-wide k-blocks of 16 KB, 32 B per K step inside a block.
-          uint64_t da = make_smem_desc_sw128(a + (kk >> 2) * (kQ * 128) + (kk & 3) * 32, 16, 1024);
-          // V: rows are keys (128 B = 64 head dims); a K step of 16 keys is 2048 B.
-          uint64_t db = make_smem_desc_sw128(bb + kk * 2048, 64 * 128, 1024);
-          mma_f16_ss(tmem_o, da, db, idesc_o, kk > 0 ? 1u : 0u);
+          // P: one 64-wide k-block, 32 B per K step. V: rows are keys (128 B = 64 head dims); 16 keys = 2048 B.
+          mma_f16_ss(tmem_o + (uint32_t)(st * kD), make_smem_desc_sw128(a + kk * 32, 16, 1024), make_smem_desc_sw128(bb + kk * 2048, 64 * 128, 1024),
+                     idesc_o, kk > 0 ? 1u : 0u);
         }
-        mma_commit(&v_empty);
-        mma_commit(&p_empty);
-        mma_commit(&o_full);
+        mma_commit(&v_empty[st]);
+        mma_commit(&p_empty[st]);
+        mma_commit(&o_full[st]);
+        // the S buffer of block j was drained into registers at the start of its softmax: refill it
+        if (j + 2 < n_blocks) { if (!issue_s(j + 2)) { ok = false; break; } }
       }
     }
   } else {
@@ -174,118 +186,131 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     float o_acc[kD];
 #pragma unroll
     for (int e = 0; e < kD; e++) o_acc[e] = 0.f;
+    const float sc = p.scale_log2;
     bool ok = true;
-    for (int j = 0; j < n_blocks && ok; j++) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&s_full, j & 1, p.status, 19))) { ok = false; break; }  // warp-uniform exits
+
+    // O = O * alpha + P_jj V_jj, read back from TMEM one block after the product was issued
+    auto o_update = [&](int jj, float a) -> bool {
+      const int st = jj & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&o_full[st], (uint32_t)((jj >> 1) & 1), p.status, 21))) return false;
       tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < kD / 32; c++) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(st * kD + c * 32), ov);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e++) o_acc[c * 32 + e] = fmaf(o_acc[c * 32 + e], a, __uint_as_float(ov[e]));
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_empty[st]);
+      return true;
+    };
+
+    float alpha_prev = 1.f;
+    for (int j = 0; j < n_blocks && ok; j++) {
+      const int st = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[st], ph, p.status, 19))) { ok = false; break; }  // warp-uniform exits
+      tc_fence_after_sync();
+      // the whole 64-column block of this row goes to registers; S can be overwritten right away
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(st * kKV), s0);
+      tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(st * kKV + 32), s1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[st]);
+
       const int col_base = j * kKV;
       // columns this row may see inside the block: [0, lim)
       int lim = p.tk - col_base;
       if (p.causal) { int c = row - col_base + 1; if (c < lim) lim = c; }
       if (lim > kKV) lim = kKV;
-      // `full` must be warp-uniform: it selects between code paths that both contain warp-collective
-      // TMEM loads. Rows of one warp can differ (the causal diagonal crosses the warp's 32 rows).
+      // warp-uniform: selects the mask-free arithmetic below
       const bool full = __all_sync(0xffffffffu, lim >= kKV);
-      // pass 1: row maximum (four independent running maxima keep the dependency chains short)
-      float m_blk = -INFINITY;
+      float m_blk;
       if (full) {
-#pragma unroll 1
-        for (int c = 0; c < kKV / 32; c++) {
-          uint32_t s[32];
-          tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
-          tmem_ld_wait();
-          float m0 = __uint_as_float(s[0]), m1 = __uint_as_float(s[1]), m2 = __uint_as_float(s[2]), m3 = __uint_as_float(s[3]);
+        float m0 = __uint_as_float(s0[0]), m1 = __uint_as_float(s0[1]), m2 = __uint_as_float(s0[2]), m3 = __uint_as_float(s0[3]);
 #pragma unroll
-          for (int e = 4; e < 32; e += 4) {
-            m0 = fmaxf(m0, __uint_as_float(s[e])); m1 = fmaxf(m1, __uint_as_float(s[e + 1]));
-            m2 = fmaxf(m2, __uint_as_float(s[e + 2])); m3 = fmaxf(m3, __uint_as_float(s[e + 3]));
-          }
-          m_blk = fmaxf(m_blk, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+        for (int e = 4; e < 32; e += 4) {
+          m0 = fmaxf(m0, __uint_as_float(s0[e])); m1 = fmaxf(m1, __uint_as_float(s0[e + 1]));
+          m2 = fmaxf(m2, __uint_as_float(s0[e + 2])); m3 = fmaxf(m3, __uint_as_float(s0[e + 3]));
+        }
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          m0 = fmaxf(m0, __uint_as_float(s1[e])); m1 = fmaxf(m1, __uint_as_float(s1[e + 1]));
+          m2 = fmaxf(m2, __uint_as_float(s1[e + 2])); m3 = fmaxf(m3, __uint_as_float(s1[e + 3]));
+        }
+        m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      } else {
+        m_blk = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          if (e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s0[e]));
+          if (32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s1[e]));
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk * sc);
+      // a row with nothing visible so far keeps its state
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = ex2_approx(m_run - m_use);
+
+      // probabilities = exp2(s * scale - m): one FFMA, one MUFU, one add per element, in place
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      if (full) {
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          s0[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s0[e]), sc, -m_use)));
+          s1[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s1[e]), sc, -m_use)));
         }
       } else {
-#pragma unroll 1
-        for (int c = 0; c < kKV / 32; c++) {
-          uint32_t s[32];
-          tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
-          tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; e++) if (c * 32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s[e]));
+        for (int e = 0; e < 32; e++) {
+          float x0 = ex2_approx(fmaf(__uint_as_float(s0[e]), sc, -m_use));
+          float x1 = ex2_approx(fmaf(__uint_as_float(s1[e]), sc, -m_use));
+          s0[e] = __float_as_uint(e < lim ? x0 : 0.f);
+          s1[e] = __float_as_uint(32 + e < lim ? x1 : 0.f);
         }
       }
-      float m_new = fmaxf(m_run, m_blk * p.scale_log2);
-      // a row with nothing visible in this block (only rows past the sequence end) keeps its state
-      float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      float alpha = ex2_approx(m_run - m_use);
-      // P overwrites the buffer the previous P.V product read
-      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty, (j & 1) ^ 1, p.status, 20))) { ok = false; break; }
-      // pass 2: probabilities = exp2(s * scale - m): one FFMA, one MUFU, one add per element; two
-      // elements per convert; 16-byte shared stores in the swizzled K-major layout
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-      const float sc = p.scale_log2;
-#pragma unroll 1
-      for (int c = 0; c < kKV / 32; c++) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(c * 32), s);
-        tmem_ld_wait();
-        float pv[32];
-        if (full) {
 #pragma unroll
-          for (int e = 0; e < 32; e++) pv[e] = ex2_approx(fmaf(__uint_as_float(s[e]), sc, -m_use));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; e++) {
-            float x = ex2_approx(fmaf(__uint_as_float(s[e]), sc, -m_use));
-            pv[e] = (c * 32 + e < lim) ? x : 0.f;
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) { l0 += pv[e]; l1 += pv[e + 1]; l2 += pv[e + 2]; l3 += pv[e + 3]; }
-        uint8_t* dst = sP + (c >> 1) * (kQ * 128) + r * 128;
-#pragma unroll
-        for (int g = 0; g < 4; g++) {
-          uint4 o;
-          o.x = pack2_t<T>(pv[g * 8 + 0], pv[g * 8 + 1]); o.y = pack2_t<T>(pv[g * 8 + 2], pv[g * 8 + 3]);
-          o.z = pack2_t<T>(pv[g * 8 + 4], pv[g * 8 + 5]); o.w = pack2_t<T>(pv[g * 8 + 6], pv[g * 8 + 7]);
-          int chunk = ((c & 1) * 4 + g) ^ (r & 7);   // 128B swizzle: 16-byte chunk index XOR row % 8
-          *reinterpret_cast<uint4*>(dst + chunk * 16) = o;
-        }
+      for (int e = 0; e < 32; e += 4) {
+        l0 += __uint_as_float(s0[e]) + __uint_as_float(s1[e]);         l1 += __uint_as_float(s0[e + 1]) + __uint_as_float(s1[e + 1]);
+        l2 += __uint_as_float(s0[e + 2]) + __uint_as_float(s1[e + 2]); l3 += __uint_as_float(s0[e + 3]) + __uint_as_float(s1[e + 3]);
       }
-      const float l_blk = (l0 + l1) + (l2 + l3);
-      // S has been read twice: the next Q K^T may overwrite it
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty);
+      // P_j overwrites the buffer that P_{j-2} V_{j-2} read
+      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[st], ph ^ 1, p.status, 20))) { ok = false; break; }
+      uint8_t* dst = sP + st * kPBytes + r * 128;
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        const uint32_t* src = g < 4 ? s0 + g * 8 : s1 + (g - 4) * 8;
+        uint4 o;
+        o.x = pack2_t<T>(__uint_as_float(src[0]), __uint_as_float(src[1])); o.y = pack2_t<T>(__uint_as_float(src[2]), __uint_as_float(src[3]));
+        o.z = pack2_t<T>(__uint_as_float(src[4]), __uint_as_float(src[5])); o.w = pack2_t<T>(__uint_as_float(src[6]), __uint_as_float(src[7]));
+        *reinterpret_cast<uint4*>(dst + ((g ^ (r & 7)) * 16)) = o;   // 128B swizzle: 16-byte chunk index XOR row % 8
+      }
       // P is complete for this warp's 32 rows: publish to the tensor core (async proxy)
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
-      l_run = l_run * alpha + l_blk;
+      if (lane == 0) mbar_arrive(&p_full[st]);
+      l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
       m_run = m_new;
-      // O = O * alpha + P V
-      if (!__all_sync(0xffffffffu, mbar_wait(&o_full, j & 1, p.status, 21))) { ok = false; break; }
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < kD / 32; c++) {
-        uint32_t ov[32];
-        tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), ov);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; e++) o_acc[c * 32 + e] = o_acc[c * 32 + e] * alpha + __uint_as_float(ov[e]);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_empty);
+      // the previous block's P V product has had a whole block time to finish
+      if (j > 0) { if (!o_update(j - 1, alpha_prev)) { ok = false; break; } }
+      alpha_prev = alpha;
     }
+    if (ok && n_blocks > 0) ok = o_update(n_blocks - 1, alpha_prev);
     if (ok && row < p.tq) {
       float inv = 1.0f / l_run;
       T* dst = reinterpret_cast<T*>(p.o) + (long long)b * p.o_b + (long long)h * p.o_h + (long long)row * p.o_t;
       if (p.o_vec) {
 #pragma unroll
         for (int g = 0; g < kD / 8; g++) {
-          Pack<T> o;
-#pragma unroll
-          for (int e = 0; e < 8; e++) o.v[e] = Cvt<T>::from(o_acc[g * 8 + e] * inv);
-          st16(dst + g * 8, o);
+          uint4 o;
+          o.x = pack2_t<T>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv); o.y = pack2_t<T>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
+          o.z = pack2_t<T>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv); o.w = pack2_t<T>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
+          *reinterpret_cast<uint4*>(dst + g * 8) = o;
         }
       } else {
 #pragma unroll
