@@ -62,9 +62,10 @@ template <int BN> struct TcCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 192) ? 5 : 6;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + kBiasBytes + 1024;  // ring + epilogue staging + bias slices + alignment slack
-  static constexpr int kTmemCols = 2 * BN;                         // two accumulator buffers
+  static constexpr int kAccStride = (BN == 192) ? 256 : BN;        // column offset of the second accumulator
+  static constexpr int kTmemCols = 2 * kAccStride;                 // two accumulator buffers (a power of two)
 };
 
 // Epilogue staging: each epilogue warp owns a [32 rows x 32 cols] 2-byte tile in shared memory with an
@@ -296,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, p.status, 2)) { ok = false; break; }
         tc_fence_after_sync();
-        uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        uint32_t tmem_d = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
         for (int kb = 0; kb < num_kb; kb++) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
           tc_fence_after_sync();
@@ -354,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       __syncwarp();
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
       tc_fence_after_sync();
-      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
 #pragma unroll 1
       for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
@@ -708,8 +709,21 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   const long long pair_tiles = ((d.m + 2 * BM - 1) / (2 * BM)) * ((d.n + kPairBN - 1) / kPairBN) * nb;
   const bool use_pair = g_force_path == 4 && d.m > BM && d.n > 128 && pair_tiles >= sm_count() / 4;
   long long tiles_m = use_pair ? (d.m + 2 * BM - 1) / (2 * BM) : (d.m + BM - 1) / BM;
+  // Tile width by modelled cost: full waves of the persistent grid times a per-tile cost that grows
+  // with the width (main loop) plus a constant (A traffic, epilogue tail). 192 wins where 256 leaves
+  // a mostly idle last wave (N = 768 or 3072 with M = 8192: 192 or 768 tiles on 148 SMs).
   int bn = 256;
-  if (!use_pair && (d.n <= 128 || tiles_m * ((d.n + 255) / 256) * nb < (long long)sm_count())) bn = 128;
+  if (!use_pair) {
+    long long best = -1;
+    const int cands[3] = {256, 192, 128};
+    for (int c : cands) {
+      if (c != 128 && d.n <= 128) continue;
+      long long tiles = tiles_m * ((d.n + c - 1) / c) * nb;
+      long long waves = (tiles + sm_count() - 1) / sm_count();
+      long long cost = waves * (c + (c == 128 ? 96 : 32));   // narrow tiles move more operand bytes per flop
+      if (best < 0 || cost < best) { best = cost; bn = c; }
+    }
+  }
   long long tiles_n = (d.n + bn - 1) / bn;
   CUtensorMap ma, mb;
   // A broadcast (stride-0) batch level is mapped as extent 1 and its coordinate pinned to 0.
@@ -743,6 +757,7 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
 #define AG_TC(BNV, MN) \
   (d.dtype == DType::BF16 ? launch_tc<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (bn == 256) return b_mn ? AG_TC(256, true) : AG_TC(256, false);
+  if (bn == 192) return b_mn ? AG_TC(192, true) : AG_TC(192, false);
   return b_mn ? AG_TC(128, true) : AG_TC(128, false);
 #undef AG_TC
 }
