@@ -20,5 +20,6 @@ from .api import (  # noqa: E402,F401
     pool_stats, pool_drain, set_pool_watermark, synchronize, quantize_weight, matmul_int8, set_fusion, set_matmul_path, set_attention_path,
     pipeline_status, launch_count, resolve_kernel, profile, profile_report,
 )
-from .gpt2 import gpt2_forward, init_gpt2_weights, load_gpt2_state_dict, GPT2_SMALL, GPT2_LARGE  # noqa: E402,F401
+from .gpt2 import gpt2_forward, init_gpt2_weights, load_gpt2_state_dict, quantize_gpt2_linears, GPT2_SMALL, GPT2_LARGE  # noqa: E402,F401
+from .bert import bert_forward, init_bert_weights, load_bert_state_dict, BERT_BASE  # noqa: E402,F401
 from .generate import generate, greedy_generate  # noqa: E402,F401

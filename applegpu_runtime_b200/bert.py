@@ -1,0 +1,149 @@
+"""BERT encoder forward as a sequence of hot-path ops (HF architecture: post-LN blocks, erf-GELU,
+LayerNorm eps 1e-12, bidirectional attention, learned position and token-type embeddings).
+
+The reference reaches encoder models through its torch backend, which routes every aten op of the
+HF module to one runtime call (python/applegpu_runtime/torch_backend.py:246-1805); this module
+issues the same runtime ops directly, in the style of the reference's models/gpt2.py. nn.Linear
+weights stay [out, in] and are read as K-major GEMM operands through a transpose view (no copy);
+Q, K and V projections are concatenated once at load time so a layer runs one [d, 3d] projection.
+The fusion pass folds bias, erf-GELU and the residual into the GEMM epilogues and the attention
+composition into one node: a layer is 4 GEMMs, 1 attention and 2 layer_norm launches.
+"""
+import numpy as np
+
+from . import api as gpu
+
+BERT_BASE = {"n_layer": 12, "n_head": 12, "n_embd": 768, "d_ff": 3072, "vocab_size": 30522, "n_positions": 512,
+             "type_vocab": 2, "eps": 1e-12}
+
+
+def init_bert_weights(config=None, seed=0, dtype="float32", std=0.02):
+    """Seeded random weights with HF BertModel names and init (N(0, std) matrices and embeddings,
+    zero biases, unit LayerNorm gains)."""
+    cfg = dict(BERT_BASE if config is None else config)
+    rng = np.random.default_rng(seed)
+    d, L, ff = cfg["n_embd"], cfg["n_layer"], cfg["d_ff"]
+    host = {}
+
+    def normal(*shape):
+        return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float32)
+
+    host["embeddings.word_embeddings.weight"] = normal(cfg["vocab_size"], d)
+    host["embeddings.position_embeddings.weight"] = normal(cfg["n_positions"], d)
+    host["embeddings.token_type_embeddings.weight"] = normal(cfg.get("type_vocab", 2), d)
+    host["embeddings.LayerNorm.weight"] = np.ones(d, np.float32)
+    host["embeddings.LayerNorm.bias"] = np.zeros(d, np.float32)
+    for i in range(L):
+        p = f"encoder.layer.{i}"
+        for name, shape in (("attention.self.query", (d, d)), ("attention.self.key", (d, d)), ("attention.self.value", (d, d)),
+                            ("attention.output.dense", (d, d)), ("intermediate.dense", (ff, d)), ("output.dense", (d, ff))):
+            host[f"{p}.{name}.weight"] = normal(*shape)
+            host[f"{p}.{name}.bias"] = np.zeros(shape[0], np.float32)
+        for name in ("attention.output.LayerNorm", "output.LayerNorm"):
+            host[f"{p}.{name}.weight"] = np.ones(d, np.float32)
+            host[f"{p}.{name}.bias"] = np.zeros(d, np.float32)
+    return load_bert_state_dict(host, cfg, dtype=dtype)
+
+
+def _to_host(arr):
+    if hasattr(arr, "detach"):
+        arr = arr.detach().cpu().float().numpy()
+    return np.ascontiguousarray(arr, dtype=np.float32)
+
+
+def load_bert_state_dict(state, config, dtype="float32", head_range=None, ff_range=None):
+    """Uploads a BertModel state dict ({name: numpy / torch array}; a leading "bert." is dropped).
+    The query / key / value projections of a layer are stacked into one [3d, d] weight.
+
+    `head_range` = (h0, h1) and `ff_range` = (f0, f1) keep only a slice of the attention heads and of
+    the feed-forward units: the shard one rank of a tensor-parallel group holds (column-parallel
+    Q/K/V and intermediate, row-parallel output projections; the row-parallel biases stay on the
+    rank that owns head / unit 0 so that the summed partial outputs carry them once)."""
+    cfg = dict(config)
+    d, n_head = cfg["n_embd"], cfg["n_head"]
+    dh = d // n_head
+    h0, h1 = head_range if head_range is not None else (0, n_head)
+    f0, f1 = ff_range if ff_range is not None else (0, cfg["d_ff"])
+    st = {(k[5:] if k.startswith("bert.") else k): v for k, v in state.items()}
+    host = {}
+    for name in ("embeddings.word_embeddings.weight", "embeddings.position_embeddings.weight",
+                 "embeddings.token_type_embeddings.weight", "embeddings.LayerNorm.weight", "embeddings.LayerNorm.bias"):
+        host[name] = _to_host(st[name])
+    for i in range(cfg["n_layer"]):
+        p = f"encoder.layer.{i}"
+        rows = slice(h0 * dh, h1 * dh)
+        host[f"{p}.qkv.weight"] = np.concatenate([_to_host(st[f"{p}.attention.self.{n}.weight"])[rows] for n in ("query", "key", "value")], 0)
+        host[f"{p}.qkv.bias"] = np.concatenate([_to_host(st[f"{p}.attention.self.{n}.bias"])[rows] for n in ("query", "key", "value")], 0)
+        host[f"{p}.attention.output.dense.weight"] = np.ascontiguousarray(_to_host(st[f"{p}.attention.output.dense.weight"])[:, rows])
+        bo = _to_host(st[f"{p}.attention.output.dense.bias"])
+        host[f"{p}.attention.output.dense.bias"] = bo if h0 == 0 else np.zeros_like(bo)
+        host[f"{p}.intermediate.dense.weight"] = np.ascontiguousarray(_to_host(st[f"{p}.intermediate.dense.weight"])[f0:f1])
+        host[f"{p}.intermediate.dense.bias"] = np.ascontiguousarray(_to_host(st[f"{p}.intermediate.dense.bias"])[f0:f1])
+        host[f"{p}.output.dense.weight"] = np.ascontiguousarray(_to_host(st[f"{p}.output.dense.weight"])[:, f0:f1])
+        b2 = _to_host(st[f"{p}.output.dense.bias"])
+        host[f"{p}.output.dense.bias"] = b2 if f0 == 0 else np.zeros_like(b2)
+        for name in ("attention.output.LayerNorm", "output.LayerNorm"):
+            host[f"{p}.{name}.weight"] = _to_host(st[f"{p}.{name}.weight"])
+            host[f"{p}.{name}.bias"] = _to_host(st[f"{p}.{name}.bias"])
+    weights = {}
+    for name, arr in host.items():
+        t = gpu.from_numpy(arr)
+        if dtype != "float32":
+            t = gpu.cast(t, dtype)
+            t.eval()
+        weights[name] = t
+    cfg["local_heads"] = h1 - h0
+    return {"weights": weights, "config": cfg, "dtype": dtype}
+
+
+def _linear(x, w, name):
+    """x [rows, in] @ W^T + b with W stored [out, in] (nn.Linear): the transpose is a view."""
+    return gpu.add_bias(x @ gpu.transpose(w[name + ".weight"]), w[name + ".bias"])
+
+
+def bert_forward(model, input_ids, token_type_ids=None, all_reduce=None):
+    """Last hidden state [B, T, d] of the encoder for int token ids [B, T] (no padding mask: every
+    sequence has full length, as in the benchmark configuration).
+
+    `all_reduce(t) -> t`, when given, sums a [B*T, d] GpuTensor over the tensor-parallel group; it is
+    called on the two row-parallel projections of every layer (after attention.output.dense and after
+    output.dense), before the residual and LayerNorm, which every rank then computes redundantly."""
+    w = model["weights"]
+    cfg = model["config"]
+    n_layer, d = cfg["n_layer"], cfg["n_embd"]
+    heads = cfg.get("local_heads", cfg["n_head"])
+    dh = d // cfg["n_head"]
+    dl = heads * dh                       # width of this rank's Q (= K = V) slice
+    eps = float(cfg.get("eps", 1e-12))
+    ids = np.asarray(input_ids, dtype=np.int64)
+    B, T = ids.shape
+    rows = B * T
+    types = np.zeros_like(ids) if token_type_ids is None else np.asarray(token_type_ids, dtype=np.int64)
+
+    tok = gpu.from_numpy(np.ascontiguousarray(ids.reshape(-1), dtype=np.int32))
+    pos = gpu.from_numpy(np.tile(np.arange(T, dtype=np.int32), B))
+    typ = gpu.from_numpy(np.ascontiguousarray(types.reshape(-1), dtype=np.int32))
+    x = gpu.embedding(w["embeddings.word_embeddings.weight"], tok) + gpu.embedding(w["embeddings.position_embeddings.weight"], pos)
+    x = x + gpu.embedding(w["embeddings.token_type_embeddings.weight"], typ)
+    x = gpu.layer_norm(x, w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)
+
+    for i in range(n_layer):
+        p = f"encoder.layer.{i}"
+        qkv = _linear(x, w, f"{p}.qkv")                                    # [rows, 3*dl]
+
+        def split(j):
+            t = gpu.slice(qkv, dim=1, start=j * dl, end=(j + 1) * dl)
+            return gpu.transpose_dims(gpu.reshape(t, [B, T, heads, dh]), 1, 2)   # [B, heads, T, dh]
+
+        attn = gpu.attention(split(0), split(1), split(2))
+        attn = gpu.reshape(gpu.transpose_dims(attn, 1, 2), [rows, dl])
+        attn = _linear(attn, w, f"{p}.attention.output.dense")
+        if all_reduce is not None:
+            attn = all_reduce(attn)
+        x = gpu.layer_norm(x + attn, w[f"{p}.attention.output.LayerNorm.weight"], w[f"{p}.attention.output.LayerNorm.bias"], eps)
+        h = gpu.gelu_exact(_linear(x, w, f"{p}.intermediate.dense"))
+        h = _linear(h, w, f"{p}.output.dense")
+        if all_reduce is not None:
+            h = all_reduce(h)
+        x = gpu.layer_norm(x + h, w[f"{p}.output.LayerNorm.weight"], w[f"{p}.output.LayerNorm.bias"], eps)
+    return gpu.reshape(x, [B, T, d])

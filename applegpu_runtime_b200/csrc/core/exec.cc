@@ -364,12 +364,40 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
       AG_LAUNCH(k::fused_elementwise(s, kd.prog, views.data(), ov));
       return Status::OK();
     }
-    case Op::Matmul: case Op::FusedLinear: {
+    case Op::Matmul: case Op::FusedLinear: case Op::MatmulInt8: {
       std::vector<TensorRec> keep;
       k::GemmDesc g;
-      AG_RETURN_IF_ERROR(build_gemm(*in[0], *in[1], *out, &g, &keep));
+      size_t idx = 2;
+      const bool int8_w = kd.op == Op::MatmulInt8 || (kd.op == Op::FusedLinear && kd.i1 == 1);
+      if (int8_w) {
+        // x [.., M, K] @ (w_q [N, K] * scales[N])^T: B is K-major int8, the per-channel scales go to the
+        // epilogue. For f16/bf16 activations the weights are widened (exactly) into a pooled [N, K]
+        // buffer of the activation type first, so the product runs on the tensor cores; the int8
+        // copy stays the resident one (half the bytes of a 16-bit weight).
+        TensorRec x, w;
+        AG_RETURN_IF_ERROR(make_contiguous(*in[0], &x));
+        AG_RETURN_IF_ERROR(make_contiguous(*in[1], &w));
+        keep.push_back(x); keep.push_back(w);
+        g.dtype = x.dtype; g.b_dtype = DType::I8;
+        g.a = x.data(); g.b = w.data(); g.c = out->data();
+        g.k = x.shape.back(); g.m = numel_of(x.shape) / (g.k ? g.k : 1); g.n = w.shape[0];
+        g.batch = 1; g.batch_inner = 1;
+        g.a_row = g.k; g.a_col = 1; g.a_batch = 0;
+        g.b_row = 1; g.b_col = g.k; g.b_batch = 0;
+        g.c_row = g.n; g.c_batch = 0;
+        g.ep.b_scales = (const float*)in[2]->data();
+        if ((x.dtype == DType::BF16 || x.dtype == DType::F16) && g.k % 8 == 0 && g.m > 0 && g.n > 0 && !dry) {
+          TensorRec wide;
+          AG_RETURN_IF_ERROR(alloc_out(w.shape, x.dtype, &wide, nullptr));
+          AG_LAUNCH(k::cast(s, w.view(), wide.view()));
+          keep.push_back(wide);
+          g.b = wide.data(); g.b_dtype = x.dtype;
+        }
+        idx = 3;
+      } else {
+        AG_RETURN_IF_ERROR(build_gemm(*in[0], *in[1], *out, &g, &keep));
+      }
       if (kd.op == Op::FusedLinear) {
-        size_t idx = 2;
         g.ep.alpha = kd.f0;
         g.ep.act = kd.act;
         TensorRec tmp;
@@ -380,23 +408,6 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
           g.ep.residual = keep.back().data();
         }
       }
-      AG_LAUNCH(k::matmul(s, g));
-      return Status::OK();
-    }
-    case Op::MatmulInt8: {
-      // x [..,M,K] @ (w_q [N,K] * scales[N])^T ; B is K-major int8, scales applied in the epilogue.
-      TensorRec x, w;
-      AG_RETURN_IF_ERROR(make_contiguous(*in[0], &x));
-      AG_RETURN_IF_ERROR(make_contiguous(*in[1], &w));
-      k::GemmDesc g;
-      g.dtype = x.dtype; g.b_dtype = DType::I8;
-      g.a = x.data(); g.b = w.data(); g.c = out->data();
-      g.k = x.shape.back(); g.m = numel_of(x.shape) / (g.k ? g.k : 1); g.n = w.shape[0];
-      g.batch = 1; g.batch_inner = 1;
-      g.a_row = g.k; g.a_col = 1; g.a_batch = 0;
-      g.b_row = 1; g.b_col = g.k; g.b_batch = 0;
-      g.c_row = g.n; g.c_batch = 0;
-      g.ep.b_scales = (const float*)in[2]->data();
       AG_LAUNCH(k::matmul(s, g));
       return Status::OK();
     }

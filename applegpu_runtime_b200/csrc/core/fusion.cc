@@ -191,11 +191,12 @@ struct Rewriter {
 
 static void rewrite_linear(Rewriter& rw, uint64_t id) {
   const OpNode* mm = rw.g.get_node(id);
-  if (!mm || mm->op.op != Op::Matmul) return;
+  if (!mm || !(mm->op.op == Op::Matmul || mm->op.op == Op::MatmulInt8)) return;
   if (mm->out_dtype == DType::F64) return;
   std::vector<uint64_t> chain{id};
   OpNode fused;
   fused.op.op = Op::FusedLinear;
+  fused.op.i1 = mm->op.op == Op::MatmulInt8 ? 1 : 0;   // inputs are then (x, int8 weights [N,K], scales [N])
   fused.op.f0 = 1.0f;
   fused.inputs = mm->inputs;
   fused.out_shape = mm->out_shape;

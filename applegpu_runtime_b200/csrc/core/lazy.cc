@@ -168,6 +168,7 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
     os << n->op.kernel_name();
     if (n->op.op == Op::FusedLinear) {
       os << "[";
+      if (n->op.i1 == 1) os << "int8,";
       if (n->op.f0 != 1.0f) os << "scale,";
       if (n->op.has_bias) os << "bias,";
       if (n->op.act == k::Act::GeluTanh) os << "gelu,"; else if (n->op.act == k::Act::GeluErf) os << "gelu_exact,"; else if (n->op.act == k::Act::Relu) os << "relu,";

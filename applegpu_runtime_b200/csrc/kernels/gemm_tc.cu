@@ -55,15 +55,19 @@ constexpr int kEpiWarps = 8;                       // two warps per TMEM lane qu
 constexpr int kStgPitch = 80;
 constexpr int kStgBytesPerWarp = 32 * kStgPitch;   // 2560
 constexpr int kStgBytes = kEpiWarps * kStgBytesPerWarp;
-constexpr int kBiasSlots = 128;                    // bias values one epilogue warp needs per tile (4 groups x 32 columns)
-constexpr int kBiasBytes = kEpiWarps * kBiasSlots * 2;
+// Per tile an epilogue warp needs the bias values (2-byte) and, for int8 weights, the per-channel
+// fp32 scales of its own column groups: half of the tile's columns.
+constexpr int epi_slots(int bn) { return bn / 2; }
+constexpr int bias_bytes(int bn) { return kEpiWarps * epi_slots(bn) * 2; }
+constexpr int scale_bytes(int bn) { return kEpiWarps * epi_slots(bn) * 4; }
 
 template <int BN> struct TcCfg {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 192) ? 5 : 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + kBiasBytes + 1024;  // ring + epilogue staging + bias slices + alignment slack
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + bias_bytes(BN) + scale_bytes(BN) + 1024;  // ring + epilogue staging + bias / scale slices + alignment slack
+  static_assert(kSmemBytes + 512 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may use");
   static constexpr int kAccStride = (BN == 192) ? 256 : BN;        // column offset of the second accumulator
   static constexpr int kTmemCols = 2 * kAccStride;                 // two accumulator buffers (a power of two)
 };
@@ -109,7 +113,7 @@ __device__ __forceinline__ void load_residual_group(const TcParams& p, const T* 
 }
 
 template <typename T>
-__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, uint4 (&rpre)[4],
+__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint4 (&rpre)[4],
                                                long long row0, int col0, int next_col0, long long c_off, int lane) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
@@ -146,9 +150,12 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 #pragma unroll
     for (int e = 0; e < 32; e++) v[e] *= p.alpha;
   }
-  if (p.b_scales) {
+  if (scale_s) {
 #pragma unroll
-    for (int e = 0; e < 32; e++) { int ci = col0 + e; v[e] *= __ldg(p.b_scales + (ci < p.n ? ci : p.n - 1)); }
+    for (int g = 0; g < 8; g++) {
+      float4 sc = *reinterpret_cast<const float4*>(scale_s + g * 4);   // same address in every lane: a broadcast
+      v[g * 4 + 0] *= sc.x; v[g * 4 + 1] *= sc.y; v[g * 4 + 2] *= sc.z; v[g * 4 + 3] *= sc.w;
+    }
   }
   if (bias_s) {
     // this group's 32 bias values were staged in shared memory before the accumulator wait:
@@ -340,13 +347,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int pair = (warp - 2) >> 2;  // the two warps of a lane quarter alternate 32-column groups
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
-      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * kBiasSlots;
+      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
       if (p.bias) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
           int ci = n0 + (pair + 2 * gi) * 32 + lane;
           bias_s[gi * 32 + lane] = ci < p.n ? __ldg(bias + ci) : Cvt<T>::from(0.f);
+        }
+      }
+      float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
+      if (p.b_scales) {
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(p.b_scales + ci) : 0.f;
         }
       }
       uint4 rpre[4];
@@ -361,7 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
         int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
-        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
                           c_off, lane);
       }
       tc_fence_before_sync();
@@ -393,7 +408,7 @@ struct PairCfg {
   static constexpr int kBBytes = (kPairBN / 2) * BK * 2;    // this CTA's half of B
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + kBiasBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + bias_bytes(kPairBN) + scale_bytes(kPairBN) + 1024;
   static constexpr int kTmemCols = 2 * kPairBN;
 };
 
@@ -516,13 +531,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int pair = (warp - 2) >> 2;
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
-      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * kBiasSlots;
+      T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
       if (p.bias) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
           int ci = n0 + (pair + 2 * gi) * 32 + lane;
           bias_s[gi * 32 + lane] = ci < p.n ? __ldg(bias + ci) : Cvt<T>::from(0.f);
+        }
+      }
+      float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
+      if (p.b_scales) {
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(p.b_scales + ci) : 0.f;
         }
       }
       uint4 rpre[4];
@@ -538,7 +561,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
           if (n0 + g * 32 >= p.n) break;
           int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
-          epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+          epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
                             c_off, lane);
         }
       }

@@ -103,3 +103,65 @@ def mlp_forward(x, w1, b1, w2, b2):
     """Linear(64,128) -> ReLU -> Linear(128,10): the reference's CPU-runnable config
     (benchmarks/bench_mlp_cpp.py, python/tests/test_cpp_backend.py:121-133)."""
     return F.linear(F.relu(F.linear(x, w1, b1)), w2, b2)
+
+
+def bert_forward(weights, config, input_ids, token_type_ids=None, dtype=torch.float32):
+    """HF-architecture BERT encoder (post-LN, erf-GELU, bidirectional attention, no padding mask),
+    the BERT-base benchmark configuration of the reference's torch backend
+    (python/applegpu_runtime/torch_backend.py:246-1805 routes these ops one by one). weights:
+    {BertModel state-dict name: tensor}; returns the last hidden state [B, T, d]. Pinned against
+    transformers.BertModel through tests/golden/bert_tiny.npz (tests/golden/make_golden_bert.py)."""
+    n_layer, n_head, d = config["n_layer"], config["n_head"], config["n_embd"]
+    eps = config.get("eps", 1e-12)
+    dh = d // n_head
+    B, T = input_ids.shape
+    if token_type_ids is None:
+        token_type_ids = torch.zeros_like(input_ids)
+    w = {k: v.to(dtype) for k, v in weights.items()}
+    pos = torch.arange(T)
+    x = w["embeddings.word_embeddings.weight"][input_ids] + w["embeddings.position_embeddings.weight"][pos][None] + \
+        w["embeddings.token_type_embeddings.weight"][token_type_ids]
+    x = F.layer_norm(x, (d,), w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)
+    for i in range(n_layer):
+        p = f"encoder.layer.{i}"
+
+        def heads(t):
+            return t.view(B, T, n_head, dh).transpose(1, 2)
+
+        q = heads(F.linear(x, w[f"{p}.attention.self.query.weight"], w[f"{p}.attention.self.query.bias"]))
+        k = heads(F.linear(x, w[f"{p}.attention.self.key.weight"], w[f"{p}.attention.self.key.bias"]))
+        v = heads(F.linear(x, w[f"{p}.attention.self.value.weight"], w[f"{p}.attention.self.value.bias"]))
+        scores = torch.matmul(q, k.transpose(-1, -2)) * (1.0 / math.sqrt(dh))
+        attn = torch.matmul(torch.softmax(scores.float(), dim=-1).to(dtype), v)
+        attn = attn.transpose(1, 2).reshape(B, T, d)
+        attn = F.linear(attn, w[f"{p}.attention.output.dense.weight"], w[f"{p}.attention.output.dense.bias"])
+        x = F.layer_norm(x + attn, (d,), w[f"{p}.attention.output.LayerNorm.weight"], w[f"{p}.attention.output.LayerNorm.bias"], eps)
+        h = F.gelu(F.linear(x, w[f"{p}.intermediate.dense.weight"], w[f"{p}.intermediate.dense.bias"]))
+        h = F.linear(h, w[f"{p}.output.dense.weight"], w[f"{p}.output.dense.bias"])
+        x = F.layer_norm(x + h, (d,), w[f"{p}.output.LayerNorm.weight"], w[f"{p}.output.LayerNorm.bias"], eps)
+    return x
+
+
+def init_bert_weights(config, seed=0, std=0.02):
+    """Seeded random BERT weights with the HF names and init (N(0, std) matrices and embeddings, zero
+    biases, unit LayerNorm gains); same generator and draw order as applegpu_runtime_b200.bert."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    d, L, ff = config["n_embd"], config["n_layer"], config["d_ff"]
+    out = {}
+
+    def normal(*shape):
+        return torch.from_numpy((rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float32))
+
+    out["embeddings.word_embeddings.weight"] = normal(config["vocab_size"], d)
+    out["embeddings.position_embeddings.weight"] = normal(config["n_positions"], d)
+    out["embeddings.token_type_embeddings.weight"] = normal(config.get("type_vocab", 2), d)
+    out["embeddings.LayerNorm.weight"] = torch.ones(d); out["embeddings.LayerNorm.bias"] = torch.zeros(d)
+    for i in range(L):
+        p = f"encoder.layer.{i}"
+        for name, shape in (("attention.self.query", (d, d)), ("attention.self.key", (d, d)), ("attention.self.value", (d, d)),
+                            ("attention.output.dense", (d, d)), ("intermediate.dense", (ff, d)), ("output.dense", (d, ff))):
+            out[f"{p}.{name}.weight"] = normal(*shape); out[f"{p}.{name}.bias"] = torch.zeros(shape[0])
+        for name in ("attention.output.LayerNorm", "output.LayerNorm"):
+            out[f"{p}.{name}.weight"] = torch.ones(d); out[f"{p}.{name}.bias"] = torch.zeros(d)
+    return out

@@ -195,6 +195,34 @@ def test_matmul_int8_weights(gpu_dev):
     np.testing.assert_allclose(got, R.matmul_int8(xf, rq, rs), rtol=1e-5, atol=1e-6)
 
 
+def test_matmul_int8_weights_on_tensor_cores_with_fused_epilogue(gpu_dev):
+    """GPT-2-large-like linear: bf16 activations, per-output-channel int8 weights [N, K]; bias, GELU and
+    the residual ride in the epilogue of the same GEMM (weights widened exactly to bf16 on the way)."""
+    rng = np.random.default_rng(10)
+    m, k, n = 512, 320, 1288
+    x = bf16_round(rng.standard_normal((m, k))); w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    bias = bf16_round(rng.standard_normal(n) * 0.1); res = bf16_round(rng.standard_normal((m, n)))
+    q, s = gpu_dev.quantize_weight(gpu_dev.from_numpy(w))
+    rq, rs = R.quantize_rows(w)
+    assert np.array_equal(q.to_numpy(), rq) and np.array_equal(s.to_numpy(), rs)      # quantisation itself is bit-exact
+    gx, gb, gr = up(gpu_dev, x, "bfloat16"), up(gpu_dev, bias, "bfloat16"), up(gpu_dev, res, "bfloat16")
+    y = gpu_dev.gelu(gpu_dev.add_bias(gpu_dev.matmul_int8(gx, q, s), gb))
+    assert "fused_linear[int8,bias,gelu,]" in y.plan()
+    wd = rq.astype(np.float64) * rs.astype(np.float64)[:, None]
+    ref = R.gelu((x.astype(np.float64) @ wd.T + bias).astype(np.float32)).astype(np.float64)
+    assert rel_err(y.to_numpy(), ref) <= 1.5e-2
+    y2 = gr + gpu_dev.add_bias(gpu_dev.matmul_int8(gx, q, s), gb)
+    assert "fused_linear[int8,bias,residual,]" in y2.plan()
+    assert rel_err(y2.to_numpy(), x.astype(np.float64) @ wd.T + bias + res) <= 1.5e-2
+    # the CUDA-core kernel computes the same product
+    gpu_dev.set_matmul_path("simt")
+    try:
+        y3 = gpu_dev.matmul_int8(gx, q, s).to_numpy()
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    assert rel_err(gpu_dev.matmul_int8(gx, q, s).to_numpy(), y3.astype(np.float64)) <= 8e-3
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])

@@ -254,3 +254,27 @@ def test_pool_size_classes_and_stats_api(gpu):
     for k in ("hits", "misses", "pooled_bytes", "bucket_count"):   # pool.rs:100-108
         assert k in s
     assert gpu.memory_usage() >= 0 and gpu.tensor_count() >= 0
+
+
+def test_graph_rewrites_collapse_the_bert_layer(gpu):
+    cfg = {"n_layer": 2, "n_head": 4, "n_embd": 64, "d_ff": 128, "vocab_size": 100, "n_positions": 32, "type_vocab": 2, "eps": 1e-12}
+    model = gpu.init_bert_weights(cfg, seed=0)
+    h = gpu.bert_forward(model, np.arange(16).reshape(2, 8))
+    assert h.shape == [2, 8, 64]
+    names = [l.split("_f32")[0] for l in h.plan().strip().splitlines()]
+    assert names.count("fused_attention[full,merge_heads]") == 2
+    assert names.count("fused_linear[bias,]") == 2 and names.count("fused_linear[bias,gelu_exact,]") == 2
+    assert names.count("fused_linear[bias,residual,]") == 4 and names.count("layer_norm") == 5
+    # a tensor-parallel shard keeps half of the heads and of the feed-forward units
+    host = {k: np.zeros(v.shape, np.float32) for k, v in model["weights"].items() if "qkv" not in k}
+    for i in range(2):
+        for n in ("query", "key", "value"):
+            host[f"encoder.layer.{i}.attention.self.{n}.weight"] = np.zeros((64, 64), np.float32)
+            host[f"encoder.layer.{i}.attention.self.{n}.bias"] = np.zeros(64, np.float32)
+    shard = gpu.load_bert_state_dict(host, cfg, head_range=(2, 4), ff_range=(64, 128))
+    assert shard["config"]["local_heads"] == 2
+    assert shard["weights"]["encoder.layer.0.qkv.weight"].shape == [96, 64]
+    assert shard["weights"]["encoder.layer.0.attention.output.dense.weight"].shape == [64, 32]
+    assert shard["weights"]["encoder.layer.0.intermediate.dense.weight"].shape == [64, 64]
+    assert shard["weights"]["encoder.layer.0.output.dense.weight"].shape == [64, 64]
+    assert gpu.bert_forward(shard, np.arange(16).reshape(2, 8), all_reduce=lambda t: t).shape == [2, 8, 64]

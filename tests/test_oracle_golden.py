@@ -118,3 +118,16 @@ def test_msl_oracle_composes_to_the_same_gpt2_block():
     qt, kt, vt = [t.view(T, h, dh).transpose(0, 1) for t in qkv_t.split(d, -1)]
     ref = torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
     np.testing.assert_allclose(out, ref.numpy(), atol=1e-5)
+
+
+def test_torch_oracle_reproduces_hf_bert_hidden_states():
+    """oracle/torch_ref.bert_forward against transformers' BertModel on CPU (tests/golden/bert_tiny.npz)."""
+    import torch
+    from oracle import torch_ref
+    z = np.load(os.path.join(HERE, "golden", "bert_tiny.npz"))
+    c = z["config"].tolist()
+    cfg = dict(n_layer=c[0], n_head=c[1], n_embd=c[2], d_ff=c[3], vocab_size=c[4], n_positions=c[5], type_vocab=c[6], eps=1e-12)
+    w = {k[2:]: torch.from_numpy(z[k]) for k in z.files if k.startswith("w:")}
+    with torch.no_grad():
+        h = torch_ref.bert_forward(w, cfg, torch.from_numpy(z["ids"]), torch.from_numpy(z["types"])).numpy()
+    np.testing.assert_allclose(h, z["hidden"], atol=1e-5)
