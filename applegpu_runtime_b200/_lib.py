@@ -158,6 +158,7 @@ EXT_SYMBOLS = {
     "applegpu_set_matmul_path": (None, [i32]),
     "applegpu_set_attention_path": (None, [i32]),
     "applegpu_pipeline_status": (i32, []),
+    "applegpu_eager_execute_graph": (i32, [vp, u32, vp, u32, vp, u32, vp, vp]),
     "applegpu_marker_record": (u64, []),
     "applegpu_marker_wait": (i32, [u64]),
     "applegpu_timer_start": (i32, []),

@@ -658,6 +658,140 @@ uint64_t applegpu_eager_find_by_data_ptr(const uint8_t* ptr) {
   return st.rt.find_by_data_ptr(ptr);
 }
 
+// ── compiled-graph executor ─────────────────────────────────────────────────
+// One call runs a whole serialized op list on the eager runtime (reference: eager_ffi.rs:661-708,
+// compiled_graph.rs:7-9,44-58,65-199). Wire format per op, little-endian:
+//   op_code u8, n_inputs u8, inputs [u16; n] (indices into the node table: graph inputs first, then
+//   one entry per executed op), out_ndim u8, out_dims [u64; ndim], out_dtype u8, params_len u8,
+//   params [f32; plen].
+// Op codes as upstream: 0 add, 1 sub, 2 mul, 3 div, 4 matmul, 5 relu, 6 neg, 7 threshold_backward
+// (param 0 = threshold), 8 scalar_mul (param 0 = scale), 9 mean_all, 10 sum_dim (params dim,
+// keepdim), 11 transpose (last two dims, a view), 12 view (contiguous strides of out_dims), 13 addmm
+// (bias, m1, m2), 255 identity. Non-contiguous matmul operands are first copied, as upstream does
+// with scalar_mul(x, 1.0). Unlike upstream every read of the byte stream is bounds-checked.
+namespace {
+struct GraphCursor {
+  const uint8_t* p; size_t n; size_t i = 0; bool ok = true;
+  bool need(size_t k) { if (i + k > n) { ok = false; return false; } return true; }
+  uint8_t u8() { if (!need(1)) return 0; return p[i++]; }
+  uint16_t u16() { if (!need(2)) return 0; uint16_t v; std::memcpy(&v, p + i, 2); i += 2; return v; }
+  uint64_t u64() { if (!need(8)) return 0; uint64_t v; std::memcpy(&v, p + i, 8); i += 8; return v; }
+  float f32() { if (!need(4)) return 0.f; float v; std::memcpy(&v, p + i, 4); i += 4; return v; }
+};
+struct GraphSlot { uint64_t id; uint8_t* ptr; bool contiguous; };
+}  // namespace
+
+int32_t applegpu_eager_execute_graph(const uint8_t* ops_data, uint32_t ops_len, const uint64_t* input_tids, uint32_t n_inputs,
+                                     const uint16_t* output_indices, uint32_t n_outputs, uint64_t* out_tids, uint8_t** out_ptrs) {
+  if (!eager_ready()) return -1;
+  std::vector<GraphSlot> nodes;
+  {
+    EagerState& st = eager_state();
+    std::lock_guard<std::mutex> g(st.mu);
+    for (uint32_t k = 0; k < n_inputs; k++) {
+      const TensorRec* t = st.rt.tensor(input_tids[k]);
+      nodes.push_back({input_tids[k], t ? static_cast<uint8_t*>(t->data()) : nullptr, t ? t->contiguous() : true});
+    }
+  }
+  auto fail = [](const std::string& m) { set_eager_error("compiled graph failed: " + m); return -1; };
+  GraphCursor c{ops_data, ops_len};
+  while (c.i < c.n) {
+    uint8_t code = c.u8();
+    uint8_t nin = c.u8();
+    std::vector<size_t> idx;
+    for (int k = 0; k < nin; k++) idx.push_back(c.u16());
+    uint8_t ondim = c.u8();
+    std::vector<uint64_t> odims;
+    for (int k = 0; k < ondim; k++) odims.push_back(c.u64());
+    (void)c.u8();  // out_dtype: informational, results take their dtype from the operands
+    uint8_t plen = c.u8();
+    std::vector<float> params;
+    for (int k = 0; k < plen; k++) params.push_back(c.f32());
+    if (!c.ok) return fail("truncated op stream");
+    for (size_t ix : idx) if (ix >= nodes.size()) return fail("input index " + std::to_string(ix) + " out of range");
+    auto need_inputs = [&](size_t k) { return idx.size() >= k; };
+    auto in = [&](size_t k) -> GraphSlot { return nodes[idx[k]]; };
+    // a contiguous copy of a strided operand (upstream: scalar_mul(x, 1.0))
+    auto contiguous_id = [&](GraphSlot s, uint64_t* id) -> bool {
+      if (s.contiguous) { *id = s.id; return true; }
+      uint64_t cid = 0;
+      if (!applegpu_eager_scalar_mul(s.id, 1.0f, &cid) && cid == 0) return false;
+      *id = cid; return true;
+    };
+    if (code == 255) { if (!need_inputs(1)) return fail("identity needs one input"); nodes.push_back(in(0)); continue; }
+    uint64_t oid = 0; uint8_t* optr = nullptr; bool ocontig = true;
+    switch (code) {
+      case 0: case 1: case 2: case 3: {
+        if (!need_inputs(2)) return fail("binary op needs two inputs");
+        uint64_t a = in(0).id, b = in(1).id;
+        optr = code == 0 ? applegpu_eager_add(a, b, &oid) : code == 1 ? applegpu_eager_sub(a, b, &oid)
+             : code == 2 ? applegpu_eager_mul(a, b, &oid) : applegpu_eager_div(a, b, &oid);
+        break;
+      }
+      case 4: {
+        if (!need_inputs(2)) return fail("matmul needs two inputs");
+        uint64_t a, b;
+        if (!contiguous_id(in(0), &a) || !contiguous_id(in(1), &b)) return -1;
+        optr = applegpu_eager_matmul(a, b, &oid);
+        break;
+      }
+      case 13: {
+        if (!need_inputs(3)) return fail("addmm needs three inputs");
+        uint64_t m1, m2, mm = 0;
+        if (!contiguous_id(in(1), &m1) || !contiguous_id(in(2), &m2)) return -1;
+        if (!applegpu_eager_matmul(m1, m2, &mm) && mm == 0) return -1;
+        optr = applegpu_eager_add(mm, in(0).id, &oid);
+        break;
+      }
+      case 5: if (!need_inputs(1)) return fail("relu needs one input"); optr = applegpu_eager_relu(in(0).id, &oid); break;
+      case 6: if (!need_inputs(1)) return fail("neg needs one input"); optr = applegpu_eager_neg(in(0).id, &oid); break;
+      case 7:
+        if (!need_inputs(2)) return fail("threshold_backward needs two inputs");
+        optr = applegpu_eager_threshold_backward(in(0).id, in(1).id, params.empty() ? 0.f : params[0], &oid);
+        break;
+      case 8: if (!need_inputs(1)) return fail("scalar_mul needs one input"); optr = applegpu_eager_scalar_mul(in(0).id, params.empty() ? 1.f : params[0], &oid); break;
+      case 9: if (!need_inputs(1)) return fail("mean_all needs one input"); optr = applegpu_eager_mean_all(in(0).id, &oid); break;
+      case 10:
+        if (!need_inputs(1)) return fail("sum_dim needs one input");
+        optr = applegpu_eager_sum_dim(in(0).id, params.empty() ? 0 : (int64_t)params[0], params.size() > 1 && params[1] != 0.f, &oid);
+        break;
+      case 11: case 12: {
+        if (!need_inputs(1)) return fail("view needs one input");
+        std::vector<uint64_t> shape, strides;
+        if (code == 11) {
+          EagerState& st = eager_state();
+          std::lock_guard<std::mutex> g(st.mu);
+          const TensorRec* t = st.rt.tensor(in(0).id);
+          if (!t) return fail("Tensor " + std::to_string(in(0).id) + " not found");
+          if (t->shape.size() < 2) return fail("Invalid tensor: transpose requires 2D+");
+          for (int64_t d : t->shape) shape.push_back((uint64_t)d);
+          for (int64_t s : t->strides) strides.push_back((uint64_t)s);
+          std::swap(shape[shape.size() - 2], shape[shape.size() - 1]);
+          std::swap(strides[strides.size() - 2], strides[strides.size() - 1]);
+          ocontig = false;
+        } else {
+          shape = odims;
+          strides.assign(shape.size(), 1);
+          for (int k = (int)shape.size() - 2; k >= 0; k--) strides[k] = strides[k + 1] * shape[k + 1];
+        }
+        optr = applegpu_eager_create_view(in(0).id, shape.data(), strides.data(), (uint32_t)shape.size(), 0, &oid);
+        break;
+      }
+      default: return fail("unsupported op: " + std::to_string((int)code));
+    }
+    if (oid == 0) return -1;  // the op recorded its own error text
+    nodes.push_back({oid, optr, ocontig});
+  }
+  uint32_t done = 0;
+  for (; done < n_outputs; done++) {
+    size_t ix = output_indices[done];
+    if (ix >= nodes.size()) return fail("output " + std::to_string(ix) + " out of range");
+    if (out_tids) out_tids[done] = nodes[ix].id;
+    if (out_ptrs) out_ptrs[done] = nodes[ix].ptr;
+  }
+  return (int32_t)done;
+}
+
 uint8_t* applegpu_eager_gelu_exact(uint64_t x, uint64_t* o) { return eager_run(mk(Op::GeluExact), {x}, o); }
 uint8_t* applegpu_eager_softmax_causal(uint64_t x, uint64_t* o) { return eager_run(mk(Op::SoftmaxCausal), {x}, o); }
 uint8_t* applegpu_eager_add_bias(uint64_t x, uint64_t b, uint64_t* o) { return eager_run(mk(Op::AddBias), {x, b}, o); }

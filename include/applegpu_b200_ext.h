@@ -143,6 +143,13 @@ APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
 /* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
 /* CUDA-event stopwatch on the runtime stream. */
+/* Compiled-graph executor: runs a serialized op list on the eager runtime in one call and returns the
+ * number of outputs written (-1 on error, text in applegpu_eager_last_error). Replaces
+ * applegpu_eager_execute_graph of the reference (crates/core/src/eager_ffi.rs:661-708; wire format and
+ * op codes of crates/core/src/compiled_graph.rs:7-9,44-58), which its torch.compile backend calls
+ * (python/applegpu_runtime/compile_backend.py). out_ptrs receive device pointers. */
+APPLEGPU_API int32_t applegpu_eager_execute_graph(const uint8_t* ops_data, uint32_t ops_len, const uint64_t* input_tids, uint32_t n_inputs,
+                                                  const uint16_t* output_indices, uint32_t n_outputs, uint64_t* out_tids, uint8_t** out_ptrs);
 /* A marker is a point in the runtime stream; wait blocks the host until everything enqueued before
  * the marker (kernels, copies of applegpu_ffi_read_bytes_async) has completed. 0 = failure. Lets a
  * serving loop keep one step in flight: record after step i, build step i+1, then wait for i. */

@@ -233,3 +233,70 @@ def test_allocation_failure_is_reported_not_fatal(lib):
     assert b"Failed to allocate GPU buffer" in lib.applegpu_eager_last_error()
     assert lib.applegpu_eager_alloc(d, nd, F32, ctypes.byref(tid))     # the runtime carries on
     lib.applegpu_eager_free(tid.value)
+
+
+# ── compiled-graph executor (crates/core/src/compiled_graph.rs wire format) ──
+def _op(code, inputs, out_dims=(), params=(), dtype=F32):
+    import struct
+    b = struct.pack("<BB", code, len(inputs)) + b"".join(struct.pack("<H", i) for i in inputs)
+    b += struct.pack("<B", len(out_dims)) + b"".join(struct.pack("<Q", d) for d in out_dims)
+    b += struct.pack("<BB", dtype, len(params)) + b"".join(struct.pack("<f", p) for p in params)
+    return b
+
+
+def _run_graph(lib, ops, input_ids, outputs):
+    buf = (ctypes.c_uint8 * len(ops)).from_buffer_copy(ops)
+    tids = (ctypes.c_uint64 * len(input_ids))(*input_ids)
+    oix = (ctypes.c_uint16 * len(outputs))(*outputs)
+    out_t = (ctypes.c_uint64 * len(outputs))()
+    out_p = (ctypes.c_void_p * len(outputs))()
+    n = lib.applegpu_eager_execute_graph(buf, len(ops), tids, len(input_ids), oix, len(outputs), out_t, out_p)
+    return n, list(out_t), list(out_p)
+
+
+def test_compiled_graph_runs_an_mlp_forward_and_backward_fragment(lib):
+    """Linear -> ReLU -> Linear and a ReLU-backward fragment, the op mix torch.compile hands the reference
+    (addmm, transpose views, relu, threshold_backward, scalar_mul, sum_dim, mean_all, view, identity)."""
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((32, 64)).astype(np.float32)
+    w1 = (rng.standard_normal((128, 64)) * 0.1).astype(np.float32); b1 = rng.standard_normal(128).astype(np.float32)
+    w2 = (rng.standard_normal((10, 128)) * 0.1).astype(np.float32); b2 = rng.standard_normal(10).astype(np.float32)
+    ids = [eager_tensor(lib, a)[0] for a in (x, w1, b1, w2, b2)]      # node table slots 0..4
+    ops = b"".join([
+        _op(11, [1], (64, 128)),                  # 5: w1^T (view)
+        _op(13, [2, 0, 5], (32, 128)),            # 6: addmm(b1, x, w1^T)
+        _op(5, [6], (32, 128)),                   # 7: relu
+        _op(11, [3], (128, 10)),                  # 8: w2^T
+        _op(13, [4, 7, 8], (32, 10)),             # 9: logits
+        _op(9, [9], (1,)),                        # 10: mean_all
+        _op(7, [7, 6], (32, 128), (0.0,)),        # 11: threshold_backward(grad = h, input = pre-activation)
+        _op(10, [11], (128,), (0.0, 0.0)),        # 12: sum over dim 0
+        _op(8, [12], (128,), (0.5,)),             # 13: scalar_mul
+        _op(12, [13], (8, 16)),                   # 14: view
+        _op(255, [14]),                           # 15: identity
+        _op(1, [9, 9], (32, 10)),                 # 16: sub -> zeros
+        _op(6, [16], (32, 10)),                   # 17: neg
+    ])
+    n, out_ids, out_ptrs = _run_graph(lib, ops, ids, [9, 10, 15, 17, 0])
+    assert n == 5, lib.applegpu_eager_last_error()
+    assert all(out_ptrs[:4]) and out_ids[4] == ids[0]                 # an input may be returned as an output
+    pre = x @ w1.T + b1
+    h = np.maximum(pre, 0)
+    logits = h @ w2.T + b2
+    np.testing.assert_allclose(eager_read(lib, out_ids[0]), logits, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(eager_read(lib, out_ids[1]), [logits.mean()], rtol=1e-4, atol=1e-5)
+    g = np.where(pre > 0, h, 0).sum(0) * 0.5
+    np.testing.assert_allclose(eager_read(lib, out_ids[2]), g.reshape(8, 16), rtol=1e-4, atol=1e-4)
+    assert not eager_read(lib, out_ids[3]).any()
+
+
+def test_compiled_graph_rejects_malformed_streams(lib):
+    x = eager_tensor(lib, np.ones((2, 2), np.float32))[0]
+    n, _, _ = _run_graph(lib, _op(5, [0], (2, 2))[:-1], [x], [1])                  # truncated
+    assert n == -1 and b"truncated" in lib.applegpu_eager_last_error()
+    n, _, _ = _run_graph(lib, _op(5, [3], (2, 2)), [x], [1])                       # input index past the table
+    assert n == -1 and b"out of range" in lib.applegpu_eager_last_error()
+    n, _, _ = _run_graph(lib, _op(99, [0], (2, 2)), [x], [1])
+    assert n == -1 and b"unsupported op: 99" in lib.applegpu_eager_last_error()
+    n, _, _ = _run_graph(lib, _op(5, [0], (2, 2)), [x], [7])
+    assert n == -1 and b"output 7 out of range" in lib.applegpu_eager_last_error()
