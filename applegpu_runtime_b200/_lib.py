@@ -89,6 +89,7 @@ EXT_SYMBOLS = {
     "applegpu_ffi_upload": (i32, [u64, vp, u64]),
     "applegpu_ffi_read_bytes": (i32, [u64, vp, u64]),
     "applegpu_ffi_read_bytes_async": (i32, [u64, vp, u64]),
+    "applegpu_ffi_device_ptr": (vp, [u64]),
     "applegpu_ffi_from_host": (u64, [vp, u64p, u32, i8]),
     "applegpu_eager_upload": (i32, [u64, vp, u64]),
     "applegpu_eager_download": (i32, [u64, vp, u64]),

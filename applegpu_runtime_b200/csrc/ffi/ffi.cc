@@ -434,6 +434,19 @@ int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nby
   if (!s.ok()) { set_ffi_error("read_bytes failed: " + s.to_string()); return -1; }
   return 0;
 }
+void* applegpu_ffi_device_ptr(uint64_t tensor_id) {
+  if (!ffi_ready("device_ptr")) return nullptr;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (st.rt.is_pending(tensor_id)) {
+    Status s = st.rt.eval(tensor_id);
+    if (!s.ok()) { set_ffi_error("device_ptr failed: " + s.to_string()); return nullptr; }
+  }
+  const TensorRec* t = st.rt.tensor(tensor_id);
+  if (!t || !t->has_meta) { set_ffi_error("device_ptr failed: Tensor " + std::to_string(tensor_id) + " not found"); return nullptr; }
+  if (!t->contiguous()) { set_ffi_error("device_ptr failed: tensor is a strided view"); return nullptr; }
+  return t->data();
+}
 int32_t applegpu_ffi_read_bytes_async(uint64_t tensor_id, void* host_ptr, uint64_t nbytes) {
   if (!ffi_ready("read_bytes_async")) return -1;
   LazyState& st = lazy_state();

@@ -30,6 +30,11 @@ extern "C" {
 APPLEGPU_API int32_t applegpu_ffi_upload(uint64_t tensor_id, const void* host_ptr, uint64_t nbytes);
 /* Evaluates if pending, copies out, and waits. Reference: LazyRuntime::read_bytes, lazy.rs:2554-2560. */
 APPLEGPU_API int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nbytes);
+/* Device address of a tensor's first element (evaluates it if pending; NULL for an unknown id or a
+ * strided view). The memory stays valid while the tensor is alive; work enqueued on applegpu_stream()
+ * is ordered with the runtime's own kernels, which is how a collective library reduces a tensor in
+ * place between two ops. No counterpart in the reference (its buffers are host-visible). */
+APPLEGPU_API void* applegpu_ffi_device_ptr(uint64_t tensor_id);
 /* Same, but only enqueues the copy on the runtime stream: the bytes are defined after the next
  * applegpu_ffi_synchronize (or any blocking read). `host_ptr` should be pinned memory (a pageable
  * buffer makes the copy block) and must stay valid until then. Lets a caller issue the next forward

@@ -278,3 +278,13 @@ def test_graph_rewrites_collapse_the_bert_layer(gpu):
     assert shard["weights"]["encoder.layer.0.intermediate.dense.weight"].shape == [64, 64]
     assert shard["weights"]["encoder.layer.0.output.dense.weight"].shape == [64, 64]
     assert gpu.bert_forward(shard, np.arange(16).reshape(2, 8), all_reduce=lambda t: t).shape == [2, 8, 64]
+
+
+def test_tensor_parallel_head_and_ff_ranges():
+    from applegpu_runtime_b200.tp import head_and_ff_ranges
+    cfg = {"n_head": 12, "d_ff": 3072}
+    spans = [head_and_ff_ranges(cfg, r, 8) for r in range(8)]
+    assert [h1 - h0 for (h0, h1), _ in spans] == [2, 2, 2, 2, 1, 1, 1, 1]      # uneven head split at 8 ranks
+    assert spans[0][0][0] == 0 and spans[-1][0][1] == 12
+    assert all(f1 - f0 == 384 for _, (f0, f1) in spans)
+    assert head_and_ff_ranges(cfg, 0, 1) == ((0, 12), (0, 3072))
