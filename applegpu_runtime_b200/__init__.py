@@ -18,7 +18,7 @@ from .api import (  # noqa: E402,F401
     cos, gelu, gelu_exact, sigmoid, layer_norm, embedding, gather, index_select, attention, matmul, slice, concat,
     concat_all, add_bias, softmax_causal, argmax, cast, quantize, dequantize, sum, mean, attention_causal, abs, sign,
     pool_stats, pool_drain, set_pool_watermark, synchronize, quantize_weight, matmul_int8, set_fusion, set_matmul_path, set_attention_path,
-    pipeline_status, launch_count, resolve_kernel, profile, profile_report,
+    pipeline_status, launch_count, resolve_kernel, profile, profile_report, Tape, tape_begin, tape_end, tape_abort,
 )
 from .gpt2 import gpt2_forward, init_gpt2_weights, load_gpt2_state_dict, quantize_gpt2_linears, GPT2_SMALL, GPT2_LARGE  # noqa: E402,F401
 from .bert import bert_forward, init_bert_weights, load_bert_state_dict, BERT_BASE  # noqa: E402,F401

@@ -90,6 +90,10 @@ EXT_SYMBOLS = {
     "applegpu_ffi_read_bytes": (i32, [u64, vp, u64]),
     "applegpu_ffi_read_bytes_async": (i32, [u64, vp, u64]),
     "applegpu_ffi_device_ptr": (vp, [u64]),
+    "applegpu_ffi_tape_begin": (i32, [vp, u32]),
+    "applegpu_ffi_tape_end": (u64, [vp, u32]),
+    "applegpu_ffi_tape_abort": (None, []),
+    "applegpu_ffi_tape_replay": (i32, [u64, vp, u32, vp, u32]),
     "applegpu_ffi_from_host": (u64, [vp, u64p, u32, i8]),
     "applegpu_eager_upload": (i32, [u64, vp, u64]),
     "applegpu_eager_download": (i32, [u64, vp, u64]),

@@ -442,6 +442,48 @@ def synchronize():
     _L().applegpu_ffi_synchronize()
 
 
+# ── op tapes ────────────────────────────────────────────────────────────────
+class Tape:
+    """The ops one pass of a host program recorded between `tape_begin` and `tape_end`; `replay` issues
+    them again on new inputs with one library call instead of one per op."""
+
+    __slots__ = ("handle", "n_inputs", "n_outputs")
+
+    def __init__(self, handle, n_inputs, n_outputs):
+        self.handle, self.n_inputs, self.n_outputs = handle, n_inputs, n_outputs
+
+    def replay(self, inputs):
+        if len(inputs) != self.n_inputs:
+            raise ValueError(f"the tape takes {self.n_inputs} inputs, got {len(inputs)}")
+        ids = (ctypes.c_uint64 * max(1, len(inputs)))(*[t.id for t in inputs])
+        out = (ctypes.c_uint64 * max(1, self.n_outputs))()
+        if _L().applegpu_ffi_tape_replay(self.handle, ids, len(inputs), out, self.n_outputs) < 0:
+            raise ValueError(_err())
+        held = {t.id for t in inputs}
+        # an output that is one of the inputs is owned by whoever passed it in
+        return [GpuTensor(out[i], owns=out[i] not in held) for i in range(self.n_outputs)]
+
+
+def tape_begin(inputs):
+    """Start noting every op call. `inputs` are the tensors that will differ between replays."""
+    ids = (ctypes.c_uint64 * max(1, len(inputs)))(*[t.id for t in inputs])
+    if _L().applegpu_ffi_tape_begin(ids, len(inputs)) != 0:
+        raise ValueError(_err())
+    return len(inputs)
+
+
+def tape_end(n_inputs, outputs):
+    ids = (ctypes.c_uint64 * max(1, len(outputs)))(*[t.id for t in outputs])
+    h = _L().applegpu_ffi_tape_end(ids, len(outputs))
+    if not h:
+        raise ValueError(_err())
+    return Tape(int(h), n_inputs, len(outputs))
+
+
+def tape_abort():
+    _L().applegpu_ffi_tape_abort()
+
+
 # ── runtime services ────────────────────────────────────────────────────────
 def pool_stats():
     out = (ctypes.c_uint64 * 7)()

@@ -8,7 +8,10 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <memory>
 #include <mutex>
+#include <unordered_map>
+#include <unordered_set>
 
 namespace ag {
 extern bool g_fused_attention;
@@ -62,6 +65,33 @@ bool eager_ready() {
 }
 
 // Validate + record one node; returns its id or 0 (message prefixed "<name> failed: ").
+// ── op tapes ────────────────────────────────────────────────────────────────
+// A tape is the op list one pass of a host program recorded (kinds, parameters, and which earlier
+// value or external tensor each input is). Replaying it re-records the same ops on new inputs in one
+// call: shapes are inferred again, so a tape taken at one KV length replays at another. Values are
+// numbered in recording order; inputs < 0 name external slots: the first n_var are the variable
+// inputs named at tape_begin, the rest are tensors that were simply alive during recording (weights)
+// and are reused by id. Guarded by the graph-flavour mutex.
+struct TapeOp { OpKind kind; std::vector<int64_t> in; };
+struct Tape {
+  std::vector<TapeOp> ops;
+  std::vector<uint64_t> ext;      // external slots; the first n_var entries are placeholders
+  uint32_t n_var = 0;
+  std::vector<int64_t> outputs;
+};
+static std::vector<std::unique_ptr<Tape>> g_tapes;
+static std::unique_ptr<Tape> g_rec;                              // tape being recorded, if any
+static std::unordered_map<uint64_t, int64_t> g_rec_slot;         // tensor id -> value index or -(slot+1)
+
+static int64_t tape_slot_of(uint64_t id) {
+  auto it = g_rec_slot.find(id);
+  if (it != g_rec_slot.end()) return it->second;
+  g_rec->ext.push_back(id);                                      // a constant of the tape
+  int64_t s = -(int64_t)g_rec->ext.size();
+  g_rec_slot[id] = s;
+  return s;
+}
+
 uint64_t record(const char* name, OpKind kind, std::vector<uint64_t> inputs) {
   if (!ffi_ready(name)) return 0;
   LazyState& st = lazy_state();
@@ -74,6 +104,13 @@ uint64_t record(const char* name, OpKind kind, std::vector<uint64_t> inputs) {
   if (!s.ok()) { set_ffi_error(std::string(name) + " failed: " + s.to_string()); return 0; }
   node.id = next_op_id();
   uint64_t id = node.id;
+  if (g_rec) {
+    TapeOp t;
+    t.kind = node.op;
+    for (uint64_t in : node.inputs) t.in.push_back(tape_slot_of(in));
+    g_rec_slot[id] = (int64_t)g_rec->ops.size();
+    g_rec->ops.push_back(std::move(t));
+  }
   st.rt.record_op(std::move(node));
   return id;
 }
@@ -433,6 +470,76 @@ int32_t applegpu_ffi_read_bytes(uint64_t tensor_id, void* host_ptr, uint64_t nby
   Status s = st.rt.read_bytes(tensor_id, host_ptr, (size_t)nbytes);
   if (!s.ok()) { set_ffi_error("read_bytes failed: " + s.to_string()); return -1; }
   return 0;
+}
+int32_t applegpu_ffi_tape_begin(const uint64_t* var_inputs, uint32_t n_var) {
+  if (!ffi_ready("tape_begin")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (g_rec) { set_ffi_error("tape_begin failed: a tape is already being recorded"); return -1; }
+  g_rec.reset(new Tape());
+  g_rec_slot.clear();
+  g_rec->n_var = n_var;
+  for (uint32_t k = 0; k < n_var; k++) { g_rec->ext.push_back(0); g_rec_slot[var_inputs[k]] = -(int64_t)(k + 1); }
+  return 0;
+}
+uint64_t applegpu_ffi_tape_end(const uint64_t* outputs, uint32_t n_out) {
+  if (!ffi_ready("tape_end")) return 0;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (!g_rec) { set_ffi_error("tape_end failed: no tape is being recorded"); return 0; }
+  std::unique_ptr<Tape> t = std::move(g_rec);
+  for (uint32_t k = 0; k < n_out; k++) {
+    auto it = g_rec_slot.find(outputs[k]);
+    if (it == g_rec_slot.end()) { g_rec_slot.clear(); set_ffi_error("tape_end failed: output " + std::to_string(outputs[k]) + " was not produced on the tape"); return 0; }
+    if (it->second < 0 && (uint64_t)(-it->second - 1) >= t->n_var) { g_rec_slot.clear(); set_ffi_error("tape_end failed: output " + std::to_string(outputs[k]) + " is a constant of the tape"); return 0; }
+    t->outputs.push_back(it->second);
+  }
+  g_rec_slot.clear();
+  g_tapes.push_back(std::move(t));
+  return (uint64_t)g_tapes.size();   // handles start at 1
+}
+void applegpu_ffi_tape_abort(void) {
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  g_rec.reset();
+  g_rec_slot.clear();
+}
+int32_t applegpu_ffi_tape_replay(uint64_t tape, const uint64_t* var_inputs, uint32_t n_var, uint64_t* out_ids, uint32_t n_out) {
+  if (!ffi_ready("tape_replay")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  if (tape == 0 || tape > g_tapes.size()) { set_ffi_error("tape_replay failed: unknown tape " + std::to_string(tape)); return -1; }
+  const Tape& t = *g_tapes[tape - 1];
+  if (n_var != t.n_var || n_out != t.outputs.size()) { set_ffi_error("tape_replay failed: the tape takes " + std::to_string(t.n_var) + " inputs and gives " + std::to_string(t.outputs.size()) + " outputs"); return -1; }
+  if (g_rec) { set_ffi_error("tape_replay failed: a tape is being recorded"); return -1; }
+  std::vector<uint64_t> vals;
+  vals.reserve(t.ops.size());
+  auto resolve = [&](int64_t s) -> uint64_t {
+    if (s >= 0) return vals[(size_t)s];
+    size_t k = (size_t)(-s - 1);
+    return k < t.n_var ? var_inputs[k] : t.ext[k];
+  };
+  LazyMetaSrc src(&st.rt);
+  for (const TapeOp& op : t.ops) {
+    OpNode node;
+    node.op = op.kind;
+    for (int64_t s : op.in) node.inputs.push_back(resolve(s));
+    Status s = infer_node(src, &node);
+    if (!s.ok()) {
+      // drop what this replay recorded so far
+      for (uint64_t v : vals) st.rt.free_tensor(v);
+      set_ffi_error("tape_replay failed: " + s.to_string());
+      return -1;
+    }
+    node.id = next_op_id();
+    vals.push_back(node.id);
+    st.rt.record_op(std::move(node));
+  }
+  std::unordered_set<uint64_t> kept;
+  for (uint32_t k = 0; k < n_out; k++) { out_ids[k] = resolve(t.outputs[k]); kept.insert(out_ids[k]); }
+  // values nobody holds a handle to are released as soon as their last consumer has run
+  for (uint64_t v : vals) if (!kept.count(v)) st.rt.free_tensor(v);
+  return (int32_t)t.ops.size();
 }
 void* applegpu_ffi_device_ptr(uint64_t tensor_id) {
   if (!ffi_ready("device_ptr")) return nullptr;

@@ -37,15 +37,17 @@ def _sample_token(logits_np, temperature=1.0, top_k=0, top_p=0.0, rng=None):
     return int(rng.choice(len(probs), p=probs))
 
 
-def greedy_generate(model, input_ids, max_tokens=50, use_cache=True):
-    """Greedy decode for a batch of equal-length prompts [B, T]; returns [B, T + max_tokens]."""
+def greedy_generate(model, input_ids, max_tokens=50, use_cache=True, compiled=True):
+    """Greedy decode for a batch of equal-length prompts [B, T]; returns [B, T + max_tokens]. With
+    `compiled` the decode steps (one new token against the KV cache) replay an op tape instead of
+    re-issuing ~300 op calls each."""
     ids = np.asarray(input_ids, dtype=np.int64)
     if ids.ndim == 1:
         ids = ids.reshape(1, -1)
     kv = None
     for _ in range(max_tokens):
         if use_cache:
-            logits, kv = gpt2_forward(model, ids, kv_cache=kv, last_only=True)
+            logits, kv = gpt2_forward(model, ids, kv_cache=kv, last_only=True, compiled=compiled and kv is not None)
         else:
             logits, _ = gpt2_forward(model, ids, kv_cache=None, last_only=True)
         nxt = gpu.argmax(logits).to_numpy().astype(np.int64).reshape(-1, 1)

@@ -88,7 +88,7 @@ def _linear(x, w, name, bias):
     return gpu.add_bias(y, bias)
 
 
-def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=None):
+def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=None, compiled=False):
     """GPT-2 forward with optional KV cache.
 
     input_ids: list of ints (the reference's form, batch 1) or an int array [B, T]. With a cache
@@ -96,7 +96,10 @@ def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=No
     [T, vocab] for list input (as upstream) or [B, T, vocab] for array input; with `last_only`
     only the final position goes through the LM head ([B, vocab]). `device_ids` = (token ids,
     position ids) as int32 GpuTensors of length B*T skips the host-to-device copy of the ids;
-    `input_ids` then only supplies the [B, T] shape.
+    `input_ids` then only supplies the [B, T] shape. `compiled=True` records the op sequence once per
+    (batch, new tokens, cache / no cache) on an op tape and replays it on later calls: one library
+    call per forward instead of one per op (shapes are re-inferred, so the tape taken at one KV length
+    serves the next).
     """
     w = dict(model["weights"])
     if "int8" in model:
@@ -128,6 +131,32 @@ def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=No
         pos = np.tile(np.arange(pos_offset, pos_offset + T, dtype=np.int32), B)
         pos_indices = gpu.from_numpy(pos)
 
+    tape_key = tape_inputs = None
+    if compiled:
+        tape_key = ("gpt2", B, T, use_cache, bool(last_only), batched, "int8" in model)
+        tape_inputs = [indices, pos_indices] + ([t for kv in kv_cache for t in kv] if use_cache else [])
+        tape = model.setdefault("_tapes", {}).get(tape_key)
+        if tape is not None:
+            out = tape.replay(tape_inputs)
+            return out[0], [(out[1 + 2 * i], out[2 + 2 * i]) for i in range(n_layer)]
+        gpu.tape_begin(tape_inputs)
+    try:
+        logits, new_kv_cache = _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, batched)
+    except Exception:
+        if compiled:
+            gpu.tape_abort()
+        raise
+    if compiled:
+        model["_tapes"][tape_key] = gpu.tape_end(len(tape_inputs), [logits] + [t for kv in new_kv_cache for t in kv])
+    return logits, new_kv_cache
+
+
+def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, batched):
+    """Issues the ops of one forward (the body the reference's gpt2_forward runs per call)."""
+    n_layer, n_head, n_embd = cfg["n_layer"], cfg["n_head"], cfg["n_embd"]
+    d_head = n_embd // n_head
+    rows = B * T
+    use_cache = kv_cache is not None
     tok_emb = gpu.embedding(w["transformer.wte.weight"], indices)
     pos_emb = gpu.embedding(w["transformer.wpe.weight"], pos_indices)
     x = tok_emb + pos_emb  # [B*T, d]

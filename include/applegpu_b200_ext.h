@@ -148,6 +148,21 @@ APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
 /* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
 /* CUDA-event stopwatch on the runtime stream. */
+/* Op tapes: record the graph-flavour ops one pass of a host program issues, then re-record the same
+ * ops on new inputs with one call (the per-op host cost of a Python driver is paid once). Between
+ * tape_begin and tape_end every applegpu_ffi_* op call is noted; tensors in `var_inputs` become the
+ * tape's parameters, any other tensor an op reads (weights) is reused by id and must stay alive.
+ * tape_end returns a handle (0 on failure). tape_replay returns the number of ops recorded (-1 on
+ * error) and writes the new ids of the tape's outputs; the caller owns those ids (free them as
+ * usual), every other value is released as soon as its last consumer has run. Shapes are inferred
+ * again on replay, so one tape serves inputs of different extents (a growing KV cache) as long as
+ * the explicit shape arguments recorded on it still apply. The reference's counterpart is its
+ * compiled-graph path (crates/core/src/compiled_graph.rs), which serialises the op list on the
+ * Python side instead. */
+APPLEGPU_API int32_t applegpu_ffi_tape_begin(const uint64_t* var_inputs, uint32_t n_var);
+APPLEGPU_API uint64_t applegpu_ffi_tape_end(const uint64_t* outputs, uint32_t n_out);
+APPLEGPU_API void applegpu_ffi_tape_abort(void);
+APPLEGPU_API int32_t applegpu_ffi_tape_replay(uint64_t tape, const uint64_t* var_inputs, uint32_t n_var, uint64_t* out_ids, uint32_t n_out);
 /* Compiled-graph executor: runs a serialized op list on the eager runtime in one call and returns the
  * number of outputs written (-1 on error, text in applegpu_eager_last_error). Replaces
  * applegpu_eager_execute_graph of the reference (crates/core/src/eager_ffi.rs:661-708; wire format and

@@ -118,6 +118,24 @@ def test_gpt2_int8_weights_bf16_activations_against_dequantised_oracle(gpu_dev):
     assert gpu_dev.pipeline_status() == 0
 
 
+def test_taped_decode_steps_give_the_same_tokens_and_logits(gpu_dev):
+    m = gpu_dev.init_gpt2_weights(CFG_MID, seed=9, dtype="bfloat16")
+    ids = np.random.default_rng(9).integers(0, CFG_MID["vocab_size"], (3, 10))
+    a = gpu_dev.greedy_generate(m, ids, max_tokens=12, use_cache=True, compiled=False)
+    b = gpu_dev.greedy_generate(m, ids, max_tokens=12, use_cache=True, compiled=True)
+    assert a.tolist() == b.tolist()
+    # prefill through a tape: recorded on the first call, replayed on the second
+    l0 = gpu_dev.gpt2_forward(m, ids)[0].to_numpy()
+    l1 = gpu_dev.gpt2_forward(m, ids, compiled=True)[0].to_numpy()
+    l2 = gpu_dev.gpt2_forward(m, ids[::-1].copy(), compiled=True)[0].to_numpy()
+    assert np.array_equal(l0, l1) and np.array_equal(l0[::-1], l2)
+    n0 = gpu_dev.tensor_count()
+    for _ in range(3):
+        gpu_dev.gpt2_forward(m, ids, compiled=True)[0].eval()
+    gpu_dev.synchronize()
+    assert gpu_dev.tensor_count() <= n0 + 4          # replayed intermediates do not pile up
+
+
 def test_mlp_config_fp32(gpu_dev):
     # BASELINE config 0: Linear(64,128) -> ReLU -> Linear(128,10), batch 32, default nn.Linear init, seed 0
     torch.manual_seed(0)

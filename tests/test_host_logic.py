@@ -288,3 +288,42 @@ def test_tensor_parallel_head_and_ff_ranges():
     assert spans[0][0][0] == 0 and spans[-1][0][1] == 12
     assert all(f1 - f0 == 384 for _, (f0, f1) in spans)
     assert head_and_ff_ranges(cfg, 0, 1) == ((0, 12), (0, 3072))
+
+
+def test_op_tape_replays_the_gpt2_forward_at_a_longer_kv_length(gpu):
+    m = _tiny_model(gpu)
+    ids = np.arange(10).reshape(2, 5)
+    logits, kv = gpu.gpt2_forward(m, ids)
+    plans = []
+    for step in range(3):
+        ids = np.concatenate([ids, np.zeros((2, 1), np.int64)], axis=1)
+        logits, kv = gpu.gpt2_forward(m, ids, kv_cache=kv, last_only=True, compiled=True)   # step 0 records, 1 and 2 replay
+        assert logits.shape == [2, 100] and kv[0][0].shape == [2, 4, 6 + step, 16]
+        plans.append([l.split(" ")[0] for l in logits.plan().strip().splitlines()])
+    # nothing is evaluated in this metadata-only mode, so each plan also holds the earlier steps' pending ops:
+    # every replay must add exactly what the recorded step added
+    per_step = len(plans[1]) - len(plans[0])
+    assert per_step > 0 and len(plans[2]) - len(plans[1]) == per_step
+    from collections import Counter
+    assert Counter(plans[2]) - Counter(plans[1]) == Counter(plans[1]) - Counter(plans[0])
+    assert len(m["_tapes"]) == 1
+    # errors: wrong input count, unknown tape, nested recording
+    tape = next(iter(m["_tapes"].values()))
+    with pytest.raises(ValueError, match="takes"):
+        tape.replay([kv[0][0]])
+    gpu.tape_begin([])
+    try:
+        with pytest.raises(ValueError, match="already being recorded"):
+            gpu.tape_begin([])
+    finally:
+        gpu.tape_abort()
+    x = gpu.from_numpy(np.ones((2, 2), np.float32))
+    n = gpu.tape_begin([x])
+    y = gpu.relu(x + x)
+    t = gpu.tape_end(n, [y])
+    z = gpu.from_numpy(np.ones((3, 5), np.float32))
+    (r,) = t.replay([z])
+    assert r.shape == [3, 5] and "fused_" in r.plan()
+    gpu.tape_begin([x])
+    with pytest.raises(ValueError, match="not produced on the tape"):
+        gpu.tape_end(1, [z])
