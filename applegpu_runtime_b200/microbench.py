@@ -76,6 +76,28 @@ def bench_matmul(rng, dtype, b, m, n, k, iters, opt):
     return {"op": "matmul", "dtype": dtype, "shape": [b, m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
+def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt):
+    """x @ W + b, then GELU or a residual add: one fused_linear launch (the four linears of a GPT-2 layer)."""
+    e = gpu.dtype_size(dtype)
+    sets = []
+    for _ in range(_nsets((m * k + k * n + (2 if residual else 1) * m * n) * e, opt.rotate)):
+        sets.append((_tensor(rng, (m, k), dtype), _tensor(rng, (k, n), dtype, 0.02), _tensor(rng, (m, n), dtype) if residual else None))
+    bias = _tensor(rng, (n,), dtype)
+
+    def make(x, w, r):
+        def fn():
+            y = gpu.add_bias(x @ w, bias)
+            if act:
+                y = gpu.gelu(y)
+            return r + y if r is not None else y
+        return fn
+
+    ms = _time([make(*t) for t in sets], iters, single=opt.single)
+    flops = 2.0 * m * n * k
+    name = "fused_linear[bias" + (",gelu" if act else "") + (",residual" if residual else "") + "]"
+    return {"op": name, "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
+
+
 def bench_lm_head(rng, dtype, m, vocab, k, iters, opt):
     a = _tensor(rng, (m, k), dtype)
     wte = _tensor(rng, (vocab, k), dtype, 0.02)
@@ -148,6 +170,10 @@ def main(argv=None):
             for (m, n, k) in [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072)]:
                 out.append(bench_matmul(rng, dt, 1, m, n, k, args.iters, args))
             out.append(bench_lm_head(rng, dt, 8192, 50257, 768, args.iters, args))
+        if args.op in ("all", "gpt2_linears") and dt != "float32":
+            for (m, n, k, act, res) in [(8192, 2304, 768, False, False), (8192, 768, 768, False, True), (8192, 3072, 768, True, False),
+                                        (8192, 768, 3072, False, True)]:
+                out.append(bench_fused_linear(rng, dt, m, n, k, act, res, args.iters, args))
         if args.op == "lm_head":
             out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args))
         if args.op in ("all", "layer_norm"):
