@@ -22,6 +22,17 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
   const float inv_cols = 1.0f / (float)cols;
   pdl_wait();
   pdl_trigger();
+  // gamma / beta do not depend on the row: fetched once, together with the first row's loads, so their
+  // latency is not exposed after the reductions (kept in registers for rows of up to 4 packs per lane)
+  constexpr bool kHoist = ITERS <= 4;
+  Pack<T> gpk[kHoist ? ITERS : 1], bpk[kHoist ? ITERS : 1];
+  if (kHoist) {
+#pragma unroll
+    for (int it = 0; it < (kHoist ? ITERS : 1); it++) {
+      int pk = lane + it * 32;
+      if (pk < packs) { gpk[it] = ld16(gamma + pk * N); bpk[it] = ld16(beta + pk * N); }
+    }
+  }
   for (int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * warps_per_block) {
     const T* x = in + row * cols;
     float v[ITERS][N];
@@ -55,8 +66,8 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
     for (int it = 0; it < ITERS; it++) {
       int pk = lane + it * 32;
       if (pk < packs) {
-        Pack<T> g = ld16(gamma + pk * N);
-        Pack<T> b = ld16(beta + pk * N);
+        Pack<T> g = kHoist ? gpk[kHoist ? it : 0] : ld16(gamma + pk * N);
+        Pack<T> b = kHoist ? bpk[kHoist ? it : 0] : ld16(beta + pk * N);
         Pack<T> o;
 #pragma unroll
         for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(Cvt<T>::to(g.v[e]) * (v[it][e] - mean) * inv_std + Cvt<T>::to(b.v[e]));
