@@ -36,9 +36,8 @@ constexpr int kKV = 64;    // keys per block
 constexpr int kD = 64;     // head dimension
 constexpr int kQBytes = kQ * kD * 2;                     // 16 KB
 constexpr int kKVBytes = kKV * kD * 2;                   // 8 KB: one K or V block
-constexpr int kPBytes = kQ * kKV * 2;                    // 16 KB: one P block
-constexpr int kAttnSmem = kQBytes + 2 * kKVBytes /*K*/ + 2 * kKVBytes /*V*/ + 2 * kPBytes + 1024;
-constexpr int kAttnTmemCols = 256;                       // S: 2 x 64, O block: 2 x 64
+constexpr int kAttnSmem = kQBytes + 2 * kKVBytes /*K*/ + 2 * kKVBytes /*V*/ + 1024;
+constexpr int kAttnTmemCols = 256;                       // S: 2 x 64 (P over the head of each), O: 64
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -65,19 +64,25 @@ struct AttnParams {
   int* status;
 };
 
+// How far (in log2 units) the running row maximum may grow before the accumulated output is rescaled.
+// Until then probabilities are taken relative to the older, smaller maximum and may reach 2^kRescaleLog2:
+// exact in the arithmetic of softmax (numerator and denominator carry the same factor), harmless in
+// range (bf16 / f16 probabilities up to 256, fp32 sums), and it keeps the output accumulator in tensor
+// memory untouched for almost every block.
+constexpr float kRescaleLog2 = 8.0f;
+
 template <typename T>
 __global__ void __launch_bounds__(kAttnThreads, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full[2], o_empty[2];
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full[2];
   __shared__ uint32_t tmem_base_slot;
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kQBytes;            // two stages
   uint8_t* sV = sK + 2 * kKVBytes;       // two stages
-  uint8_t* sP = sV + 2 * kKVBytes;       // two stages
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (p.tq + kQ - 1) / kQ;
@@ -97,10 +102,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int s = 0; s < 2; s++) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
-      mbar_init(&p_full[s], 4); mbar_init(&p_empty[s], 1);
-      mbar_init(&o_full[s], 1); mbar_init(&o_empty[s], 4);
+      mbar_init(&s_full[s], 1); mbar_init(&p_full[s], 4);
     }
+    mbar_init(&o_full[0], 1); mbar_init(&o_full[1], 1);
     mbar_fence_init();
     prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
   }
@@ -109,7 +113,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kKV;   // each: two buffers of 64 columns
+  // columns 0..127: two S buffers of 64 fp32 columns; P_j (64 keys as 32 packed columns) overwrites the
+  // head of the S buffer it was computed from. Columns 128..191: the output accumulator.
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kKV;
   pdl_wait();      // the prologue above may overlap the tail of the kernel that produces Q, K and V
   pdl_trigger();
 
@@ -131,8 +137,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ── MMA issuer. S_j = Q K_j^T runs two blocks ahead of the softmax (two S buffers), O_j = P_j V_j
-    //    is issued as soon as P_j is published and is read back one block later. ──
+    // ── MMA issuer. S_j = Q K_j^T runs two blocks ahead of the softmax (two S buffers); O += P_j V_j
+    //    reads P_j from tensor memory and accumulates in tensor memory. MMAs execute in issue order,
+    //    so S_{j+2} (issued after P_j V_j) cannot overwrite P_j before that product has read it. ──
     if (lane == 0) {
       constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc_s = make_idesc_f16(fmt, 0, 0, kQ, kKV);   // S = Q K^T: both K-major, N = 64
@@ -140,9 +147,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = mbar_wait(&q_full, 0, p.status, 13);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait(&k_full[st], ph, p.status, 14)) return false;
-        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, 15)) return false;
+        if (!mbar_wait(&k_full[st], (uint32_t)((j >> 1) & 1), p.status, 14)) return false;
         tc_fence_after_sync();
         const uint32_t a = smem_u32(sQ), bb = smem_u32(sK + st * kKVBytes);
 #pragma unroll
@@ -159,20 +164,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int st = j & 1;
         const uint32_t ph = (uint32_t)((j >> 1) & 1);
         if (!mbar_wait(&v_full[st], ph, p.status, 16)) { ok = false; break; }
-        if (!mbar_wait(&p_full[st], ph, p.status, 17)) { ok = false; break; }
-        if (!mbar_wait(&o_empty[st], ph ^ 1, p.status, 18)) { ok = false; break; }
+        if (!mbar_wait(&p_full[st], ph, p.status, 17)) { ok = false; break; }   // P_j stored, O rescaled if it had to be
         tc_fence_after_sync();
-        const uint32_t a = smem_u32(sP + st * kPBytes), bb = smem_u32(sV + st * kKVBytes);
+        const uint32_t bb = smem_u32(sV + st * kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < kKV / 16; kk++) {
-          // P: one 64-wide k-block, 32 B per K step. V: rows are keys (128 B = 64 head dims); 16 keys = 2048 B.
-          mma_f16_ss(tmem_o + (uint32_t)(st * kD), make_smem_desc_sw128(a + kk * 32, 16, 1024), make_smem_desc_sw128(bb + kk * 2048, 64 * 128, 1024),
-                     idesc_o, kk > 0 ? 1u : 0u);
+          // P: 16 keys = 8 packed columns. V: rows are keys (128 B = 64 head dims); 16 keys = 2048 B.
+          mma_f16_ts(tmem_o, tmem_s + (uint32_t)(st * kKV + kk * 8), make_smem_desc_sw128(bb + kk * 2048, 64 * 128, 1024), idesc_o,
+                     (j > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(&v_empty[st]);
-        mma_commit(&p_empty[st]);
+        // Even and odd blocks signal different barriers: a waiter can then be at most one phase behind
+        // (P_{j-2} V_{j-2} is always complete before S_j is), so its parity test cannot alias.
         mma_commit(&o_full[st]);
-        // the S buffer of block j was drained into registers at the start of its softmax: refill it
         if (j + 2 < n_blocks) { if (!issue_s(j + 2)) { ok = false; break; } }
       }
     }
@@ -182,46 +186,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int r = quarter * 32 + lane;          // row inside the tile = TMEM lane
     const int row = q0 + r;                     // row inside the sequence
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o_acc[kD];
-#pragma unroll
-    for (int e = 0; e < kD; e++) o_acc[e] = 0.f;
+    float m_ref = -INFINITY;   // the maximum the stored probabilities and sums are relative to
+    float l_run = 0.f;
     const float sc = p.scale_log2;
     bool ok = true;
 
-    // O = O * alpha + P_jj V_jj, read back from TMEM one block after the product was issued
-    auto o_update = [&](int jj, float a) -> bool {
-      const int st = jj & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&o_full[st], (uint32_t)((jj >> 1) & 1), p.status, 21))) return false;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < kD / 32; c++) {
-        uint32_t ov[32];
-        tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(st * kD + c * 32), ov);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; e++) o_acc[c * 32 + e] = fmaf(o_acc[c * 32 + e], a, __uint_as_float(ov[e]));
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&o_empty[st]);
-      return true;
-    };
-
-    float alpha_prev = 1.f;
     for (int j = 0; j < n_blocks && ok; j++) {
       const int st = j & 1;
       const uint32_t ph = (uint32_t)((j >> 1) & 1);
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[st], ph, p.status, 19))) { ok = false; break; }  // warp-uniform exits
       tc_fence_after_sync();
-      // the whole 64-column block of this row goes to registers; S can be overwritten right away
       uint32_t s0[32], s1[32];
       tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(st * kKV), s0);
       tmem_ld_32x32(tmem_s + lane_addr + (uint32_t)(st * kKV + 32), s1);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[st]);
 
       const int col_base = j * kKV;
       // columns this row may see inside the block: [0, lim)
@@ -252,12 +230,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s1[e]));
         }
       }
-      const float m_new = fmaxf(m_run, m_blk * sc);
-      // a row with nothing visible so far keeps its state
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = ex2_approx(m_run - m_use);
+      // Move the reference maximum only when this row's maximum outgrew it by more than the margin (or
+      // when the row sees its first scores); the accumulated output and sum are then rescaled.
+      const float m_cand = fmaxf(m_ref, m_blk * sc);
+      const bool moves = (m_cand - m_ref > kRescaleLog2) || (m_ref == -INFINITY && m_cand != -INFINITY);
+      const float alpha = moves ? ex2_approx(m_ref - m_cand) : 1.0f;      // exp2(-inf) = 0 for a first block
+      if (moves) m_ref = m_cand;
+      if (j > 0 && __any_sync(0xffffffffu, moves)) {
+        // O holds the products up to block j-1: wait for the last of them, scale this row, write it back
+        if (!__all_sync(0xffffffffu, mbar_wait(&o_full[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), p.status, 21))) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kD / 32; c++) {
+          uint32_t ov[32];
+          tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+          tmem_st_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), ov);
+        }
+        tmem_st_wait();
+      }
+      l_run *= alpha;
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
 
-      // probabilities = exp2(s * scale - m): one FFMA, one MUFU, one add per element, in place
+      // probabilities = exp2(s * scale - m_ref): one FFMA, one MUFU, one add per element, in place
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
       if (full) {
 #pragma unroll
@@ -279,42 +276,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         l0 += __uint_as_float(s0[e]) + __uint_as_float(s1[e]);         l1 += __uint_as_float(s0[e + 1]) + __uint_as_float(s1[e + 1]);
         l2 += __uint_as_float(s0[e + 2]) + __uint_as_float(s1[e + 2]); l3 += __uint_as_float(s0[e + 3]) + __uint_as_float(s1[e + 3]);
       }
-      // P_j overwrites the buffer that P_{j-2} V_{j-2} read
-      if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[st], ph ^ 1, p.status, 20))) { ok = false; break; }
-      uint8_t* dst = sP + st * kPBytes + r * 128;
+      l_run += (l0 + l1) + (l2 + l3);
+      // P_j: keys 2c and 2c+1 of this row packed into column c, over the head of the S buffer just read
+      uint32_t pk[32];
 #pragma unroll
-      for (int g = 0; g < 8; g++) {
-        const uint32_t* src = g < 4 ? s0 + g * 8 : s1 + (g - 4) * 8;
-        uint4 o;
-        o.x = pack2_t<T>(__uint_as_float(src[0]), __uint_as_float(src[1])); o.y = pack2_t<T>(__uint_as_float(src[2]), __uint_as_float(src[3]));
-        o.z = pack2_t<T>(__uint_as_float(src[4]), __uint_as_float(src[5])); o.w = pack2_t<T>(__uint_as_float(src[6]), __uint_as_float(src[7]));
-        *reinterpret_cast<uint4*>(dst + ((g ^ (r & 7)) * 16)) = o;   // 128B swizzle: 16-byte chunk index XOR row % 8
+      for (int c = 0; c < 16; c++) {
+        pk[c] = pack2_t<T>(__uint_as_float(s0[2 * c]), __uint_as_float(s0[2 * c + 1]));
+        pk[16 + c] = pack2_t<T>(__uint_as_float(s1[2 * c]), __uint_as_float(s1[2 * c + 1]));
       }
-      // P is complete for this warp's 32 rows: publish to the tensor core (async proxy)
-      fence_proxy_async_smem();
+      tmem_st_32x32(tmem_s + lane_addr + (uint32_t)(st * kKV), pk);
+      tmem_st_wait();
+      tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[st]);
-      l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
-      m_run = m_new;
-      // the previous block's P V product has had a whole block time to finish
-      if (j > 0) { if (!o_update(j - 1, alpha_prev)) { ok = false; break; } }
-      alpha_prev = alpha;
     }
-    if (ok && n_blocks > 0) ok = o_update(n_blocks - 1, alpha_prev);
-    if (ok && row < p.tq) {
-      float inv = 1.0f / l_run;
+    // the last product
+    if (ok && n_blocks > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_full[(n_blocks - 1) & 1], (uint32_t)(((n_blocks - 1) >> 1) & 1), p.status, 22));
+    if (ok && n_blocks > 0) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l_run;
       T* dst = reinterpret_cast<T*>(p.o) + (long long)b * p.o_b + (long long)h * p.o_h + (long long)row * p.o_t;
-      if (p.o_vec) {
 #pragma unroll
-        for (int g = 0; g < kD / 8; g++) {
-          uint4 o;
-          o.x = pack2_t<T>(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv); o.y = pack2_t<T>(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv);
-          o.z = pack2_t<T>(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv); o.w = pack2_t<T>(o_acc[g * 8 + 6] * inv, o_acc[g * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + g * 8) = o;
+      for (int c = 0; c < kD / 32; c++) {
+        uint32_t ov[32];
+        tmem_ld_32x32(tmem_o + lane_addr + (uint32_t)(c * 32), ov);
+        tmem_ld_wait();
+        if (row < p.tq) {
+          if (p.o_vec) {
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+              uint4 o;
+              o.x = pack2_t<T>(__uint_as_float(ov[g * 8 + 0]) * inv, __uint_as_float(ov[g * 8 + 1]) * inv);
+              o.y = pack2_t<T>(__uint_as_float(ov[g * 8 + 2]) * inv, __uint_as_float(ov[g * 8 + 3]) * inv);
+              o.z = pack2_t<T>(__uint_as_float(ov[g * 8 + 4]) * inv, __uint_as_float(ov[g * 8 + 5]) * inv);
+              o.w = pack2_t<T>(__uint_as_float(ov[g * 8 + 6]) * inv, __uint_as_float(ov[g * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = o;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++) dst[c * 32 + e] = Cvt<T>::from(__uint_as_float(ov[e]) * inv);
+          }
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < kD; e++) dst[e] = Cvt<T>::from(o_acc[e] * inv);
       }
     }
   }
