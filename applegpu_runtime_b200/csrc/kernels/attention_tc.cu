@@ -209,7 +209,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // warp-uniform: selects the mask-free arithmetic below
       const bool full = __all_sync(0xffffffffu, lim >= kKV);
       float m_blk;
-      if (full) {
+      if (!full) {
+        // masked columns become -inf once, so both paths share the four-chain maximum below
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          if (e >= lim) s0[e] = 0xff800000u;
+          if (32 + e >= lim) s1[e] = 0xff800000u;
+        }
+      }
+      {
         float m0 = __uint_as_float(s0[0]), m1 = __uint_as_float(s0[1]), m2 = __uint_as_float(s0[2]), m3 = __uint_as_float(s0[3]);
 #pragma unroll
         for (int e = 4; e < 32; e += 4) {
@@ -222,13 +230,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           m2 = fmaxf(m2, __uint_as_float(s1[e + 2])); m3 = fmaxf(m3, __uint_as_float(s1[e + 3]));
         }
         m_blk = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-      } else {
-        m_blk = -INFINITY;
-#pragma unroll
-        for (int e = 0; e < 32; e++) {
-          if (e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s0[e]));
-          if (32 + e < lim) m_blk = fmaxf(m_blk, __uint_as_float(s1[e]));
-        }
       }
       // Move the reference maximum only when this row's maximum outgrew it by more than the margin (or
       // when the row sees its first scores); the accumulated output and sum are then rescaled.
@@ -256,20 +257,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
       // probabilities = exp2(s * scale - m_ref): one FFMA, one MUFU, one add per element, in place
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-      if (full) {
+      // masked columns hold -inf: exp2(-inf) = 0, no separate path (the scale is positive)
 #pragma unroll
-        for (int e = 0; e < 32; e++) {
-          s0[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s0[e]), sc, -m_use)));
-          s1[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s1[e]), sc, -m_use)));
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; e++) {
-          float x0 = ex2_approx(fmaf(__uint_as_float(s0[e]), sc, -m_use));
-          float x1 = ex2_approx(fmaf(__uint_as_float(s1[e]), sc, -m_use));
-          s0[e] = __float_as_uint(e < lim ? x0 : 0.f);
-          s1[e] = __float_as_uint(32 + e < lim ? x1 : 0.f);
-        }
+      for (int e = 0; e < 32; e++) {
+        s0[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s0[e]), sc, -m_use)));
+        s1[e] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(s1[e]), sc, -m_use)));
       }
 #pragma unroll
       for (int e = 0; e < 32; e += 4) {
