@@ -262,6 +262,7 @@ static double node_work(const OpNode& node, const std::vector<const TensorRec*>&
   double out_elems = (double)numel_of(node.out_shape);
   if (kd.op == Op::Matmul || kd.op == Op::FusedLinear || kd.op == Op::MatmulInt8) {
     double k = in[0]->shape.empty() ? 1.0 : (double)in[0]->shape.back();
+    if (kd.op == Op::FusedLinear && kd.i2 == 1 && !in[1]->shape.empty()) out_elems *= (double)in[1]->shape.back();  // rows x vocab, not rows
     return 2.0 * out_elems * k;
   }
   if (kd.op == Op::FusedAttention) {
@@ -394,6 +395,34 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
           g.b = wide.data(); g.b_dtype = x.dtype;
         }
         idx = 3;
+      } else if (kd.op == Op::FusedLinear && kd.i2 == 1) {
+        // Row argmax of a product that is never stored: out is int32 [rows...]; the GEMM merges per-row
+        // (value, column) keys into a zeroed u64 scratch, a small kernel turns them into indices.
+        TensorRec cmeta;
+        cmeta.dtype = in[0]->dtype;
+        cmeta.shape = {in[0]->shape[in[0]->shape.size() - 2], in[1]->shape.back()};
+        cmeta.strides = contiguous_strides(cmeta.shape);
+        AG_RETURN_IF_ERROR(build_gemm(*in[0], *in[1], cmeta, &g, &keep));
+        if (dry) return Status::OK();
+        if (std::string(k::matmul_path(g)) == "tcgen05" && g.batch == 1 && g.batch_inner == 1) {
+          TensorRec keys;
+          AG_RETURN_IF_ERROR(alloc_out({g.m}, DType::I64, &keys, nullptr));
+          cudaError_t ce = cudaMemsetAsync(keys.data(), 0, (size_t)g.m * 8, s);
+          if (ce != cudaSuccess) return Status::compute(std::string("argmax keys: ") + cudaGetErrorString(ce));
+          g.c = nullptr;
+          g.ep.argmax_keys = static_cast<unsigned long long*>(keys.data());
+          AG_LAUNCH(k::matmul(s, g));
+          AG_LAUNCH(k::argmax_finalize(s, g.ep.argmax_keys, static_cast<int32_t*>(out->data()), g.m));
+          return Status::OK();
+        }
+        // operands the tensor-core kernel cannot take: materialise the product, then the plain argmax
+        TensorRec prod;
+        AG_RETURN_IF_ERROR(alloc_out(cmeta.shape, cmeta.dtype, &prod, nullptr));
+        g.c = prod.data();
+        AG_LAUNCH(k::matmul(s, g));
+        TView pv = prod.view();
+        AG_LAUNCH(k::argmax(s, pv, ov));
+        return Status::OK();
       } else {
         AG_RETURN_IF_ERROR(build_gemm(*in[0], *in[1], *out, &g, &keep));
       }

@@ -156,6 +156,7 @@ struct Rewriter {
   const std::unordered_set<uint64_t>& keep;
   std::unordered_map<uint64_t, std::vector<uint64_t>> consumers;
   std::unordered_set<uint64_t> removed;
+  const std::unordered_set<uint64_t>* released = nullptr;   // ids whose caller-side handle is gone (null: unknown)
 
   Rewriter(Graph& gr, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& kp) : g(gr), keep(kp) {
     for (uint64_t id : order) {
@@ -304,6 +305,39 @@ static void rewrite_bias_act(Rewriter& rw, uint64_t id) {
   rw.replace({ab->id, c->id}, std::move(fused));
 }
 
+// matmul -> [reshape that keeps the last dim]* -> argmax, each with one consumer: the product is never
+// needed as a tensor, so the GEMM's epilogue takes the row maximum itself (a greedy-decoding LM head
+// then neither writes nor re-reads the [rows, vocab] logits). Half-precision 2-D products only: that is
+// what the tensor-core kernel computes; the executor falls back to matmul + argmax if operands turn
+// out not to be eligible for it.
+static void rewrite_matmul_argmax(Rewriter& rw, uint64_t id) {
+  const OpNode* mm = rw.g.get_node(id);
+  if (!mm || mm->op.op != Op::Matmul) return;
+  if (!(mm->out_dtype == DType::BF16 || mm->out_dtype == DType::F16) || mm->out_shape.size() != 2) return;
+  // Unlike the other rewrites this one removes a tensor a caller is likely to come back to (the logits),
+  // so it only fires once the caller has dropped its handles to the product and its reshapes.
+  auto dropped = [&](uint64_t nid) { return rw.released && rw.released->count(nid) != 0; };
+  if (!dropped(id)) return;
+  std::vector<uint64_t> chain{id};
+  const OpNode* c = rw.sole_consumer(id);
+  while (c && c->op.op == Op::Reshape && !c->out_shape.empty() && c->out_shape.back() == mm->out_shape.back()) {
+    if (!dropped(c->id)) return;
+    chain.push_back(c->id);
+    c = rw.sole_consumer(c->id);
+  }
+  if (!c || c->op.op != Op::Argmax) return;
+  chain.push_back(c->id);
+  OpNode fused;
+  fused.id = c->id;
+  fused.op.op = Op::FusedLinear;
+  fused.op.f0 = 1.0f;
+  fused.op.i2 = 1;                       // row argmax instead of a stored product
+  fused.inputs = mm->inputs;
+  fused.out_shape = c->out_shape;
+  fused.out_dtype = c->out_dtype;
+  rw.replace(chain, std::move(fused));
+}
+
 static void rewrite_embed_add(Rewriter& rw, uint64_t id) {
   const OpNode* add = rw.g.get_node(id);
   if (!add || add->op.op != Op::Add || add->inputs.size() != 2 || add->inputs[0] == add->inputs[1]) return;
@@ -323,15 +357,18 @@ static void rewrite_embed_add(Rewriter& rw, uint64_t id) {
   rw.replace({e0->id, e1->id, add->id}, std::move(fused));
 }
 
-std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep) {
+std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
+                               const std::unordered_set<uint64_t>* released) {
   std::vector<uint64_t> cur = order;
   if (g_patterns) {
     Rewriter rw(g, cur, keep);
+    rw.released = released;
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention_merge(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_linear(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_embed_add(rw, id); }
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_bias_act(rw, id); }
+    for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_matmul_argmax(rw, id); }
     std::vector<uint64_t> next;
     for (uint64_t id : cur) if (!rw.removed.count(id) && g.has_node(id)) next.push_back(id);
     cur.swap(next);

@@ -113,7 +113,7 @@ Status LazyRuntime::eval(uint64_t id) {
   AG_RETURN_IF_ERROR(graph_.topo_sort(id, &order));
   std::unordered_set<uint64_t> keep{id};
   for (auto& kv : prealloc_) keep.insert(kv.first);  // outputs the caller already holds pointers to
-  order = fusion::optimize(graph_, order, keep);
+  order = fusion::optimize(graph_, order, keep, &deferred_free_);
 
   // remaining uses inside this evaluation, to drop dead intermediates early
   for (uint64_t nid : order) {
@@ -161,7 +161,7 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
   AG_RETURN_IF_ERROR(copy.topo_sort(id, &order));
   std::unordered_set<uint64_t> keep{id};
   for (auto& kv : prealloc_) keep.insert(kv.first);
-  order = fusion::optimize(copy, order, keep);
+  order = fusion::optimize(copy, order, keep, &deferred_free_);
   for (uint64_t nid : order) {
     const OpNode* n = copy.get_node(nid);
     if (!n) continue;
@@ -169,6 +169,7 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
     if (n->op.op == Op::FusedLinear) {
       os << "[";
       if (n->op.i1 == 1) os << "int8,";
+      if (n->op.i2 == 1) os << "argmax,";
       if (n->op.f0 != 1.0f) os << "scale,";
       if (n->op.has_bias) os << "bias,";
       if (n->op.act == k::Act::GeluTanh) os << "gelu,"; else if (n->op.act == k::Act::GeluErf) os << "gelu_exact,"; else if (n->op.act == k::Act::Relu) os << "relu,";

@@ -176,7 +176,9 @@ Status infer_node(const MetaSource& src, OpNode* node);
 namespace fusion {
 // Reference rule (fusion.rs:243-285): linear element-wise chains -> FusedElementwise, plus the
 // graph-level rewrites of this build (linear epilogues, attention, embedding sum, layout sinks).
-std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep);
+// `released`: ids whose caller-side handle has been freed while ops still consume them.
+std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
+                               const std::unordered_set<uint64_t>* released = nullptr);
 void set_enabled(bool elementwise, bool patterns);
 void get_enabled(bool* elementwise, bool* patterns);
 }

@@ -48,6 +48,7 @@ struct TcParams {
   int tiles_m, tiles_n;
   int vec_ok;                  // C (and residual) rows are 16-byte aligned: 16-byte global accesses
   int bias_vec;                // bias pointer is 16-byte aligned
+  unsigned long long* argmax_keys;   // non-null: merge per-row (value, column) keys instead of storing C
   int* status;
 };
 
@@ -114,7 +115,7 @@ __device__ __forceinline__ void load_residual_group(const TcParams& p, const T* 
 
 template <typename T>
 __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint4 (&rpre)[4],
-                                               long long row0, int col0, int next_col0, long long c_off, int lane) {
+                                               long long row0, int col0, int next_col0, long long c_off, int lane, unsigned long long& best_key) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
   const int sub_row = lane >> 2, sub_chunk = lane & 3;
@@ -196,6 +197,23 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
       for (int e = 0; e < 32; e++) v[e] = fmaxf(v[e], 0.f);
       break;
     default: break;
+  }
+  if (p.argmax_keys) {
+    // Row argmax over this group's columns of the value as it would have been stored (rounded to T).
+    // Key = order-preserving bits of the value in the high word, inverted column in the low word: the
+    // larger key is the larger value, or the lower column among equals. NaNs are never selected,
+    // except in column 0, which then keeps the row (the serial scan's behaviour).
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+      int col = col0 + e;
+      float r = Cvt<T>::to(Cvt<T>::from(v[e]));
+      uint32_t b = __float_as_uint(r);
+      uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+      unsigned long long key = ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)col);
+      if (r != r) key = (col == 0) ? 0xffffffffffffffffull : 0ull;
+      if (col < p.n && key > best_key) best_key = key;
+    }
+    return;
   }
   uint8_t* my_row = stg + lane * kStgPitch;
   if (R) {
@@ -387,13 +405,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_after_sync();
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      unsigned long long best_key = 0;   // argmax mode: this row's best over the warp's column groups of the tile
 #pragma unroll 1
       for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
         int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
         epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                          c_off, lane);
+                          c_off, lane, best_key);
       }
+      if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
@@ -571,15 +591,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_after_sync();
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      unsigned long long best_key = 0;
       if (row0 < p.m) {   // a peer CTA whose rows lie past M has nothing to store
 #pragma unroll 1
         for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
           if (n0 + g * 32 >= p.n) break;
           int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
           epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                            c_off, lane);
+                            c_off, lane, best_key);
         }
       }
+      if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[acc]), 0));
@@ -783,6 +805,8 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.batch = (int)nb; p.batch_inner = (int)d.batch_inner;
   p.c_row = d.c_row; p.c_batch = d.c_batch; p.c_batch_inner = d.c_batch_inner; p.a_bcast = a_bcast; p.b_bcast = b_bcast;
   p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
+  p.argmax_keys = d.ep.argmax_keys;
+  if (p.argmax_keys && nb != 1) return Status::invalid("matmul: the row-argmax epilogue takes an unbatched product");
   auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
   p.vec_ok = (al16p(d.c) && d.c_row % 8 == 0 && d.c_batch % 8 == 0 && d.c_batch_inner % 8 == 0 &&
               (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
@@ -838,9 +862,26 @@ int matmul_take_status(cudaStream_t s) {
   return v;
 }
 
+__global__ void argmax_finalize_kernel(const unsigned long long* __restrict__ keys, int32_t* __restrict__ out, int64_t rows) {
+  pdl_wait();
+  pdl_trigger();
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  unsigned long long k = keys[i];
+  // no key (an all-NaN row) and the sticky-NaN key both mean column 0
+  out[i] = (k == 0ull || k == 0xffffffffffffffffull) ? 0 : (int32_t)(0xffffffffu - (uint32_t)(k & 0xffffffffu));
+}
+Status argmax_finalize(cudaStream_t s, const unsigned long long* keys, int32_t* out, int64_t rows) {
+  if (rows == 0) return Status::OK();
+  cudaError_t e = launch_pdl(argmax_finalize_kernel, dim3((unsigned)((rows + 255) / 256)), dim3(256), 0, s, keys, out, rows);
+  if (e != cudaSuccess) return cuda_status(e, "argmax_finalize");
+  return Status::OK();
+}
+
 Status matmul(cudaStream_t s, const GemmDesc& d) {
   if (d.m == 0 || d.n == 0 || d.batch == 0) return Status::OK();
   bool elig = tc_eligible(d);
+  if (d.ep.argmax_keys && (!elig || g_force_path == 1)) return Status::invalid("matmul: the row-argmax epilogue needs the tensor-core kernel");
   if (g_force_path == 2 && !elig) return Status::compute("matmul: tcgen05 path forced but operands are not TMA-compatible");
   if (elig && g_force_path != 1) {
     int* st = matmul_status_word();

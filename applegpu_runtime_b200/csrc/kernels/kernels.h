@@ -64,6 +64,10 @@ struct GemmEpilogue {
   Act act = Act::None;
   float alpha = 1.0f;              // applied to the accumulator before bias
   const float* b_scales = nullptr; // int8-weight path: per-output-channel scales [N]
+  // Row argmax instead of a stored product (tensor-core kernels, unbatched): each row's best
+  // (value rounded to the storage type, lowest column on ties) is merged into keys[row] with a 64-bit
+  // atomic max; C is not written. keys must be zeroed first; argmax_finalize turns them into int32.
+  unsigned long long* argmax_keys = nullptr;
 };
 struct GemmDesc {
   DType dtype;            // dtype of A and C (f32/f16/bf16)
@@ -82,6 +86,7 @@ struct GemmDesc {
 Status matmul(cudaStream_t s, const GemmDesc& d);
 // Reports which kernel family `matmul` would choose: "tcgen05" or "simt".
 const char* matmul_path(const GemmDesc& d);
+Status argmax_finalize(cudaStream_t s, const unsigned long long* keys, int32_t* out, int64_t rows);
 
 struct AttnDesc {
   DType dtype;

@@ -50,7 +50,9 @@ def greedy_generate(model, input_ids, max_tokens=50, use_cache=True, compiled=Tr
             logits, kv = gpt2_forward(model, ids, kv_cache=kv, last_only=True, compiled=compiled and kv is not None)
         else:
             logits, _ = gpt2_forward(model, ids, kv_cache=None, last_only=True)
-        nxt = gpu.argmax(logits).to_numpy().astype(np.int64).reshape(-1, 1)
+        nxt_t = gpu.argmax(logits)
+        del logits   # with the handle gone the LM head takes the row maximum in its own epilogue: no logits tensor
+        nxt = nxt_t.to_numpy().astype(np.int64).reshape(-1, 1)
         ids = np.concatenate([ids, nxt], axis=1)
     return ids
 

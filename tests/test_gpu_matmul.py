@@ -223,6 +223,34 @@ def test_matmul_int8_weights_on_tensor_cores_with_fused_epilogue(gpu_dev):
     assert rel_err(gpu_dev.matmul_int8(gx, q, s).to_numpy(), y3.astype(np.float64)) <= 8e-3
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k,kmajor", [(300, 50257, 64, True), (1000, 777, 96, True), (512, 1032, 128, False), (5, 40, 64, True)])
+def test_matmul_argmax_epilogue_is_bit_exact_with_matmul_then_argmax(gpu_dev, dtype, m, n, k, kmajor):
+    """argmax(x @ W) with the logits handle dropped runs as one GEMM whose epilogue takes the row maximum
+    (no logits tensor). The indices must equal those of the stored-then-scanned form exactly: same
+    rounding of each value to the storage type, lowest column on ties (half-precision logits tie often)."""
+    rng = np.random.default_rng(m + n)
+    a = (rng.integers(-3, 4, (m, k))).astype(np.float32)            # small integers: exact products, many ties
+    b = (rng.integers(-2, 3, (n, k) if kmajor else (k, n))).astype(np.float32)
+    ga, gb = up(gpu_dev, a, dtype), up(gpu_dev, b, dtype)
+    w = gpu_dev.transpose(gb) if kmajor else gb
+    logits = ga @ w
+    ref_idx = gpu_dev.argmax(logits).to_numpy()                      # handle held: two kernels
+    stored = logits.to_numpy().astype(np.float32)
+    assert np.array_equal(ref_idx, R.argmax(stored))
+    fused = gpu_dev.argmax(gpu_dev.reshape(ga @ w, [m, n]))
+    plan = fused.plan()
+    assert "fused_linear[argmax,]" in plan and "argmax_" not in plan.replace("fused_linear[argmax,]", "")
+    assert np.array_equal(fused.to_numpy(), ref_idx)
+    # random real-valued case as well
+    a2 = rng.standard_normal((m, k)).astype(np.float32); b2 = rng.standard_normal(b.shape).astype(np.float32)
+    ga2, gb2 = up(gpu_dev, a2, dtype), up(gpu_dev, b2, dtype)
+    w2 = gpu_dev.transpose(gb2) if kmajor else gb2
+    l2 = ga2 @ w2
+    want = gpu_dev.argmax(l2).to_numpy()
+    assert np.array_equal(gpu_dev.argmax(ga2 @ w2).to_numpy(), want)
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])

@@ -327,3 +327,23 @@ def test_op_tape_replays_the_gpt2_forward_at_a_longer_kv_length(gpu):
     gpu.tape_begin([x])
     with pytest.raises(ValueError, match="not produced on the tape"):
         gpu.tape_end(1, [z])
+
+
+def test_lm_head_argmax_fuses_only_after_the_logits_handle_is_dropped(gpu):
+    x = gpu.cast(gpu.from_numpy(np.ones((8, 32), np.float32)), "bfloat16")
+    wte = gpu.cast(gpu.from_numpy(np.ones((50, 32), np.float32)), "bfloat16")
+    logits = gpu.reshape(x @ gpu.transpose(wte), [2, 4, 50])      # the tail of gpt2_forward
+    nxt = gpu.argmax(logits)
+    assert nxt.shape == [2, 4]
+    held = [l.split(" ")[0] for l in nxt.plan().strip().splitlines()]
+    assert held[-1].startswith("argmax")                           # logits still reachable: kept as a tensor
+    assert not any(h.startswith("fused_linear[argmax") for h in held)
+    del logits
+    dropped = [l.split(" ")[0] for l in nxt.plan().strip().splitlines()]
+    assert dropped[-1].startswith("fused_linear[argmax,]") and not any(h.startswith("argmax") for h in dropped)
+    # fp32 products keep the two-kernel form (the tensor-core kernel is half precision only)
+    x32 = gpu.from_numpy(np.ones((8, 32), np.float32)); w32 = gpu.from_numpy(np.ones((50, 32), np.float32))
+    l32 = x32 @ gpu.transpose(w32)
+    n32 = gpu.argmax(l32)
+    del l32
+    assert not any(l.startswith("fused_linear[argmax") for l in n32.plan().splitlines())
