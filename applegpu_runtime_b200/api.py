@@ -518,6 +518,11 @@ def set_matmul_path(mode):
     _L().applegpu_set_matmul_path({"auto": 0, "simt": 1, "tcgen05": 2, "tcgen05_1cta": 3, "tcgen05_pair": 4}[mode])
 
 
+def set_f32_split(on=True):
+    """Large float32 matmuls as a three-term bf16 split on the tensor cores (default) or always on CUDA cores."""
+    _L().applegpu_set_f32_split(bool(on))
+
+
 def set_attention_path(mode):
     """'auto' (single-kernel attention when eligible) or 'composed' (GEMM + softmax + GEMM)."""
     _L().applegpu_set_attention_path({"auto": 0, "composed": 1}[mode])

@@ -191,6 +191,50 @@ static Status build_gemm(const TensorRec& a, const TensorRec& b, const TensorRec
   return Status::OK();
 }
 
+// float32 matmul on the tensor cores: each operand is split into three bf16 terms (kernels/index_quant.cu
+// split_bf16x3) and one bf16 GEMM over the six-fold K extent accumulates the six largest cross terms in
+// float32, smallest first; C, bias and residual stay float32. Error is ~2^-22 relative to the exact
+// product (inside the reference's 1e-4 tolerance by three orders of magnitude) at about a sixth of the
+// bf16 tensor rate, against the CUDA-core kernel's ~30 TFLOP/s. Taken for products large enough to pay for
+// the two split passes and whose layouts the TMA path accepts; *done stays false otherwise.
+namespace { bool g_f32_split = true; }
+void set_f32_split(bool on) { g_f32_split = on; }
+static Status matmul_f32_split(cudaStream_t s, const k::GemmDesc& g, bool* done) {
+  *done = false;
+  if (!g_f32_split) return Status::OK();
+  const double flops = 2.0 * (double)g.m * (double)g.n * (double)g.k * (double)g.batch * (double)g.batch_inner;
+  if (flops < 2.0e9 || g.batch_inner != 1 || g.k % 8 != 0 || g.m < 64 || g.n < 64) return Status::OK();
+  if (g.a_col != 1 || g.a_row % 4 != 0 || g.a_batch % 4 != 0) return Status::OK();
+  const bool b_nmajor = g.b_col == 1;            // [K, N] rows
+  const bool b_kmajor = g.b_row == 1;            // [N, K] rows (a transposed view)
+  if (!b_nmajor && !b_kmajor) return Status::OK();
+  if (b_nmajor && (g.n % 8 != 0 || g.b_row % 4 != 0)) return Status::OK();
+  if (b_kmajor && !b_nmajor && g.b_col % 4 != 0) return Status::OK();
+  if (g.b_batch % 4 != 0) return Status::OK();
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(g.a) || !al16(g.b)) return Status::OK();
+  const int64_t a_copies = (g.batch > 1 && g.a_batch != 0) ? g.batch : 1;
+  const int64_t b_copies = (g.batch > 1 && g.b_batch != 0) ? g.batch : 1;
+  if (a_copies > 65535 || b_copies > 65535) return Status::OK();
+  TensorRec a2, b2;
+  AG_RETURN_IF_ERROR(alloc_out({a_copies, g.m, 6 * g.k}, DType::BF16, &a2, nullptr));
+  AG_RETURN_IF_ERROR(alloc_out({b_copies, 6 * g.k, g.n}, DType::BF16, &b2, nullptr));
+  k::GemmDesc h = g;
+  h.dtype = DType::BF16; h.b_dtype = DType::BF16; h.c_f32 = true;
+  h.k = 6 * g.k;
+  h.a = a2.data(); h.a_row = 6 * g.k; h.a_col = 1; h.a_batch = a_copies > 1 ? g.m * 6 * g.k : 0;
+  h.b = b2.data();
+  if (b_nmajor) { h.b_row = g.n; h.b_col = 1; } else { h.b_row = 1; h.b_col = 6 * g.k; }
+  h.b_batch = b_copies > 1 ? 6 * g.k * g.n : 0;
+  if (std::string(k::matmul_path(h)) != "tcgen05") return Status::OK();   // e.g. the CUDA-core kernel is forced
+  AG_LAUNCH(k::split_bf16x3(s, static_cast<const float*>(g.a), a2.data(), g.m, g.k, g.a_row, a_copies, g.a_batch, /*stack_rows=*/false, /*b_side=*/false));
+  if (b_nmajor) AG_LAUNCH(k::split_bf16x3(s, static_cast<const float*>(g.b), b2.data(), g.k, g.n, g.b_row, b_copies, g.b_batch, /*stack_rows=*/true, /*b_side=*/true));
+  else AG_LAUNCH(k::split_bf16x3(s, static_cast<const float*>(g.b), b2.data(), g.n, g.k, g.b_col, b_copies, g.b_batch, /*stack_rows=*/false, /*b_side=*/true));
+  AG_LAUNCH(k::matmul(s, h));
+  *done = true;
+  return Status::OK();
+}
+
 static k::UnOp unop_of(Op op) {
   switch (op) {
     case Op::Neg: return k::UnOp::Neg; case Op::Relu: return k::UnOp::Relu; case Op::Exp: return k::UnOp::Exp;
@@ -436,6 +480,11 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
           if (keep.back().shape != out->shape) return Status::compute("fused residual shape mismatch");
           g.ep.residual = keep.back().data();
         }
+      }
+      if (!int8_w && g.dtype == DType::F32 && g.b_dtype == DType::F32 && !dry) {
+        bool done = false;
+        AG_RETURN_IF_ERROR(matmul_f32_split(s, g, &done));
+        if (done) return Status::OK();
       }
       AG_LAUNCH(k::matmul(s, g));
       return Status::OK();

@@ -15,6 +15,7 @@
 
 namespace ag {
 extern bool g_fused_attention;
+void set_f32_split(bool on);
 uint64_t launch_count();
 namespace profile { void enable(bool on); void clear(); std::string report(); }
 namespace k {
@@ -1075,6 +1076,7 @@ int32_t applegpu_device(void) { return DeviceCtx::get().device; }
 const char* applegpu_device_name(void) { return DeviceCtx::get().name.c_str(); }
 uint64_t applegpu_launch_count(void) { return ag::launch_count(); }
 void applegpu_set_matmul_path(int32_t mode) { k::set_matmul_path(mode); }
+void applegpu_set_f32_split(bool on) { ag::set_f32_split(on); }
 void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();

@@ -49,6 +49,7 @@ struct TcParams {
   int vec_ok;                  // C (and residual) rows are 16-byte aligned: 16-byte global accesses
   int bias_vec;                // bias pointer is 16-byte aligned
   unsigned long long* argmax_keys;   // non-null: merge per-row (value, column) keys instead of storing C
+  int c_f32;                         // C, bias and residual are float32 (operands are still 16-bit)
   int* status;
 };
 
@@ -122,7 +123,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 
   // 1. residual tile -> shared (coalesced). On the vector path the values were fetched one group
   //    ahead; the next group's fetch is issued here and lands while this group is computed.
-  if (R) {
+  if (R && !p.c_f32) {
     if (p.vec_ok) {
 #pragma unroll
       for (int it = 0; it < 4; it++)
@@ -145,6 +146,55 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
   float v[32];
 #pragma unroll
   for (int e = 0; e < 32; e++) v[e] = __uint_as_float(acc[e]);
+
+  if (p.c_f32) {
+    // float32 output (split-precision fp32 product): bias (staged as floats where the int8 scales
+    // would be) and residual are float32; each lane stores its own row's 32 columns, 128 contiguous bytes.
+    float* Cf = reinterpret_cast<float*>(p.c) + c_off;
+    const float* Rf = p.residual ? reinterpret_cast<const float*>(p.residual) + c_off : nullptr;
+    if (p.alpha != 1.0f) {
+#pragma unroll
+      for (int e = 0; e < 32; e++) v[e] *= p.alpha;
+    }
+    if (scale_s) {
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        float4 b4 = *reinterpret_cast<const float4*>(scale_s + g * 4);
+        v[g * 4 + 0] += b4.x; v[g * 4 + 1] += b4.y; v[g * 4 + 2] += b4.z; v[g * 4 + 3] += b4.w;
+      }
+    }
+    switch ((Act)p.act) {
+      case Act::GeluTanh:
+#pragma unroll
+        for (int e = 0; e < 32; e++) v[e] = gelu_tanh_f(v[e]);
+        break;
+      case Act::GeluErf:
+#pragma unroll
+        for (int e = 0; e < 32; e++) v[e] = gelu_erf_f(v[e]);
+        break;
+      case Act::Relu:
+#pragma unroll
+        for (int e = 0; e < 32; e++) v[e] = fmaxf(v[e], 0.f);
+        break;
+      default: break;
+    }
+    const long long gm = row0 + lane;
+    if (gm < p.m) {
+      float* crow = Cf + gm * p.c_row + col0;
+      const float* rrow = Rf ? Rf + gm * p.c_row + col0 : nullptr;
+      if (p.vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+          float4 o = make_float4(v[g * 4 + 0], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+          if (rrow) { float4 r4 = *reinterpret_cast<const float4*>(rrow + g * 4); o.x += r4.x; o.y += r4.y; o.z += r4.z; o.w += r4.w; }
+          *reinterpret_cast<float4*>(crow + g * 4) = o;
+        }
+      } else {
+        for (int e = 0; e < 32 && col0 + e < p.n; e++) crow[e] = v[e] + (rrow ? rrow[e] : 0.f);
+      }
+    }
+    return;
+  }
 
   // 3. epilogue math: one uniform test per option, then a straight 32-element loop
   if (p.alpha != 1.0f) {
@@ -190,7 +240,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
       break;
     case Act::GeluErf:
 #pragma unroll
-      for (int e = 0; e < 32; e++) v[e] = gelu_erf_f(v[e]);
+      for (int e = 0; e < 32; e++) v[e] = gelu_erf_fast_f(v[e]);
       break;
     case Act::Relu:
 #pragma unroll
@@ -381,7 +431,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
-      if (p.bias) {
+      if (p.bias && !p.c_f32) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -390,15 +440,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       }
       float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
-      if (p.b_scales) {
+      // the float slots hold the int8 per-channel scales, or the float32 bias of a float32-output product
+      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : p.b_scales;
+      if (fsrc) {
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
           int ci = n0 + (pair + 2 * gi) * 32 + lane;
-          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(p.b_scales + ci) : 0.f;
+          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(fsrc + ci) : 0.f;
         }
       }
       uint4 rpre[4];
-      if (p.residual && p.vec_ok && n0 + pair * 32 < p.n)
+      if (p.residual && p.vec_ok && !p.c_f32 && n0 + pair * 32 < p.n)
         load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
       __syncwarp();
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
@@ -410,7 +462,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
         int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
-        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+        epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
                           c_off, lane, best_key);
       }
       if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
@@ -567,7 +619,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
-      if (p.bias) {
+      if (p.bias && !p.c_f32) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -576,15 +628,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
       float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
-      if (p.b_scales) {
+      // the float slots hold the int8 per-channel scales, or the float32 bias of a float32-output product
+      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : p.b_scales;
+      if (fsrc) {
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
           int ci = n0 + (pair + 2 * gi) * 32 + lane;
-          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(p.b_scales + ci) : 0.f;
+          scale_s[gi * 32 + lane] = ci < p.n ? __ldg(fsrc + ci) : 0.f;
         }
       }
       uint4 rpre[4];
-      if (p.residual && p.vec_ok && n0 + pair * 32 < p.n)
+      if (p.residual && p.vec_ok && !p.c_f32 && n0 + pair * 32 < p.n)
         load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
       __syncwarp();
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }
@@ -597,7 +651,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
           if (n0 + g * 32 >= p.n) break;
           int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
-          epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, p.bias ? bias_s + gi * 32 : nullptr, p.b_scales ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
+          epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
                             c_off, lane, best_key);
         }
       }
@@ -806,9 +860,11 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   p.c_row = d.c_row; p.c_batch = d.c_batch; p.c_batch_inner = d.c_batch_inner; p.a_bcast = a_bcast; p.b_bcast = b_bcast;
   p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
   p.argmax_keys = d.ep.argmax_keys;
+  p.c_f32 = d.c_f32 ? 1 : 0;
   if (p.argmax_keys && nb != 1) return Status::invalid("matmul: the row-argmax epilogue takes an unbatched product");
   auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-  p.vec_ok = (al16p(d.c) && d.c_row % 8 == 0 && d.c_batch % 8 == 0 && d.c_batch_inner % 8 == 0 &&
+  const int64_t cvec = d.c_f32 ? 4 : 8;   // elements per 16 bytes of C
+  p.vec_ok = (al16p(d.c) && d.c_row % cvec == 0 && d.c_batch % cvec == 0 && d.c_batch_inner % cvec == 0 &&
               (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
   p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
   long long num_tiles = tiles_m * tiles_n * nb;

@@ -298,4 +298,53 @@ Status cast(cudaStream_t s, const TView& in, const TView& out) {
   }
 }
 
+
+// ── fp32 -> 3 x bf16 split (operands of the split-precision fp32 matmul) ─────
+// A product of two split sums keeps the six largest cross terms:
+//   a*b ~ a2*b0 + a1*b1 + a0*b2 + a1*b0 + a0*b1 + a0*b0      (smallest first)
+// so the A side is laid out as terms {2,1,0,1,0,0} and the B side as {0,1,2,0,1,0}; one bf16 GEMM over
+// the six-fold K extent with fp32 accumulation then yields the fp32 product to ~2^-22 relative.
+__global__ void __launch_bounds__(256) split_bf16x3_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t rows, int64_t cols,
+                                                            int64_t in_row_stride, int64_t in_batch_stride, int stack_rows, int b_side) {
+  const int64_t packs_per_row = cols / 8;
+  const int64_t total = rows * packs_per_row;
+  const float* src = in + (int64_t)blockIdx.y * in_batch_stride;
+  __nv_bfloat16* dst = out + (int64_t)blockIdx.y * rows * cols * 6;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / packs_per_row, c = (i % packs_per_row) * 8;
+    const float4 x0 = *reinterpret_cast<const float4*>(src + r * in_row_stride + c);
+    const float4 x1 = *reinterpret_cast<const float4*>(src + r * in_row_stride + c + 4);
+    const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    Pack<__nv_bfloat16> t[3];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      __nv_bfloat16 h0 = __float2bfloat16_rn(x[e]);
+      float r1 = x[e] - __bfloat162float(h0);
+      __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+      float r2 = r1 - __bfloat162float(h1);
+      t[0].v[e] = h0; t[1].v[e] = h1; t[2].v[e] = __float2bfloat16_rn(r2);
+    }
+#pragma unroll
+    for (int k = 0; k < 6; k++) {
+      const int a_pat[6] = {2, 1, 0, 1, 0, 0}, b_pat[6] = {0, 1, 2, 0, 1, 0};
+      const int term = b_side ? b_pat[k] : a_pat[k];
+      __nv_bfloat16* o = stack_rows ? dst + ((int64_t)k * rows + r) * cols + c : dst + r * (cols * 6) + (int64_t)k * cols + c;
+      st16(o, t[term]);
+    }
+  }
+}
+
+Status split_bf16x3(cudaStream_t s, const float* in, void* out_bf16, int64_t rows, int64_t cols, int64_t in_row_stride, int64_t batches,
+                    int64_t in_batch_stride, bool stack_rows, bool b_side) {
+  if (rows == 0 || cols == 0 || batches == 0) return Status::OK();
+  if (cols % 8 != 0 || in_row_stride % 4 != 0 || in_batch_stride % 4 != 0 || !aligned16(in) || !aligned16(out_bf16))
+    return Status::invalid("split_bf16x3 needs 16-byte aligned rows of a multiple of 8 columns");
+  if (batches > 65535) return Status::invalid("split_bf16x3: too many batches");
+  dim3 grid((unsigned)grid_for(rows * (cols / 8), 256, 8), (unsigned)batches, 1);
+  split_bf16x3_kernel<<<grid, 256, 0, s>>>(in, static_cast<__nv_bfloat16*>(out_bf16), rows, cols, in_row_stride, in_batch_stride, stack_rows ? 1 : 0,
+                                           b_side ? 1 : 0);
+  AG_CHECK_LAUNCH("split_bf16x3");
+  return Status::OK();
+}
+
 }}  // namespace ag::k

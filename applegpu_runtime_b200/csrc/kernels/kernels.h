@@ -81,11 +81,19 @@ struct GemmDesc {
   int64_t a_row, a_col, a_batch, a_batch_inner = 0;
   int64_t b_row, b_col, b_batch, b_batch_inner = 0;  // b_row = stride along k, b_col = stride along n
   int64_t c_row, c_batch, c_batch_inner = 0;
+  // Operands are f16/bf16 but C, bias and residual are float32 (the split-precision fp32 product).
+  bool c_f32 = false;
   GemmEpilogue ep;
 };
 Status matmul(cudaStream_t s, const GemmDesc& d);
 // Reports which kernel family `matmul` would choose: "tcgen05" or "simt".
 const char* matmul_path(const GemmDesc& d);
+// fp32 -> three bf16 terms x = x0 + x1 + x2 (each the bf16 rounding of what the previous ones left), written
+// six times in the order a product of two such sums is accumulated: out holds, for t = 0..5, term pattern[t]
+// of the input, either side by side along the columns (stack_rows = false: out[r, t*cols + c], row pitch
+// 6*cols) or block over block (stack_rows = true: out[t*rows + r, c]). `batches` matrices, strides in elements.
+Status split_bf16x3(cudaStream_t s, const float* in, void* out_bf16, int64_t rows, int64_t cols, int64_t in_row_stride, int64_t batches,
+                    int64_t in_batch_stride, bool stack_rows, bool b_side);
 Status argmax_finalize(cudaStream_t s, const unsigned long long* keys, int32_t* out, int64_t rows);
 
 struct AttnDesc {

@@ -163,8 +163,6 @@ def main(argv=None):
     for dt in dtypes:
         if args.op in ("all", "matmul"):
             for s in ([shape] if shape else [[8, 1024, 1024, 1024], [8, 2048, 2048, 2048], [8, 4096, 4096, 4096]]):
-                if dt == "float32" and s[1] >= 4096 and not shape:
-                    continue  # 1.1 TFLOP on the CUDA-core kernel: run explicitly with --shape
                 out.append(bench_matmul(rng, dt, *s, args.iters, args))
         if args.op in ("all", "gpt2_gemms") and dt != "float32":
             for (m, n, k) in [(8192, 2304, 768), (8192, 768, 768), (8192, 3072, 768), (8192, 768, 3072)]:

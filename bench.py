@@ -204,7 +204,7 @@ def run_b200(args):
         h = host_ids[i % n_buf]
         ids_t = gpu.GpuTensor(lib.applegpu_ffi_from_host(ctypes.c_void_p(h.data_ptr()), (ctypes.c_uint64 * 1)(n_tok), 1, 5))
         pos_t = gpu.GpuTensor(lib.applegpu_ffi_from_host(ctypes.c_void_p(host_pos.data_ptr()), (ctypes.c_uint64 * 1)(n_tok), 1, 5))
-        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(ids_t, pos_t))
+        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(ids_t, pos_t), compiled=True)   # op tape: one library call per forward
         nxt = gpu.argmax(logits)  # [B, T] int32: the step's result
         del logits
         if lib.applegpu_ffi_read_bytes(nxt.id, ctypes.c_void_p(host_out.data_ptr()), n_tok * 4) != 0:
@@ -246,7 +246,7 @@ def run_b200(args):
         h = host_ids[i % n_buf]
         ids_t = gpu.GpuTensor(lib.applegpu_ffi_from_host(ctypes.c_void_p(h.data_ptr()), (ctypes.c_uint64 * 1)(n_tok), 1, 5))
         pos_t = gpu.GpuTensor(lib.applegpu_ffi_from_host(ctypes.c_void_p(host_pos.data_ptr()), (ctypes.c_uint64 * 1)(n_tok), 1, 5))
-        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(ids_t, pos_t))
+        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(ids_t, pos_t), compiled=True)   # op tape: one library call per forward
         nxt = gpu.argmax(logits)
         del logits  # greedy serving keeps only the tokens: the LM head's epilogue then takes the row maximum itself
         if lib.applegpu_ffi_read_bytes_async(nxt.id, ctypes.c_void_p(host_outs[i % 2].data_ptr()), n_tok * 4) != 0:

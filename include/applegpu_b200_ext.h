@@ -142,6 +142,9 @@ APPLEGPU_API const char* applegpu_matmul_path(uint64_t a_id, uint64_t b_id, bool
 /* 0 auto, 1 force the CUDA-core kernel, 2 require a tcgen05 kernel, 3 tcgen05 with single-CTA
  * tiles only, 4 tcgen05 with CTA-pair 256 x 256 tiles (cta_group::2) where the shape is large enough. */
 APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
+/* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
+ * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
+APPLEGPU_API void applegpu_set_f32_split(bool on);
 /* 0 auto (single-kernel attention when head dim is 64 and dtype is f16/bf16), 1 always compose
  * attention from GEMM + softmax + GEMM with materialised scores. */
 APPLEGPU_API void applegpu_set_attention_path(int32_t mode);

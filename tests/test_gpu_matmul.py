@@ -251,6 +251,34 @@ def test_matmul_argmax_epilogue_is_bit_exact_with_matmul_then_argmax(gpu_dev, dt
     assert np.array_equal(gpu_dev.argmax(ga2 @ w2).to_numpy(), want)
 
 
+@pytest.mark.parametrize("shape_a,shape_b,bt", [((1024, 1024), (1024, 1024), False), ((3, 520, 768), (3, 768, 1032), False), ((2, 1000, 512), (512, 776), False),
+                                                ((2048, 768), (1000, 768), True)])
+def test_matmul_f32_split_precision_on_tensor_cores(gpu_dev, shape_a, shape_b, bt):
+    """float32 products of at least 2 GFLOP: three bf16 terms per operand, six cross terms accumulated in
+    float32 on the tensor cores. Bar: the reference's 1e-4 (python/tests/test_batched_ops.py:20-54); measured
+    error is orders of magnitude below it and must match the CUDA-core kernel to 1e-5 of the largest entry."""
+    rng = np.random.default_rng(sum(shape_a) + sum(shape_b))
+    a = rng.standard_normal(shape_a).astype(np.float32); b = rng.standard_normal(shape_b).astype(np.float32)
+    ga, gb = gpu_dev.from_numpy(a), gpu_dev.from_numpy(b)
+    w = gpu_dev.transpose(gb) if bt else gb
+    got = (ga @ w).to_numpy()
+    ref = np.matmul(a.astype(np.float64), (b.T if bt else b).astype(np.float64))
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-4)
+    assert rel_err(got, ref) <= 2e-6
+    gpu_dev.set_f32_split(False)
+    try:
+        simt = (ga @ w).to_numpy()
+    finally:
+        gpu_dev.set_f32_split(True)
+    assert rel_err(got, simt.astype(np.float64)) <= 1e-5
+    # fused epilogue in float32: bias, GELU, residual
+    if a.ndim == 2 and not bt:
+        bias = rng.standard_normal(shape_b[-1]).astype(np.float32); res = rng.standard_normal(ref.shape).astype(np.float32)
+        y = gpu_dev.from_numpy(res) + gpu_dev.gelu(gpu_dev.add_bias(ga @ gb, gpu_dev.from_numpy(bias)))
+        want = R.gelu((ref + bias).astype(np.float32)).astype(np.float64) + res
+        np.testing.assert_allclose(y.to_numpy(), want, rtol=1e-4, atol=1e-4)
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])
