@@ -86,8 +86,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tiles = (p.tq + kQ - 1) / kQ;
-  const int qt = q_tiles - 1 - (int)blockIdx.x;   // heaviest (longest causal prefix) tiles first
-  const int bh = (int)blockIdx.y;
+  // blockIdx.x (the index CTAs are launched along first) runs over (batch, head); blockIdx.y over query
+  // tiles, longest causal prefix first: every heavy tile of every head starts before any light one, which
+  // is the longest-processing-time order and keeps the last wave short.
+  const int qt = q_tiles - 1 - (int)blockIdx.y;
+  const int bh = (int)blockIdx.x;
   const int b = bh / p.heads, h = bh % p.heads;
   const int q0 = qt * kQ;
   int n_blocks = (p.tk + kKV - 1) / kKV;
@@ -331,7 +334,7 @@ bool attention_fused_eligible(const AttnDesc& d) {
   if (!(d.dtype == DType::BF16 || d.dtype == DType::F16)) return false;
   if (d.d != kD || d.dv != kD) return false;
   if (d.tq < 1 || d.tk < 1 || d.batch < 1 || d.heads < 1) return false;
-  if (d.tq > 0x3fffffff || d.tk > 0x3fffffff || d.batch * d.heads > 65535) return false;
+  if (d.tq > 0x3fffffff || d.tk > 0x3fffffff || d.batch * d.heads > 0x7fffffff || (d.tq + kQ - 1) / kQ > 65535) return false;
   return attn_view_ok(d.q, d.q_b, d.q_h, d.q_t, d.batch, d.heads) && attn_view_ok(d.k, d.k_b, d.k_h, d.k_t, d.batch, d.heads) &&
          attn_view_ok(d.v, d.v_b, d.v_h, d.v_t, d.batch, d.heads);
 }
@@ -365,7 +368,7 @@ Status attention(cudaStream_t s, const AttnDesc& d) {
   p.o_vec = ((reinterpret_cast<uintptr_t>(d.o) & 15u) == 0 && d.o_t % 8 == 0 && d.o_h % 8 == 0 && d.o_b % 8 == 0) ? 1 : 0;
   p.scale_log2 = d.scale * 1.4426950408889634f;
   p.status = st;
-  dim3 grid((unsigned)((d.tq + kQ - 1) / kQ), (unsigned)(d.batch * d.heads), 1);
+  dim3 grid((unsigned)(d.batch * d.heads), (unsigned)((d.tq + kQ - 1) / kQ), 1);
   if (d.dtype == DType::BF16) return launch_attention<__nv_bfloat16>(s, mq, mk, mv, p, grid);
   return launch_attention<__half>(s, mq, mk, mv, p, grid);
 }
