@@ -196,7 +196,8 @@ def run_b200(args):
     gpu.synchronize()
 
     def step_resident(i):
-        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(dev_ids[i % n_buf], dev_pos))
+        # compiled=True: the forward's op list is recorded once on an op tape and replayed (one library call per step)
+        logits, _ = gpu.gpt2_forward(model, shape_ids, device_ids=(dev_ids[i % n_buf], dev_pos), compiled=True)
         logits.eval()
         return logits
 
