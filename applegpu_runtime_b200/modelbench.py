@@ -48,7 +48,7 @@ def bench_prefill(dtype, batch, seq, iters):
     ids = np.random.default_rng(0).integers(0, GPT2_SMALL["vocab_size"], (batch, seq))
 
     def step():
-        gpt2_forward(model, ids)[0].eval()
+        gpt2_forward(model, ids, compiled=True)[0].eval()   # op tape: recorded by the first warm-up call, replayed after
 
     ms = _time(step, iters, 3)
     flops = batch * seq * (_gemm_flops_per_token(GPT2_SMALL) + 4 * seq * GPT2_SMALL["n_embd"] * GPT2_SMALL["n_layer"])
