@@ -136,6 +136,20 @@ def test_taped_decode_steps_give_the_same_tokens_and_logits(gpu_dev):
     assert gpu_dev.tensor_count() <= n0 + 4          # replayed intermediates do not pile up
 
 
+def test_kv_cache_decode_is_not_slower_than_recomputing(gpu_dev):
+    """The reference's benchmark-as-test (python/tests/test_gpt2.py:106-123): generating with the KV cache
+    must take at most 1.5x the time of recomputing the whole prefix every step."""
+    import time
+    m = gpu_dev.init_gpt2_weights(CFG_MID, seed=10, dtype="bfloat16")
+    ids = np.random.default_rng(10).integers(0, CFG_MID["vocab_size"], (2, 128))
+    gpu_dev.greedy_generate(m, ids, max_tokens=3, use_cache=True)       # warm both paths (pool, tensor maps, tape)
+    gpu_dev.greedy_generate(m, ids, max_tokens=3, use_cache=False)
+    t0 = time.perf_counter(); a = gpu_dev.greedy_generate(m, ids, max_tokens=12, use_cache=True); t_cached = time.perf_counter() - t0
+    t0 = time.perf_counter(); b = gpu_dev.greedy_generate(m, ids, max_tokens=12, use_cache=False); t_full = time.perf_counter() - t0
+    assert a.shape == b.shape == (2, 140)
+    assert t_cached <= 1.5 * t_full, (t_cached, t_full)
+
+
 def test_mlp_config_fp32(gpu_dev):
     # BASELINE config 0: Linear(64,128) -> ReLU -> Linear(128,10), batch 32, default nn.Linear init, seed 0
     torch.manual_seed(0)
