@@ -1,0 +1,177 @@
+// Skinny matmul: C[M, N] = A[M, K] * B[K, N] with M <= 16 (a decode step: one new token per sequence)
+// and 16-bit operands. The product is bound by reading B once (a weight matrix); the 128-row
+// tensor-core tiles would leave it on N/256 CTAs (3..12 of 148 SMs) at one SM's share of HBM bandwidth
+// each. Here the grid is (N / 64 column slabs) x (K / 128 row slabs): every CTA streams a 128 x 64 block
+// of B with coalesced 128-byte rows, keeps its 16 x 128 block of A in shared memory, and writes an fp32
+// partial [M, 64] to a workspace; the last CTA to finish a column slab (a counter per slab) adds the
+// partials in K order (so the result does not depend on scheduling), applies the epilogue (alpha,
+// bias, activation, residual) and stores the slab. Same arithmetic contract as the other matmul kernels
+// (kernel_templates.rs:1029-1066): float accumulation, one rounding on store.
+#include "common.cuh"
+#include <mutex>
+
+namespace ag { namespace k {
+
+constexpr int kSkN = 64;      // columns per CTA
+constexpr int kSkK = 128;     // K rows per CTA
+constexpr int kSkMaxM = 16;
+constexpr int kSkThreads = 256;
+constexpr int64_t kSkMaxN = 65536;      // one counter per 64-column slab
+constexpr int kSkMaxKSlabs = 64;
+constexpr int64_t kSkMaxPartials = 1 << 18;   // k_slabs * n per launch: a 16 MB fp32 workspace
+
+struct SkinnyParams {
+  const void* a; const void* b; void* c;
+  const void* bias; const void* residual;
+  float alpha; int act;
+  int m, n, k;
+  long long a_row, b_row, c_row;
+  int a_vec;                 // A rows are 16-byte aligned
+  float* partial;            // [k_slabs][16][n]
+  unsigned int* counters;    // one per column slab, zero between launches
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kSkThreads) gemm_skinny_kernel(const SkinnyParams p) {
+  __shared__ float sA[kSkMaxM][kSkK];              // this CTA's block of A, as float
+  __shared__ float sSum[kSkThreads / 32][kSkMaxM][kSkN];
+  __shared__ unsigned int s_last;
+  const int n0 = blockIdx.x * kSkN, k0 = blockIdx.y * kSkK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* A = reinterpret_cast<const T*>(p.a);
+  const T* B = reinterpret_cast<const T*>(p.b);
+  pdl_wait();
+  pdl_trigger();
+  // B first: every load of this CTA's 128 x 64 block is issued before anything waits on one. A warp owns
+  // 16 consecutive K rows; per instruction its two half-warps read two rows, 16 lanes x 8 bytes each.
+  const int half = lane >> 4, cl = lane & 15;
+  const int col = n0 + cl * 4;
+  uint2 bv[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int kk = warp * 16 + i * 2 + half;
+    bv[i] = make_uint2(0u, 0u);
+    if (k0 + kk < p.k && col < p.n) bv[i] = __ldcs(reinterpret_cast<const uint2*>(B + (long long)(k0 + kk) * p.b_row + col));
+  }
+  // A block -> shared as float (M x 128, zero rows beyond M): one 16-byte load per thread
+  {
+    const int m = threadIdx.x >> 4, ch = threadIdx.x & 15;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) v[e] = 0.f;
+    if (m < p.m) {
+      const T* src = A + (long long)m * p.a_row + k0 + ch * 8;
+      if (p.a_vec && k0 + ch * 8 + 8 <= p.k) {
+        Pack<T> q = ld16(src);
+#pragma unroll
+        for (int e = 0; e < 8; e++) v[e] = Cvt<T>::to(q.v[e]);
+      } else {
+        for (int e = 0; e < 8; e++) if (k0 + ch * 8 + e < p.k) v[e] = Cvt<T>::to(src[e]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++) sA[m][ch * 8 + e] = v[e];
+  }
+  __syncthreads();
+  float acc[kSkMaxM][4];
+#pragma unroll
+  for (int m = 0; m < kSkMaxM; m++) { acc[m][0] = 0.f; acc[m][1] = 0.f; acc[m][2] = 0.f; acc[m][3] = 0.f; }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int kk = warp * 16 + i * 2 + half;
+    const T* pr = reinterpret_cast<const T*>(&bv[i]);
+    const float b0 = Cvt<T>::to(pr[0]), b1 = Cvt<T>::to(pr[1]), b2 = Cvt<T>::to(pr[2]), b3 = Cvt<T>::to(pr[3]);
+#pragma unroll
+    for (int m = 0; m < kSkMaxM; m++) {
+      const float a = sA[m][kk];           // two addresses per warp (one per half): broadcasts
+      acc[m][0] = fmaf(a, b0, acc[m][0]); acc[m][1] = fmaf(a, b1, acc[m][1]);
+      acc[m][2] = fmaf(a, b2, acc[m][2]); acc[m][3] = fmaf(a, b3, acc[m][3]);
+    }
+  }
+  // the two half-warps hold different rows of the same columns
+#pragma unroll
+  for (int m = 0; m < kSkMaxM; m++) {
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc[m][e] += __shfl_xor_sync(0xffffffffu, acc[m][e], 16);
+  }
+  if (half == 0) {
+#pragma unroll
+    for (int m = 0; m < kSkMaxM; m++) *reinterpret_cast<float4*>(&sSum[warp][m][cl * 4]) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+  }
+  __syncthreads();
+  const int k_slabs = gridDim.y;
+  float* my_partial = p.partial + ((long long)blockIdx.y * kSkMaxM) * p.n;
+  for (int i = threadIdx.x; i < kSkMaxM * kSkN; i += kSkThreads) {
+    int m = i / kSkN, c = i % kSkN;
+    if (m < p.m && n0 + c < p.n) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSkThreads / 32; w++) v += sSum[w][m][c];    // warp order = K order
+      my_partial[(long long)m * p.n + n0 + c] = v;
+    }
+  }
+  // the last CTA of this column slab finishes it
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+    s_last = (prev == (unsigned int)(k_slabs - 1)) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  T* C = reinterpret_cast<T*>(p.c);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  const T* R = reinterpret_cast<const T*>(p.residual);
+  for (int i = threadIdx.x; i < kSkMaxM * kSkN; i += kSkThreads) {
+    int m = i / kSkN, c = i % kSkN;
+    if (m < p.m && n0 + c < p.n) {
+      float v = 0.f;
+      for (int ks = 0; ks < k_slabs; ks++) v += __ldcg(p.partial + ((long long)ks * kSkMaxM + m) * p.n + n0 + c);   // K order: deterministic
+      v *= p.alpha;
+      if (bias) v += Cvt<T>::to(bias[n0 + c]);
+      v = apply_act(v, (Act)p.act);
+      if (R) v += Cvt<T>::to(R[(long long)m * p.c_row + n0 + c]);
+      C[(long long)m * p.c_row + n0 + c] = Cvt<T>::from(v);
+    }
+  }
+  if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch on this stream
+}
+
+static float* g_sk_partial = nullptr;
+static unsigned int* g_sk_counters = nullptr;
+static std::once_flag g_sk_once;
+
+bool skinny_eligible(const GemmDesc& d) {
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
+  if (d.c_f32 || d.ep.argmax_keys || d.ep.b_scales) return false;
+  if (d.batch != 1 || d.batch_inner != 1) return false;
+  if (d.m < 1 || d.m > kSkMaxM || d.n < 256 || d.n > kSkMaxN || d.k < kSkK) return false;
+  if (d.a_col != 1 || d.b_col != 1) return false;                       // A rows along K, B stored [K, N]
+  if (d.b_row % 4 != 0 || d.n % 4 != 0 || (reinterpret_cast<uintptr_t>(d.b) & 7u) != 0) return false;   // 8-byte loads of B
+  const int64_t ks = (d.k + kSkK - 1) / kSkK;
+  if (ks > kSkMaxKSlabs || ks * d.n > kSkMaxPartials) return false;
+  return true;
+}
+
+Status matmul_skinny(cudaStream_t s, const GemmDesc& d) {
+  std::call_once(g_sk_once, [] {
+    if (cudaMalloc(&g_sk_partial, (size_t)kSkMaxPartials * kSkMaxM * sizeof(float)) != cudaSuccess) { g_sk_partial = nullptr; cudaGetLastError(); return; }
+    if (cudaMalloc(&g_sk_counters, (size_t)(kSkMaxN / kSkN) * sizeof(unsigned int)) != cudaSuccess) { g_sk_counters = nullptr; cudaGetLastError(); return; }
+    cudaMemset(g_sk_counters, 0, (size_t)(kSkMaxN / kSkN) * sizeof(unsigned int));
+  });
+  if (!g_sk_partial || !g_sk_counters) return Status::compute("matmul (skinny): cannot allocate the partial-sum workspace");
+  SkinnyParams p;
+  p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
+  p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_row; p.c_row = d.c_row;
+  p.partial = g_sk_partial; p.counters = g_sk_counters;
+  p.a_vec = (d.a_row % 8 == 0 && (reinterpret_cast<uintptr_t>(d.a) & 15u) == 0) ? 1 : 0;
+  dim3 grid((unsigned)((d.n + kSkN - 1) / kSkN), (unsigned)((d.k + kSkK - 1) / kSkK), 1);
+  cudaError_t e;
+  if (d.dtype == DType::BF16) e = launch_pdl(gemm_skinny_kernel<__nv_bfloat16>, grid, dim3(kSkThreads), 0, s, p);
+  else e = launch_pdl(gemm_skinny_kernel<__half>, grid, dim3(kSkThreads), 0, s, p);
+  if (e != cudaSuccess) return cuda_status(e, "matmul (skinny)");
+  return Status::OK();
+}
+
+}}  // namespace ag::k

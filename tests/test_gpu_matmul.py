@@ -279,6 +279,32 @@ def test_matmul_f32_split_precision_on_tensor_cores(gpu_dev, shape_a, shape_b, b
         np.testing.assert_allclose(y.to_numpy(), want, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k", [(8, 2304, 768), (1, 768, 768), (16, 3072, 768), (8, 768, 3072), (5, 1000, 200), (8, 1288, 1280)])
+def test_matmul_skinny_rows_against_a_weight_matrix(gpu_dev, dtype, m, n, k):
+    """A decode step: at most 16 rows against a [K, N] weight. Takes the weight-streaming kernel (column
+    slabs x K slabs, partials summed in K order); checked against fp64, against the tensor-core kernel, with a
+    fused epilogue, and for run-to-run determinism."""
+    rng = np.random.default_rng(m * 7 + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32); b = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    bias = rounded(rng.standard_normal(n).astype(np.float32), dtype); res = rounded(rng.standard_normal((m, n)).astype(np.float32), dtype)
+    ga, gb, gbias, gres = up(gpu_dev, a, dtype), up(gpu_dev, b, dtype), up(gpu_dev, bias, dtype), up(gpu_dev, res, dtype)
+    ref = np.matmul(rounded(a, dtype).astype(np.float64), rounded(b, dtype).astype(np.float64))
+    got = (ga @ gb).to_numpy().astype(np.float32)
+    assert rel_err(got, ref) <= 6e-3
+    again = (ga @ gb).to_numpy().astype(np.float32)
+    assert np.array_equal(got, again)                                     # K-ordered reduction: no dependence on scheduling
+    gpu_dev.set_matmul_path("tcgen05")
+    try:
+        tc = (ga @ gb).to_numpy().astype(np.float32)
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    assert rel_err(got, tc.astype(np.float64)) <= 4e-3
+    y = gres + gpu_dev.gelu(gpu_dev.add_bias(ga @ gb, gbias))
+    want = R.gelu((ref + bias).astype(np.float32)).astype(np.float64) + res
+    assert rel_err(y.to_numpy(), want) <= 1.5e-2
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])
