@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Headline benchmark: GPT-2-small-architecture forward tokens/s (BASELINE.json `metric`).
+"""Headline benchmark: GPT-2-small-architecture forward tokens/s.
 
   python bench.py --gpus N --steps K --warmup W              the B200 path (this library)
   python bench.py --impl reference --gpus N --steps K ...    the reference's CPU path (PyTorch CPU eager)
