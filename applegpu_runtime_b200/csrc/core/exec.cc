@@ -10,6 +10,7 @@
 #include <array>
 #include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <sstream>
@@ -197,7 +198,10 @@ static Status build_gemm(const TensorRec& a, const TensorRec& b, const TensorRec
 // product (inside the reference's 1e-4 tolerance by three orders of magnitude) at about a sixth of the
 // bf16 tensor rate, against the CUDA-core kernel's ~30 TFLOP/s. Taken for products large enough to pay for
 // the two split passes and whose layouts the TMA path accepts; *done stays false otherwise.
-namespace { bool g_f32_split = true; }
+namespace {
+bool g_f32_split = true;
+bool g_pitch_rows = [] { const char* v = std::getenv("APPLEGPU_PITCH_ROWS"); return !(v && v[0] == '0'); }();   // APPLEGPU_PITCH_ROWS=0: always dense outputs
+}
 void set_f32_split(bool on) { g_f32_split = on; }
 static Status matmul_f32_split(cudaStream_t s, const k::GemmDesc& g, bool* done) {
   *done = false;
@@ -386,7 +390,20 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
     return attention_exec(*in[0], *in[1], *in[2], kd.causal, dst);
   }
 
-  AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
+  // A large 16-bit product whose rows are not a multiple of 16 bytes (the 50257-wide LM head) gets a
+  // row pitch rounded up to 16 bytes: the GEMM's epilogue then stores 64-byte row segments instead of
+  // 2-byte elements. The result is an ordinary strided view; consumers that need dense rows copy it,
+  // argmax and reshape read it as it lies.
+  bool pitched = false;
+  if ((kd.op == Op::Matmul || (kd.op == Op::FusedLinear && kd.i2 != 1 && kd.i1 != 1 && !kd.has_residual)) && !out_buf && !dry && g_pitch_rows &&
+      node.out_shape.size() == 2 && dtype_size(node.out_dtype) == 2 && node.out_shape[1] % 8 != 0 && node.out_shape[1] >= 1024 &&
+      node.out_shape[0] >= 128) {
+    const int64_t pitch = (node.out_shape[1] + 7) / 8 * 8;
+    out->shape = node.out_shape; out->strides = {pitch, 1}; out->dtype = node.out_dtype; out->byte_offset = 0; out->has_meta = true;
+    AG_RETURN_IF_ERROR(Shared::get().pool.acquire((size_t)(node.out_shape[0] * pitch) * 2, &out->buf));
+    pitched = true;
+  }
+  if (!pitched) AG_RETURN_IF_ERROR(alloc_out(node.out_shape, node.out_dtype, out, out_buf));
   if (dry) return Status::OK();
   TView ov = out->view();
 
@@ -518,6 +535,23 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
       return Status::OK();
     }
     case Op::Argmax: {
+      // rows may carry a pitch (a padded GEMM output, also seen through a reshape): the kernel takes a row stride
+      const TensorRec& t = *in[0];
+      bool rows_ok = !t.shape.empty() && t.strides.back() == 1 && t.shape.size() >= 2;
+      if (rows_ok) {
+        const int64_t pitch = t.strides[t.shape.size() - 2];
+        int64_t expect = pitch;
+        for (int d = (int)t.shape.size() - 2; d >= 0 && rows_ok; d--) {
+          if (t.shape[d] != 1 && t.strides[d] != expect) rows_ok = false;
+          expect *= t.shape[d];
+        }
+        rows_ok = rows_ok && pitch >= t.shape.back();
+      }
+      if (rows_ok && !t.contiguous()) {
+        TView v = t.view();
+        AG_LAUNCH(k::argmax(s, v, ov));
+        return Status::OK();
+      }
       TensorRec c; AG_RETURN_IF_ERROR(make_contiguous(*in[0], &c));
       AG_LAUNCH(k::argmax(s, c.view(), ov));
       return Status::OK();

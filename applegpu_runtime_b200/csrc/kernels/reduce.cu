@@ -270,11 +270,11 @@ __device__ __forceinline__ ArgPair arg_better(ArgPair a, ArgPair b) {
   return a;
 }
 template <typename T>
-__global__ void __launch_bounds__(256) argmax_kernel(const T* __restrict__ in, int32_t* __restrict__ out, int64_t rows, int64_t cols) {
+__global__ void __launch_bounds__(256) argmax_kernel(const T* __restrict__ in, int32_t* __restrict__ out, int64_t rows, int64_t cols, int64_t row_stride) {
   __shared__ float sv[32];
   __shared__ int si[32];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* x = in + row * cols;
+    const T* x = in + row * row_stride;
     ArgPair best{-INFINITY, 0x7fffffff};
     // Each thread visits its elements in ascending index order, so a strict '>' keeps the first
     // maximum; NaNs never compare greater. Rows start on arbitrary element boundaries (a 50257-wide
@@ -351,16 +351,22 @@ __global__ void argmax_int_kernel(const T* __restrict__ in, int32_t* __restrict_
 }
 
 Status argmax(cudaStream_t s, const TView& in, const TView& out) {
-  if (!in.contiguous()) return Status::compute("argmax needs a contiguous tensor");
+  // rows dense, or all at one pitch (last stride 1, leading dims collapsing onto the row stride)
   int64_t cols = in.shape.back();
   if (cols == 0) return Status::compute("argmax over an empty row");
   int64_t rows = in.numel() / cols;
+  int64_t row_stride = cols;
+  if (!in.contiguous()) {
+    if (in.shape.size() < 2 || in.strides.back() != 1) return Status::compute("argmax needs dense rows");
+    row_stride = in.strides[in.shape.size() - 2];
+    if (in.dtype != DType::F32 && in.dtype != DType::F16 && in.dtype != DType::BF16) return Status::compute("argmax needs a contiguous tensor");
+  }
   if (rows == 0) return Status::OK();
   int grid = (int)(rows < (int64_t)sm_count() * 8 ? rows : (int64_t)sm_count() * 8);
   switch (in.dtype) {
-    case DType::F32: argmax_kernel<float><<<grid, 256, 0, s>>>((const float*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
-    case DType::F16: argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
-    case DType::BF16: argmax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
+    case DType::F32: argmax_kernel<float><<<grid, 256, 0, s>>>((const float*)in.ptr, (int32_t*)out.ptr, rows, cols, row_stride); break;
+    case DType::F16: argmax_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in.ptr, (int32_t*)out.ptr, rows, cols, row_stride); break;
+    case DType::BF16: argmax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in.ptr, (int32_t*)out.ptr, rows, cols, row_stride); break;
     case DType::I32: argmax_int_kernel<int32_t><<<(int)((rows + 127) / 128), 128, 0, s>>>((const int32_t*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
     case DType::I64: argmax_int_kernel<int64_t><<<(int)((rows + 127) / 128), 128, 0, s>>>((const int64_t*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
     case DType::U8: argmax_int_kernel<uint8_t><<<(int)((rows + 127) / 128), 128, 0, s>>>((const uint8_t*)in.ptr, (int32_t*)out.ptr, rows, cols); break;
