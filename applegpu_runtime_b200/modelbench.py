@@ -9,6 +9,7 @@ events on the runtime stream after warm-up:
   gpt2_small_decode    8 prompts x 64 tokens, then 50 greedy steps with the KV cache (tokens/s = 8*50/time)
   gpt2_large_int8      GPT-2-large, per-output-channel int8 weights, bf16 activations, 32 x 512 tokens
   bert_base            BERT-base encoder, 256 x 512 tokens, bf16
+  bert_base_tp         the same, heads / feed-forward units sharded over the ranks of a torchrun launch (NCCL)
 
   python -m applegpu_runtime_b200.modelbench --config all --dtype bfloat16
 """
@@ -105,9 +106,56 @@ def bench_bert_base(dtype, batch, seq, iters):
             "tflops": flops / ms / 1e9}
 
 
+def _bert_host_state(cfg, seed=0, std=0.02):
+    rng = np.random.default_rng(seed)
+    d, L, ff = cfg["n_embd"], cfg["n_layer"], cfg["d_ff"]
+    st = {}
+
+    def normal(*shape):
+        return (rng.standard_normal(shape, dtype=np.float32) * std).astype(np.float32)
+
+    st["embeddings.word_embeddings.weight"] = normal(cfg["vocab_size"], d)
+    st["embeddings.position_embeddings.weight"] = normal(cfg["n_positions"], d)
+    st["embeddings.token_type_embeddings.weight"] = normal(cfg.get("type_vocab", 2), d)
+    st["embeddings.LayerNorm.weight"] = np.ones(d, np.float32); st["embeddings.LayerNorm.bias"] = np.zeros(d, np.float32)
+    for i in range(L):
+        p = f"encoder.layer.{i}"
+        for name, shape in (("attention.self.query", (d, d)), ("attention.self.key", (d, d)), ("attention.self.value", (d, d)),
+                            ("attention.output.dense", (d, d)), ("intermediate.dense", (ff, d)), ("output.dense", (d, ff))):
+            st[f"{p}.{name}.weight"] = normal(*shape); st[f"{p}.{name}.bias"] = np.zeros(shape[0], np.float32)
+        for name in ("attention.output.LayerNorm", "output.LayerNorm"):
+            st[f"{p}.{name}.weight"] = np.ones(d, np.float32); st[f"{p}.{name}.bias"] = np.zeros(d, np.float32)
+    return st
+
+
+def bench_bert_base_tp(dtype, batch, seq, iters):
+    """BERT-base with heads and feed-forward units sharded over the launcher's ranks (torchrun, one rank per
+    GPU): 2 NCCL all-reduces of [batch*seq, 768] per layer on the runtime stream. Rank 0 prints the line;
+    the time is the MAX over ranks of the CUDA-event time."""
+    from .sharding import RankGroup
+    from .tp import TensorParallelGroup, load_bert_shard
+    group = RankGroup.from_env()
+    tp = TensorParallelGroup(group)
+    model = load_bert_shard(_bert_host_state(BERT_BASE), BERT_BASE, group, dtype=dtype)
+    ids = np.random.default_rng(3).integers(0, BERT_BASE["vocab_size"], (batch, seq))
+
+    def step():
+        bert_forward(model, ids, all_reduce=tp.all_reduce).eval()
+
+    group.barrier()
+    ms = group.max(_time(step, iters, 2))
+    group.barrier()
+    payload = batch * seq * BERT_BASE["n_embd"] * gpu.dtype_size(dtype)
+    r = {"config": "bert_base_tp", "dtype": dtype, "batch": batch, "seq": seq, "ranks": group.world, "ms": ms,
+         "tokens_per_s": batch * seq / ms * 1e3, "all_reduce_bytes": payload, "all_reduces_per_forward": 2 * BERT_BASE["n_layer"]}
+    rank = group.rank
+    group.close()
+    return r if rank == 0 else None
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="all", choices=["all", "gpt2_small_prefill", "gpt2_small_decode", "gpt2_large_int8", "bert_base"])
+    ap.add_argument("--config", default="all", choices=["all", "gpt2_small_prefill", "gpt2_small_decode", "gpt2_large_int8", "bert_base", "bert_base_tp"])
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=5)
     args = ap.parse_args(argv)
@@ -127,6 +175,10 @@ def main(argv=None):
         emit(bench_gpt2_large_int8(32, 512, max(1, args.iters // 2)))
     if args.config in ("all", "bert_base"):
         emit(bench_bert_base(args.dtype, 256, 512, max(1, args.iters // 2)))
+    if args.config == "bert_base_tp":   # under torchrun: one rank per GPU
+        r = bench_bert_base_tp(args.dtype, 256, 512, max(1, args.iters // 2))
+        if r is not None:
+            emit(r)
     st = gpu.pipeline_status()
     if st:
         print(json.dumps({"pipeline_status": st}))
