@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
         Pack<T> o;
 #pragma unroll
         for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(Cvt<T>::to(g.v[e]) * (v[it][e] - mean) * inv_std + Cvt<T>::to(b.v[e]));
-        st16_stream(y + pk * N, o);
+        st16(y + pk * N, o);   // the next kernel (a GEMM) reads this from L2: no evict-first hint
       }
     }
   }
