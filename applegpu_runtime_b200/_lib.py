@@ -162,6 +162,8 @@ EXT_SYMBOLS = {
     "applegpu_matmul_path": (cstr, [u64, u64, cbool]),
     "applegpu_set_matmul_path": (None, [i32]),
     "applegpu_set_f32_split": (None, [ctypes.c_bool]),
+    "applegpu_set_host_visible": (i32, [i32]),
+    "applegpu_host_visible": (i32, []),
     "applegpu_set_attention_path": (None, [i32]),
     "applegpu_pipeline_status": (i32, []),
     "applegpu_eager_execute_graph": (i32, [vp, u32, vp, u32, vp, u32, vp, vp]),

@@ -101,6 +101,8 @@ Status EagerRuntime::add_scaled_inplace(uint64_t self, uint64_t other, float alp
   Dims bs;
   AG_RETURN_IF_ERROR(broadcast_shapes(a->shape, b->shape, &bs));
   if (bs != a->shape) return Status::invalid("in-place add cannot broadcast self from " + dims_str(a->shape) + " to " + dims_str(bs));
+  if (a->buf) ctx.prefetch(a->buf->ptr, a->buf->capacity);
+  if (b->buf) ctx.prefetch(b->buf->ptr, b->buf->capacity);
   return k::add_scaled_inplace(ctx.stream, a->view(), b->view(), alpha);
 }
 

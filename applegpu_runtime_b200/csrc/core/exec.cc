@@ -328,6 +328,14 @@ static double node_work(const OpNode& node, const std::vector<const TensorRec*>&
 static Status execute_node_impl(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf);
 
 Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
+  {
+    // host-visible mode: the host may have read or written any operand since its last use on the device
+    const DeviceCtx& ctx = DeviceCtx::get();
+    if (ctx.host_visible) {
+      for (const TensorRec* t : in) if (t && t->buf && !t->buf->borrowed) ctx.prefetch(t->buf->ptr, t->buf->capacity);
+      if (out_buf && !out_buf->borrowed) ctx.prefetch(out_buf->ptr, out_buf->capacity);
+    }
+  }
   if (!profile::enabled()) return execute_node_impl(node, in, out, out_buf);
   std::string name = node.op.kernel_name();
   if (node.op.op == Op::FusedElementwise) name = "fused_elementwise";

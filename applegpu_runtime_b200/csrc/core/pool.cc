@@ -31,6 +31,27 @@ static int env_int(const char* name, int dflt) {
   return std::atoi(v);
 }
 
+static std::atomic<int> g_host_visible_request{-1};   // -1: follow the environment
+void DeviceCtx::request_host_visible(bool on) { g_host_visible_request.store(on ? 1 : 0); }
+
+void DeviceCtx::prefetch(const void* ptr, size_t bytes) const {
+  if (!host_visible || dry || !ptr || !bytes) return;
+  if (cudaMemPrefetchAsync(ptr, bytes, device, stream) != cudaSuccess) cudaGetLastError();   // a hint: the kernels fault pages in otherwise
+}
+
+// Backing store of the pool: stream-ordered device memory, or managed memory in host-visible mode.
+static cudaError_t backing_alloc(const DeviceCtx& ctx, void** ptr, size_t bytes) {
+  if (!ctx.host_visible) return cudaMallocAsync(ptr, bytes, ctx.stream);
+  cudaError_t e = cudaMallocManaged(ptr, bytes, cudaMemAttachGlobal);
+  if (e == cudaSuccess) ctx.prefetch(*ptr, bytes);
+  return e;
+}
+static void backing_free(const DeviceCtx& ctx, void* ptr) {
+  if (!ctx.host_visible) { cudaFreeAsync(ptr, ctx.stream); return; }
+  cudaStreamSynchronize(ctx.stream);   // queued kernels may still use the range
+  cudaFree(ptr);
+}
+
 Status DeviceCtx::init(bool allow_dry) {
   static std::mutex mu;
   std::lock_guard<std::mutex> g(mu);
@@ -60,6 +81,14 @@ Status DeviceCtx::init(bool allow_dry) {
   if (cudaDeviceGetDefaultMemPool(&mp, dev) == cudaSuccess) {
     uint64_t thr = UINT64_MAX;  // keep freed memory in the pool instead of returning it to the OS
     cudaMemPoolSetAttribute(mp, cudaMemPoolAttrReleaseThreshold, &thr);
+  }
+  int want_hv = g_host_visible_request.load();
+  if (want_hv < 0) want_hv = env_int("APPLEGPU_HOST_VISIBLE", 0);
+  if (want_hv == 1) {
+    int concurrent = 0;
+    cudaDeviceGetAttribute(&concurrent, cudaDevAttrConcurrentManagedAccess, dev);
+    if (!concurrent) return Status::no_device("host-visible mode needs concurrent managed access, which this device / driver does not offer");
+    host_visible = true;
   }
   device = dev; sm_count = prop.multiProcessorCount; total_mem = prop.totalGlobalMem; name = prop.name;
   ready = true;
@@ -124,18 +153,19 @@ Status BufferPool::acquire(size_t size, std::shared_ptr<Buffer>* out) {
       if (fail_next_ > 0) { fail_next_--; return Status::alloc_failed(size); }
     }
   }
+  if (ptr) ctx.prefetch(ptr, cls);   // a recycled managed buffer may sit in host memory after a host read
   if (!ptr) {
     if (ctx.dry) {
       std::lock_guard<std::mutex> g(mu_);
       ptr = reinterpret_cast<void*>(fake_ptr_);
       fake_ptr_ += (cls + 255) & ~(size_t)255;
     } else {
-      cudaError_t e = cudaMallocAsync(&ptr, cls, ctx.stream);
+      cudaError_t e = backing_alloc(ctx, &ptr, cls);
       if (e != cudaSuccess) {
         cudaGetLastError();
         // Give pooled memory back and retry once before reporting failure.
         drain();
-        e = cudaMallocAsync(&ptr, cls, ctx.stream);
+        e = backing_alloc(ctx, &ptr, cls);
         if (e != cudaSuccess) { cudaGetLastError(); return Status::alloc_failed(size); }
       }
     }
@@ -164,7 +194,7 @@ void BufferPool::release(Buffer* b) {
       keep = true;
     }
   }
-  if (!keep && !ctx.dry) cudaFreeAsync(b->ptr, ctx.stream);
+  if (!keep && !ctx.dry) backing_free(ctx, b->ptr);
 }
 
 PoolStats BufferPool::stats() const {
@@ -184,7 +214,7 @@ void BufferPool::drain() {
     pooled_bytes_ = 0;
   }
   if (ctx.dry) return;
-  for (auto& kv : taken) for (void* p : kv.second) cudaFreeAsync(p, ctx.stream);
+  for (auto& kv : taken) for (void* p : kv.second) backing_free(ctx, p);
 }
 
 void BufferPool::set_max_pooled_bytes(size_t n) {
@@ -202,7 +232,7 @@ void BufferPool::set_max_pooled_bytes(size_t n) {
       if (it->second.empty()) free_.erase(it);
     }
   }
-  if (!ctx.dry) for (void* p : drop) cudaFreeAsync(p, ctx.stream);
+  if (!ctx.dry) for (void* p : drop) backing_free(ctx, p);
 }
 
 Status BufferPool::prewarm(const std::vector<size_t>& sizes) {

@@ -24,6 +24,13 @@ struct DeviceCtx {
   cudaStream_t stream = nullptr;
   bool dry = false;       // metadata-only mode: no device, nothing executes
   bool ready = false;
+  // Host-visible mode: pool buffers are CUDA managed memory, so the pointers the C-ABI returns can be read and
+  // written by the host after a flush, as the reference's shared Metal buffers can (the PrivateUse1 shim does
+  // memcpy on them). Chosen before the context is created (APPLEGPU_HOST_VISIBLE=1 or request_host_visible).
+  bool host_visible = false;
+  static void request_host_visible(bool on);
+  // Moves a managed range to the device ahead of the kernels that use it (no-op outside host-visible mode).
+  void prefetch(const void* ptr, size_t bytes) const;
   int sm_count = 0;
   size_t total_mem = 0;
   std::string name;

@@ -1077,6 +1077,13 @@ const char* applegpu_device_name(void) { return DeviceCtx::get().name.c_str(); }
 uint64_t applegpu_launch_count(void) { return ag::launch_count(); }
 void applegpu_set_matmul_path(int32_t mode) { k::set_matmul_path(mode); }
 void applegpu_set_f32_split(bool on) { ag::set_f32_split(on); }
+int32_t applegpu_set_host_visible(int32_t on) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (ctx.ready) return (ctx.host_visible == (on != 0)) ? 0 : -1;   // buffers of the other kind may already be out
+  DeviceCtx::request_host_visible(on != 0);
+  return 0;
+}
+int32_t applegpu_host_visible(void) { return DeviceCtx::get().host_visible ? 1 : 0; }
 void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();

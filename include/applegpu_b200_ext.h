@@ -145,6 +145,15 @@ APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
 /* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
  * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
 APPLEGPU_API void applegpu_set_f32_split(bool on);
+/* Host-visible mode. Upstream every returned `uint8_t*` is host-dereferenceable (shared Metal buffers;
+ * backend_cpp/applegpu_backend.cpp:264-342 copies with memcpy, :691-749 builds CPU views over them). By
+ * default this library returns plain device pointers. With APPLEGPU_HOST_VISIBLE=1 in the environment, or
+ * applegpu_set_host_visible(1) before the first init call, the buffer pool is backed by CUDA managed memory:
+ * the host may read and write a returned pointer once applegpu_eager_flush_and_wait / _synchronize /
+ * applegpu_ffi_eval has returned, and every operand is moved back to the device ahead of the kernels that
+ * use it. Returns 0, or -1 when the device context already exists in the other mode. */
+APPLEGPU_API int32_t applegpu_set_host_visible(int32_t on);
+APPLEGPU_API int32_t applegpu_host_visible(void);
 /* 0 auto (single-kernel attention when head dim is 64 and dtype is f16/bf16), 1 always compose
  * attention from GEMM + softmax + GEMM with materialised scores. */
 APPLEGPU_API void applegpu_set_attention_path(int32_t mode);

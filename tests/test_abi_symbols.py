@@ -46,3 +46,21 @@ def test_no_product_module_imports_the_oracle():
                 with open(os.path.join(dirpath, fn)) as f:
                     text = f.read()
                 assert "import oracle" not in text and "from oracle" not in text and "msl_ref" not in text, fn
+
+
+def test_reference_shim_links_against_the_library():
+    """Every applegpu_* symbol the reference's PrivateUse1 shim leaves undefined (a build of its unmodified
+    source, oracle/build_ref_shim.py) is exported by this library."""
+    import shutil
+    import subprocess
+    import pytest
+    shim = os.path.join(ROOT, "oracle", "_ref", "applegpu_backend.so")
+    if not os.path.exists(shim) or not shutil.which("nm"):
+        pytest.skip("shim not built here")
+    from applegpu_runtime_b200 import _lib
+    out = subprocess.run(["nm", "-D", "--undefined-only", shim], capture_output=True, text=True, check=True).stdout
+    needed = sorted({ln.split()[-1] for ln in out.splitlines() if ln.split() and ln.split()[-1].startswith("applegpu_")})
+    assert len(needed) >= 25
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    assert not [n for n in needed if not hasattr(lib, n)]
+    assert set(needed) <= set(_lib.REFERENCE_SYMBOLS)
