@@ -190,6 +190,84 @@ struct Rewriter {
   }
 };
 
+// reshape([M, N] -> [.., N]) of a linear layer's output followed by an activation or a residual add: apply
+// the op to the 2-D tensor and reshape afterwards, so that the linear rewrite below sees
+// matmul -> add_bias -> gelu -> add as one chain even when the program reshapes to [batch, tokens, features]
+// between the ops (what torch's nn.Linear on a 3-D input records). The activation takes the reshape's id and
+// the reshape takes the activation's, so ids that later nodes refer to keep their shapes; for an add the
+// other operand gets a 2-D reshape (a view at run time) and the pair moves to the add's place in the order.
+static void sink_row_reshapes(Graph& g, std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
+                              const std::unordered_set<uint64_t>* released, std::vector<uint64_t>* minted) {
+  if (!released || !minted) return;   // the reshape's id changes meaning: only when its caller-side handle is known to be gone
+  std::unordered_map<uint64_t, std::vector<uint64_t>> consumers;
+  bool any_reshape = false;
+  for (uint64_t id : order) {
+    const OpNode* n = g.get_node(id);
+    if (!n) continue;
+    if (n->op.op == Op::Reshape) any_reshape = true;
+    for (uint64_t in : n->inputs) {
+      auto& v = consumers[in];
+      if (std::find(v.begin(), v.end(), id) == v.end()) v.push_back(id);
+    }
+  }
+  if (!any_reshape) return;
+  std::unordered_map<uint64_t, std::vector<uint64_t>> before;   // ids to emit right before a node
+  std::unordered_set<uint64_t> moved;
+  for (size_t oi = 0; oi < order.size(); oi++) {
+    const uint64_t rid = order[oi];
+    const OpNode* r = g.get_node(rid);
+    if (!r || r->op.op != Op::Reshape || r->inputs.size() != 1) continue;
+    if (keep.count(rid) || g.ref_count(rid) != 1 || !released->count(rid)) continue;
+    auto ci = consumers.find(rid);
+    if (ci == consumers.end() || ci->second.size() != 1) continue;
+    const OpNode* x = g.get_node(r->inputs[0]);
+    if (!x || x->out_shape.size() != 2 || r->out_shape.size() < 3 || r->out_shape.back() != x->out_shape[1]) continue;
+    const Op xo = x->op.op;
+    if (!(xo == Op::Matmul || xo == Op::MatmulInt8 || xo == Op::AddBias || xo == Op::ScalarMul || xo == Op::Gelu || xo == Op::GeluExact || xo == Op::Relu)) continue;
+    const OpNode* c = g.get_node(ci->second[0]);
+    if (!c || c->out_shape != r->out_shape || c->out_dtype != r->out_dtype || keep.count(x->id)) continue;
+    const uint64_t cid = c->id, xid = x->id;
+    const Dims flat = x->out_shape;
+    const Op co = c->op.op;
+    if (co == Op::Gelu || co == Op::GeluExact || co == Op::Relu) {
+      OpNode act = *c, rs = *r;
+      g.remove_node(cid); g.remove_node(rid);
+      act.id = rid; act.inputs = {xid}; act.out_shape = flat;
+      rs.id = cid; rs.inputs = {rid};
+      g.add_node(std::move(act)); g.add_node(std::move(rs));
+    } else if (co == Op::Add && c->inputs.size() == 2 && c->inputs[0] != c->inputs[1]) {
+      const bool first = c->inputs[0] == rid;
+      const uint64_t other = first ? c->inputs[1] : c->inputs[0];
+      const OpNode* on = g.get_node(other);
+      if (!on || on->out_shape != r->out_shape || on->out_dtype != r->out_dtype) continue;   // pending and not broadcast
+      OpNode add = *c, rs = *r, o2;
+      o2.id = next_fused_id(); o2.op.op = Op::Reshape; o2.op.shape = flat; o2.inputs = {other}; o2.out_shape = flat; o2.out_dtype = on->out_dtype;
+      g.remove_node(cid); g.remove_node(rid);
+      add.id = rid; add.out_shape = flat;
+      if (first) add.inputs = {xid, o2.id}; else add.inputs = {o2.id, xid};
+      rs.id = cid; rs.inputs = {rid};
+      const uint64_t o2id = o2.id;
+      g.add_node(std::move(o2)); g.add_node(std::move(add)); g.add_node(std::move(rs));
+      moved.insert(rid);
+      minted->push_back(o2id);
+      before[cid] = {o2id, rid};
+      auto& oc = consumers[other];
+      std::replace(oc.begin(), oc.end(), cid, o2id);
+      consumers[o2id] = {rid};
+    }
+  }
+  if (moved.empty()) return;
+  std::vector<uint64_t> next;
+  next.reserve(order.size() + before.size());
+  for (uint64_t id : order) {
+    if (moved.count(id)) continue;
+    auto b = before.find(id);
+    if (b != before.end()) for (uint64_t pre : b->second) next.push_back(pre);
+    next.push_back(id);
+  }
+  order.swap(next);
+}
+
 static void rewrite_linear(Rewriter& rw, uint64_t id) {
   const OpNode* mm = rw.g.get_node(id);
   if (!mm || !(mm->op.op == Op::Matmul || mm->op.op == Op::MatmulInt8)) return;
@@ -358,9 +436,10 @@ static void rewrite_embed_add(Rewriter& rw, uint64_t id) {
 }
 
 std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
-                               const std::unordered_set<uint64_t>* released) {
+                               const std::unordered_set<uint64_t>* released, std::vector<uint64_t>* minted) {
   std::vector<uint64_t> cur = order;
   if (g_patterns) {
+    sink_row_reshapes(g, cur, keep, released, minted);
     Rewriter rw(g, cur, keep);
     rw.released = released;
     for (uint64_t id : order) { if (!rw.removed.count(id)) rewrite_attention(rw, id); }

@@ -113,7 +113,9 @@ Status LazyRuntime::eval(uint64_t id) {
   AG_RETURN_IF_ERROR(graph_.topo_sort(id, &order));
   std::unordered_set<uint64_t> keep{id};
   for (auto& kv : prealloc_) keep.insert(kv.first);  // outputs the caller already holds pointers to
-  order = fusion::optimize(graph_, order, keep, &deferred_free_);
+  std::vector<uint64_t> minted;
+  order = fusion::optimize(graph_, order, keep, &deferred_free_, &minted);
+  for (uint64_t m : minted) deferred_free_.insert(m);   // nobody holds a handle: dropped after the last consumer ran
 
   // remaining uses inside this evaluation, to drop dead intermediates early
   for (uint64_t nid : order) {
@@ -161,7 +163,8 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
   AG_RETURN_IF_ERROR(copy.topo_sort(id, &order));
   std::unordered_set<uint64_t> keep{id};
   for (auto& kv : prealloc_) keep.insert(kv.first);
-  order = fusion::optimize(copy, order, keep, &deferred_free_);
+  std::vector<uint64_t> minted;
+  order = fusion::optimize(copy, order, keep, &deferred_free_, &minted);
   for (uint64_t nid : order) {
     const OpNode* n = copy.get_node(nid);
     if (!n) continue;

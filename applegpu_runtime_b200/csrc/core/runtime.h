@@ -184,8 +184,9 @@ namespace fusion {
 // Reference rule (fusion.rs:243-285): linear element-wise chains -> FusedElementwise, plus the
 // graph-level rewrites of this build (linear epilogues, attention, embedding sum, layout sinks).
 // `released`: ids whose caller-side handle has been freed while ops still consume them.
+// `minted`: receives the ids of nodes the pass created that no caller knows (to be freed after their last use).
 std::vector<uint64_t> optimize(Graph& g, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
-                               const std::unordered_set<uint64_t>* released = nullptr);
+                               const std::unordered_set<uint64_t>* released = nullptr, std::vector<uint64_t>* minted = nullptr);
 void set_enabled(bool elementwise, bool patterns);
 void get_enabled(bool* elementwise, bool* patterns);
 }
