@@ -310,7 +310,7 @@ def run_b200(args):
                 "frac": (achieved / peaks["bf16_tflops_sustained"]) if achieved else None, "peak_source": peaks["source"] + " (sustained: timed inside a long step)",
                 # mean DRAM bytes per GEMM launch of one forward, from the ncu captures summarised under profiles/
                 # (gemm_tc_kernel__gpt2_small_linears_8192_bf16.md, gemm_tc_kernel__lm_head_8192x50257x768_bf16.md)
-                "traffic": 49.8e6, "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)", "launches_per_step": g_launch / prof_steps, "avg_launch_ms": g_ms / max(g_launch, 1),
+                "traffic": 49.2e6, "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum)", "launches_per_step": g_launch / prof_steps, "avg_launch_ms": g_ms / max(g_launch, 1),
                 "share_of_step": g_ms / total_ms if total_ms else None,
                 "per_kernel_ms_per_step": {k: round(v["ms"] / prof_steps, 4) for k, v in sorted(rep.items(), key=lambda kv: -kv[1]["ms"])}}
 
