@@ -152,12 +152,22 @@ def _unwrap(t, dtype=None):
             t = t.to(_GPU_TO_TORCH[dtype])
         if t.dim() == 0:
             t = t.reshape(1)
-        return gpu.from_torch(t)
+        return _upload(t)
     raise TypeError(f"cannot move {type(t)} to the device")
 
 
+_recording_consts = None     # while compile_forward records: host tensors uploaded on the way (kept alive with the tape)
+
+
+def _upload(t):
+    g = gpu.from_torch(t)
+    if _recording_consts is not None:
+        _recording_consts.append(g)
+    return g
+
+
 def _scalar_tensor(value, dtype):
-    return gpu.from_torch(torch.tensor([float(value)], dtype=_GPU_TO_TORCH[dtype]))
+    return _upload(torch.tensor([float(value)], dtype=_GPU_TO_TORCH[dtype]))
 
 
 def _is_dev(t):
@@ -402,8 +412,8 @@ def _op_native_layer_norm(x, normalized_shape, weight, bias, eps):
         return NotImplemented
     dt = x._gpu_tensor.dtype
     n = normalized_shape[0]
-    gw = _unwrap(weight, dt) if weight is not None else gpu.from_torch(torch.ones(n, dtype=_GPU_TO_TORCH[dt]))
-    gb = _unwrap(bias, dt) if bias is not None else gpu.from_torch(torch.zeros(n, dtype=_GPU_TO_TORCH[dt]))
+    gw = _unwrap(weight, dt) if weight is not None else _upload(torch.ones(n, dtype=_GPU_TO_TORCH[dt]))
+    gb = _unwrap(bias, dt) if bias is not None else _upload(torch.zeros(n, dtype=_GPU_TO_TORCH[dt]))
     out = _wrap(gpu.layer_norm(x._gpu_tensor, gw, gb, float(eps)), x)
     stat_shape = list(x.shape[:-1]) + [1]
     empty = torch.empty(stat_shape, dtype=torch.float32)      # mean / rstd: only the backward pass reads them
@@ -647,3 +657,56 @@ def to_applegpu(model_or_tensor, dtype=None):
                 seen[key] = to_applegpu(b, dtype)
             mod._buffers[name] = seen[key]
     return module
+
+
+def compile_forward(fn, select=None):
+    """Records the ops `fn` issues once per input signature and replays them afterwards.
+
+    The Python side of a forward (module calls, aten dispatch, shape logic) costs several times the
+    device time of a GPT-2-small prefill; a replay issues the same ops with one library call
+    (`applegpu_ffi_tape_replay`: shapes are re-inferred, fusion runs as usual). The counterpart
+    upstream is the compiled-graph path (python/applegpu_runtime/compile_backend.py -> one
+    `applegpu_eager_execute_graph` call per forward). `fn` takes tensors (host tensors are moved to
+    the device; integer tensors as int32) and returns a tensor, a tuple / list of tensors, or any
+    object from which `select` picks those. Requirements, as for any trace: the ops `fn` issues may
+    depend on the shapes and dtypes of its inputs, not on their values; tensors `fn` creates on the
+    host (position ids, masks) are captured as constants.
+    """
+    cache = {}
+
+    def run(*args):
+        global _recording_consts
+        dev = []
+        for a in args:
+            if not isinstance(a, ApplegpuTensor):
+                a = a.to(torch.int32) if not a.is_floating_point() and a.dtype != torch.bool else a
+                a = ApplegpuTensor.from_torch(a)
+            dev.append(a)
+        key = tuple((tuple(a.shape), a.dtype) for a in dev)
+        hit = cache.get(key)
+        if hit is not None:
+            tape, _consts, many = hit
+            outs = [ApplegpuTensor(g) for g in tape.replay([a._gpu_tensor for a in dev])]
+            return outs if many else outs[0]
+        if _recording_consts is not None:
+            raise RuntimeError("compile_forward: a recording is already in progress")
+        n = gpu.tape_begin([a._gpu_tensor for a in dev])
+        _recording_consts = []
+        try:
+            out = fn(*dev)
+            picked = select(out) if select is not None else out
+            many = isinstance(picked, (list, tuple))
+            outs = list(picked) if many else [picked]
+            if not all(isinstance(o, ApplegpuTensor) for o in outs):
+                raise TypeError("compile_forward: the function must return device tensors")
+            tape = gpu.tape_end(n, [o._gpu_tensor for o in outs])
+        except Exception:
+            gpu.tape_abort()
+            raise
+        finally:
+            consts, _recording_consts = _recording_consts, None
+        cache[key] = (tape, consts, many)
+        return outs if many else outs[0]
+
+    run.cache = cache
+    return run

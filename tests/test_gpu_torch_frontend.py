@@ -90,3 +90,17 @@ def test_hf_gpt2_random_init_logits_and_greedy_tokens(tb):
             nxt = torch.argmax(model(seq_dev).logits[:, -1, :], dim=-1)
             seq_dev = torch.cat([seq_dev, nxt.reshape(-1, 1)], dim=1)
     assert torch.equal(seq_ref, seq_dev)
+
+
+def test_compile_forward_matches_the_uncompiled_forward(tb):
+    torch.manual_seed(0)
+    ref = TinyLM().eval()
+    model = tb.to_applegpu(copy.deepcopy(ref))
+    run = tb.compile_forward(lambda ids: model(ids))
+    import applegpu_runtime_b200 as gpu
+    with torch.no_grad():
+        for seed in range(3):                                  # call 0 records, 1 and 2 replay
+            ids = torch.randint(0, 128, (3, 40), generator=torch.Generator().manual_seed(seed))
+            got = run(ids).to_torch_cpu()
+            assert _rel(got, ref(ids)) < 2e-4
+    assert len(run.cache) == 1 and gpu.pipeline_status() == 0

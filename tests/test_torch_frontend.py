@@ -73,3 +73,26 @@ def test_hf_gpt2_records_without_fallback(tb, gpu):
         kinds = [l.split(" ")[0] for l in out._gpu.plan().strip().splitlines()]
         assert kinds.count("fused_attention[causal,merge_heads]_f32") == 2
         assert kinds.count("fused_linear[bias,gelu,]_f32") == 2 and kinds.count("fused_linear[bias,residual,]_f32") == 4
+
+
+def test_compile_forward_replays_the_recorded_ops(tb, gpu):
+    from collections import Counter
+    torch.manual_seed(0)
+    model = tb.to_applegpu(TinyLM().eval(), torch.bfloat16)
+    run = tb.compile_forward(lambda ids: model(ids))
+    with torch.no_grad():
+        first = run(torch.randint(0, 128, (2, 16)))            # records
+        second = run(torch.randint(0, 128, (2, 16)))           # replays
+        other = run(torch.randint(0, 128, (2, 24)))            # new signature: records again
+    assert len(run.cache) == 2
+    assert first.shape == second.shape == (2, 16, 128) and other.shape == (2, 24, 128) and second.dtype == torch.bfloat16
+    if not gpu.has_device:
+        kinds = lambda t: Counter(l.split(" ")[0] for l in t._gpu.plan().strip().splitlines())
+        a, b = kinds(first), kinds(second)
+        # the replayed pass consists of the same kernels (the id upload / cast differs: it is outside the tape)
+        for k in ("fused_linear[bias,gelu,]_bf16", "fused_linear[bias,residual,]_bf16", "fused_attention[causal,merge_heads]_bf16", "layer_norm_bf16"):
+            assert a[k] == b[k] and a[k] > 0, k
+    with pytest.raises(TypeError, match="device tensors"):
+        tb.compile_forward(lambda ids: 3)(torch.zeros(2, 2))
+    # the failed recording was aborted: a new one can start
+    assert tb.compile_forward(lambda x: x + x)(torch.ones(2, 2)).shape == (2, 2)
