@@ -570,14 +570,13 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
       return Status::OK();
     }
     case Op::Concat: {
-      // two strided copies into disjoint slices of the output
+      // two strided copies into disjoint slices of the output, one launch
       int64_t dim = kd.i0;
       TensorRec lo = *out, hi = *out;
       lo.shape[dim] = in[0]->shape[dim];
       hi.shape[dim] = in[1]->shape[dim];
       hi.byte_offset += (size_t)(in[0]->shape[dim] * out->strides[dim]) * dtype_size(out->dtype);
-      AG_LAUNCH(k::copy_strided(s, in[0]->view(), lo.view()));
-      AG_LAUNCH(k::copy_strided(s, in[1]->view(), hi.view()));
+      AG_LAUNCH(k::copy_strided_pair(s, in[0]->view(), lo.view(), in[1]->view(), hi.view()));
       return Status::OK();
     }
     case Op::Gather: case Op::IndexSelect: {

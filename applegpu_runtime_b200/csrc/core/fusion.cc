@@ -61,17 +61,25 @@ static std::vector<Chain> find_chains(const Graph& g, const std::vector<uint64_t
   std::vector<Chain> chains;
   std::unordered_set<uint64_t> consumed;
   // position of each id in the order, so "first successor in execution order" is cheap
+  // only element-wise nodes can start or extend a chain: consumers are tracked for those alone
+  std::unordered_set<uint64_t> elem;
+  for (uint64_t id : order) {
+    const OpNode* n = g.get_node(id);
+    if (n && n->op.is_elementwise()) elem.insert(id);
+  }
+  if (elem.size() < 2) return chains;
   std::unordered_map<uint64_t, std::vector<uint64_t>> consumers;
   for (uint64_t id : order) {
     const OpNode* n = g.get_node(id);
     if (!n) continue;
     for (uint64_t in : n->inputs) {
+      if (!elem.count(in)) continue;
       auto& v = consumers[in];
       if (v.empty() || v.back() != id) v.push_back(id);
     }
   }
   for (uint64_t id : order) {
-    if (consumed.count(id)) continue;
+    if (consumed.count(id) || !elem.count(id)) continue;
     const OpNode* n = g.get_node(id);
     if (!n || !n->op.is_elementwise()) continue;
     Chain c;
@@ -152,19 +160,23 @@ static OpNode build_fused(const Graph& g, const Chain& c) {
 
 // ── graph-level rewrites ────────────────────────────────────────────────────
 struct Rewriter {
+  // Consumers of an id inside this evaluation: how many distinct nodes, and which one when it is the only one.
+  struct Cons { uint64_t first = 0, last = 0; uint32_t n = 0; };
   Graph& g;
   const std::unordered_set<uint64_t>& keep;
-  std::unordered_map<uint64_t, std::vector<uint64_t>> consumers;
+  std::unordered_map<uint64_t, Cons> consumers;
   std::unordered_set<uint64_t> removed;
   const std::unordered_set<uint64_t>* released = nullptr;   // ids whose caller-side handle is gone (null: unknown)
 
   Rewriter(Graph& gr, const std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& kp) : g(gr), keep(kp) {
+    consumers.reserve(order.size() * 2);
     for (uint64_t id : order) {
       const OpNode* n = g.get_node(id);
       if (!n) continue;
       for (uint64_t in : n->inputs) {
-        auto& v = consumers[in];
-        if (std::find(v.begin(), v.end(), id) == v.end()) v.push_back(id);
+        Cons& c = consumers[in];
+        if (c.n == 0) { c.first = c.last = id; c.n = 1; }
+        else if (c.last != id) { c.last = id; c.n++; }   // nodes arrive in order: one node's inputs are visited together
       }
     }
   }
@@ -174,18 +186,27 @@ struct Rewriter {
     if (keep.count(id)) return nullptr;
     if (g.ref_count(id) != 1) return nullptr;
     auto it = consumers.find(id);
-    if (it == consumers.end() || it->second.size() != 1) return nullptr;
-    if (removed.count(it->second[0])) return nullptr;
-    return g.get_node(it->second[0]);
+    if (it == consumers.end() || it->second.n != 1) return nullptr;
+    if (removed.count(it->second.first)) return nullptr;
+    return g.get_node(it->second.first);
   }
   void replace(const std::vector<uint64_t>& old_ids, OpNode fused) {
-    for (uint64_t id : old_ids) { g.remove_node(id); if (id != fused.id) removed.insert(id); }
-    // consumer bookkeeping for the fused node's inputs
-    for (uint64_t in : fused.inputs) {
-      auto& v = consumers[in];
-      v.erase(std::remove_if(v.begin(), v.end(), [&](uint64_t c) { return std::find(old_ids.begin(), old_ids.end(), c) != old_ids.end(); }), v.end());
-      v.push_back(fused.id);
+    // consumer bookkeeping for the fused node's inputs: the old nodes that read an input become one reader
+    for (size_t i = 0; i < fused.inputs.size(); i++) {
+      const uint64_t in = fused.inputs[i];
+      if (std::find(fused.inputs.begin(), fused.inputs.begin() + i, in) != fused.inputs.begin() + i) continue;
+      uint32_t readers = 0;
+      for (uint64_t oid : old_ids) {
+        const OpNode* on = g.get_node(oid);
+        if (on && std::find(on->inputs.begin(), on->inputs.end(), in) != on->inputs.end()) readers++;
+      }
+      Cons& c = consumers[in];
+      if (readers == 0) { if (c.n == 0) c.first = fused.id; c.last = fused.id; c.n++; continue; }
+      c.n -= (readers - 1);
+      if (c.n <= 1) { c.n = 1; c.first = fused.id; }
+      c.last = fused.id;
     }
+    for (uint64_t id : old_ids) { g.remove_node(id); if (id != fused.id) removed.insert(id); }
     g.add_node(std::move(fused));
   }
 };
@@ -199,18 +220,28 @@ struct Rewriter {
 static void sink_row_reshapes(Graph& g, std::vector<uint64_t>& order, const std::unordered_set<uint64_t>& keep,
                               const std::unordered_set<uint64_t>* released, std::vector<uint64_t>* minted) {
   if (!released || !minted) return;   // the reshape's id changes meaning: only when its caller-side handle is known to be gone
+  // candidates first (a reshape of a 2-D linear-layer node to 3 or more dims): most graphs have none
+  auto candidate = [&](const OpNode* r) -> const OpNode* {
+    if (!r || r->op.op != Op::Reshape || r->inputs.size() != 1 || r->out_shape.size() < 3) return nullptr;
+    const OpNode* x = g.get_node(r->inputs[0]);
+    if (!x || x->out_shape.size() != 2 || r->out_shape.back() != x->out_shape[1]) return nullptr;
+    const Op xo = x->op.op;
+    if (!(xo == Op::Matmul || xo == Op::MatmulInt8 || xo == Op::AddBias || xo == Op::ScalarMul || xo == Op::Gelu || xo == Op::GeluExact || xo == Op::Relu)) return nullptr;
+    return x;
+  };
+  bool any = false;
+  for (uint64_t id : order) if (candidate(g.get_node(id))) { any = true; break; }
+  if (!any) return;
   std::unordered_map<uint64_t, std::vector<uint64_t>> consumers;
-  bool any_reshape = false;
+  consumers.reserve(order.size() * 2);
   for (uint64_t id : order) {
     const OpNode* n = g.get_node(id);
     if (!n) continue;
-    if (n->op.op == Op::Reshape) any_reshape = true;
     for (uint64_t in : n->inputs) {
       auto& v = consumers[in];
       if (std::find(v.begin(), v.end(), id) == v.end()) v.push_back(id);
     }
   }
-  if (!any_reshape) return;
   std::unordered_map<uint64_t, std::vector<uint64_t>> before;   // ids to emit right before a node
   std::unordered_set<uint64_t> moved;
   for (size_t oi = 0; oi < order.size(); oi++) {
@@ -220,10 +251,8 @@ static void sink_row_reshapes(Graph& g, std::vector<uint64_t>& order, const std:
     if (keep.count(rid) || g.ref_count(rid) != 1 || !released->count(rid)) continue;
     auto ci = consumers.find(rid);
     if (ci == consumers.end() || ci->second.size() != 1) continue;
-    const OpNode* x = g.get_node(r->inputs[0]);
-    if (!x || x->out_shape.size() != 2 || r->out_shape.size() < 3 || r->out_shape.back() != x->out_shape[1]) continue;
-    const Op xo = x->op.op;
-    if (!(xo == Op::Matmul || xo == Op::MatmulInt8 || xo == Op::AddBias || xo == Op::ScalarMul || xo == Op::Gelu || xo == Op::GeluExact || xo == Op::Relu)) continue;
+    const OpNode* x = candidate(r);
+    if (!x) continue;
     const OpNode* c = g.get_node(ci->second[0]);
     if (!c || c->out_shape != r->out_shape || c->out_dtype != r->out_dtype || keep.count(x->id)) continue;
     const uint64_t cid = c->id, xid = x->id;

@@ -520,26 +520,32 @@ __global__ void __launch_bounds__(256) copy_strided_kernel(const E* __restrict__
   }
 }
 
-Status copy_strided(cudaStream_t s, const TView& src, const TView& dst) {
+// One strided copy, prepared for launch: collapsed shape / strides in units of `w` bytes.
+struct CopyJob {
+  const void* src; void* dst;
+  NdIndex idx; NdStrides<2> st;
+  int64_t n;          // elements of width w
+  bool flat;          // both sides are one contiguous run
+};
+
+static Status prepare_copy(const TView& src, const TView& dst, size_t max_w, CopyJob* job, size_t* width) {
   if (src.shape != dst.shape) return Status::compute("copy_strided shape mismatch " + dims_str(src.shape) + " vs " + dims_str(dst.shape));
   size_t esz = dtype_size(src.dtype);
   if (esz != dtype_size(dst.dtype)) return Status::compute("copy_strided element size mismatch");
   int64_t n = src.numel();
-  if (n == 0) return Status::OK();
+  if (n == 0) { job->src = src.ptr; job->dst = dst.ptr; job->n = 0; job->flat = true; job->idx.nd = 0; *width = esz; return Status::OK(); }
   int64_t shape_tmp[kMaxDims], strides_tmp[2][kMaxDims];
   int nd = src.nd();
   for (int d = 0; d < nd; d++) { shape_tmp[d] = src.shape[d]; strides_tmp[0][d] = src.strides[d]; strides_tmp[1][d] = dst.strides[d]; }
   nd = collapse(nd, shape_tmp, strides_tmp, 2);
-  if (nd == 1 && strides_tmp[0][0] == 1 && strides_tmp[1][0] == 1) {
-    cudaError_t e = cudaMemcpyAsync(dst.ptr, src.ptr, (size_t)n * esz, cudaMemcpyDeviceToDevice, s);
-    return cuda_status(e, "copy");
-  }
+  job->flat = nd == 1 && strides_tmp[0][0] == 1 && strides_tmp[1][0] == 1;
   // Widen the element to 16 bytes when the innermost runs allow it.
   size_t w = esz;
   int last = nd - 1;
-  if (strides_tmp[0][last] == 1 && strides_tmp[1][last] == 1) {
+  if (n > 0 && strides_tmp[0][last] == 1 && strides_tmp[1][last] == 1) {
     for (size_t cand : {16, 8, 4, 2}) {
       if (cand <= esz) break;
+      if (cand > max_w) continue;
       int64_t ratio = (int64_t)(cand / esz);
       bool ok = shape_tmp[last] % ratio == 0 &&
                 (reinterpret_cast<uintptr_t>(src.ptr) % cand) == 0 && (reinterpret_cast<uintptr_t>(dst.ptr) % cand) == 0;
@@ -552,9 +558,25 @@ Status copy_strided(cudaStream_t s, const TView& src, const TView& dst) {
       }
     }
   }
-  NdIndex idx; NdStrides<2> st;
-  idx.nd = nd;
-  for (int d = 0; d < kMaxDims; d++) { idx.shape[d] = d < nd ? shape_tmp[d] : 1; st.s[0][d] = d < nd ? strides_tmp[0][d] : 0; st.s[1][d] = d < nd ? strides_tmp[1][d] : 0; }
+  job->src = src.ptr; job->dst = dst.ptr; job->n = n;
+  job->idx.nd = nd;
+  for (int d = 0; d < kMaxDims; d++) {
+    job->idx.shape[d] = d < nd ? shape_tmp[d] : 1;
+    job->st.s[0][d] = d < nd ? strides_tmp[0][d] : 0; job->st.s[1][d] = d < nd ? strides_tmp[1][d] : 0;
+  }
+  *width = w;
+  return Status::OK();
+}
+
+Status copy_strided(cudaStream_t s, const TView& src, const TView& dst) {
+  CopyJob job; size_t w;
+  AG_RETURN_IF_ERROR(prepare_copy(src, dst, 16, &job, &w));
+  if (src.numel() == 0) return Status::OK();
+  if (job.flat) {
+    cudaError_t e = cudaMemcpyAsync(dst.ptr, src.ptr, (size_t)src.numel() * dtype_size(src.dtype), cudaMemcpyDeviceToDevice, s);
+    return cuda_status(e, "copy");
+  }
+  const NdIndex& idx = job.idx; const NdStrides<2>& st = job.st; const int64_t n = job.n;
   int grid = grid_for(n, 256, 8);
   switch (w) {
     case 16: copy_strided_kernel<uint4><<<grid, 256, 0, s>>>((const uint4*)src.ptr, (uint4*)dst.ptr, idx, st, n); break;
@@ -564,6 +586,54 @@ Status copy_strided(cudaStream_t s, const TView& src, const TView& dst) {
     default: copy_strided_kernel<uint8_t><<<grid, 256, 0, s>>>((const uint8_t*)src.ptr, (uint8_t*)dst.ptr, idx, st, n); break;
   }
   AG_CHECK_LAUNCH("copy_strided");
+  return Status::OK();
+}
+
+// Two strided copies in one launch (the two halves of a concat): blocks [0, blocks_a) run the first job,
+// the rest the second; both use the widest element both allow.
+template <typename E>
+__global__ void __launch_bounds__(256) copy_strided_pair_kernel(CopyJob a, CopyJob b, int blocks_a) {
+  const bool second = (int)blockIdx.x >= blocks_a;
+  const CopyJob& j = second ? b : a;
+  const int64_t nblocks = second ? (int64_t)gridDim.x - blocks_a : blocks_a;
+  const int64_t first = second ? (int64_t)blockIdx.x - blocks_a : blockIdx.x;
+  const E* __restrict__ src = reinterpret_cast<const E*>(j.src);
+  E* __restrict__ dst = reinterpret_cast<E*>(j.dst);
+  const int64_t stride = nblocks * blockDim.x;
+  for (int64_t i = first * blockDim.x + threadIdx.x; i < j.n; i += stride) {
+    int64_t r = i, oa = 0, ob = 0;
+    for (int d = j.idx.nd - 1; d >= 0; d--) {
+      int64_t c = r % j.idx.shape[d]; r /= j.idx.shape[d];
+      oa += c * j.st.s[0][d]; ob += c * j.st.s[1][d];
+    }
+    dst[ob] = src[oa];
+  }
+}
+
+Status copy_strided_pair(cudaStream_t s, const TView& src_a, const TView& dst_a, const TView& src_b, const TView& dst_b) {
+  if (src_a.numel() == 0) return copy_strided(s, src_b, dst_b);
+  if (src_b.numel() == 0) return copy_strided(s, src_a, dst_a);
+  CopyJob ja, jb; size_t wa, wb;
+  AG_RETURN_IF_ERROR(prepare_copy(src_a, dst_a, 16, &ja, &wa));
+  AG_RETURN_IF_ERROR(prepare_copy(src_b, dst_b, 16, &jb, &wb));
+  if (wa != wb) {
+    const size_t w = wa < wb ? wa : wb;
+    AG_RETURN_IF_ERROR(prepare_copy(src_a, dst_a, w, &ja, &wa));
+    AG_RETURN_IF_ERROR(prepare_copy(src_b, dst_b, w, &jb, &wb));
+    if (wa != wb) {   // one side cannot reach the common width (alignment): fall back to two launches
+      AG_RETURN_IF_ERROR(copy_strided(s, src_a, dst_a));
+      return copy_strided(s, src_b, dst_b);
+    }
+  }
+  const int ga = grid_for(ja.n, 256, 8), gb = grid_for(jb.n, 256, 8);
+  switch (wa) {
+    case 16: copy_strided_pair_kernel<uint4><<<ga + gb, 256, 0, s>>>(ja, jb, ga); break;
+    case 8: copy_strided_pair_kernel<uint64_t><<<ga + gb, 256, 0, s>>>(ja, jb, ga); break;
+    case 4: copy_strided_pair_kernel<uint32_t><<<ga + gb, 256, 0, s>>>(ja, jb, ga); break;
+    case 2: copy_strided_pair_kernel<uint16_t><<<ga + gb, 256, 0, s>>>(ja, jb, ga); break;
+    default: copy_strided_pair_kernel<uint8_t><<<ga + gb, 256, 0, s>>>(ja, jb, ga); break;
+  }
+  AG_CHECK_LAUNCH("copy_strided_pair");
   return Status::OK();
 }
 

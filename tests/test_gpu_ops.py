@@ -313,6 +313,33 @@ def test_cast_matrix(gpu_dev):
 
 
 # ── layout ops ──────────────────────────────────────────────────────────────
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "int32", "int8"])
+def test_concat_is_bit_exact_on_every_axis_and_layout(gpu_dev, dtype):
+    """Both halves of a concat are copied by one launch; the halves may allow different vector widths
+    (odd extents, strided views), and either may be a view."""
+    rng = np.random.default_rng(23)
+    def make(shape):
+        if dtype == "bfloat16":
+            bits = R.to_bf16(rng.standard_normal(shape).astype(np.float32))
+            return bits, gpu_dev.from_bytes(bits.tobytes(), list(shape), "bfloat16")
+        x = (rng.standard_normal(shape) * 50).astype({"float32": np.float32, "int32": np.int32, "int8": np.int8}[dtype])
+        return x, gpu_dev.from_numpy(x)
+    def host(t):
+        return np.frombuffer(t.to_bytes(), np.uint16).reshape(t.shape) if dtype == "bfloat16" else t.to_numpy()
+    for shape_a, shape_b, dim in [((4, 6, 8), (4, 6, 8), 0), ((4, 6, 8), (4, 3, 8), 1), ((4, 6, 8), (4, 6, 5), 2), ((3, 5, 7), (3, 5, 1), 2),
+                                  ((2, 3, 4, 16), (2, 3, 1, 16), 2), ((1, 64), (7, 64), 0), ((5, 1), (5, 9), 1)]:
+        a, ga = make(shape_a); b, gb = make(shape_b)
+        assert np.array_equal(host(gpu_dev.concat(ga, gb, dim=dim)), np.concatenate([a, b], dim)), (shape_a, shape_b, dim)
+    # the decode KV append: cache [B, h, T, d] and a new entry that is a transposed view of [B, 1, h, d]
+    cache, gc = make((2, 3, 5, 16)); new, gn = make((2, 1, 3, 16))
+    got = gpu_dev.concat(gc, gpu_dev.transpose_dims(gn, 1, 2), dim=2)
+    assert np.array_equal(host(got), np.concatenate([cache, new.transpose(0, 2, 1, 3)], 2))
+    # both operands strided
+    x, gx = make((6, 10)); y, gy = make((4, 10))
+    got = gpu_dev.concat(gpu_dev.transpose(gx), gpu_dev.transpose(gy), dim=1)
+    assert np.array_equal(host(got), np.concatenate([x.T, y.T], 1))
+
+
 def test_views_and_copies_match_numpy(gpu_dev):
     rng = np.random.default_rng(16)
     x = rng.standard_normal((6, 10, 8)).astype(np.float32)
