@@ -1,8 +1,8 @@
-// Skinny matmul: C[M, N] = A[M, K] * B[K, N] with M <= 16 (a decode step: one new token per sequence)
-// and 16-bit operands. The product is bound by reading B once (a weight matrix); the 128-row
+// Skinny matmul: C[M, N] = A[M, K] * B[K, N] with M <= 16 (a decode step: one new token per sequence),
+// 16-bit or float32 operands (float32: true fp32 multiply-adds, as kernel_templates.rs:987-1027 computes). The product is bound by reading B once (a weight matrix); the 128-row
 // tensor-core tiles would leave it on N/256 CTAs (3..12 of 148 SMs) at one SM's share of HBM bandwidth
 // each. Here the grid is (N / 64 column slabs) x (K / 128 row slabs): every CTA streams a 128 x 64 block
-// of B with coalesced 128-byte rows, keeps its 16 x 128 block of A in shared memory, and writes an fp32
+// of B with coalesced 128-byte (16-bit) or 256-byte (float32) rows, keeps its 16 x 128 block of A in shared memory, and writes an fp32
 // partial [M, 64] to a workspace; the last CTA to finish a column slab (a counter per slab) adds the
 // partials in K order (so the result does not depend on scheduling), applies the epilogue (alpha,
 // bias, activation, residual) and stores the slab. Same arithmetic contract as the other matmul kernels
@@ -31,8 +31,13 @@ struct SkinnyParams {
   unsigned int* counters;    // one per column slab, zero between launches
 };
 
+// four consecutive elements of B as one load
+template <typename T> struct BVec { using type = uint2; };
+template <> struct BVec<float> { using type = uint4; };
+
 template <typename T>
 __global__ void __launch_bounds__(kSkThreads) gemm_skinny_kernel(const SkinnyParams p) {
+  using V = typename BVec<T>::type;
   __shared__ float sA[kSkMaxM][kSkK];              // this CTA's block of A, as float
   __shared__ float sSum[kSkThreads / 32][kSkMaxM][kSkN];
   __shared__ unsigned int s_last;
@@ -46,12 +51,12 @@ __global__ void __launch_bounds__(kSkThreads) gemm_skinny_kernel(const SkinnyPar
   // 16 consecutive K rows; per instruction its two half-warps read two rows, 16 lanes x 8 bytes each.
   const int half = lane >> 4, cl = lane & 15;
   const int col = n0 + cl * 4;
-  uint2 bv[8];
+  V bv[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int kk = warp * 16 + i * 2 + half;
-    bv[i] = make_uint2(0u, 0u);
-    if (k0 + kk < p.k && col < p.n) bv[i] = __ldcs(reinterpret_cast<const uint2*>(B + (long long)(k0 + kk) * p.b_row + col));
+    bv[i] = V{};
+    if (k0 + kk < p.k && col < p.n) bv[i] = __ldcs(reinterpret_cast<const V*>(B + (long long)(k0 + kk) * p.b_row + col));
   }
   // A block -> shared as float (M x 128, zero rows beyond M): one 16-byte load per thread
   {
@@ -62,9 +67,14 @@ __global__ void __launch_bounds__(kSkThreads) gemm_skinny_kernel(const SkinnyPar
     if (m < p.m) {
       const T* src = A + (long long)m * p.a_row + k0 + ch * 8;
       if (p.a_vec && k0 + ch * 8 + 8 <= p.k) {
-        Pack<T> q = ld16(src);
+        if constexpr (sizeof(T) == 4) {
+          const float4 q0 = *reinterpret_cast<const float4*>(src), q1 = *reinterpret_cast<const float4*>(src + 4);
+          v[0] = q0.x; v[1] = q0.y; v[2] = q0.z; v[3] = q0.w; v[4] = q1.x; v[5] = q1.y; v[6] = q1.z; v[7] = q1.w;
+        } else {
+          Pack<T> q = ld16(src);
 #pragma unroll
-        for (int e = 0; e < 8; e++) v[e] = Cvt<T>::to(q.v[e]);
+          for (int e = 0; e < 8; e++) v[e] = Cvt<T>::to(q.v[e]);
+        }
       } else {
         for (int e = 0; e < 8; e++) if (k0 + ch * 8 + e < p.k) v[e] = Cvt<T>::to(src[e]);
       }
@@ -143,12 +153,13 @@ static unsigned int* g_sk_counters = nullptr;
 static std::once_flag g_sk_once;
 
 bool skinny_eligible(const GemmDesc& d) {
-  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16 || d.dtype == DType::F32) || d.b_dtype != d.dtype) return false;
   if (d.c_f32 || d.ep.argmax_keys || d.ep.b_scales) return false;
   if (d.batch != 1 || d.batch_inner != 1) return false;
   if (d.m < 1 || d.m > kSkMaxM || d.n < 256 || d.n > kSkMaxN || d.k < kSkK) return false;
   if (d.a_col != 1 || d.b_col != 1) return false;                       // A rows along K, B stored [K, N]
-  if (d.b_row % 4 != 0 || d.n % 4 != 0 || (reinterpret_cast<uintptr_t>(d.b) & 7u) != 0) return false;   // 8-byte loads of B
+  const uintptr_t b_align = d.dtype == DType::F32 ? 15u : 7u;                                            // 4-element loads of B
+  if (d.b_row % 4 != 0 || d.n % 4 != 0 || (reinterpret_cast<uintptr_t>(d.b) & b_align) != 0) return false;
   const int64_t ks = (d.k + kSkK - 1) / kSkK;
   if (ks > kSkMaxKSlabs || ks * d.n > kSkMaxPartials) return false;
   return true;
@@ -165,10 +176,11 @@ Status matmul_skinny(cudaStream_t s, const GemmDesc& d) {
   p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_row; p.c_row = d.c_row;
   p.partial = g_sk_partial; p.counters = g_sk_counters;
-  p.a_vec = (d.a_row % 8 == 0 && (reinterpret_cast<uintptr_t>(d.a) & 15u) == 0) ? 1 : 0;
+  p.a_vec = (d.a_row % (d.dtype == DType::F32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(d.a) & 15u) == 0) ? 1 : 0;
   dim3 grid((unsigned)((d.n + kSkN - 1) / kSkN), (unsigned)((d.k + kSkK - 1) / kSkK), 1);
   cudaError_t e;
   if (d.dtype == DType::BF16) e = launch_pdl(gemm_skinny_kernel<__nv_bfloat16>, grid, dim3(kSkThreads), 0, s, p);
+  else if (d.dtype == DType::F32) e = launch_pdl(gemm_skinny_kernel<float>, grid, dim3(kSkThreads), 0, s, p);
   else e = launch_pdl(gemm_skinny_kernel<__half>, grid, dim3(kSkThreads), 0, s, p);
   if (e != cudaSuccess) return cuda_status(e, "matmul (skinny)");
   return Status::OK();

@@ -305,6 +305,34 @@ def test_matmul_skinny_rows_against_a_weight_matrix(gpu_dev, dtype, m, n, k):
     assert rel_err(y.to_numpy(), want) <= 1.5e-2
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 2304, 768), (1, 768, 768), (16, 3072, 768), (8, 768, 3072), (5, 1000, 200), (3, 260, 129)])
+def test_matmul_skinny_float32(gpu_dev, m, n, k):
+    """The float32 form of the weight-streaming kernel: true fp32 multiply-adds (1e-5 relative of fp64),
+    equal to the CUDA-core tile kernel within rounding, deterministic, epilogue fused."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k)).astype(np.float32); b = (rng.standard_normal((k, n)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32); res = rng.standard_normal((m, n)).astype(np.float32)
+    ga, gb, gbias, gres = (gpu_dev.from_numpy(x) for x in (a, b, bias, res))
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    got = (ga @ gb).to_numpy()
+    assert rel_err(got, ref) <= 1e-5
+    assert np.array_equal(got, (ga @ gb).to_numpy())
+    gpu_dev.set_matmul_path("simt")
+    try:
+        simt = (ga @ gb).to_numpy()
+    finally:
+        gpu_dev.set_matmul_path("auto")
+    assert rel_err(got, simt.astype(np.float64)) <= 1e-5
+    y = gres + gpu_dev.relu(gpu_dev.add_bias(ga @ gb, gbias))
+    assert rel_err(y.to_numpy(), np.maximum(ref + bias, 0) + res) <= 1e-5
+    # a strided A (rows of a wider matrix) still qualifies; a transposed B does not and must still be right
+    wide = rng.standard_normal((m, k + 8)).astype(np.float32)
+    gs = gpu_dev.slice(gpu_dev.from_numpy(wide), 1, 4, 4 + k)
+    assert rel_err((gs @ gb).to_numpy(), wide[:, 4:4 + k].astype(np.float64) @ b.astype(np.float64)) <= 1e-5
+    gbt = gpu_dev.transpose(gpu_dev.from_numpy(np.ascontiguousarray(b.T)))
+    assert rel_err((ga @ gbt).to_numpy(), ref) <= 1e-5
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])
