@@ -101,13 +101,15 @@ def _linear(x, w, name):
     return gpu.add_bias(x @ gpu.transpose(w[name + ".weight"]), w[name + ".bias"])
 
 
-def bert_forward(model, input_ids, token_type_ids=None, all_reduce=None):
+def bert_forward(model, input_ids, token_type_ids=None, all_reduce=None, compiled=False):
     """Last hidden state [B, T, d] of the encoder for int token ids [B, T] (no padding mask: every
     sequence has full length, as in the benchmark configuration).
 
     `all_reduce(t) -> t`, when given, sums a [B*T, d] GpuTensor over the tensor-parallel group; it is
     called on the two row-parallel projections of every layer (after attention.output.dense and after
-    output.dense), before the residual and LayerNorm, which every rank then computes redundantly."""
+    output.dense), before the residual and LayerNorm, which every rank then computes redundantly.
+    `compiled=True` (single-rank form only) records the op sequence once per [B, T] on an op tape and replays
+    it on later calls: one library call per forward instead of ~500."""
     w = model["weights"]
     cfg = model["config"]
     n_layer, d = cfg["n_layer"], cfg["n_embd"]
@@ -123,6 +125,30 @@ def bert_forward(model, input_ids, token_type_ids=None, all_reduce=None):
     tok = gpu.from_numpy(np.ascontiguousarray(ids.reshape(-1), dtype=np.int32))
     pos = gpu.from_numpy(np.tile(np.arange(T, dtype=np.int32), B))
     typ = gpu.from_numpy(np.ascontiguousarray(types.reshape(-1), dtype=np.int32))
+    if compiled and all_reduce is None:
+        key = ("bert", B, T)
+        tape = model.setdefault("_tapes", {}).get(key)
+        if tape is not None:
+            return tape.replay([tok, pos, typ])[0]
+        gpu.tape_begin([tok, pos, typ])
+        try:
+            out = _record_forward(w, cfg, tok, pos, typ, B, T, None)
+        except Exception:
+            gpu.tape_abort()
+            raise
+        model["_tapes"][key] = gpu.tape_end(3, [out])
+        return out
+    return _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce)
+
+
+def _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce):
+    """Issues the ops of one encoder forward."""
+    n_layer, d = cfg["n_layer"], cfg["n_embd"]
+    heads = cfg.get("local_heads", cfg["n_head"])
+    dh = d // cfg["n_head"]
+    dl = heads * dh
+    eps = float(cfg.get("eps", 1e-12))
+    rows = B * T
     x = gpu.embedding(w["embeddings.word_embeddings.weight"], tok) + gpu.embedding(w["embeddings.position_embeddings.weight"], pos)
     x = x + gpu.embedding(w["embeddings.token_type_embeddings.weight"], typ)
     x = gpu.layer_norm(x, w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)

@@ -88,13 +88,13 @@ def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt):
         def fn():
             y = gpu.add_bias(x @ w, bias)
             if act:
-                y = gpu.gelu(y)
+                y = gpu.gelu_exact(y) if act == "erf" else gpu.gelu(y)
             return r + y if r is not None else y
         return fn
 
     ms = _time([make(*t) for t in sets], iters, single=opt.single)
     flops = 2.0 * m * n * k
-    name = "fused_linear[bias" + (",gelu" if act else "") + (",residual" if residual else "") + "]"
+    name = "fused_linear[bias" + (",gelu_erf" if act == "erf" else ",gelu" if act else "") + (",residual" if residual else "") + "]"
     return {"op": name, "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
@@ -152,6 +152,7 @@ def main(argv=None):
     ap.add_argument("--shape", default="")
     ap.add_argument("--dtype", default="")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--act", default="", help="'erf' for the exact GELU in --op linears")
     ap.add_argument("--single", action="store_true", help="time every launch with its own event pair (includes launch latency)")
     ap.add_argument("--no-rotate", dest="rotate", action="store_false", help="one buffer set: inputs stay L2-warm between launches")
     args = ap.parse_args(argv)
@@ -172,6 +173,11 @@ def main(argv=None):
             for (m, n, k, act, res) in [(8192, 2304, 768, False, False), (8192, 768, 768, False, True), (8192, 3072, 768, True, False),
                                         (8192, 768, 3072, False, True)]:
                 out.append(bench_fused_linear(rng, dt, m, n, k, act, res, args.iters, args))
+        if args.op == "linears" and dt != "float32":
+            # the four linears of a transformer layer at --shape rows,width (BERT-base: 131072,768 with --act erf)
+            rows, d = shape or [131072, 768]
+            for (n, k, act, res) in [(3 * d, d, False, False), (d, d, False, True), (4 * d, d, args.act or True, False), (d, 4 * d, False, True)]:
+                out.append(bench_fused_linear(rng, dt, rows, n, k, act, res, args.iters, args))
         if args.op == "lm_head":
             out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args))
         if args.op in ("all", "layer_norm"):

@@ -98,7 +98,7 @@ def bench_bert_base(dtype, batch, seq, iters):
     ids = np.random.default_rng(3).integers(0, BERT_BASE["vocab_size"], (batch, seq))
 
     def step():
-        bert_forward(model, ids).eval()
+        bert_forward(model, ids, compiled=True).eval()   # op tape: recorded by the first warm-up call
 
     ms = _time(step, iters, 2)
     flops = batch * seq * (_gemm_flops_per_token(BERT_BASE, BERT_BASE["d_ff"], lm_head=False) + 4 * seq * BERT_BASE["n_embd"] * BERT_BASE["n_layer"])

@@ -62,6 +62,12 @@ def test_mid_bert_fp32_and_bf16_against_torch_oracle(gpu_dev):
     got16 = gpu_dev.bert_forward(m16, ids, types).to_numpy()
     scale = float(np.max(np.abs(ref)))
     assert np.max(np.abs(got16 - ref)) <= 2e-2 * scale
+    # the taped forward: the recording call and two replays (the second on other ids) give the untaped results
+    for _ in range(2):
+        assert np.array_equal(gpu_dev.bert_forward(m16, ids, types, compiled=True).to_numpy(), got16)
+    ids2 = rng.integers(0, CFG_MID["vocab_size"], (3, 192))
+    assert np.array_equal(gpu_dev.bert_forward(m16, ids2, types, compiled=True).to_numpy(), gpu_dev.bert_forward(m16, ids2, types).to_numpy())
+    assert len(m16["_tapes"]) == 1
     assert gpu_dev.pipeline_status() == 0
 
 
