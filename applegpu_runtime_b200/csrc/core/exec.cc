@@ -278,10 +278,15 @@ static Status attention_exec(const TensorRec& q, const TensorRec& kk, const Tens
     };
     lead(q, &ad.q_b, &ad.q_h, &ad.q_t); lead(kk, &ad.k_b, &ad.k_h, &ad.k_t); lead(v, &ad.v_b, &ad.v_h, &ad.v_t);
     ad.scale = 1.0f / std::sqrt((float)dk); ad.causal = causal;
-    if (q.dtype == kk.dtype && q.dtype == v.dtype && k::attention_fused_eligible(ad)) {
-      ad.o = dst.data();
-      lead(dst, &ad.o_b, &ad.o_h, &ad.o_t);
+    ad.o = dst.data();
+    lead(dst, &ad.o_b, &ad.o_h, &ad.o_t);
+    const bool same_dtype = q.dtype == kk.dtype && q.dtype == v.dtype && q.dtype == dst.dtype;
+    if (same_dtype && k::attention_fused_eligible(ad)) {
       AG_LAUNCH(k::attention(ctx.stream, ad));
+      return Status::OK();
+    }
+    if (same_dtype && dst.strides.back() == 1 && k::attention_f32_eligible(ad)) {
+      AG_LAUNCH(k::attention_f32(ctx.stream, ad));
       return Status::OK();
     }
   }

@@ -113,6 +113,10 @@ struct AttnDesc {
 // tells whether `attention` accepts the problem, otherwise the caller composes it from GEMMs.
 bool attention_fused_eligible(const AttnDesc& d);
 Status attention(cudaStream_t s, const AttnDesc& d);
+// float32 form (CUDA-core multiply-adds, online softmax, d = dv = 64, 16-byte aligned rows; `o` and its strides
+// take part in the eligibility test).
+bool attention_f32_eligible(const AttnDesc& d);
+Status attention_f32(cudaStream_t s, const AttnDesc& d);
 
 // Writes more than the L2 capacity so the next timed kernel starts cold.
 Status flush_l2(cudaStream_t s, void* scratch, size_t bytes);

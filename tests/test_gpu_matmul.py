@@ -334,6 +334,29 @@ def test_matmul_skinny_float32(gpu_dev, m, n, k):
 
 
 # ── attention ───────────────────────────────────────────────────────────────
+@pytest.mark.parametrize("tq,tk,causal", [(1, 70, False), (5, 129, False), (200, 200, True), (64, 64, True), (65, 300, False)])
+def test_attention_f32_single_kernel_ragged_and_cached(gpu_dev, tq, tk, causal):
+    """Head dim 64 in float32 runs as one kernel (online softmax over 64-key blocks): query / key counts that are
+    not multiples of the tile, a single query against a cache, and strided (sliced) operands."""
+    rng = np.random.default_rng(tq * 1000 + tk)
+    q = rng.standard_normal((2, 3, tq, 64)).astype(np.float32)
+    k = rng.standard_normal((2, 3, tk, 64)).astype(np.float32)
+    v = rng.standard_normal((2, 3, tk, 64)).astype(np.float32)
+    fn = gpu_dev.attention_causal if causal else gpu_dev.attention
+    launches = gpu_dev.launch_count()
+    got = fn(gpu_dev.from_numpy(q), gpu_dev.from_numpy(k), gpu_dev.from_numpy(v)).to_numpy()
+    assert gpu_dev.launch_count() - launches == 1
+    ref = R.attention(q, k, v, causal)
+    np.testing.assert_allclose(got, ref, rtol=1e-4, atol=1e-5)
+    # operands that are slices of wider tensors (row pitch 192): still one kernel
+    wide = rng.standard_normal((2, 3, tk, 192)).astype(np.float32)
+    gw = gpu_dev.from_numpy(wide)
+    kk, vv = gpu_dev.slice(gw, 3, 64, 128), gpu_dev.slice(gw, 3, 128, 192)
+    got2 = fn(gpu_dev.from_numpy(q), kk, vv).to_numpy() if not causal or tq == tk else None
+    if got2 is not None:
+        np.testing.assert_allclose(got2, R.attention(q, wide[..., 64:128], wide[..., 128:192], causal), rtol=1e-4, atol=1e-5)
+
+
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(2, 8, 8), (3, 33, 16), (1, 4, 130, 64), (2, 12, 128, 64)])
 def test_attention_f32_matches_oracle(gpu_dev, causal, shape):
