@@ -142,7 +142,11 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
   const int packs = cols / N;
   for (int64_t row = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); row < total_rows; row += (int64_t)gridDim.x * wpb) {
     int valid = cols;
-    if (CAUSAL) { int r = (int)(row % rows_per_mat); valid = r + 1 < cols ? r + 1 : cols; }
+    if (CAUSAL) {
+      // 32-bit remainder where the row count allows it: the 64-bit one costs about a fifth of a 1024-column row
+      int r = total_rows <= 0x7fffffff ? (int)((unsigned int)row % (unsigned int)rows_per_mat) : (int)(row % rows_per_mat);
+      valid = r + 1 < cols ? r + 1 : cols;
+    }
     const T* x = in + row * cols;
     float v[ITERS][N];
     float m = CAUSAL ? -1e9f : -INFINITY;
