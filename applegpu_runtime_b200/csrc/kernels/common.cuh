@@ -37,6 +37,24 @@ __device__ __forceinline__ Pack<T> ld16(const T* p) {
   *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
   return r;
 }
+// Pack<T> from floats: 16-bit types convert two values per instruction.
+template <typename T>
+__device__ __forceinline__ void pack_from_floats(Pack<T>& o, const float* r) {
+#pragma unroll
+  for (int e = 0; e < Pack<T>::N; e++) o.v[e] = Cvt<T>::from(r[e]);
+}
+template <>
+__device__ __forceinline__ void pack_from_floats<__nv_bfloat16>(Pack<__nv_bfloat16>& o, const float* r) {
+  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int q = 0; q < 4; q++) o2[q] = __floats2bfloat162_rn(r[2 * q], r[2 * q + 1]);
+}
+template <>
+__device__ __forceinline__ void pack_from_floats<__half>(Pack<__half>& o, const float* r) {
+  __half2* o2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int q = 0; q < 4; q++) o2[q] = __floats2half2_rn(r[2 * q], r[2 * q + 1]);
+}
 // Streaming variants: data touched once should not displace reusable lines.
 template <typename T>
 __device__ __forceinline__ Pack<T> ld16_stream(const T* p) {

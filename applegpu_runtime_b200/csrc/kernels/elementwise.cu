@@ -400,14 +400,29 @@ __global__ void __launch_bounds__(256) add_bias_rows_kernel(const T* __restrict_
       if (col >= packs_per_row) col -= packs_per_row;
     }
     float v[U * N];
+    if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      // packed bf16 add: two sums per instruction, each rounded once to bf16 (what the separate add_bias kernel
+      // of the reference stores), then widened for the activation
 #pragma unroll
-    for (int u = 0; u < U; u++)
+      for (int u = 0; u < U; u++) {
+        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x[u]);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b[u]);
 #pragma unroll
-      for (int e = 0; e < N; e++) {
-        // The sum is rounded to the storage type before the activation, as two separate
-        // reference kernels (add_bias then gelu) would do.
-        v[u * N + e] = Cvt<T>::to(Cvt<T>::from(Cvt<T>::to(x[u].v[e]) + Cvt<T>::to(b[u].v[e])));
+        for (int q = 0; q < N / 2; q++) {
+          const float2 f = __bfloat1622float2(__hadd2(x2[q], b2[q]));
+          v[u * N + 2 * q] = f.x; v[u * N + 2 * q + 1] = f.y;
+        }
       }
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; u++)
+#pragma unroll
+        for (int e = 0; e < N; e++) {
+          // The sum is rounded to the storage type before the activation, as two separate
+          // reference kernels (add_bias then gelu) would do.
+          v[u * N + e] = Cvt<T>::to(Cvt<T>::from(Cvt<T>::to(x[u].v[e]) + Cvt<T>::to(b[u].v[e])));
+        }
+    }
     switch (act) {  // tested once per trip, not per element
       case Act::GeluTanh:
         if (std::is_same<T, __nv_bfloat16>::value) {
@@ -443,8 +458,14 @@ __global__ void __launch_bounds__(256) add_bias_rows_kernel(const T* __restrict_
       int64_t pk = pk0 + u * stride;
       if (pk >= n_packs) break;
       Pack<T> o;
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-      for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(v[u * N + e]);
+        for (int q = 0; q < N / 2; q++) o2[q] = __floats2bfloat162_rn(v[u * N + 2 * q], v[u * N + 2 * q + 1]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(v[u * N + e]);
+      }
       st16_stream(out + pk * N, o);
     }
   }

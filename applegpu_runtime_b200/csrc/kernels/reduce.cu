@@ -69,8 +69,10 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
         Pack<T> g = kHoist ? gpk[kHoist ? it : 0] : ld16(gamma + pk * N);
         Pack<T> b = kHoist ? bpk[kHoist ? it : 0] : ld16(beta + pk * N);
         Pack<T> o;
+        float r[N];
 #pragma unroll
-        for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(Cvt<T>::to(g.v[e]) * (v[it][e] - mean) * inv_std + Cvt<T>::to(b.v[e]));
+        for (int e = 0; e < N; e++) r[e] = Cvt<T>::to(g.v[e]) * (v[it][e] - mean) * inv_std + Cvt<T>::to(b.v[e]);
+        pack_from_floats<T>(o, r);
         st16(y + pk * N, o);   // the next kernel (a GEMM) reads this from L2: no evict-first hint
       }
     }
@@ -195,8 +197,10 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
       if (pk < packs) {
         Pack<T> o;
         if (c0 < valid) {
+          float r[N];
 #pragma unroll
-          for (int e = 0; e < N; e++) o.v[e] = (c0 + e < valid) ? Cvt<T>::from(v[it][e] * inv) : Cvt<T>::from(0.f);
+          for (int e = 0; e < N; e++) r[e] = (c0 + e < valid) ? v[it][e] * inv : 0.f;
+          pack_from_floats<T>(o, r);
         } else {
 #pragma unroll
           for (int e = 0; e < N; e++) o.v[e] = Cvt<T>::from(0.f);
