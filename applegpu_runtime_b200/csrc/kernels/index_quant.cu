@@ -280,10 +280,45 @@ static Status cast_from(cudaStream_t s, const S* in, const TView& out, int64_t n
   return Status::OK();
 }
 
+// int8 -> 16-bit float, 16 elements per thread (the widening of int8 weights ahead of a tensor-core GEMM: 1 byte
+// read and 2 written per element, so it has to run at memory speed). A byte b = v ^ 0x80 placed in the low
+// mantissa bits of 2^23 gives the float 8388608 + b exactly; subtracting 8388736 leaves v, which every 16-bit
+// float format holds exactly: no integer-to-float conversion instruction (a quarter-rate pipe) is needed.
+template <typename D>
+__global__ void __launch_bounds__(256) widen_i8_kernel(const int8_t* __restrict__ in, D* __restrict__ out, int64_t n16) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < n16; g += stride) {
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(in) + g);
+    const uint32_t w[4] = {raw.x ^ 0x80808080u, raw.y ^ 0x80808080u, raw.z ^ 0x80808080u, raw.w ^ 0x80808080u};
+    Pack<D> o[2];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float f[4];
+#pragma unroll
+      for (int b = 0; b < 4; b++) f[b] = __uint_as_float(0x4B000000u | ((w[i] >> (8 * b)) & 0xffu)) - 8388736.0f;
+      // elements 4*i .. 4*i+3 of the 16: the first 8 go to o[0], the rest to o[1]
+      float r[4] = {f[0], f[1], f[2], f[3]};
+      D* dst = &o[i >> 1].v[(i & 1) * 4];
+#pragma unroll
+      for (int b = 0; b < 4; b++) dst[b] = Cvt<D>::from(r[b]);
+    }
+    st16(out + g * 16, o[0]);          // the GEMM that follows reads these from L2: no evict-first hint
+    st16(out + g * 16 + 8, o[1]);
+  }
+}
+
 Status cast(cudaStream_t s, const TView& in, const TView& out) {
   if (!in.contiguous() || !out.contiguous()) return Status::compute("cast needs contiguous tensors");
   int64_t n = in.numel();
   if (n == 0) return Status::OK();
+  if (in.dtype == DType::I8 && (out.dtype == DType::BF16 || out.dtype == DType::F16) && n % 16 == 0 && aligned16(in.ptr) && aligned16(out.ptr)) {
+    const int64_t n16 = n / 16;
+    int grid = grid_for(n16, 256, 8);
+    if (out.dtype == DType::BF16) widen_i8_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const int8_t*)in.ptr, (__nv_bfloat16*)out.ptr, n16);
+    else widen_i8_kernel<__half><<<grid, 256, 0, s>>>((const int8_t*)in.ptr, (__half*)out.ptr, n16);
+    AG_CHECK_LAUNCH("cast (int8 widen)");
+    return Status::OK();
+  }
   switch (in.dtype) {
     case DType::F32: return cast_from<float>(s, (const float*)in.ptr, out, n);
     case DType::F16: return cast_from<__half>(s, (const __half*)in.ptr, out, n);

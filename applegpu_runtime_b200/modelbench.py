@@ -85,7 +85,7 @@ def bench_gpt2_large_int8(batch, seq, iters):
     ids = np.random.default_rng(2).integers(0, GPT2_LARGE["vocab_size"], (batch, seq))
 
     def step():
-        gpt2_forward(model, ids)[0].eval()
+        gpt2_forward(model, ids, compiled=True)[0].eval()   # op tape: recorded by the first warm-up call, replayed after
 
     ms = _time(step, iters, 2)
     flops = batch * seq * (_gemm_flops_per_token(GPT2_LARGE) + 4 * seq * GPT2_LARGE["n_embd"] * GPT2_LARGE["n_layer"])

@@ -310,6 +310,12 @@ def test_cast_matrix(gpu_dev):
     i64 = rng.integers(0, 50257, 777).astype(np.int64)
     assert np.array_equal(gpu_dev.cast(gpu_dev.from_numpy(i64), "int32").to_numpy(), i64.astype(np.int32))   # the int64->int32 index cast of applegpu_backend.cpp:901-903
     assert np.array_equal(gpu_dev.cast(g, "bool").to_numpy(), x != 0)
+    # int8 -> 16-bit floats (the widening of int8 weights before a tensor-core GEMM): every value, vector and scalar tails
+    for n in (256 * 40, 16 * 3, 1000):
+        q = np.resize(np.arange(-128, 128, dtype=np.int8), n)
+        gq = gpu_dev.from_numpy(q)
+        assert np.array_equal(gpu_dev.cast(gq, "float16").to_numpy(), q.astype(np.float16))
+        assert np.array_equal(np.frombuffer(gpu_dev.cast(gq, "bfloat16").to_bytes(), np.uint16), R.to_bf16(q.astype(np.float32)))
 
 
 # ── layout ops ──────────────────────────────────────────────────────────────
