@@ -10,6 +10,7 @@ events on the runtime stream after warm-up:
   gpt2_large_int8      GPT-2-large, per-output-channel int8 weights, bf16 activations, 32 x 512 tokens
   bert_base            BERT-base encoder, 256 x 512 tokens, bf16
   bert_base_tp         the same, heads / feed-forward units sharded over the ranks of a torchrun launch (NCCL)
+  gpt2_large_int8_sharded, bert_base_sharded   the batch of those configurations split over the ranks of a torchrun launch
 
   python -m applegpu_runtime_b200.modelbench --config all --dtype bfloat16
 """
@@ -153,9 +154,29 @@ def bench_bert_base_tp(dtype, batch, seq, iters):
     return r if rank == 0 else None
 
 
+def bench_batch_sharded(config, dtype, iters):
+    """gpt2_large_int8 or bert_base with the batch split over the launcher's ranks (torchrun, one rank per GPU): no
+    data-path collective, every rank runs the single-GPU forward on batch / world sequences. The time is the MAX
+    over ranks of the CUDA-event time; tokens/s counts every rank's tokens. Rank 0 returns the line."""
+    from .sharding import RankGroup, shard_range
+    group = RankGroup.from_env()
+    full = 32 if config == "gpt2_large_int8" else 256
+    lo, hi = shard_range(full, group.rank, group.world)
+    local = hi - lo
+    group.barrier()
+    r = bench_gpt2_large_int8(local, 512, iters) if config == "gpt2_large_int8" else bench_bert_base(dtype, local, 512, iters)
+    ms = group.max(r["ms"])
+    group.barrier()
+    out = {"config": config + "_batch_sharded", "dtype": r["dtype"], "ranks": group.world, "global_batch": full, "batch_per_rank": local, "seq": 512,
+           "ms": ms, "tokens_per_s": full * 512 / ms * 1e3, "tflops": r["tflops"] * r["ms"] / ms * full / local}
+    rank = group.rank
+    group.close()
+    return out if rank == 0 else None
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="all", choices=["all", "gpt2_small_prefill", "gpt2_small_decode", "gpt2_large_int8", "bert_base", "bert_base_tp"])
+    ap.add_argument("--config", default="all", choices=["all", "gpt2_small_prefill", "gpt2_small_decode", "gpt2_large_int8", "bert_base", "bert_base_tp", "gpt2_large_int8_sharded", "bert_base_sharded"])
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--iters", type=int, default=5)
     args = ap.parse_args(argv)
@@ -175,6 +196,10 @@ def main(argv=None):
         emit(bench_gpt2_large_int8(32, 512, max(1, args.iters // 2)))
     if args.config in ("all", "bert_base"):
         emit(bench_bert_base(args.dtype, 256, 512, max(1, args.iters // 2)))
+    if args.config in ("gpt2_large_int8_sharded", "bert_base_sharded"):   # under torchrun: one rank per GPU
+        r = bench_batch_sharded(args.config[:-len("_sharded")], args.dtype, max(1, args.iters // 2))
+        if r is not None:
+            emit(r)
     if args.config == "bert_base_tp":   # under torchrun: one rank per GPU
         r = bench_bert_base_tp(args.dtype, 256, 512, max(1, args.iters // 2))
         if r is not None:
