@@ -27,7 +27,7 @@ struct AttnF32Params {
 };
 
 template <bool CAUSAL>
-__global__ void __launch_bounds__(256) attention_f32_kernel(const AttnF32Params p) {
+__global__ void __launch_bounds__(256, 3) attention_f32_kernel(const AttnF32Params p) {
   extern __shared__ __align__(16) float af_smem[];
   float* Qs = af_smem;
   float* Ks = Qs + kAfQ * kAfPitch;

@@ -186,7 +186,7 @@ def main(argv=None):
             out.append(bench_softmax_causal(rng, dt, *(shape or [96, 1024, 1024]), args.iters, args))
         if args.op in ("all", "gelu_add_bias"):
             out.append(bench_gelu_add_bias(rng, dt, *(shape or [8192, 3072]), args.iters, args))
-        if args.op in ("all", "attention") and dt != "float32":
+        if args.op in ("all", "attention"):
             out.append(bench_attention(rng, dt, *(shape or [8, 12, 1024, 64]), True, args.iters, args))
         for r in out:
             if not r.get("_printed"):
