@@ -148,6 +148,132 @@ __global__ void __launch_bounds__(kSkThreads) gemm_skinny_kernel(const SkinnyPar
   if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;   // ready for the next launch on this stream
 }
 
+// ── K-major B ───────────────────────────────────────────────────────────────
+// The same problem with B stored [N, K] (rows along K: the tied LM head reads the embedding table this way).
+// Every output column is a dot product of a B row with the M rows of A: a warp takes four B rows at a time,
+// its lanes split K in 16-byte pieces (512 contiguous bytes per load instruction), A sits in shared memory as
+// floats, the partial sums are combined with shuffles, and 2 x 32 lanes apply the epilogue to the 16 x 4
+// results. No workspace, no cross-CTA step: the sum over K is in a fixed order.
+constexpr int kSkR = 4;   // B rows per warp and pass
+
+template <typename T, int MR>
+__global__ void __launch_bounds__(kSkThreads) gemm_skinny_kmajor_kernel(const SkinnyParams p) {
+  extern __shared__ __align__(16) float sAk[];     // [MR][K]
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* A = reinterpret_cast<const T*>(p.a);
+  const T* B = reinterpret_cast<const T*>(p.b);
+  pdl_wait();
+  pdl_trigger();
+  for (int i = threadIdx.x; i < MR * p.k; i += kSkThreads) {
+    const int m = i / p.k, kk = i - m * p.k;
+    sAk[i] = m < p.m ? Cvt<T>::to(A[(long long)m * p.a_row + kk]) : 0.f;
+  }
+  __syncthreads();
+  const long long warps_total = (long long)gridDim.x * (kSkThreads / 32);
+  for (long long n0 = ((long long)blockIdx.x * (kSkThreads / 32) + warp) * kSkR; n0 < p.n; n0 += warps_total * kSkR) {
+    float acc[MR][kSkR];
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+      for (int r = 0; r < kSkR; r++) acc[m][r] = 0.f;
+    for (int kc = lane * VEC; kc < p.k; kc += 32 * VEC) {
+      float bf[kSkR][VEC];
+#pragma unroll
+      for (int r = 0; r < kSkR; r++) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (n0 + r < p.n) raw = __ldcs(reinterpret_cast<const uint4*>(B + (n0 + r) * p.b_row + kc));   // b_row: elements between B rows here
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int x = 0; x < VEC; x++) bf[r][x] = Cvt<T>::to(e[x]);
+      }
+#pragma unroll
+      for (int m = 0; m < MR; m++) {
+        float af[VEC];
+#pragma unroll
+        for (int q = 0; q < VEC / 4; q++) {
+          const float4 a4 = *reinterpret_cast<const float4*>(sAk + m * p.k + kc + q * 4);
+          af[q * 4] = a4.x; af[q * 4 + 1] = a4.y; af[q * 4 + 2] = a4.z; af[q * 4 + 3] = a4.w;
+        }
+#pragma unroll
+        for (int r = 0; r < kSkR; r++)
+#pragma unroll
+          for (int x = 0; x < VEC; x++) acc[m][r] = fmaf(af[x], bf[r][x], acc[m][r]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+      for (int r = 0; r < kSkR; r++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[m][r] += __shfl_xor_sync(0xffffffffu, acc[m][r], o);
+    // every lane holds all MR x 4 sums: lane l finishes (m, r) pairs l, l + 32, ...
+    T* C = reinterpret_cast<T*>(p.c);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    const T* R = reinterpret_cast<const T*>(p.residual);
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+      for (int r = 0; r < kSkR; r++) {
+        if (((m * kSkR + r) & 31) != lane) continue;
+        const long long n = n0 + r;
+        if (m >= p.m || n >= p.n) continue;
+        float v = acc[m][r] * p.alpha;
+        if (bias) v += Cvt<T>::to(bias[n]);
+        v = apply_act(v, (Act)p.act);
+        if (R) v += Cvt<T>::to(R[(long long)m * p.c_row + n]);
+        C[(long long)m * p.c_row + n] = Cvt<T>::from(v);
+      }
+  }
+}
+
+constexpr int kSkKmMaxSmem = 96 * 1024;
+
+bool skinny_kmajor_eligible(const GemmDesc& d) {
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16 || d.dtype == DType::F32) || d.b_dtype != d.dtype) return false;
+  if (d.c_f32 || d.ep.argmax_keys || d.ep.b_scales) return false;
+  if (d.batch != 1 || d.batch_inner != 1) return false;
+  if (d.m < 1 || d.m > kSkMaxM || d.n < 256 || d.k < 64) return false;
+  if (d.a_col != 1 || d.b_row != 1) return false;                       // A rows along K, B stored [N, K]
+  const int vec = d.dtype == DType::F32 ? 4 : 8;
+  if (d.k % vec != 0 || d.b_col % vec != 0 || (reinterpret_cast<uintptr_t>(d.b) & 15u) != 0) return false;   // 16-byte loads of B rows
+  const int mr = d.m <= 8 ? 8 : 16;
+  if ((int64_t)mr * d.k * (int64_t)sizeof(float) > kSkKmMaxSmem) return false;
+  return true;
+}
+
+template <typename T>
+static cudaError_t launch_kmajor(cudaStream_t s, const SkinnyParams& p, int mr, size_t smem, dim3 grid) {
+  auto k8 = gemm_skinny_kmajor_kernel<T, 8>;
+  auto k16 = gemm_skinny_kmajor_kernel<T, 16>;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k8, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkKmMaxSmem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k16, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkKmMaxSmem);
+    if (e != cudaSuccess) return e;
+    attr = true;
+  }
+  return mr == 8 ? launch_pdl(k8, grid, dim3(kSkThreads), smem, s, p) : launch_pdl(k16, grid, dim3(kSkThreads), smem, s, p);
+}
+
+Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d) {
+  SkinnyParams p;
+  p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
+  p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_col; p.c_row = d.c_row;   // b_row: stride between B's [N, K] rows
+  p.partial = nullptr; p.counters = nullptr; p.a_vec = 0;
+  const int mr = d.m <= 8 ? 8 : 16;
+  const size_t smem = (size_t)mr * d.k * sizeof(float);
+  const long long groups = (d.n + kSkR - 1) / kSkR, per_block = kSkThreads / 32;
+  long long blocks = (groups + per_block - 1) / per_block;
+  const long long cap = (long long)sm_count() * (smem > 48 * 1024 ? 2 : 4);
+  if (blocks > cap) blocks = cap;
+  cudaError_t e = d.dtype == DType::F32 ? launch_kmajor<float>(s, p, mr, smem, dim3((unsigned)blocks))
+                : d.dtype == DType::BF16 ? launch_kmajor<__nv_bfloat16>(s, p, mr, smem, dim3((unsigned)blocks))
+                                         : launch_kmajor<__half>(s, p, mr, smem, dim3((unsigned)blocks));
+  if (e != cudaSuccess) return cuda_status(e, "matmul (skinny, K-major B)");
+  return Status::OK();
+}
+
 static float* g_sk_partial = nullptr;
 static unsigned int* g_sk_counters = nullptr;
 static std::once_flag g_sk_once;

@@ -763,6 +763,8 @@ static bool tc_eligible(const GemmDesc& d) {
 Status matmul_simt(cudaStream_t s, const GemmDesc& d);
 bool skinny_eligible(const GemmDesc& d);
 Status matmul_skinny(cudaStream_t s, const GemmDesc& d);
+bool skinny_kmajor_eligible(const GemmDesc& d);
+Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d);
 
 static int* g_status_word = nullptr;   // device int, lazily allocated once per process
 static int* g_status_host = nullptr;   // pinned mirror
@@ -942,6 +944,9 @@ Status matmul(cudaStream_t s, const GemmDesc& d) {
   if (d.ep.argmax_keys && (!elig || g_force_path == 1)) return Status::invalid("matmul: the row-argmax epilogue needs the tensor-core kernel");
   // a handful of rows against a [K, N] weight: bound by streaming B, spread over every SM
   if (g_force_path == 0 && skinny_eligible(d)) return matmul_skinny(s, d);
+  // the same against a [N, K] weight; 16-bit products that large keep the tensor-core kernel (it is as fast there and
+  // feeds the fused argmax), float32 ones would otherwise fall to the CUDA-core tile kernel
+  if (g_force_path == 0 && d.dtype == DType::F32 && skinny_kmajor_eligible(d)) return matmul_skinny_kmajor(s, d);
   if (g_force_path == 2 && !elig) return Status::compute("matmul: tcgen05 path forced but operands are not TMA-compatible");
   if (elig && g_force_path != 1) {
     int* st = matmul_status_word();

@@ -305,7 +305,7 @@ def test_matmul_skinny_rows_against_a_weight_matrix(gpu_dev, dtype, m, n, k):
     assert rel_err(y.to_numpy(), want) <= 1.5e-2
 
 
-@pytest.mark.parametrize("m,n,k", [(8, 2304, 768), (1, 768, 768), (16, 3072, 768), (8, 768, 3072), (5, 1000, 200), (3, 260, 129)])
+@pytest.mark.parametrize("m,n,k", [(8, 2304, 768), (1, 768, 768), (16, 3072, 768), (8, 768, 3072), (5, 1000, 200), (3, 260, 129), (8, 50257, 768), (12, 1001, 1536)])
 def test_matmul_skinny_float32(gpu_dev, m, n, k):
     """The float32 form of the weight-streaming kernel: true fp32 multiply-adds (1e-5 relative of fp64),
     equal to the CUDA-core tile kernel within rounding, deterministic, epilogue fused."""
@@ -325,12 +325,17 @@ def test_matmul_skinny_float32(gpu_dev, m, n, k):
     assert rel_err(got, simt.astype(np.float64)) <= 1e-5
     y = gres + gpu_dev.relu(gpu_dev.add_bias(ga @ gb, gbias))
     assert rel_err(y.to_numpy(), np.maximum(ref + bias, 0) + res) <= 1e-5
-    # a strided A (rows of a wider matrix) still qualifies; a transposed B does not and must still be right
+    # a strided A (rows of a wider matrix) still qualifies
     wide = rng.standard_normal((m, k + 8)).astype(np.float32)
     gs = gpu_dev.slice(gpu_dev.from_numpy(wide), 1, 4, 4 + k)
     assert rel_err((gs @ gb).to_numpy(), wide[:, 4:4 + k].astype(np.float64) @ b.astype(np.float64)) <= 1e-5
+    # B stored [N, K] (the tied LM head): the K-major weight-streaming kernel where K is a multiple of 4, else the tile kernel
     gbt = gpu_dev.transpose(gpu_dev.from_numpy(np.ascontiguousarray(b.T)))
-    assert rel_err((ga @ gbt).to_numpy(), ref) <= 1e-5
+    got_t = (ga @ gbt).to_numpy()
+    assert rel_err(got_t, ref) <= 1e-5
+    assert np.array_equal(got_t, (ga @ gbt).to_numpy())
+    yt = gres + gpu_dev.relu(gpu_dev.add_bias(ga @ gbt, gbias))
+    assert rel_err(yt.to_numpy(), np.maximum(ref + bias, 0) + res) <= 1e-5
 
 
 # ── attention ───────────────────────────────────────────────────────────────
