@@ -119,12 +119,12 @@ Status LazyRuntime::eval(uint64_t id) {
 
   // remaining uses inside this evaluation, to drop dead intermediates early
   for (uint64_t nid : order) {
-    OpNode node;
     const OpNode* np = graph_.get_node(nid);
     if (!np) return Status::graph("node " + std::to_string(nid) + " vanished during evaluation");
-    node = *np;
+    const OpNode& node_ref = *np;   // executed in place; moved out of the graph afterwards (no deep copy per node)
     std::vector<const TensorRec*> ins;
-    for (uint64_t in : node.inputs) {
+    ins.reserve(node_ref.inputs.size());
+    for (uint64_t in : node_ref.inputs) {
       auto t = tensors_.find(in);
       if (t == tensors_.end() || !t->second.has_meta)
         return Status::graph("Input tensor " + std::to_string(in) + " for op " + std::to_string(nid) + " is not materialized");
@@ -134,10 +134,11 @@ Status LazyRuntime::eval(uint64_t id) {
     auto pa = prealloc_.find(nid);
     if (pa != prealloc_.end()) { ob = pa->second; }
     TensorRec out;
-    Status st = execute_node(node, ins, &out, ob);
+    Status st = execute_node(node_ref, ins, &out, ob);
     if (!st.ok()) return st;  // the graph keeps the unevaluated remainder, like abort_batch upstream
     if (pa != prealloc_.end()) prealloc_.erase(pa);
-    graph_.remove_node(nid);
+    OpNode node;
+    graph_.remove_node(nid, &node);
     out.has_meta = true;
     tensors_[nid] = std::move(out);
     kernels_launched++;
