@@ -104,3 +104,19 @@ def test_compile_forward_matches_the_uncompiled_forward(tb):
             got = run(ids).to_torch_cpu()
             assert _rel(got, ref(ids)) < 2e-4
     assert len(run.cache) == 1 and gpu.pipeline_status() == 0
+
+
+def test_hf_bert_random_init_matches_cpu(tb):
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.BertConfig(num_hidden_layers=2, hidden_size=128, num_attention_heads=2, intermediate_size=512, vocab_size=200,
+                                  max_position_embeddings=64, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    ref = transformers.BertModel(cfg, add_pooling_layer=False).eval()
+    ids = torch.randint(0, 200, (3, 40))
+    with torch.no_grad():
+        want = ref(ids).last_hidden_state
+        got = tb.to_applegpu(copy.deepcopy(ref))(ids).last_hidden_state
+        got16 = tb.to_applegpu(copy.deepcopy(ref), torch.bfloat16)(ids).last_hidden_state
+    assert tb.fallback_stats() == {}
+    assert _rel(got.to_torch_cpu(), want) < 2e-4
+    assert _rel(got16.to_torch_cpu().float(), want) < 3e-2     # 64-wide heads in bf16: tensor-core attention and linears

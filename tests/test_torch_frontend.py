@@ -96,3 +96,20 @@ def test_compile_forward_replays_the_recorded_ops(tb, gpu):
         tb.compile_forward(lambda ids: 3)(torch.zeros(2, 2))
     # the failed recording was aborted: a new one can start
     assert tb.compile_forward(lambda x: x + x)(torch.ones(2, 2)).shape == (2, 2)
+
+
+def test_hf_bert_records_without_fallback(tb, gpu):
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.BertConfig(num_hidden_layers=2, hidden_size=128, num_attention_heads=2, intermediate_size=512, vocab_size=200,
+                                  max_position_embeddings=64, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = tb.to_applegpu(transformers.BertModel(cfg, add_pooling_layer=False).eval())
+    with torch.no_grad():
+        out = model(torch.randint(0, 200, (2, 16))).last_hidden_state
+    assert isinstance(out, tb.ApplegpuTensor) and out.shape == (2, 16, 128)
+    assert tb.fallback_stats() == {}
+    if not gpu.has_device:
+        kinds = [l.split(" ")[0] for l in out._gpu.plan().strip().splitlines()]
+        assert kinds.count("fused_attention[full,merge_heads]_f32") == 2            # bidirectional, head merge absorbed
+        assert kinds.count("fused_linear[bias,gelu_exact,]_f32") == 2                # erf-GELU in the GEMM epilogue
+        assert kinds.count("fused_linear[bias,residual,]_f32") == 4 and kinds.count("layer_norm_f32") == 5
