@@ -151,7 +151,7 @@ def test_kv_cache_decode_is_not_slower_than_recomputing(gpu_dev):
 
 
 def test_mlp_config_fp32(gpu_dev):
-    # BASELINE config 0: Linear(64,128) -> ReLU -> Linear(128,10), batch 32, default nn.Linear init, seed 0
+    # the first benchmark configuration: Linear(64,128) -> ReLU -> Linear(128,10), batch 32, default nn.Linear init, seed 0
     torch.manual_seed(0)
     l1 = torch.nn.Linear(64, 128); l2 = torch.nn.Linear(128, 10)
     x = torch.randn(32, 64)

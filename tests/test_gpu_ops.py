@@ -1,7 +1,7 @@
 """Parity of the CUDA kernels with the CPU oracle, through the C ABI (graph flavour via the
 Python surface, eager flavour via raw ctypes in test_gpu_eager_abi.py).
 
-Bars (BASELINE north_star): bit-exact for quantize, argmax, gather, index_select, embedding;
+Bars: bit-exact for quantize, argmax, gather, index_select, embedding;
 <= 1e-5 relative for fp32 element-wise and reduction ops; bf16/f16 compared with the oracle run
 in the same storage type. Shapes mirror the reference's tests (python/tests/test_transformer_ops.py,
 test_batched_ops.py, crates/core/src/ops.rs tests) plus ragged / empty / non-multiple-of-vector sizes.
