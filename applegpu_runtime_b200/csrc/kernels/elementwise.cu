@@ -385,6 +385,8 @@ __global__ void __launch_bounds__(256) add_bias_rows_kernel(const T* __restrict_
                                                              int64_t n_packs, int packs_per_row, Act act) {
   constexpr int N = Pack<T>::N;
   constexpr int U = 4;       // independent 16-byte loads in flight per thread and trip
+  pdl_wait();
+  pdl_trigger();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   // the pack's column is tracked incrementally: a 64-bit modulo per pack costs more than the activation
   const int step = (int)(stride % packs_per_row);
@@ -493,7 +495,9 @@ Status add_bias(cudaStream_t s, const TView& in, const TView& bias, Act act, con
   if (inner == 1 && channels % per == 0 && aligned16(in.ptr) && aligned16(out.ptr) && aligned16(bias.ptr)) {
     int64_t n_packs = n / per;
     int grid = grid_for(n_packs, 256, 8);
-    AG_DISPATCH_FLOAT(in.dtype, T, (add_bias_rows_kernel<T><<<grid, 256, 0, s>>>((const T*)in.ptr, (const T*)bias.ptr, (T*)out.ptr, n_packs, (int)(channels / per), act)));
+    cudaError_t le = cudaSuccess;
+    AG_DISPATCH_FLOAT(in.dtype, T, (le = launch_pdl(add_bias_rows_kernel<T>, dim3(grid), dim3(256), 0, s, (const T*)in.ptr, (const T*)bias.ptr, (T*)out.ptr, n_packs, (int)(channels / per), act)));
+    if (le != cudaSuccess) return cuda_status(le, "add_bias");
   } else {
     int grid = grid_for(n, 256, 8);
     AG_DISPATCH_FLOAT(in.dtype, T, (add_bias_generic_kernel<T><<<grid, 256, 0, s>>>((const T*)in.ptr, (const T*)bias.ptr, (T*)out.ptr, n, inner, channels, act)));
