@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int packs = cols / N;
+  pdl_wait();
+  pdl_trigger();
   for (int64_t row = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); row < total_rows; row += (int64_t)gridDim.x * wpb) {
     int valid = cols;
     if (CAUSAL) {
@@ -249,10 +251,12 @@ static Status softmax_t(cudaStream_t s, const TView& in, const TView& out) {
     const int threads = 128, wpb = 4;
     int grid = grid_for(total_rows, wpb, 16);
     int iters = (int)((packs + 31) / 32);
-#define AG_SM(I) softmax_warp_kernel<T, I, CAUSAL><<<grid, threads, 0, s>>>(x, y, total_rows, (int)rows_per_mat, (int)cols)
+    cudaError_t le = cudaSuccess;
+#define AG_SM(I) le = launch_pdl(softmax_warp_kernel<T, I, CAUSAL>, dim3(grid), dim3(threads), 0, s, x, y, total_rows, (int)rows_per_mat, (int)cols)
     if (iters <= 1) AG_SM(1); else if (iters <= 2) AG_SM(2); else if (iters <= 4) AG_SM(4);
     else if (iters <= 8) AG_SM(8); else AG_SM(16);
 #undef AG_SM
+    if (le != cudaSuccess) return cuda_status(le, "softmax");
   } else {
     int grid = (int)(total_rows < (int64_t)sm_count() * 8 ? total_rows : (int64_t)sm_count() * 8);
     softmax_block_kernel<T, CAUSAL><<<grid, 256, 0, s>>>(x, y, total_rows, rows_per_mat, cols);
