@@ -177,6 +177,8 @@ EXT_SYMBOLS = {
     "applegpu_profile_report": (i64, [ctypes.c_char_p, u64]),
     "applegpu_resolve_kernel": (cstr, [cstr, i8]),
     "applegpu_attention_noalloc": (i32, [vp, vp, vp, vp, i8, u64, u64, u64, u64, u64, cbool, vp]),
+    "applegpu_attention_noalloc_status": (i32, [vp]),
+    "applegpu_test_wait_runs_out": (i32, [i32, u32]),
 }
 
 _lib = None

@@ -518,6 +518,14 @@ def set_matmul_path(mode):
     _L().applegpu_set_matmul_path({"auto": 0, "simt": 1, "tcgen05": 2, "tcgen05_1cta": 3, "tcgen05_pair": 4}[mode])
 
 
+def matmul_path(a, b):
+    """Which kernel family `a @ b` would take for these two (materialised) tensors: 'tcgen05' or 'simt'."""
+    r = _L().applegpu_matmul_path(a.id, b.id, False)
+    if not r:
+        raise ValueError("matmul_path: unknown tensor id or not a matrix")
+    return r.decode()
+
+
 def set_f32_split(on=True):
     """Large float32 matmuls as a three-term bf16 split on the tensor cores (default) or always on CUDA cores."""
     _L().applegpu_set_f32_split(bool(on))

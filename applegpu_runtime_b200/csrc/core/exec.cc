@@ -113,8 +113,12 @@ Status download(const TensorRec& t, void* host, size_t nbytes, bool wait) {
     if (e != cudaSuccess) return Status::compute(std::string("download: ") + cudaGetErrorString(e));
   }
   if (!wait) return Status::OK();  // stream-ordered: the bytes are defined after the next synchronize
+  k::status_snapshot(ctx.stream, 0);
   cudaError_t e = cudaStreamSynchronize(ctx.stream);
   if (e != cudaSuccess) return Status::compute(std::string("synchronize: ") + cudaGetErrorString(e));
+  // a tcgen05 kernel whose bounded wait gave up left its code in the pipeline status word: the bytes are not a result
+  int code = k::status_take(ctx.stream, 0);
+  if (code != 0) return Status::compute("tensor-core pipeline wait timed out (code " + std::to_string(code) + ")");
   return Status::OK();
 }
 

@@ -7,6 +7,7 @@
 // backing store is cudaMallocAsync on the runtime's stream, so release -> acquire needs no
 // device synchronisation.
 #include "runtime.h"
+#include "../kernels/kernels.h"
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -91,6 +92,9 @@ Status DeviceCtx::init(bool allow_dry) {
     host_visible = true;
   }
   device = dev; sm_count = prop.multiProcessorCount; total_mem = prop.totalGlobalMem; name = prop.name;
+  // the kernel layer's fixed workspace (status word, skinny-GEMM partials): here, not inside an op call
+  Status ws = k::init_device_workspace(stream);
+  if (!ws.ok()) return Status::no_device("Failed to create the kernel workspace: " + ws.to_string());
   ready = true;
   return Status::OK();
 }

@@ -5,6 +5,7 @@
 #include "../../../include/applegpu_b200_ffi.h"
 #include "../../../include/applegpu_b200_ext.h"
 #include "../core/runtime.h"
+#include "../kernels/kernels.h"
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -20,7 +21,6 @@ uint64_t launch_count();
 namespace profile { void enable(bool on); void clear(); std::string report(); }
 namespace k {
 void set_matmul_path(int mode);
-int matmul_take_status(cudaStream_t s);
 }
 }
 using namespace ag;
@@ -148,7 +148,7 @@ Status init_device(bool dry) {
 }
 
 cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
-void* g_flush_buf = nullptr;
+std::shared_ptr<Buffer> g_flush_buf;   // taken from the stream-ordered pool on first use, kept
 constexpr size_t kFlushBytes = (size_t)256 << 20;  // 2x the 126 MB L2
 
 }  // namespace
@@ -444,9 +444,20 @@ int32_t applegpu_ffi_eval(uint64_t tensor_id) {
   if (!s.ok()) { set_ffi_error("eval failed: " + s.to_string()); return -1; }
   return 0;
 }
+// Waits for the runtime stream. A tcgen05 kernel whose bounded wait gave up leaves its code in the
+// pipeline status word; every blocking point of the library reads that word once the stream is idle
+// and turns a non-zero value into an error (here, where the signature returns nothing, into the
+// last-error text of both flavours), so a timed-out pipeline cannot pass for a result.
 void applegpu_ffi_synchronize(void) {
   DeviceCtx& ctx = DeviceCtx::get();
-  if (ctx.ready && !ctx.dry) cudaStreamSynchronize(ctx.stream);
+  if (!ctx.ready || ctx.dry) return;
+  k::status_snapshot(ctx.stream, 0);
+  cudaStreamSynchronize(ctx.stream);
+  int code = k::status_take(ctx.stream, 0);
+  if (code != 0) {
+    std::string m = "synchronize failed: tensor-core pipeline wait timed out (code " + std::to_string(code) + "); results since the last synchronisation are undefined";
+    set_ffi_error(m); set_eager_error(m);
+  }
 }
 int32_t applegpu_ffi_read_f32(uint64_t tensor_id, float* out_ptr, uint64_t max_elements) {
   if (!ffi_ready("read_f32")) return -1;
@@ -1139,6 +1150,7 @@ uint64_t applegpu_marker_record(void) {
   uint64_t seq = ++g_marker_seq;
   cudaEvent_t& ev = g_markers[seq % kMarkerSlots];
   if (!ev && cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { ev = nullptr; return 0; }
+  k::status_snapshot(ctx.stream, 1 + (int)(seq % kMarkerSlots));   // read back by marker_wait
   if (cudaEventRecord(ev, ctx.stream) != cudaSuccess) return 0;
   return seq;
 }
@@ -1154,13 +1166,26 @@ int32_t applegpu_marker_wait(uint64_t marker) {
     ev = g_markers[marker % kMarkerSlots];
   }
   if (!ev) return -1;
-  return cudaEventSynchronize(ev) == cudaSuccess ? 0 : -1;
+  if (cudaEventSynchronize(ev) != cudaSuccess) return -1;
+  int code = k::status_take(ctx.stream, 1 + (int)(marker % kMarkerSlots));
+  if (code != 0) {
+    set_ffi_error("marker_wait failed: tensor-core pipeline wait timed out (code " + std::to_string(code) + ")");
+    return -1;
+  }
+  return 0;
 }
 int32_t applegpu_flush_l2(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return -1;
-  if (!g_flush_buf && cudaMalloc(&g_flush_buf, kFlushBytes) != cudaSuccess) { g_flush_buf = nullptr; return -1; }
-  return k::flush_l2(ctx.stream, g_flush_buf, kFlushBytes).ok() ? 0 : -1;
+  if (!g_flush_buf && !Shared::get().pool.acquire(kFlushBytes, &g_flush_buf).ok()) { g_flush_buf.reset(); return -1; }
+  return k::flush_l2(ctx.stream, g_flush_buf->ptr, kFlushBytes).ok() ? 0 : -1;
+}
+int32_t applegpu_test_wait_runs_out(int32_t code, uint32_t limit_us) {
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (!ctx.ready || ctx.dry) return -1;
+  Status s = k::launch_wait_runs_out(ctx.stream, code, (unsigned long long)limit_us * 1000ull);
+  if (!s.ok()) { set_ffi_error("test_wait_runs_out failed: " + s.to_string()); return -1; }
+  return 0;
 }
 void applegpu_profile_enable(bool on) { ag::profile::enable(on); }
 void applegpu_profile_clear(void) { ag::profile::clear(); }

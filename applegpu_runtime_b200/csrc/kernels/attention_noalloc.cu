@@ -35,6 +35,10 @@ DeviceSlots g_slots[kMaxDevices];
 std::mutex g_slots_mu;
 
 // First call on a device resolves the two symbols; later calls reuse the pointers.
+// The device the first successful call saw (-1 before that).
+int g_first_device = -1;
+int first_device_seen() { std::lock_guard<std::mutex> g(g_slots_mu); return g_first_device; }
+
 ag::Status slots_for_current_device(DeviceSlots** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
@@ -50,6 +54,7 @@ ag::Status slots_for_current_device(DeviceSlots** out) {
     e = cudaGetSymbolAddress((void**)&st, g_noalloc_status);
     if (e != cudaSuccess) return ag::Status::compute(std::string("cudaGetSymbolAddress(status): ") + cudaGetErrorString(e));
     sl.scratch = p; sl.status = reinterpret_cast<int*>(st); sl.ready = true;
+    if (g_first_device < 0) g_first_device = dev;
   }
   *out = &sl;
   return ag::Status::OK();
@@ -77,6 +82,14 @@ extern "C" int32_t applegpu_attention_noalloc(const void* q, const void* k, cons
   DeviceSlots* sl = nullptr;
   Status s = slots_for_current_device(&sl);
   if (!s.ok()) return fail(s.to_string());
+  {
+    // The kernels' one-time setup (shared-memory opt-in, SM count) is held per process, for the device
+    // the process first used: a call with another device current is refused instead of mis-launched.
+    int cur = -1, first = first_device_seen();
+    cudaGetDevice(&cur);
+    if (first >= 0 && cur != first)
+      return fail("this process already runs kernels on device " + std::to_string(first) + "; one process serves one GPU (current device is " + std::to_string(cur) + ")");
+  }
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
 
   // The scratch keeps whatever the previous call left; every score element is rewritten by the
@@ -108,4 +121,24 @@ extern "C" int32_t applegpu_attention_noalloc(const void* q, const void* k, cons
   s = k::matmul_with_status(stream, g2, sl->status);
   if (!s.ok()) return fail(s.to_string());
   return 0;
+}
+
+// The tensor-core GEMMs inside applegpu_attention_noalloc bound every wait; one that gives up leaves a
+// code in this entry point's own status word (not the one applegpu_pipeline_status reads) and `out`
+// undefined. This reads that word back without allocating: it waits for `cuda_stream`, then copies the
+// four bytes into a local variable. 0 = the last call on this device ran to completion; a positive
+// value = the code of the wait that timed out; -1 = the query itself failed (see last_error).
+extern "C" int32_t applegpu_attention_noalloc_status(void* cuda_stream) {
+  using namespace ag;
+  auto fail = [](const std::string& m) { set_ffi_error_text("attention_noalloc_status failed: " + m); return -1; };
+  DeviceSlots* sl = nullptr;
+  Status s = slots_for_current_device(&sl);
+  if (!s.ok()) return fail(s.to_string());
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(std::string("cudaStreamSynchronize: ") + cudaGetErrorString(e));
+  int v = 0;
+  e = cudaMemcpy(&v, sl->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(std::string("cudaMemcpy: ") + cudaGetErrorString(e));
+  return v;
 }

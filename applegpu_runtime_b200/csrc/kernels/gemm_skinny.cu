@@ -274,9 +274,8 @@ Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d) {
   return Status::OK();
 }
 
-static float* g_sk_partial = nullptr;
-static unsigned int* g_sk_counters = nullptr;
-static std::once_flag g_sk_once;
+float* skinny_partials();            // workspace.cu: created with the device context
+unsigned int* skinny_counters();
 
 bool skinny_eligible(const GemmDesc& d) {
   if (!(d.dtype == DType::BF16 || d.dtype == DType::F16 || d.dtype == DType::F32) || d.b_dtype != d.dtype) return false;
@@ -292,16 +291,13 @@ bool skinny_eligible(const GemmDesc& d) {
 }
 
 Status matmul_skinny(cudaStream_t s, const GemmDesc& d) {
-  std::call_once(g_sk_once, [] {
-    if (cudaMalloc(&g_sk_partial, (size_t)kSkMaxPartials * kSkMaxM * sizeof(float)) != cudaSuccess) { g_sk_partial = nullptr; cudaGetLastError(); return; }
-    if (cudaMalloc(&g_sk_counters, (size_t)(kSkMaxN / kSkN) * sizeof(unsigned int)) != cudaSuccess) { g_sk_counters = nullptr; cudaGetLastError(); return; }
-    cudaMemset(g_sk_counters, 0, (size_t)(kSkMaxN / kSkN) * sizeof(unsigned int));
-  });
-  if (!g_sk_partial || !g_sk_counters) return Status::compute("matmul (skinny): cannot allocate the partial-sum workspace");
+  float* partial = skinny_partials();
+  unsigned int* counters = skinny_counters();
+  if (!partial || !counters) return Status::compute("matmul (skinny): the kernel workspace is not initialised");
   SkinnyParams p;
   p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_row; p.c_row = d.c_row;
-  p.partial = g_sk_partial; p.counters = g_sk_counters;
+  p.partial = partial; p.counters = counters;
   p.a_vec = (d.a_row % (d.dtype == DType::F32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(d.a) & 15u) == 0) ? 1 : 0;
   dim3 grid((unsigned)((d.n + kSkN - 1) / kSkN), (unsigned)((d.k + kSkK - 1) / kSkK), 1);
   cudaError_t e;

@@ -766,8 +766,7 @@ Status matmul_skinny(cudaStream_t s, const GemmDesc& d);
 bool skinny_kmajor_eligible(const GemmDesc& d);
 Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d);
 
-static int* g_status_word = nullptr;   // device int, lazily allocated once per process
-static int* g_status_host = nullptr;   // pinned mirror
+int* matmul_status_word();            // workspace.cu: created with the device context
 
 template <int BN, bool B_MN, typename T>
 static Status launch_tc(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, long long num_tiles) {
@@ -902,26 +901,6 @@ const char* matmul_path(const GemmDesc& d) {
   return tc_eligible(d) ? "tcgen05" : "simt";
 }
 
-int* matmul_status_word() {
-  if (!g_status_word) {
-    if (cudaMalloc(&g_status_word, sizeof(int)) != cudaSuccess) { g_status_word = nullptr; return nullptr; }
-    cudaMemset(g_status_word, 0, sizeof(int));
-    cudaMallocHost(&g_status_host, sizeof(int));
-    if (g_status_host) *g_status_host = 0;
-  }
-  return g_status_word;
-}
-
-// Reads and clears the pipeline status word; non-zero means a bounded wait gave up.
-int matmul_take_status(cudaStream_t s) {
-  if (!g_status_word || !g_status_host) return 0;
-  if (cudaMemcpyAsync(g_status_host, g_status_word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
-  if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
-  int v = *g_status_host;
-  if (v != 0) cudaMemsetAsync(g_status_word, 0, sizeof(int), s);
-  return v;
-}
-
 __global__ void argmax_finalize_kernel(const unsigned long long* __restrict__ keys, int32_t* __restrict__ out, int64_t rows) {
   pdl_wait();
   pdl_trigger();
@@ -950,7 +929,7 @@ Status matmul(cudaStream_t s, const GemmDesc& d) {
   if (g_force_path == 2 && !elig) return Status::compute("matmul: tcgen05 path forced but operands are not TMA-compatible");
   if (elig && g_force_path != 1) {
     int* st = matmul_status_word();
-    if (!st) return Status::compute("matmul: cannot allocate status word");
+    if (!st) return Status::compute("matmul: the kernel workspace is not initialised");
     return matmul_tc(s, d, st);
   }
   return matmul_simt(s, d);

@@ -118,6 +118,21 @@ Status attention(cudaStream_t s, const AttnDesc& d);
 bool attention_f32_eligible(const AttnDesc& d);
 Status attention_f32(cudaStream_t s, const AttnDesc& d);
 
+// Fixed workspace of the kernel layer (pipeline status word + pinned mirror, skinny-GEMM partials):
+// created once, when the device context is set up, so that no op call allocates.
+Status init_device_workspace(cudaStream_t s);
+// Pipeline status word of the tcgen05 kernels: a bounded wait that gives up records a code there.
+// status_snapshot enqueues a copy into pinned slot `slot` (0 .. status_slots()-1); once the stream, or
+// an event recorded after the snapshot, has been waited for, status_take returns the value and, when
+// it is non-zero, clears the device word. matmul_take_status does snapshot + wait + take on slot 0.
+int status_slots();
+Status status_snapshot(cudaStream_t s, int slot);
+int status_take(cudaStream_t s, int slot);
+int matmul_take_status(cudaStream_t s);
+// Test hook: one thread waits (for at most limit_ns, capped at 50 ms) on a barrier nothing arrives at,
+// records `code` in the status word and returns.
+Status launch_wait_runs_out(cudaStream_t s, int code, unsigned long long limit_ns);
+
 // Writes more than the L2 capacity so the next timed kernel starts cold.
 Status flush_l2(cudaStream_t s, void* scratch, size_t bytes);
 

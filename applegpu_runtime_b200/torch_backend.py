@@ -18,9 +18,9 @@ Differences in design, made for a discrete 180 GB device instead of unified memo
 * bfloat16 is a first-class dtype;
 * `F.scaled_dot_product_attention` without a mask is routed to the library's attention op
   (`__torch_function__`), so the score matrix is never materialised;
-* ops outside the table run through PyTorch CPU like upstream, but are counted
-  (`fallback_stats()`), and `enable(strict=True)` turns them into errors so a forward pass can be
-  shown to stay on the device.
+* an aten op outside the table raises (`strict`, the default): nothing falls back to the host
+  unasked. `enable(strict=False)` opts into the reference's behaviour (the op runs through PyTorch
+  CPU), and every such call is counted (`fallback_stats()`).
 """
 import collections
 import math
@@ -41,14 +41,15 @@ _FLOAT = ("float32", "float16", "bfloat16")
 _TANH_GELU_MODULES = ("NewGELUActivation", "GELUTanh", "PytorchGELUTanh", "FastGELUActivation")
 SUPPORTED_OPS = {}
 _fallbacks = collections.Counter()
-_strict = False
+_strict = True
 _enabled = False
 _in_fallback = False
 
 
-def enable(strict=False):
-    """Initialise the device and the frontend. `strict=True`: an aten op outside the table raises
-    instead of running through PyTorch CPU."""
+def enable(strict=True):
+    """Initialise the device and the frontend. By default an aten op outside the table raises;
+    `strict=False` lets it run through PyTorch CPU (the reference's fallback), counted in
+    `fallback_stats()`."""
     global _enabled, _strict
     gpu.init_backend()
     _enabled = True

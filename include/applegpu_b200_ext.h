@@ -157,8 +157,16 @@ APPLEGPU_API int32_t applegpu_host_visible(void);
 /* 0 auto (single-kernel attention when head dim is 64 and dtype is f16/bf16), 1 always compose
  * attention from GEMM + softmax + GEMM with materialised scores. */
 APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
-/* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). */
+/* Reads and clears the pipeline status word of the tcgen05 kernels (0 = no bounded wait gave up). Every
+ * blocking point of the library (read_bytes / read_f32 / eager_download, applegpu_ffi_synchronize,
+ * applegpu_eager_flush_and_wait, applegpu_marker_wait) makes the same check once the stream is idle and
+ * reports a non-zero word as an error ("tensor-core pipeline wait timed out (code N)"), so a caller of
+ * the reference ABI alone cannot read an undefined result as success. */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
+/* Test hook (no counterpart in the reference): launches one thread that waits, for at most `limit_us`
+ * microseconds (capped at 50 ms), on a barrier nothing arrives at, then records `code` in the pipeline
+ * status word and returns. It exercises the error path of the bounded waits without a fault or a hang. */
+APPLEGPU_API int32_t applegpu_test_wait_runs_out(int32_t code, uint32_t limit_us);
 /* CUDA-event stopwatch on the runtime stream. */
 /* Op tapes: record the graph-flavour ops one pass of a host program issues, then re-record the same
  * ops on new inputs with one call (the per-op host cost of a Python driver is paid once). Between
@@ -224,9 +232,17 @@ APPLEGPU_API const char* applegpu_resolve_kernel(const char* base_name, int8_t d
  * device (with that device current); make that first call before any stream capture. All calls
  * share the one scratch array, which keeps the previous call's contents: calls whose GPU work
  * overlaps (different streams, different threads) race on it and must be serialised by the caller.
- * Returns 0 on success. */
+ * One process serves one GPU: a call made with another device current than the one the process's
+ * kernels first ran on is rejected. Returns 0 on success.
+ *
+ * applegpu_attention_noalloc_status(stream): the tensor-core GEMMs inside bound every wait and record
+ * a code in this entry point's own status word when one gives up (applegpu_pipeline_status does not
+ * see that word). The status call waits for `cuda_stream`, copies the word to the host without
+ * allocating, and returns it: 0 = the last call completed, > 0 = a wait timed out and `out` is
+ * undefined, -1 = the query failed. */
 #define APPLEGPU_NOALLOC_SCRATCH_BYTES (64ull << 20)
 APPLEGPU_API int32_t applegpu_attention_noalloc(const void* q, const void* k, const void* v, void* out, int8_t dtype, uint64_t batch_heads, uint64_t q_len, uint64_t kv_len, uint64_t d_k, uint64_t d_v, bool causal, void* cuda_stream);
+APPLEGPU_API int32_t applegpu_attention_noalloc_status(void* cuda_stream);
 
 #ifdef __cplusplus
 }

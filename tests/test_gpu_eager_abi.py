@@ -300,3 +300,37 @@ def test_compiled_graph_rejects_malformed_streams(lib):
     assert n == -1 and b"unsupported op: 99" in lib.applegpu_eager_last_error()
     n, _, _ = _run_graph(lib, _op(5, [0], (2, 2)), [x], [7])
     assert n == -1 and b"output 7 out of range" in lib.applegpu_eager_last_error()
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable(lib, gpu_dev):
+    """Every mbarrier wait of the tcgen05 kernels is bounded and reports through the pipeline status word. Here a
+    test-only kernel waits (for at most a millisecond) on a barrier nothing arrives at: the wait gives up, the
+    kernel returns, the word carries the code, every blocking point of the library reports it as an error and
+    clears it, and the next launch runs normally. Nothing faults, traps or spins without a limit."""
+    gpu_dev.synchronize()
+    assert gpu_dev.pipeline_status() == 0
+    # 1. the explicit poll sees the code and clears the word
+    assert lib.applegpu_test_wait_runs_out(77, 1000) == 0
+    assert gpu_dev.pipeline_status() == 77
+    assert gpu_dev.pipeline_status() == 0
+    # 2. a blocking read turns the code into an error instead of handing back bytes as a result
+    a, _ = eager_tensor(lib, np.ones((4, 4), np.float32))
+    assert lib.applegpu_test_wait_runs_out(78, 1000) == 0
+    out = np.empty((4, 4), np.float32)
+    assert lib.applegpu_eager_download(a, out.ctypes.data_as(ctypes.c_void_p), out.nbytes) == -1
+    assert b"pipeline wait timed out (code 78)" in lib.applegpu_eager_last_error()
+    assert lib.applegpu_eager_download(a, out.ctypes.data_as(ctypes.c_void_p), out.nbytes) == 0       # cleared: the next read succeeds
+    # 3. a marker wait reports it too
+    assert lib.applegpu_test_wait_runs_out(79, 1000) == 0
+    m = lib.applegpu_marker_record()
+    assert m and lib.applegpu_marker_wait(m) == -1
+    assert b"code 79" in lib.applegpu_ffi_last_error()
+    # 4. the tensor-core path works afterwards (a stale word would make its waits bail out)
+    rng = np.random.default_rng(0)
+    x = R.to_bf16(rng.standard_normal((256, 128)).astype(np.float32)); w = R.to_bf16(rng.standard_normal((128, 256)).astype(np.float32))
+    gx = gpu_dev.from_bytes(x.tobytes(), [256, 128], "bfloat16"); gw = gpu_dev.from_bytes(w.tobytes(), [128, 256], "bfloat16")
+    got = (gx @ gw).to_numpy()
+    ref = R.from_bf16(x).astype(np.float64) @ R.from_bf16(w).astype(np.float64)
+    assert np.max(np.abs(got - ref)) <= 2e-2 * np.max(np.abs(ref))
+    assert gpu_dev.pipeline_status() == 0
+    lib.applegpu_eager_free(a)

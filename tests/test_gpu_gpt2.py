@@ -74,7 +74,11 @@ def test_mid_gpt2_fp32_and_bf16_against_torch_oracle(gpu_dev):
     assert np.mean(got32.argmax(-1) == ref.argmax(-1)) == 1.0
     m16 = gpu_dev.init_gpt2_weights(CFG_MID, seed=3, dtype="bfloat16")
     logits16 = gpu_dev.gpt2_forward(m16, ids)[0]
-    assert "tcgen05" or True
+    plan16 = logits16.plan()
+    assert plan16.count("fused_attention[causal,merge_heads]_bf16") == CFG_MID["n_layer"]   # the single-kernel tcgen05 attention
+    assert plan16.count("fused_linear[") == 4 * CFG_MID["n_layer"] and "_f32" not in plan16
+    x16 = gpu_dev.from_bytes(bytes(2 * 128 * 256), [128, 256], "bfloat16")
+    assert gpu_dev.matmul_path(x16, m16["weights"]["transformer.h.0.attn.c_attn.weight"]) == "tcgen05"
     got16 = logits16.to_numpy()
     scale = float(np.max(np.abs(ref)))
     assert np.max(np.abs(got16 - ref)) <= 2e-2 * scale                      # bf16 bar: 2e-2 relative of fp32

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture()
 def tb(gpu_dev):
     import applegpu_runtime_b200.torch_backend as tb
-    tb.enable(strict=False)
+    tb.enable()                                  # strict: an op outside the table raises, nothing falls back to the host
     tb.reset_fallback_stats()
     return tb
 
@@ -55,12 +55,8 @@ def test_torch_transformer_matches_cpu(tb, dtype, tol):
         import applegpu_runtime_b200 as gpu
         launches = gpu.launch_count()
         model = tb.to_applegpu(copy.deepcopy(ref), dtype)
-        tb._strict = True                        # the whole forward stays in the op table
-        try:
-            got = model(ids)
-            out = got.to_torch_cpu()
-        finally:
-            tb._strict = False
+        got = model(ids)                         # strict (the default): the whole forward stays in the op table
+        out = got.to_torch_cpu()
     assert got.dtype == dtype and _rel(out.float(), want) < tol
     # 2 blocks: the fused plan launches ~20 kernels (+ uploads); the unfused composition would need > 60
     assert 15 <= gpu.launch_count() - launches <= 40

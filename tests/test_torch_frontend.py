@@ -19,7 +19,6 @@ def tb(gpu):
     tb._strict = True
     tb.reset_fallback_stats()
     yield tb
-    tb._strict = False
 
 
 def test_wrapper_keeps_shape_dtype_and_identity(tb):

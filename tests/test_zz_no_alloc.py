@@ -78,7 +78,41 @@ def test_noalloc_attention_bf16_tensor_core_path_twice_in_a_row(lib, gpu_dev):
         assert np.max(np.abs(a - b)) <= 2e-2 * np.max(np.abs(b))            # bf16 bar; in practice identical
         ref = R.attention(R.from_bf16(q), R.from_bf16(k), R.from_bf16(v), causal)
         assert np.max(np.abs(a - ref)) <= 2e-2 * np.max(np.abs(ref))
+        # the entry point's OWN status word (its GEMMs do not write the one pipeline_status() reads)
+        assert lib.applegpu_attention_noalloc_status(lib.applegpu_stream()) == 0
     assert gpu_dev.pipeline_status() == 0
+
+
+def test_noalloc_attention_allocates_nothing_and_accepts_the_default_stream(lib, gpu_dev):
+    """The property the entry point exists for: after one warm-up call (which resolves the scratch address)
+    a further call leaves the pool statistics and the device's free-memory figure unchanged. Also the one
+    success path the other tests do not take: cuda_stream = NULL (the legacy default stream)."""
+    import torch
+    rng = np.random.default_rng(2)
+    q, k, v = (R.to_bf16(rng.standard_normal((8, 192, 64)).astype(np.float32)) for _ in range(3))
+    iq, pq = _eager(lib, q, BF16); ik, pk = _eager(lib, k, BF16); iv, pv = _eager(lib, v, BF16)
+    io, po = _eager(lib, np.zeros((8, 192, 64), np.uint16), BF16)
+    stream = lib.applegpu_stream()
+    assert lib.applegpu_attention_noalloc(pq, pk, pv, po, BF16, 8, 192, 192, 64, 64, True, stream) == 0      # warm-up
+    gpu_dev.synchronize()
+    want = _read(lib, io, (8, 192, 64), np.uint16)
+    stats0 = gpu_dev.pool_stats()
+    free0 = torch.cuda.mem_get_info(lib.applegpu_device())[0]
+    assert lib.applegpu_attention_noalloc(pq, pk, pv, po, BF16, 8, 192, 192, 64, 64, True, stream) == 0
+    assert lib.applegpu_attention_noalloc_status(stream) == 0
+    stats1 = gpu_dev.pool_stats()
+    free1 = torch.cuda.mem_get_info(lib.applegpu_device())[0]
+    for key in ("misses", "live_bytes", "pooled_bytes", "live_buffers"):
+        assert stats1[key] == stats0[key], key
+    assert free1 == free0
+    # NULL stream: the runtime stream is non-blocking, so order the two by hand
+    gpu_dev.synchronize()
+    assert lib.applegpu_attention_noalloc(pq, pk, pv, po, BF16, 8, 192, 192, 64, 64, True, None) == 0, lib.applegpu_ffi_last_error()
+    assert lib.applegpu_attention_noalloc_status(None) == 0
+    got = _read(lib, io, (8, 192, 64), np.uint16)
+    assert np.array_equal(got, want)
+    for t in (iq, ik, iv, io):
+        lib.applegpu_eager_free(t)
 
 
 def test_noalloc_attention_rejects_problems_larger_than_its_scratch(lib):
