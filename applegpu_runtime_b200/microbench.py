@@ -23,7 +23,7 @@ from . import api as gpu
 
 
 def _tensor(rng, shape, dtype, scale=1.0):
-    t = gpu.from_numpy((rng.standard_normal(shape) * scale).astype(np.float32))
+    t = gpu.from_numpy(rng.standard_normal(shape, dtype=np.float32) * np.float32(scale))
     if dtype != "float32":
         t = gpu.cast(t, dtype)
         t.eval()
