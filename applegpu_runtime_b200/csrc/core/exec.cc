@@ -415,7 +415,7 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
   if ((kd.op == Op::Matmul || (kd.op == Op::FusedLinear && kd.i2 != 1 && kd.i1 != 1 && !kd.has_residual)) && !out_buf && !dry && g_pitch_rows &&
       node.out_shape.size() == 2 && dtype_size(node.out_dtype) == 2 && node.out_shape[1] % 8 != 0 && node.out_shape[1] >= 1024 &&
       node.out_shape[0] >= 128) {
-    const int64_t pitch = (node.out_shape[1] + 7) / 8 * 8;
+    const int64_t pitch = (node.out_shape[1] + 15) / 16 * 16;   // 32-byte rows: the GEMM stores one row per lane with 256-bit accesses
     out->shape = node.out_shape; out->strides = {pitch, 1}; out->dtype = node.out_dtype; out->byte_offset = 0; out->has_meta = true;
     AG_RETURN_IF_ERROR(Shared::get().pool.acquire((size_t)(node.out_shape[0] * pitch) * 2, &out->buf));
     pitched = true;

@@ -21,6 +21,7 @@ uint64_t launch_count();
 namespace profile { void enable(bool on); void clear(); std::string report(); }
 namespace k {
 void set_matmul_path(int mode);
+void set_gemm_tile(int code);
 }
 }
 using namespace ag;
@@ -1096,6 +1097,7 @@ int32_t applegpu_set_host_visible(int32_t on) {
 }
 int32_t applegpu_host_visible(void) { return DeviceCtx::get().host_visible ? 1 : 0; }
 void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
+void applegpu_set_gemm_tile(int32_t code) { k::set_gemm_tile(code); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return 0;

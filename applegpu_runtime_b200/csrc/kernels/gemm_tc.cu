@@ -51,12 +51,19 @@ struct TcParams {
   unsigned long long* argmax_keys;   // non-null: merge per-row (value, column) keys instead of storing C
   int c_f32;                         // C, bias and residual are float32 (operands are still 16-bit)
   int* status;
+#ifdef AG_GEMM_PROBE
+  long long* probe;   // per CTA: [0] cycles the MMA thread waited for a free accumulator, [1] cycles in the k loops, [2] k steps, [3] cycles epilogue warp 2 waited for a full accumulator, [4] cycles it spent in the epilogue, [5] tiles, [6] kernel cycles
+#endif
 };
 
 constexpr int kEpiWarps = 8;                       // two warps per TMEM lane quarter, alternating column groups
-constexpr int kStgPitch = 80;
-constexpr int kStgBytesPerWarp = 32 * kStgPitch;   // 2560
+constexpr int kStgBytesPerWarp = 32 * 64;           // a dense 32 x 32 tile of 2-byte elements, 64-byte swizzle
 constexpr int kStgBytes = kEpiWarps * kStgBytesPerWarp;
+// Byte offset of 16-byte chunk `chunk` (0..3) of row `row` inside a warp's staging tile. The tile is dense (64-byte
+// rows) in the 64-byte swizzle of the TMA unit: the chunk index is XOR-ed with bits 7..8 of the address, i.e. with
+// (row / 2) % 4, so a tiled bulk store can read it as it lies. Row-per-lane accesses (8 lanes per 128-bit phase: rows
+// r..r+7 at one chunk) and 4-lanes-per-row accesses (2 rows x 4 chunks per phase) both touch 8 distinct bank groups.
+__device__ __forceinline__ int stg_off(int row, int chunk) { return row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4); }
 // Per tile an epilogue warp needs the bias values (2-byte) and, for int8 weights, the per-channel
 // fp32 scales of its own column groups: half of the tile's columns.
 constexpr int epi_slots(int bn) { return bn / 2; }
@@ -74,9 +81,10 @@ template <int BN> struct TcCfg {
   static constexpr int kTmemCols = 2 * kAccStride;                 // two accumulator buffers (a power of two)
 };
 
-// Epilogue staging: each epilogue warp owns a [32 rows x 32 cols] 2-byte tile in shared memory with an
-// 80-byte row pitch (64 B of data + 16 B pad: the row-per-lane accesses of the math phase are
-// bank-conflict free, the 4-lanes-per-row accesses of the global phase at most 2-way).
+// Epilogue staging: each epilogue warp owns a [32 rows x 32 cols] 2-byte tile in shared memory (stg_off above).
+// Results leave it through one tiled bulk store per 32 x 32 group (cp.async.bulk.tensor, issued by one lane and
+// drained by the TMA unit while the warp computes the next group) when C's rows are 16-byte aligned; otherwise,
+// and for float32 or argmax outputs, through plain global stores.
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
@@ -88,55 +96,84 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One 32-column group of one warp's 32 rows: TMEM -> registers -> epilogue math -> shared -> global.
-// Every epilogue option is tested once per group (uniform branches around 32-element loops), and
-// global traffic is issued with 4 lanes per row (64 contiguous bytes per row per instruction) when
-// rows are 16-byte aligned, or 32 consecutive 2-byte elements per instruction otherwise (e.g. the
-// 50257-wide LM head), instead of one row per lane.
-// Residual rows of one 32x32 group, 4 lanes per row, into registers (vector path only). Issued one
-// group ahead of its use so that the global-load latency overlaps the previous group's math and stores.
+// 256-bit global accesses (sm_100): one lane moves 32 contiguous bytes, a whole L2 sector. With one output row per
+// lane (the layout tcgen05.ld delivers) a lane's 32 columns of 16-bit results are two such stores, every sector is
+// written in full, and nothing has to be transposed through shared memory first.
+__device__ __forceinline__ void st_global_256(void* ptr, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
+__device__ __forceinline__ void ld_global_256(const void* ptr, uint32_t* r) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "l"(ptr));
+}
+
+// This lane's residual row of one 32-column group (64 bytes) into registers; issued one group ahead of its use so
+// that the load latency overlaps the previous group's math. Direct (32-byte aligned) layout only.
 template <typename T>
-__device__ __forceinline__ void load_residual_group(const TcParams& p, const T* R, long long row0, int col0, int lane, uint4 (&rpre)[4]) {
-  const int sub_row = lane >> 2, sub_chunk = lane & 3;
-  const int gc = col0 + sub_chunk * 8;
+__device__ __forceinline__ void load_residual_row(const TcParams& p, const T* R, long long gm, int col0, uint32_t (&rpre)[16]) {
 #pragma unroll
-  for (int it = 0; it < 4; it++) {
-    long long gm = row0 + it * 8 + sub_row;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (gm < p.m && gc + 8 <= p.n) v = *reinterpret_cast<const uint4*>(R + gm * p.c_row + gc);
-    else if (gm < p.m && gc < p.n) {
-      alignas(16) T tmp[8];
+  for (int j = 0; j < 2; j++) {
+    const int gc = col0 + 16 * j;
+    if (gm < p.m && gc + 16 <= p.n) ld_global_256(R + gm * p.c_row + gc, &rpre[8 * j]);
+    else {
+      alignas(16) T tmp[16];
 #pragma unroll
-      for (int e = 0; e < 8; e++) tmp[e] = gc + e < p.n ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
-      v = *reinterpret_cast<uint4*>(tmp);
+      for (int e = 0; e < 16; e++) tmp[e] = (gm < p.m && gc + e < p.n) ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
+#pragma unroll
+      for (int w = 0; w < 8; w++) rpre[8 * j + w] = reinterpret_cast<const uint32_t*>(tmp)[w];
     }
-    rpre[it] = v;
   }
 }
 
+// One 32-column group of one warp's 32 rows: TMEM -> registers -> epilogue math -> global memory.
+// Every epilogue option is tested once per group (uniform branches around 32-element loops).
+//   p.vec_ok == 2  rows of C (and of the residual) are 32-byte aligned: each lane stores its own row's 64 bytes with
+//                  two 256-bit stores and reads its residual row the same way; no shared memory on the path
+//   p.vec_ok == 1  rows are 16-byte aligned: results are transposed through the warp's staging tile and stored with
+//                  4 lanes per row (64 contiguous bytes per row per instruction)
+//   p.vec_ok == 0  unaligned rows (a dense 50257-wide LM head): staged, 32 consecutive elements per instruction
 template <typename T>
-__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint4 (&rpre)[4],
+__device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint32_t (&rpre)[16],
                                                long long row0, int col0, int next_col0, long long c_off, int lane, unsigned long long& best_key) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
   const int sub_row = lane >> 2, sub_chunk = lane & 3;
+  const bool direct = p.vec_ok == 2;
 
-  // 1. residual tile -> shared (coalesced). On the vector path the values were fetched one group
-  //    ahead; the next group's fetch is issued here and lands while this group is computed.
+  // 1. residual. Direct layout: this group's row was fetched one group ahead; the next group's fetch is issued here
+  //    and lands while this group is computed. Staged layouts: the tile goes to shared memory (coalesced reads).
+  uint32_t rcur[16];
   if (R && !p.c_f32) {
-    if (p.vec_ok) {
+    if (direct) {
 #pragma unroll
-      for (int it = 0; it < 4; it++)
-        *reinterpret_cast<uint4*>(stg + (it * 8 + sub_row) * kStgPitch + sub_chunk * 16) = rpre[it];
-      if (next_col0 >= 0) load_residual_group<T>(p, R, row0, next_col0, lane, rpre);
+      for (int w = 0; w < 16; w++) rcur[w] = rpre[w];
+      if (next_col0 >= 0) load_residual_row<T>(p, R, row0 + lane, next_col0, rpre);
     } else {
-      for (int r = 0; r < 32; r++) {
-        long long gm = row0 + r;
-        T v = (gm < p.m && col0 + lane < p.n) ? R[gm * p.c_row + col0 + lane] : Cvt<T>::from(0.f);
-        *reinterpret_cast<T*>(stg + r * kStgPitch + lane * 2) = v;
+      if (p.vec_ok) {
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+          long long gm = row0 + it * 8 + sub_row;
+          int gc = col0 + sub_chunk * 8;
+          uint4 v4 = make_uint4(0, 0, 0, 0);
+          if (gm < p.m && gc + 8 <= p.n) v4 = *reinterpret_cast<const uint4*>(R + gm * p.c_row + gc);
+          else if (gm < p.m && gc < p.n) {
+            alignas(16) T tmp[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) tmp[e] = gc + e < p.n ? R[gm * p.c_row + gc + e] : Cvt<T>::from(0.f);
+            v4 = *reinterpret_cast<uint4*>(tmp);
+          }
+          *reinterpret_cast<uint4*>(stg + stg_off(it * 8 + sub_row, sub_chunk)) = v4;
+        }
+      } else {
+        for (int r = 0; r < 32; r++) {
+          long long gm = row0 + r;
+          T v = (gm < p.m && col0 + lane < p.n) ? R[gm * p.c_row + col0 + lane] : Cvt<T>::from(0.f);
+          *reinterpret_cast<T*>(stg + stg_off(r, lane >> 3) + (lane & 7) * 2) = v;
+        }
       }
+      __syncwarp();
     }
-    __syncwarp();
   }
 
   // 2. accumulators -> registers
@@ -265,11 +302,39 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
     }
     return;
   }
-  uint8_t* my_row = stg + lane * kStgPitch;
+
+  if (direct) {
+    // 4a. residual from registers, then two 256-bit stores of this lane's own row
+    if (R) {
+#pragma unroll
+      for (int w = 0; w < 16; w++) {
+        const T* rv = reinterpret_cast<const T*>(&rcur[w]);
+        v[2 * w] += Cvt<T>::to(rv[0]); v[2 * w + 1] += Cvt<T>::to(rv[1]);
+      }
+    }
+    uint32_t o[16];
+#pragma unroll
+    for (int w = 0; w < 16; w++) o[w] = pack2<T>(v[2 * w], v[2 * w + 1]);
+    const long long gm = row0 + lane;
+    if (gm < p.m) {
+      T* crow = C + gm * p.c_row + col0;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        if (col0 + 16 * j + 16 <= p.n) st_global_256(crow + 16 * j, &o[8 * j]);
+        else {
+          const T* tv = reinterpret_cast<const T*>(&o[8 * j]);
+          for (int e = 0; e < 16 && col0 + 16 * j + e < p.n; e++) crow[16 * j + e] = tv[e];
+        }
+      }
+    }
+    return;
+  }
+
+  // 4b. staged layouts: residual from the staging tile, results back into it, then coalesced stores
   if (R) {
 #pragma unroll
     for (int g = 0; g < 4; g++) {
-      Pack<T> r = *reinterpret_cast<const Pack<T>*>(my_row + g * 16);
+      Pack<T> r = *reinterpret_cast<const Pack<T>*>(stg + stg_off(lane, g));
 #pragma unroll
       for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(r.v[e]);
     }
@@ -279,11 +344,9 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
     uint4 o;
     o.x = pack2<T>(v[g * 8 + 0], v[g * 8 + 1]); o.y = pack2<T>(v[g * 8 + 2], v[g * 8 + 3]);
     o.z = pack2<T>(v[g * 8 + 4], v[g * 8 + 5]); o.w = pack2<T>(v[g * 8 + 6], v[g * 8 + 7]);
-    *reinterpret_cast<uint4*>(my_row + g * 16) = o;
+    *reinterpret_cast<uint4*>(stg + stg_off(lane, g)) = o;
   }
   __syncwarp();
-
-  // 4. shared -> global (coalesced)
   if (p.vec_ok) {
 #pragma unroll
     for (int it = 0; it < 4; it++) {
@@ -291,7 +354,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
       long long gm = row0 + r;
       int gc = col0 + sub_chunk * 8;
       if (gm < p.m && gc < p.n) {
-        uint4 o = *reinterpret_cast<const uint4*>(stg + r * kStgPitch + sub_chunk * 16);
+        uint4 o = *reinterpret_cast<const uint4*>(stg + stg_off(r, sub_chunk));
         if (gc + 8 <= p.n) *reinterpret_cast<uint4*>(C + gm * p.c_row + gc) = o;
         else {
           const T* tv = reinterpret_cast<const T*>(&o);
@@ -303,7 +366,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
     for (int r = 0; r < 32; r++) {
       long long gm = row0 + r;
       if (gm >= p.m) break;
-      C[gm * p.c_row + col0 + lane] = *reinterpret_cast<const T*>(stg + r * kStgPitch + lane * 2);
+      C[gm * p.c_row + col0 + lane] = *reinterpret_cast<const T*>(stg + stg_off(r, lane >> 3) + (lane & 7) * 2);
     }
   }
   __syncwarp();
@@ -384,9 +447,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
+#ifdef AG_GEMM_PROBE
+      long long pr_wait = 0, pr_main = 0, pr_steps = 0, pr_t0 = clock64();
+#endif
       for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+#ifdef AG_GEMM_PROBE
+        long long pc0 = clock64();
+#endif
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, p.status, 2)) { ok = false; break; }
         tc_fence_after_sync();
+#ifdef AG_GEMM_PROBE
+        long long pc1 = clock64(); pr_wait += pc1 - pc0;
+#endif
         uint32_t tmem_d = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
         for (int kb = 0; kb < num_kb; kb++) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
@@ -412,8 +484,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (!ok) break;
         mma_commit(&tmem_full_bar[acc]);  // accumulator complete
+#ifdef AG_GEMM_PROBE
+        pr_main += clock64() - pc1; pr_steps += num_kb;
+#endif
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+#ifdef AG_GEMM_PROBE
+      if (p.probe) { p.probe[blockIdx.x * 16 + 0] = pr_wait; p.probe[blockIdx.x * 16 + 1] = pr_main; p.probe[blockIdx.x * 16 + 2] = pr_steps; p.probe[blockIdx.x * 16 + 6] = pr_t0; }
+#endif
     }
   } else {
     // ── epilogue warps ──
@@ -449,12 +527,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           scale_s[gi * 32 + lane] = ci < p.n ? __ldg(fsrc + ci) : 0.f;
         }
       }
-      uint4 rpre[4];
-      if (p.residual && p.vec_ok && !p.c_f32 && n0 + pair * 32 < p.n)
-        load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
+      uint32_t rpre[16];
+      if (p.residual && p.vec_ok == 2 && !p.c_f32 && n0 + pair * 32 < p.n)
+        load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0 + lane, n0 + pair * 32, rpre);
       __syncwarp();
+#ifdef AG_GEMM_PROBE
+      long long pe0 = clock64();
+#endif
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }  // warp-uniform
       tc_fence_after_sync();
+#ifdef AG_GEMM_PROBE
+      long long pe1 = clock64();
+#endif
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
       unsigned long long best_key = 0;   // argmax mode: this row's best over the warp's column groups of the tile
@@ -469,6 +553,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+#ifdef AG_GEMM_PROBE
+      if (p.probe && warp == 2 && lane == 0) {
+        long long pe2 = clock64();
+        p.probe[blockIdx.x * 16 + 3] += pe1 - pe0; p.probe[blockIdx.x * 16 + 4] += pe2 - pe1; p.probe[blockIdx.x * 16 + 5] += 1; p.probe[blockIdx.x * 16 + 7] = pe2;
+      }
+#endif
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
@@ -480,31 +570,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }
 
 // ── CTA-pair variant ────────────────────────────────────────────────────────
-// Two CTAs of a cluster compute one 256 x 256 tile with cta_group::2 MMAs. Each CTA loads its own
-// 128 rows of A and only HALF of the B tile (128 of the 256 columns); the tensor cores of the pair
-// exchange the halves. Per CTA and 64-deep K step that is 32 KB written to and read from shared
-// memory instead of 48 KB, which is what bounds the single-CTA kernel (its MMAs wait on shared-
-// memory bandwidth, not on the tensor pipe).
+// Two CTAs of a cluster compute one 256 x BN tile with cta_group::2 MMAs. Each CTA loads its own
+// 128 rows of A and only HALF of the B tile (BN / 2 columns); the tensor cores of the pair
+// exchange the halves. Per CTA and 64-deep K step that is 32 KB (BN = 256) fetched from L2 instead
+// of the 48 KB a single-CTA 128 x 256 tile needs, and the L2 -> shared-memory feed is what bounds
+// the single-CTA main loop (measured: about 100 bytes per clock per SM at best, against the 96 the
+// tensor pipe consumes at full rate for that tile). A pipeline stage holds TWO k-blocks (BK = 128 per
+// barrier round trip): a barrier in the peer CTA is a cluster-level arrive, and with one k-block per
+// stage that latency is paid every 512 tensor cycles and shows (650 cycles per step measured);
+// with two per stage the main loop runs at the tensor rate (517 cycles per step).
 //   full barriers     live in the even CTA; both CTAs' TMA loads credit their bytes there
 //   empty/tmem_full   one copy per CTA; the even CTA's MMA thread commits to both
 //   tmem_empty        lives in the even CTA; the epilogue warps of both CTAs arrive there
 // Everything else (warp roles, epilogue, bounded waits) is as in the single-CTA kernel.
-constexpr int kPairBN = 256;
-struct PairCfg {
-  static constexpr int kABytes = BM * BK * 2;               // this CTA's 128 rows of A
-  static constexpr int kBBytes = (kPairBN / 2) * BK * 2;    // this CTA's half of B
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = 6;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + bias_bytes(kPairBN) + scale_bytes(kPairBN) + 1024;
-  static constexpr int kTmemCols = 2 * kPairBN;
+constexpr int kPairKbPerStage = 2;
+template <int BN> struct PairCfg {
+  static constexpr int kABytes = BM * BK * 2;               // this CTA's 128 rows of A, one k-block
+  static constexpr int kBBytes = (BN / 2) * BK * 2;         // this CTA's half of B, one k-block
+  static constexpr int kKbBytes = kABytes + kBBytes;
+  static constexpr int kStageBytes = kPairKbPerStage * kKbBytes;
+  static constexpr int kStages = (BN == 256) ? 3 : 4;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + bias_bytes(BN) + scale_bytes(BN) + 1024;
+  static_assert(kSmemBytes + 512 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may use");
+  static constexpr int kTmemCols = 2 * BN;                  // two accumulator buffers
 };
 
-template <bool B_MN, typename T>
+template <int BN, bool B_MN, typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
-  using Cfg = PairCfg;
+  using Cfg = PairCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
-  constexpr int BN = kPairBN;
+  constexpr int KBS = kPairKbPerStage;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[STAGES];
   __shared__ uint64_t empty_bar[STAGES];
@@ -517,7 +613,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();       // 0 = even CTA (issues the MMAs), 1 = its peer
   const int num_kb = (p.k + BK - 1) / BK;
-  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;   // tiles of 256 x 256
+  const int rounds = (num_kb + KBS - 1) / KBS;   // a k-block past the end of K is fetched as zeros (TMA out-of-range fill)
+  const long long tiles_per_batch = (long long)p.tiles_m * p.tiles_n;   // tiles of 256 x BN
   const long long num_tiles = tiles_per_batch * p.batch;
   const long long first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
 
@@ -537,6 +634,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   cluster_sync_all();   // the peer's barriers exist before anything is signalled on them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();
+  pdl_trigger();
 
   if (warp == 0) {
     // ── TMA producer (both CTAs) ──
@@ -551,19 +650,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int bo = batch / p.batch_inner, bi = batch % p.batch_inner;
         int a_bo = (p.a_bcast & 1) ? 0 : bo, a_bi = (p.a_bcast & 2) ? 0 : bi;
         int b_bo = (p.b_bcast & 1) ? 0 : bo, b_bi = (p.b_bcast & 2) ? 0 : bi;
-        for (int kb = 0; kb < num_kb; kb++) {
+        for (int r = 0; r < rounds; r++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, 1)) { ok = false; break; }
-          uint8_t* sa = smem + stage * Cfg::kStageBytes;
-          uint8_t* sb = sa + Cfg::kABytes;
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);   // both CTAs' bytes
           const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
-          tma_load_4d_pair(sa, &tmap_a, bar, kb * BK, m0, a_bi, a_bo);
-          if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 128; j++)
-              tma_load_4d_pair(sb + j * (64 * BK * 2), &tmap_b, bar, n0 + j * 64, kb * BK, b_bi, b_bo);
-          } else {
-            tma_load_4d_pair(sb, &tmap_b, bar, kb * BK, n0, b_bi, b_bo);
+          for (int j = 0; j < KBS; j++) {
+            const int kc = (r * KBS + j) * BK;
+            uint8_t* sa = smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes;
+            uint8_t* sb = sa + Cfg::kABytes;
+            tma_load_4d_pair(sa, &tmap_a, bar, kc, m0, a_bi, a_bo);
+            if (B_MN) {
+#pragma unroll
+              for (int q = 0; q < BN / 128; q++)
+                tma_load_4d_pair(sb + q * (64 * BK * 2), &tmap_b, bar, n0 + q * 64, kc, b_bi, b_bo);
+            } else {
+              tma_load_4d_pair(sb, &tmap_b, bar, kc, n0, b_bi, b_bo);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -576,21 +679,33 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
+#ifdef AG_GEMM_PROBE
+      long long pr_wait = 0, pr_main = 0, pr_steps = 0, pr_t0 = clock64();
+#endif
       for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
+#ifdef AG_GEMM_PROBE
+        long long pc0 = clock64();
+#endif
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, p.status, 2)) { ok = false; break; }
         tc_fence_after_sync();
+#ifdef AG_GEMM_PROBE
+        long long pc1 = clock64(); pr_wait += pc1 - pc0;
+#endif
         uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; kb++) {
+        for (int r = 0; r < rounds; r++) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
           tc_fence_after_sync();
-          uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
-          uint32_t sb = sa + Cfg::kABytes;
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; kk++) {
-            uint64_t da = make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
-            uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 64 * 128, 1024)
-                               : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
-            mma_f16_ss_pair(tmem_d, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          for (int j = 0; j < KBS; j++) {
+            uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes);
+            uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; kk++) {
+              uint64_t da = make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+              uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 64 * 128, 1024)
+                                 : make_smem_desc_sw128(sb + kk * (UMMA_K * 2), 16, 1024);
+              mma_f16_ss_pair(tmem_d, da, db, idesc, (r > 0 || j > 0 || kk > 0) ? 1u : 0u);
+            }
           }
           // the stage is free in both CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[stage]);
@@ -602,8 +717,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
         mma_commit_pair(mapa_u32(fb, 0));
         mma_commit_pair(mapa_u32(fb, 1));
+#ifdef AG_GEMM_PROBE
+        pr_main += clock64() - pc1; pr_steps += num_kb;
+#endif
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+#ifdef AG_GEMM_PROBE
+      if (p.probe) { p.probe[blockIdx.x * 16 + 0] = pr_wait; p.probe[blockIdx.x * 16 + 1] = pr_main; p.probe[blockIdx.x * 16 + 2] = pr_steps; p.probe[blockIdx.x * 16 + 6] = pr_t0; }
+#endif
     }
   } else {
     // ── epilogue warps (both CTAs; each reads its own 128 accumulator lanes) ──
@@ -637,12 +758,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           scale_s[gi * 32 + lane] = ci < p.n ? __ldg(fsrc + ci) : 0.f;
         }
       }
-      uint4 rpre[4];
-      if (p.residual && p.vec_ok && !p.c_f32 && n0 + pair * 32 < p.n)
-        load_residual_group<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0, n0 + pair * 32, lane, rpre);
+      uint32_t rpre[16];
+      if (p.residual && p.vec_ok == 2 && !p.c_f32 && n0 + pair * 32 < p.n)
+        load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0 + lane, n0 + pair * 32, rpre);
       __syncwarp();
+#ifdef AG_GEMM_PROBE
+      long long pe0 = clock64();
+#endif
       if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, p.status, 4))) { ok = false; break; }
       tc_fence_after_sync();
+#ifdef AG_GEMM_PROBE
+      long long pe1 = clock64();
+#endif
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
       unsigned long long best_key = 0;
@@ -659,6 +786,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[acc]), 0));
+#ifdef AG_GEMM_PROBE
+      if (p.probe && warp == 2 && lane == 0 && rank == 0) {
+        long long pe2 = clock64();
+        p.probe[blockIdx.x * 16 + 3] += pe1 - pe0; p.probe[blockIdx.x * 16 + 4] += pe2 - pe1; { long long ti = p.probe[blockIdx.x * 16 + 5]; if (ti < 6) p.probe[blockIdx.x * 16 + 8 + ti] = pe2 - pe1; } p.probe[blockIdx.x * 16 + 5] += 1; p.probe[blockIdx.x * 16 + 7] = pe2;
+      }
+#endif
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   }
@@ -706,7 +839,7 @@ static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
 // 4-D map over (inner, rows, batch_inner, batch_outer) of 2-byte elements with a 128B-swizzled
 // box {b0, b1, 1, 1}. Strides are in elements; a dimension of extent 1 may carry any stride.
 Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uint64_t rows, uint64_t nbi, uint64_t nbo,
-                       uint64_t row_stride, uint64_t bi_stride, uint64_t bo_stride, uint32_t b0, uint32_t b1) {
+                uint64_t row_stride, uint64_t bi_stride, uint64_t bo_stride, uint32_t b0, uint32_t b1) {
   MapKey key;
   std::memset(&key, 0, sizeof(key));
   key.ptr = ptr; key.d[0] = inner; key.d[1] = rows; key.d[2] = nbi; key.d[3] = nbo;
@@ -785,16 +918,17 @@ static Status launch_tc(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap
 }
 
 // Clusters of two CTAs (one CTA per SM) that can be resident at once; 0 if the query fails.
-template <bool B_MN, typename T>
+template <int BN, bool B_MN, typename T>
 static int pair_clusters() {
   static int cached = -1;
   if (cached >= 0) return cached;
-  auto kern = gemm_tc_pair_kernel<B_MN, T>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::kSmemBytes) != cudaSuccess) { cudaGetLastError(); return cached = 0; }
+  using Cfg = PairCfg<BN>;
+  auto kern = gemm_tc_pair_kernel<BN, B_MN, T>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) { cudaGetLastError(); return cached = 0; }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * (sm_count() / 2)), 1, 1);
   cfg.blockDim = dim3(kTcThreads, 1, 1);
-  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
   attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
@@ -805,42 +939,63 @@ static int pair_clusters() {
   return cached = n;
 }
 
-template <bool B_MN, typename T>
+template <int BN, bool B_MN, typename T>
 static Status launch_tc_pair(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, long long num_tiles) {
-  int clusters = pair_clusters<B_MN, T>();
+  int clusters = pair_clusters<BN, B_MN, T>();
   if (clusters <= 0) return Status::compute("matmul (tcgen05, CTA pairs): no resident cluster available");
   int grid = 2 * (int)(num_tiles < clusters ? num_tiles : clusters);
-  gemm_tc_pair_kernel<B_MN, T><<<grid, kTcThreads, PairCfg::kSmemBytes, s>>>(ma, mb, p);
-  AG_CHECK_LAUNCH("matmul (tcgen05, CTA pairs)");
+  cudaError_t le = launch_pdl(gemm_tc_pair_kernel<BN, B_MN, T>, dim3(grid), dim3(kTcThreads), PairCfg<BN>::kSmemBytes, s, ma, mb, p);
+  if (le != cudaSuccess) return cuda_status(le, "matmul (tcgen05, CTA pairs)");
   return Status::OK();
 }
 
+#ifdef AG_GEMM_PROBE
+long long* g_tc_probe = nullptr;   // set by the probe harness; the kernel then records where its cycles go
+#endif
 static int g_force_path = 0;   // 0 auto, 1 simt, 2 tcgen05 (error if not eligible), 3 single-CTA tiles only, 4 CTA-pair tiles where they apply
+
+// Tile shape by modelled cost. A candidate is a CTA-pair tile (256 x 256 or 256 x 128, one tile per two SMs) or a
+// single-CTA tile (128 x 256 / 192 / 128). Cost = full waves of the persistent grid x k-steps x the measured
+// main-loop cycles per 64-deep k-step of that shape, plus the exposed epilogue of a CTA's last tile. The pair
+// tiles run their main loop at the tensor rate (they fetch a third less operand data per flop from L2) and win
+// wherever they fill their waves; the single-CTA tiles win where the coarser pair grid would leave a mostly idle last
+// wave (N = 768 with M = 8192).
+struct TileChoice { bool pair; int bn; };
+static bool g_direct_store = [] { const char* v = std::getenv("APPLEGPU_GEMM_DIRECT_STORE"); return !(v && v[0] == '0'); }();   // APPLEGPU_GEMM_DIRECT_STORE=0: always transpose results through shared memory
+static int g_tile_override = 0;   // APPLEGPU_GEMM_TILE / set_gemm_tile: 0 auto, else pair*1000 + bn
+static TileChoice choose_tile(const GemmDesc& d, long long nb, int force_path) {
+  struct Cand { bool pair; int bn; int step; };
+  // cycles per k-step (64 deep) of one CTA's tile, measured on a B200 with the kernel's own cycle probes
+  static const Cand cands[5] = {{true, 256, 530}, {true, 128, 400}, {false, 256, 780}, {false, 192, 640}, {false, 128, 590}};
+  const long long num_kb = (d.k + BK - 1) / BK;
+  const bool pair_ok = d.m > BM && force_path != 3;
+  if (g_tile_override) {
+    TileChoice t{g_tile_override >= 1000, g_tile_override % 1000};
+    if (!t.pair || pair_ok) return t;
+  }
+  TileChoice best{false, 128};
+  long long best_cost = -1;
+  for (const Cand& c : cands) {
+    if (c.pair && !pair_ok) continue;
+    if (!c.pair && force_path == 4 && pair_ok) continue;
+    if (c.bn != 128 && d.n <= 128) continue;
+    const long long bm = c.pair ? 2 * BM : BM;
+    const long long units = c.pair ? sm_count() / 2 : sm_count();
+    const long long tiles = ((d.m + bm - 1) / bm) * ((d.n + c.bn - 1) / c.bn) * nb;
+    const long long waves = (tiles + units - 1) / units;
+    const long long cost = waves * num_kb * c.step + 1500 + 26 * c.bn;   // fill + the last tile's exposed epilogue
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = TileChoice{c.pair, c.bn}; }
+  }
+  return best;
+}
 
 Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   const bool b_mn = classify_b(d) == 2;
   const long long nb = d.batch * d.batch_inner;
-  // Single-CTA tiles, 256 wide when those fill the machine, else 128. The CTA-pair kernel (256 x 256
-  // tiles) is opt-in: on the transformer shapes measured here it runs within a few percent of the
-  // single-CTA kernel (slightly slower), so the simpler kernel stays the default.
-  const long long pair_tiles = ((d.m + 2 * BM - 1) / (2 * BM)) * ((d.n + kPairBN - 1) / kPairBN) * nb;
-  const bool use_pair = g_force_path == 4 && d.m > BM && d.n > 128 && pair_tiles >= sm_count() / 4;
+  const TileChoice tile = choose_tile(d, nb, g_force_path);
+  const bool use_pair = tile.pair;
+  const int bn = tile.bn;
   long long tiles_m = use_pair ? (d.m + 2 * BM - 1) / (2 * BM) : (d.m + BM - 1) / BM;
-  // Tile width by modelled cost: full waves of the persistent grid times a per-tile cost that grows
-  // with the width (main loop) plus a constant (A traffic, epilogue tail). 192 wins where 256 leaves
-  // a mostly idle last wave (N = 768 or 3072 with M = 8192: 192 or 768 tiles on 148 SMs).
-  int bn = 256;
-  if (!use_pair) {
-    long long best = -1;
-    const int cands[3] = {256, 192, 128};
-    for (int c : cands) {
-      if (c != 128 && d.n <= 128) continue;
-      long long tiles = tiles_m * ((d.n + c - 1) / c) * nb;
-      long long waves = (tiles + sm_count() - 1) / sm_count();
-      long long cost = waves * (c + (c == 128 ? 96 : 32));   // narrow tiles move more operand bytes per flop
-      if (best < 0 || cost < best) { best = cost; bn = c; }
-    }
-  }
   long long tiles_n = (d.n + bn - 1) / bn;
   CUtensorMap ma, mb;
   // A broadcast (stride-0) batch level is mapped as extent 1 and its coordinate pinned to 0.
@@ -852,7 +1007,7 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
                               (uint64_t)d.a_batch_inner, (uint64_t)d.a_batch, BK, BM));
   if (!b_mn) {
     AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.k, (uint64_t)d.n, b_nbi, b_nbo, (uint64_t)d.b_col,
-                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)(use_pair ? kPairBN / 2 : bn)));
+                                (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)(use_pair ? bn / 2 : bn)));
   } else {
     AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.n, (uint64_t)d.k, b_nbi, b_nbo, (uint64_t)d.b_row,
                                 (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, 64, BK));
@@ -864,17 +1019,28 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
   p.argmax_keys = d.ep.argmax_keys;
   p.c_f32 = d.c_f32 ? 1 : 0;
+#ifdef AG_GEMM_PROBE
+  p.probe = g_tc_probe;
+#endif
   if (p.argmax_keys && nb != 1) return Status::invalid("matmul: the row-argmax epilogue takes an unbatched product");
   auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
   const int64_t cvec = d.c_f32 ? 4 : 8;   // elements per 16 bytes of C
   p.vec_ok = (al16p(d.c) && d.c_row % cvec == 0 && d.c_batch % cvec == 0 && d.c_batch_inner % cvec == 0 &&
               (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
+  // 16-bit C whose rows (and batch strides, and residual) are 32-byte aligned: one row per lane, 256-bit accesses
+  auto al32p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
+  if (p.vec_ok && !d.c_f32 && g_direct_store && al32p(d.c) && d.c_row % 16 == 0 && d.c_batch % 16 == 0 && d.c_batch_inner % 16 == 0 &&
+      (!d.ep.residual || al32p(d.ep.residual)))
+    p.vec_ok = 2;
   p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
   long long num_tiles = tiles_m * tiles_n * nb;
+#define AG_TCP(BNV, MN) \
+  (d.dtype == DType::BF16 ? launch_tc_pair<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (use_pair) {
-    if (d.dtype == DType::BF16) return b_mn ? launch_tc_pair<true, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair<false, __nv_bfloat16>(s, ma, mb, p, num_tiles);
-    return b_mn ? launch_tc_pair<true, __half>(s, ma, mb, p, num_tiles) : launch_tc_pair<false, __half>(s, ma, mb, p, num_tiles);
+    if (bn == 256) return b_mn ? AG_TCP(256, true) : AG_TCP(256, false);
+    return b_mn ? AG_TCP(128, true) : AG_TCP(128, false);
   }
+#undef AG_TCP
 #define AG_TC(BNV, MN) \
   (d.dtype == DType::BF16 ? launch_tc<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (bn == 256) return b_mn ? AG_TC(256, true) : AG_TC(256, false);
@@ -895,6 +1061,19 @@ static int initial_force_path() {
 }
 static const int g_force_path_init = (g_force_path = initial_force_path());
 void set_matmul_path(int mode) { g_force_path = mode; }
+// APPLEGPU_GEMM_TILE=pair256|pair128|s256|s192|s128 pins the tile shape of the tensor-core kernel (a tuning override).
+static int initial_tile_override() {
+  const char* v = std::getenv("APPLEGPU_GEMM_TILE");
+  if (!v) return 0;
+  if (std::strcmp(v, "pair256") == 0) return 1256;
+  if (std::strcmp(v, "pair128") == 0) return 1128;
+  if (std::strcmp(v, "s256") == 0) return 256;
+  if (std::strcmp(v, "s192") == 0) return 192;
+  if (std::strcmp(v, "s128") == 0) return 128;
+  return 0;
+}
+static const int g_tile_override_init = (g_tile_override = initial_tile_override());
+void set_gemm_tile(int code) { g_tile_override = code; }
 
 const char* matmul_path(const GemmDesc& d) {
   if (g_force_path == 1) return "simt";

@@ -142,6 +142,9 @@ APPLEGPU_API const char* applegpu_matmul_path(uint64_t a_id, uint64_t b_id, bool
 /* 0 auto, 1 force the CUDA-core kernel, 2 require a tcgen05 kernel, 3 tcgen05 with single-CTA
  * tiles only, 4 tcgen05 with CTA-pair 256 x 256 tiles (cta_group::2) where the shape is large enough. */
 APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
+/* Tuning override of the tensor-core kernel's tile shape: 0 = chosen per problem by the cost model (default);
+ * 1256 / 1128 = CTA-pair tiles of 256 x 256 / 256 x 128; 256 / 192 / 128 = single-CTA tiles of 128 x that width. */
+APPLEGPU_API void applegpu_set_gemm_tile(int32_t code);
 /* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
  * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
 APPLEGPU_API void applegpu_set_f32_split(bool on);
