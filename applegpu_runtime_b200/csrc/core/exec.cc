@@ -26,13 +26,18 @@ namespace profile {
 struct Span { std::string name; cudaEvent_t a, b; double work; };
 static bool g_on = false;
 static std::vector<Span> g_spans;
+static std::vector<cudaEvent_t> g_free_events;   // events are reused: creating one costs more host time than a small kernel runs
 static std::mutex g_mu;
 void enable(bool on) { std::lock_guard<std::mutex> g(g_mu); g_on = on; }
 bool enabled() { return g_on; }
 void clear() {
   std::lock_guard<std::mutex> g(g_mu);
-  for (auto& s : g_spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
+  for (auto& s : g_spans) { g_free_events.push_back(s.a); g_free_events.push_back(s.b); }
   g_spans.clear();
+}
+static bool take_event(cudaEvent_t* e) {
+  if (!g_free_events.empty()) { *e = g_free_events.back(); g_free_events.pop_back(); return true; }
+  return cudaEventCreate(e) == cudaSuccess;
 }
 struct Scope {
   bool live = false; size_t idx = 0;
@@ -41,9 +46,9 @@ struct Scope {
     DeviceCtx& ctx = DeviceCtx::get();
     if (ctx.dry) return;
     Span sp; sp.name = name; sp.work = work;
-    if (cudaEventCreate(&sp.a) != cudaSuccess || cudaEventCreate(&sp.b) != cudaSuccess) return;
-    cudaEventRecord(sp.a, ctx.stream);
     std::lock_guard<std::mutex> g(g_mu);
+    if (!take_event(&sp.a) || !take_event(&sp.b)) return;
+    cudaEventRecord(sp.a, ctx.stream);
     g_spans.push_back(sp); idx = g_spans.size() - 1; live = true;
   }
   ~Scope() {
@@ -345,7 +350,9 @@ Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in,
       if (out_buf && !out_buf->borrowed) ctx.prefetch(out_buf->ptr, out_buf->capacity);
     }
   }
-  if (!profile::enabled()) return execute_node_impl(node, in, out, out_buf);
+  // layout-only ops that return views launch nothing: no span (an event pair around nothing would only add host work)
+  const bool view_only = !out_buf && (node.op.op == Op::Transpose || node.op.op == Op::Slice || node.op.op == Op::Reshape);
+  if (!profile::enabled() || view_only) return execute_node_impl(node, in, out, out_buf);
   std::string name = node.op.kernel_name();
   if (node.op.op == Op::FusedElementwise) name = "fused_elementwise";
   profile::Scope scope(name + dtype_suffix(node.out_dtype), node_work(node, in));
@@ -450,9 +457,10 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
       const bool int8_w = kd.op == Op::MatmulInt8 || (kd.op == Op::FusedLinear && kd.i1 == 1);
       if (int8_w) {
         // x [.., M, K] @ (w_q [N, K] * scales[N])^T: B is K-major int8, the per-channel scales go to the
-        // epilogue. For f16/bf16 activations the weights are widened (exactly) into a pooled [N, K]
-        // buffer of the activation type first, so the product runs on the tensor cores; the int8
-        // copy stays the resident one (half the bytes of a 16-bit weight).
+        // epilogue. With f16/bf16 activations and more than one row block the tensor-core kernel reads the
+        // int8 weights as they lie and widens them in its prologue (one launch, no widened copy in global
+        // memory). Shapes that kernel does not take (a single row block: decode steps; K not a multiple of
+        // 16) get the weights widened (exactly) into a pooled [N, K] buffer of the activation type first.
         TensorRec x, w;
         AG_RETURN_IF_ERROR(make_contiguous(*in[0], &x));
         AG_RETURN_IF_ERROR(make_contiguous(*in[1], &w));
@@ -465,7 +473,7 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
         g.b_row = 1; g.b_col = g.k; g.b_batch = 0;
         g.c_row = g.n; g.c_batch = 0;
         g.ep.b_scales = (const float*)in[2]->data();
-        if ((x.dtype == DType::BF16 || x.dtype == DType::F16) && g.k % 8 == 0 && g.m > 0 && g.n > 0 && !dry) {
+        if ((x.dtype == DType::BF16 || x.dtype == DType::F16) && g.k % 8 == 0 && g.m > 0 && g.n > 0 && !dry && !k::matmul_w8_fused_eligible(g)) {
           TensorRec wide;
           AG_RETURN_IF_ERROR(alloc_out(w.shape, x.dtype, &wide, nullptr));
           AG_LAUNCH(k::cast(s, w.view(), wide.view()));

@@ -595,15 +595,47 @@ template <int BN> struct PairCfg {
   static constexpr int kTmemCols = 2 * BN;                  // two accumulator buffers
 };
 
-template <int BN, bool B_MN, typename T>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTcThreads, 1)
+// W8 = the B operand is an int8 [N, K] weight (per-output-channel symmetric quantisation): the dequantisation
+// happens inside this kernel's prologue. TMA brings each CTA's half of the weight tile in as raw bytes (64-byte
+// swizzle) into the upper half of the stage's B area; four converter warps read their rows into registers, meet
+// at a named barrier (the raw bytes lie where widened rows will be written), widen the integers exactly to the
+// activation type in the 128-byte-swizzled K-major layout the MMA descriptor expects, and arrive on the stage's
+// full barrier in the even CTA, which therefore counts the A bytes of both CTAs plus eight converter warps. The
+// per-channel scales multiply the accumulator in the epilogue (exact for per-output-channel scaling), so the
+// only copy of the weights in global memory is the int8 one and no widened copy is ever written there.
+constexpr int kConvWarps = 4;
+constexpr int kTcThreadsW8 = kTcThreads + kConvWarps * 32;
+// Four int8 values (one 32-bit word) -> two words of packed 16-bit floats, exactly. Each byte is biased to
+// unsigned (u = v + 128), dropped into the mantissa of 2^23 (0x4B000000 | u = 8388608 + u), and the float
+// subtraction of 8388736 leaves v; values of at most 8 significant bits survive the narrowing unchanged.
+template <typename T>
+__device__ __forceinline__ void widen_s8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;
+  float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7440)) - 8388736.0f;
+  float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7441)) - 8388736.0f;
+  float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7442)) - 8388736.0f;
+  float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7443)) - 8388736.0f;
+  if (std::is_same<T, __nv_bfloat16>::value) {
+    lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);   // upper halves: bf16 is a truncated float
+    hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+  } else {
+    lo = pack2<T>(f0, f1);
+    hi = pack2<T>(f2, f3);
+  }
+}
+
+template <int BN, bool B_MN, typename T, bool W8 = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W8 ? kTcThreadsW8 : kTcThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const TcParams p) {
   using Cfg = PairCfg<BN>;
+  static_assert(!W8 || (BN == 256 && !B_MN), "the int8-weight form takes a K-major [N, K] weight and 256-wide tiles");
   constexpr int STAGES = Cfg::kStages;
   constexpr int KBS = kPairKbPerStage;
+  constexpr int kRawBytes = (BN / 2) * BK;                  // this CTA's half of the int8 weight tile, one k-block
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[STAGES];
   __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t raw_bar[STAGES];                      // W8: the raw int8 bytes of a stage have landed (per CTA)
   __shared__ uint64_t tmem_full_bar[2];
   __shared__ uint64_t tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
@@ -619,7 +651,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const long long first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], W8 ? 1 + 2 * kConvWarps : 1); mbar_init(&empty_bar[s], 1); mbar_init(&raw_bar[s], 1); }
     for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps); }
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
@@ -652,7 +684,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int b_bo = (p.b_bcast & 1) ? 0 : bo, b_bi = (p.b_bcast & 2) ? 0 : bi;
         for (int r = 0; r < rounds; r++) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, 1)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);   // both CTAs' bytes
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], W8 ? 2 * KBS * Cfg::kABytes : 2 * Cfg::kStageBytes);   // both CTAs' bytes
+          if (W8) mbar_expect_tx(&raw_bar[stage], KBS * kRawBytes);
           const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
 #pragma unroll
           for (int j = 0; j < KBS; j++) {
@@ -660,7 +693,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             uint8_t* sa = smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes;
             uint8_t* sb = sa + Cfg::kABytes;
             tma_load_4d_pair(sa, &tmap_a, bar, kc, m0, a_bi, a_bo);
-            if (B_MN) {
+            if (W8) {
+              // raw bytes into the upper half of the B area (the lower half is written first by the converters)
+              tma_load_4d(sb + Cfg::kBBytes - kRawBytes, &tmap_b, &raw_bar[stage], kc, n0, 0, 0);
+            } else if (B_MN) {
 #pragma unroll
               for (int q = 0; q < BN / 128; q++)
                 tma_load_4d_pair(sb + q * (64 * BK * 2), &tmap_b, bar, n0 + q * 64, kc, b_bi, b_bo);
@@ -725,6 +761,47 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef AG_GEMM_PROBE
       if (p.probe) { p.probe[blockIdx.x * 16 + 0] = pr_wait; p.probe[blockIdx.x * 16 + 1] = pr_main; p.probe[blockIdx.x * 16 + 2] = pr_steps; p.probe[blockIdx.x * 16 + 6] = pr_t0; }
 #endif
+    }
+  } else if (W8 && warp >= 2 + kEpiWarps) {
+    // ── converter warps (both CTAs): int8 rows -> 16-bit rows of this CTA's half of the B tile ──
+    const int row = (warp - 2 - kEpiWarps) * 32 + lane;       // 0 .. BN/2 - 1: one weight row per thread
+    int stage = 0; uint32_t phase = 0;
+    bool ok = true;
+    for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
+      for (int r = 0; r < rounds; r++) {
+        const bool landed = mbar_wait(&raw_bar[stage], phase, p.status, 5);
+        uint4 q[KBS][4];
+#pragma unroll
+        for (int j = 0; j < KBS; j++) {
+          const uint8_t* raw = smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes + Cfg::kABytes + Cfg::kBBytes - kRawBytes;
+#pragma unroll
+          for (int c = 0; c < 4; c++) q[j][c] = *reinterpret_cast<const uint4*>(raw + stg_off(row, c));   // 64-byte rows, 64-byte swizzle
+        }
+        // Every converter thread of this CTA holds its raw rows: the widened rows may now overwrite them. The same
+        // barrier carries the AND of `landed`, so that after a wait that gave up all four warps leave together
+        // (a warp that went on alone would wait at this barrier for ever).
+        uint32_t all_landed;
+        asm volatile("{\n .reg .pred p, q;\n setp.ne.b32 q, %1, 0;\n bar.red.and.pred p, 1, %2, q;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(all_landed) : "r"((uint32_t)landed), "n"(kConvWarps * 32) : "memory");
+        if (!all_landed) { ok = false; break; }
+#pragma unroll
+        for (int j = 0; j < KBS; j++) {
+          uint8_t* dst = smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes + Cfg::kABytes + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            // 16 int8 = words x, y, z, w -> two 16-byte chunks (2c, 2c + 1) of the 128-byte row, chunk index XOR (row % 8)
+            uint4 lo4, hi4;
+            widen_s8x4<T>(q[j][c].x, lo4.x, lo4.y); widen_s8x4<T>(q[j][c].y, lo4.z, lo4.w);
+            widen_s8x4<T>(q[j][c].z, hi4.x, hi4.y); widen_s8x4<T>(q[j][c].w, hi4.z, hi4.w);
+            *reinterpret_cast<uint4*>(dst + (((2 * c) ^ (row & 7)) << 4)) = lo4;
+            *reinterpret_cast<uint4*>(dst + (((2 * c + 1) ^ (row & 7)) << 4)) = hi4;
+          }
+        }
+        fence_proxy_async_smem();   // the MMA reads these rows through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&full_bar[stage]), 0));
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
     }
   } else {
     // ── epilogue warps (both CTAs; each reads its own 128 accumulator lanes) ──
@@ -821,6 +898,13 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// APPLEGPU_W8_FUSED: 'auto' (default) widens int8 weights inside the GEMM for up to kW8FusedMaxRows activation rows and by one
+// separate pass per call above that; '1' always inside the GEMM; '0' always by the separate pass.
+static int g_w8_fused = [] { const char* v = std::getenv("APPLEGPU_W8_FUSED"); return !v ? 2 : v[0] == '0' ? 0 : v[0] == '1' ? 1 : 2; }();
+// Measured on a B200 (GPT-2-large linears, bf16 activations): at 2048 rows both forms take the same time; at 16384 rows the
+// prologue form is 6-20 % slower, because it widens the same weight tile again for every 256-row block of the activations
+// and those instructions compete with the epilogue for issue slots and with the tensor pipe for power.
+constexpr int64_t kW8FusedMaxRows = 2048;
 struct MapKey {
   const void* ptr; uint64_t d[4]; uint64_t s[3]; uint32_t b0, b1; int dt; int pad;
   bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
@@ -870,6 +954,33 @@ Status make_map(CUtensorMap* out, DType dt, const void* ptr, uint64_t inner, uin
   return Status::OK();
 }
 
+// Map over an int8 [rows, inner] matrix (bytes; 64-byte swizzle, box {b0 bytes, b1 rows}): the raw weight tiles of
+// the int8-weight kernel.
+static Status make_map_u8(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t rows, uint64_t row_stride, uint32_t b0, uint32_t b1) {
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = ptr; key.d[0] = inner; key.d[1] = rows; key.s[0] = row_stride; key.b0 = b0; key.b1 = b1; key.dt = (int)DType::I8;
+  {
+    std::lock_guard<std::mutex> g(g_map_mu);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) { *out = it->second; return Status::OK(); }
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return Status::compute("cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[4] = {inner, rows, 1, 1};
+  cuuint64_t gstride[3] = {row_stride, rows * row_stride, rows * row_stride};
+  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Status::compute("cuTensorMapEncodeTiled (int8) failed with code " + std::to_string((int)r));
+  {
+    std::lock_guard<std::mutex> g(g_map_mu);
+    g_map_cache.emplace(key, *out);
+  }
+  return Status::OK();
+}
+
 // 0 = not expressible, 1 = K-major ([N,K] rows), 2 = N-major ([K,N] rows).
 static int classify_b(const GemmDesc& d) {
   if (d.b_row == 1 && d.b_col % 8 == 0 && d.b_col >= d.k) return 1;
@@ -877,7 +988,22 @@ static int classify_b(const GemmDesc& d) {
   return 0;
 }
 
+// int8 weights [N, K] (contiguous rows of K bytes, K a multiple of 16, 16-byte aligned) against 16-bit activations with
+// more than one row block: the CTA-pair kernel widens them in its prologue.
+bool matmul_w8_fused_eligible(const GemmDesc& d) {
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != DType::I8) return false;
+  if (d.batch != 1 || d.batch_inner != 1 || d.c_f32 || d.ep.argmax_keys || !d.ep.b_scales) return false;
+  if (d.m <= BM || d.n < 1 || d.k < 16 || d.k % 16 != 0) return false;
+  if (d.m > 0x7fffffff || d.n > 0x7fffffff || d.k > 0x7fffffff) return false;
+  if (d.b_row != 1 || d.b_col != d.k) return false;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!al16(d.a) || !al16(d.b)) return false;
+  if (d.a_col != 1 || d.a_row % 8 != 0 || d.a_row < d.k) return false;
+  return g_w8_fused == 1 || (g_w8_fused == 2 && d.m <= kW8FusedMaxRows);
+}
+
 static bool tc_eligible(const GemmDesc& d) {
+  if (matmul_w8_fused_eligible(d)) return true;
   if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
   if (d.m < 1 || d.n < 1 || d.k < 1 || d.batch < 1 || d.batch_inner < 1) return false;
   if (d.m > 0x7fffffff || d.n > 0x7fffffff || d.k > 0x7fffffff || d.batch * d.batch_inner > 0x7fffffff) return false;
@@ -949,6 +1075,33 @@ static Status launch_tc_pair(cudaStream_t s, const CUtensorMap& ma, const CUtens
   return Status::OK();
 }
 
+template <typename T>
+static Status launch_tc_pair_w8(cudaStream_t s, const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, long long num_tiles) {
+  static int clusters = -1;
+  auto kern = gemm_tc_pair_kernel<256, false, T, true>;
+  if (clusters < 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<256>::kSmemBytes) != cudaSuccess) { cudaGetLastError(); clusters = 0; }
+    else {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(2 * (sm_count() / 2)), 1, 1);
+      cfg.blockDim = dim3(kTcThreadsW8, 1, 1);
+      cfg.dynamicSmemBytes = PairCfg<256>::kSmemBytes;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+      clusters = n > sm_count() / 2 ? sm_count() / 2 : n;
+    }
+  }
+  if (clusters <= 0) return Status::compute("matmul (tcgen05, int8 weights): no resident cluster available");
+  int grid = 2 * (int)(num_tiles < clusters ? num_tiles : clusters);
+  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(kTcThreadsW8), PairCfg<256>::kSmemBytes, s, ma, mb, p);
+  if (le != cudaSuccess) return cuda_status(le, "matmul (tcgen05, int8 weights)");
+  return Status::OK();
+}
+
 #ifdef AG_GEMM_PROBE
 long long* g_tc_probe = nullptr;   // set by the probe harness; the kernel then records where its cycles go
 #endif
@@ -990,9 +1143,10 @@ static TileChoice choose_tile(const GemmDesc& d, long long nb, int force_path) {
 }
 
 Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
-  const bool b_mn = classify_b(d) == 2;
+  const bool w8 = d.b_dtype == DType::I8;
+  const bool b_mn = !w8 && classify_b(d) == 2;
   const long long nb = d.batch * d.batch_inner;
-  const TileChoice tile = choose_tile(d, nb, g_force_path);
+  const TileChoice tile = w8 ? TileChoice{true, 256} : choose_tile(d, nb, g_force_path);
   const bool use_pair = tile.pair;
   const int bn = tile.bn;
   long long tiles_m = use_pair ? (d.m + 2 * BM - 1) / (2 * BM) : (d.m + BM - 1) / BM;
@@ -1005,7 +1159,9 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   uint64_t b_nbo = (b_bcast & 1) ? 1 : (uint64_t)d.batch, b_nbi = (b_bcast & 2) ? 1 : (uint64_t)d.batch_inner;
   AG_RETURN_IF_ERROR(make_map(&ma, d.dtype, d.a, (uint64_t)d.k, (uint64_t)d.m, a_nbi, a_nbo, (uint64_t)d.a_row,
                               (uint64_t)d.a_batch_inner, (uint64_t)d.a_batch, BK, BM));
-  if (!b_mn) {
+  if (w8) {
+    AG_RETURN_IF_ERROR(make_map_u8(&mb, d.b, (uint64_t)d.k, (uint64_t)d.n, (uint64_t)d.b_col, BK, (uint32_t)(bn / 2)));
+  } else if (!b_mn) {
     AG_RETURN_IF_ERROR(make_map(&mb, d.dtype, d.b, (uint64_t)d.k, (uint64_t)d.n, b_nbi, b_nbo, (uint64_t)d.b_col,
                                 (uint64_t)d.b_batch_inner, (uint64_t)d.b_batch, BK, (uint32_t)(use_pair ? bn / 2 : bn)));
   } else {
@@ -1034,6 +1190,7 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
     p.vec_ok = 2;
   p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
   long long num_tiles = tiles_m * tiles_n * nb;
+  if (w8) return d.dtype == DType::BF16 ? launch_tc_pair_w8<__nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair_w8<__half>(s, ma, mb, p, num_tiles);
 #define AG_TCP(BNV, MN) \
   (d.dtype == DType::BF16 ? launch_tc_pair<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (use_pair) {

@@ -88,6 +88,10 @@ struct GemmDesc {
   GemmEpilogue ep;
 };
 Status matmul(cudaStream_t s, const GemmDesc& d);
+// int8 [N, K] weights against f16 / bf16 activations: true when the tensor-core kernel takes the int8 operand as it
+// lies and widens it in its own prologue (per-channel scales in the epilogue); false when the caller has to hand the
+// kernel a 16-bit copy instead (a single row block, K not a multiple of 16, unaligned operands).
+bool matmul_w8_fused_eligible(const GemmDesc& d);
 // Reports which kernel family `matmul` would choose: "tcgen05" or "simt".
 const char* matmul_path(const GemmDesc& d);
 // fp32 -> three bf16 terms x = x0 + x1 + x2 (each the bf16 rounding of what the previous ones left), written

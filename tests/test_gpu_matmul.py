@@ -195,6 +195,29 @@ def test_matmul_int8_weights(gpu_dev):
     np.testing.assert_allclose(got, R.matmul_int8(xf, rq, rs), rtol=1e-5, atol=1e-6)
 
 
+def test_matmul_int8_prologue_widening_is_exact_and_one_launch(gpu_dev):
+    """The tensor-core kernel reads int8 weights as they lie and widens them in its prologue. Identity activations
+    make the product return the widened weights themselves: every int8 value, at every position of the swizzled
+    tile, must come out exactly, from a single launch (no separate widening pass, no 16-bit copy of the weights)."""
+    rng = np.random.default_rng(11)
+    k, n = 384, 700                                            # 6 k-blocks; N is not a multiple of the tile width
+    w = rng.integers(-127, 128, (n, k)).astype(np.float32)
+    w[:, 0] = 127.0                                            # max |w| = 127 in every row: scale exactly 1
+    w[5, 1:129] = np.arange(-127, 1, dtype=np.float32)         # the whole negative range in one row
+    q, s = gpu_dev.quantize_weight(gpu_dev.from_numpy(w))
+    assert np.array_equal(q.to_numpy(), w.astype(np.int8)) and np.all(s.to_numpy() == 1.0)
+    x = np.zeros((2 * k, k), np.float32)
+    x[np.arange(2 * k), np.arange(2 * k) % k] = 1.0            # two stacked identities: 768 rows, several row blocks
+    for dt in ("bfloat16", "float16"):
+        gx = up(gpu_dev, x, dt)
+        y = gpu_dev.matmul_int8(gx, q, s)
+        launches = gpu_dev.launch_count()
+        got = y.to_numpy()
+        assert gpu_dev.launch_count() - launches == 1
+        assert np.array_equal(got, np.concatenate([w.T, w.T], axis=0))
+    assert gpu_dev.pipeline_status() == 0
+
+
 def test_matmul_int8_weights_on_tensor_cores_with_fused_epilogue(gpu_dev):
     """GPT-2-large-like linear: bf16 activations, per-output-channel int8 weights [N, K]; bias, GELU and
     the residual ride in the epilogue of the same GEMM (weights widened exactly to bf16 on the way)."""
