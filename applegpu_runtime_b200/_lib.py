@@ -179,6 +179,12 @@ EXT_SYMBOLS = {
     "applegpu_resolve_kernel": (cstr, [cstr, i8]),
     "applegpu_attention_noalloc": (i32, [vp, vp, vp, vp, i8, u64, u64, u64, u64, u64, cbool, vp]),
     "applegpu_attention_noalloc_status": (i32, [vp]),
+    "applegpu_gpt2_decoder_create": (u64, [u64p, u32, u32, u32, u32, u32, u32, u32, u32]),
+    "applegpu_gpt2_decoder_prefill": (i32, [u64, u64p, u32, u64, u32]),
+    "applegpu_gpt2_decoder_steps": (i32, [u64, u32, vp, cbool]),
+    "applegpu_gpt2_decoder_launches_per_step": (i32, [u64]),
+    "applegpu_gpt2_decoder_uses_graph": (i32, [u64]),
+    "applegpu_gpt2_decoder_destroy": (None, [u64]),
     "applegpu_test_wait_runs_out": (i32, [i32, u32]),
 }
 

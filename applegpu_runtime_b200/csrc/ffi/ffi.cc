@@ -19,6 +19,13 @@ extern bool g_fused_attention;
 void set_f32_split(bool on);
 uint64_t launch_count();
 namespace profile { void enable(bool on); void clear(); std::string report(); }
+struct Gpt2DecoderCfg { int n_layer, n_head, n_embd, vocab, n_positions, batch, max_len; };
+Status decoder_create(const std::vector<TensorRec>& weights, const Gpt2DecoderCfg& cfg, uint64_t* handle);
+Status decoder_prefill(uint64_t handle, const std::vector<TensorRec>& kvs, const TensorRec& first_tokens, int prompt_len);
+Status decoder_steps(uint64_t handle, int n_steps, int32_t* host_tokens, bool use_graph);
+int decoder_launches_per_step(uint64_t handle);
+int decoder_uses_graph(uint64_t handle);
+void decoder_destroy(uint64_t handle);
 namespace k {
 void set_matmul_path(int mode);
 void set_gemm_tile(int code);
@@ -1182,6 +1189,55 @@ int32_t applegpu_flush_l2(void) {
   if (!g_flush_buf && !Shared::get().pool.acquire(kFlushBytes, &g_flush_buf).ok()) { g_flush_buf.reset(); return -1; }
   return k::flush_l2(ctx.stream, g_flush_buf->ptr, kFlushBytes).ok() ? 0 : -1;
 }
+// ── GPT-2 greedy decoder (preallocated KV cache, captured step) ─────────────
+static Status materialised(LazyRuntime& rt, uint64_t id, TensorRec* out) {
+  if (rt.is_pending(id)) AG_RETURN_IF_ERROR(rt.eval(id));
+  const TensorRec* t = rt.tensor(id);
+  if (!t || !t->has_meta || !t->buf) return Status::invalid("Tensor " + std::to_string(id) + " not found");
+  *out = *t;
+  return Status::OK();
+}
+uint64_t applegpu_gpt2_decoder_create(const uint64_t* weight_ids, uint32_t n_weights, uint32_t n_layer, uint32_t n_head, uint32_t n_embd, uint32_t vocab,
+                                      uint32_t n_positions, uint32_t batch, uint32_t max_len) {
+  if (!ffi_ready("gpt2_decoder_create")) return 0;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  std::vector<TensorRec> w(n_weights);
+  for (uint32_t i = 0; i < n_weights; i++) {
+    Status s = materialised(st.rt, weight_ids[i], &w[i]);
+    if (!s.ok()) { set_ffi_error("gpt2_decoder_create failed: " + s.to_string()); return 0; }
+  }
+  Gpt2DecoderCfg cfg{(int)n_layer, (int)n_head, (int)n_embd, (int)vocab, (int)n_positions, (int)batch, (int)max_len};
+  uint64_t h = 0;
+  Status s = decoder_create(w, cfg, &h);
+  if (!s.ok()) { set_ffi_error("gpt2_decoder_create failed: " + s.to_string()); return 0; }
+  return h;
+}
+int32_t applegpu_gpt2_decoder_prefill(uint64_t decoder, const uint64_t* kv_ids, uint32_t n_kv, uint64_t first_tokens_id, uint32_t prompt_len) {
+  if (!ffi_ready("gpt2_decoder_prefill")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  std::vector<TensorRec> kv(n_kv);
+  TensorRec tok;
+  Status s = Status::OK();
+  for (uint32_t i = 0; i < n_kv && s.ok(); i++) s = materialised(st.rt, kv_ids[i], &kv[i]);
+  if (s.ok()) s = materialised(st.rt, first_tokens_id, &tok);
+  if (s.ok()) s = decoder_prefill(decoder, kv, tok, (int)prompt_len);
+  if (!s.ok()) { set_ffi_error("gpt2_decoder_prefill failed: " + s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_gpt2_decoder_steps(uint64_t decoder, uint32_t n_steps, int32_t* host_tokens, bool use_graph) {
+  if (!ffi_ready("gpt2_decoder_steps")) return -1;
+  LazyState& st = lazy_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  Status s = decoder_steps(decoder, (int)n_steps, host_tokens, use_graph);
+  if (!s.ok()) { set_ffi_error("gpt2_decoder_steps failed: " + s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_gpt2_decoder_launches_per_step(uint64_t decoder) { return decoder_launches_per_step(decoder); }
+int32_t applegpu_gpt2_decoder_uses_graph(uint64_t decoder) { return decoder_uses_graph(decoder); }
+void applegpu_gpt2_decoder_destroy(uint64_t decoder) { decoder_destroy(decoder); }
+
 int32_t applegpu_test_wait_runs_out(int32_t code, uint32_t limit_us) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return -1;

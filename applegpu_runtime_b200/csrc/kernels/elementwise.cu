@@ -24,9 +24,11 @@ int sm_count() {
   return g_sm_count;
 }
 
+static int g_pdl_override = -1;
+void set_pdl_override(int on) { g_pdl_override = on; }
 bool pdl_enabled() {
   static const bool on = [] { const char* v = std::getenv("APPLEGPU_PDL"); return !(v && v[0] == '0'); }();
-  return on;
+  return g_pdl_override < 0 ? on : g_pdl_override != 0;
 }
 
 // ── index helpers ───────────────────────────────────────────────────────────

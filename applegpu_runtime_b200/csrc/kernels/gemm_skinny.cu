@@ -29,6 +29,9 @@ struct SkinnyParams {
   int a_vec;                 // A rows are 16-byte aligned
   float* partial;            // [k_slabs][16][n]
   unsigned int* counters;    // one per column slab, zero between launches
+  const void* ln_gamma;      // K-major kernel only: layer_norm of A's rows (gamma, beta of length k) before the product
+  const void* ln_beta;
+  float ln_eps;
 };
 
 // four consecutive elements of B as one load
@@ -170,6 +173,23 @@ __global__ void __launch_bounds__(kSkThreads) gemm_skinny_kmajor_kernel(const Sk
     sAk[i] = m < p.m ? Cvt<T>::to(A[(long long)m * p.a_row + kk]) : 0.f;
   }
   __syncthreads();
+  if (p.ln_gamma) {
+    // layer_norm of the staged rows, in place (kernel_templates.rs:1097-1109: mean, population variance,
+    // 1/sqrt(var + eps), gamma * (x - mean) * inv_std + beta): a warp per row, two passes over shared memory.
+    const T* G = reinterpret_cast<const T*>(p.ln_gamma);
+    const T* Bt = reinterpret_cast<const T*>(p.ln_beta);
+    for (int m = warp; m < p.m; m += kSkThreads / 32) {
+      float* row = sAk + m * p.k;
+      float sum = 0.f;
+      for (int kk = lane; kk < p.k; kk += 32) sum += row[kk];
+      const float mean = warp_sum(sum) / (float)p.k;
+      float sq = 0.f;
+      for (int kk = lane; kk < p.k; kk += 32) { const float dlt = row[kk] - mean; sq += dlt * dlt; }
+      const float inv_std = 1.0f / sqrtf(warp_sum(sq) / (float)p.k + p.ln_eps);
+      for (int kk = lane; kk < p.k; kk += 32) row[kk] = Cvt<T>::to(G[kk]) * (row[kk] - mean) * inv_std + Cvt<T>::to(Bt[kk]);
+    }
+    __syncthreads();
+  }
   const long long warps_total = (long long)gridDim.x * (kSkThreads / 32);
   for (long long n0 = ((long long)blockIdx.x * (kSkThreads / 32) + warp) * kSkR; n0 < p.n; n0 += warps_total * kSkR) {
     float acc[MR][kSkR];
@@ -261,6 +281,7 @@ Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d) {
   p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_col; p.c_row = d.c_row;   // b_row: stride between B's [N, K] rows
   p.partial = nullptr; p.counters = nullptr; p.a_vec = 0;
+  p.ln_gamma = d.ln_gamma; p.ln_beta = d.ln_beta; p.ln_eps = d.ln_eps;
   const int mr = d.m <= 8 ? 8 : 16;
   const size_t smem = (size_t)mr * d.k * sizeof(float);
   const long long groups = (d.n + kSkR - 1) / kSkR, per_block = kSkThreads / 32;
@@ -278,6 +299,7 @@ float* skinny_partials();            // workspace.cu: created with the device co
 unsigned int* skinny_counters();
 
 bool skinny_eligible(const GemmDesc& d) {
+  if (d.ln_gamma) return false;
   if (!(d.dtype == DType::BF16 || d.dtype == DType::F16 || d.dtype == DType::F32) || d.b_dtype != d.dtype) return false;
   if (d.c_f32 || d.ep.argmax_keys || d.ep.b_scales) return false;
   if (d.batch != 1 || d.batch_inner != 1) return false;
@@ -298,6 +320,7 @@ Status matmul_skinny(cudaStream_t s, const GemmDesc& d) {
   p.a = d.a; p.b = d.b; p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
   p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.a_row = d.a_row; p.b_row = d.b_row; p.c_row = d.c_row;
   p.partial = partial; p.counters = counters;
+  p.ln_gamma = nullptr; p.ln_beta = nullptr; p.ln_eps = 0.f;
   p.a_vec = (d.a_row % (d.dtype == DType::F32 ? 4 : 8) == 0 && (reinterpret_cast<uintptr_t>(d.a) & 15u) == 0) ? 1 : 0;
   dim3 grid((unsigned)((d.n + kSkN - 1) / kSkN), (unsigned)((d.k + kSkK - 1) / kSkK), 1);
   cudaError_t e;

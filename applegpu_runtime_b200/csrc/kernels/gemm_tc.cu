@@ -1255,6 +1255,10 @@ Status argmax_finalize(cudaStream_t s, const unsigned long long* keys, int32_t* 
 
 Status matmul(cudaStream_t s, const GemmDesc& d) {
   if (d.m == 0 || d.n == 0 || d.batch == 0) return Status::OK();
+  if (d.ln_gamma) {
+    if (!skinny_kmajor_eligible(d)) return Status::invalid("matmul: the layer_norm prologue needs at most 16 rows against a [N, K] weight");
+    return matmul_skinny_kmajor(s, d);
+  }
   bool elig = tc_eligible(d);
   if (d.ep.argmax_keys && (!elig || g_force_path == 1)) return Status::invalid("matmul: the row-argmax epilogue needs the tensor-core kernel");
   // a handful of rows against a [K, N] weight: bound by streaming B, spread over every SM

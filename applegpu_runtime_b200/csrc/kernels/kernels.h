@@ -85,6 +85,11 @@ struct GemmDesc {
   int64_t c_row, c_batch, c_batch_inner = 0;
   // Operands are f16/bf16 but C, bias and residual are float32 (the split-precision fp32 product).
   bool c_f32 = false;
+  // Prologue: layer_norm over A's rows (gamma, beta of length k, same dtype as A) before the product. Taken only by
+  // the K-major skinny kernel (at most 16 rows against a [N, K] weight: a decode step), which stages A's rows whole.
+  const void* ln_gamma = nullptr;
+  const void* ln_beta = nullptr;
+  float ln_eps = 1e-5f;
   GemmEpilogue ep;
 };
 Status matmul(cudaStream_t s, const GemmDesc& d);
@@ -92,6 +97,10 @@ Status matmul(cudaStream_t s, const GemmDesc& d);
 // lies and widens it in its own prologue (per-channel scales in the epilogue); false when the caller has to hand the
 // kernel a 16-bit copy instead (a single row block, K not a multiple of 16, unaligned operands).
 bool matmul_w8_fused_eligible(const GemmDesc& d);
+// At most 16 rows against a weight stored [N, K] (rows along K): each warp streams four weight rows at a time, A's rows
+// wait in shared memory as floats, no workspace, fixed summation order. Takes the layer_norm prologue of GemmDesc.
+bool skinny_kmajor_eligible(const GemmDesc& d);
+Status matmul_skinny_kmajor(cudaStream_t s, const GemmDesc& d);
 // Reports which kernel family `matmul` would choose: "tcgen05" or "simt".
 const char* matmul_path(const GemmDesc& d);
 // fp32 -> three bf16 terms x = x0 + x1 + x2 (each the bf16 rounding of what the previous ones left), written
@@ -136,6 +145,21 @@ int matmul_take_status(cudaStream_t s);
 // Test hook: one thread waits (for at most limit_ns, capped at 50 ms) on a barrier nothing arrives at,
 // records `code` in the status word and returns.
 Status launch_wait_runs_out(cudaStream_t s, int code, unsigned long long limit_ns);
+
+// Decode step against a preallocated KV cache [B, heads, t_max, 64]: writes the new token's key / value row at index
+// *len_ptr and attends over rows 0 .. *len_ptr (q, k, v of the new token are the thirds of qkv's [B, 3 * heads * 64] rows).
+Status attention_decode(cudaStream_t s, DType dt, const void* qkv, void* kcache, void* vcache, void* out, const int* len_ptr, int batch, int heads,
+                        int t_max, float scale);
+// Linear layer of a decode step (at most 16 rows against a [K, N] MODEL WEIGHT, i.e. a matrix no kernel of the step
+// writes: its loads are issued ahead of the programmatic dependency wait); takes the layer_norm prologue of GemmDesc
+// and the bias / activation / residual epilogue.
+bool decode_linear_eligible(const GemmDesc& d);
+Status decode_linear(cudaStream_t s, const GemmDesc& d);
+// End of a decode step: history[step] = tok, pos_ids = len + 1, step and len advance (all in device memory).
+Status decode_finish(cudaStream_t s, const int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps);
+Status decode_reset(cudaStream_t s, int* counters, int32_t* pos_ids, int batch, int len);
+// Programmatic dependent launch can be switched off for a region of host code (stream capture of a decode step).
+void set_pdl_override(int on);   // -1 follow the environment, 0 off, 1 on
 
 // Writes more than the L2 capacity so the next timed kernel starts cold.
 Status flush_l2(cudaStream_t s, void* scratch, size_t bytes);

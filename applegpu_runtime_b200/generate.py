@@ -37,16 +37,96 @@ def _sample_token(logits_np, temperature=1.0, top_k=0, top_p=0.0, rng=None):
     return int(rng.choice(len(probs), p=probs))
 
 
-def greedy_generate(model, input_ids, max_tokens=50, use_cache=True, compiled=True):
-    """Greedy decode for a batch of equal-length prompts [B, T]; returns [B, T + max_tokens]. With
-    `compiled` the decode steps (one new token against the KV cache) replay an op tape instead of
-    re-issuing ~300 op calls each. With the cache, the token a step picks stays on the device and
-    feeds the next step's embedding lookup directly (position ids come from one table uploaded up
-    front), so the host never waits for the GPU inside the loop: it records step i+1 while step i
-    runs, and the picked tokens are read back once at the end."""
+_WEIGHT_ORDER = ("ln_1.weight", "ln_1.bias", "attn.c_attn.weight", "attn.c_attn.bias", "attn.c_proj.weight", "attn.c_proj.bias",
+                 "ln_2.weight", "ln_2.bias", "mlp.c_fc.weight", "mlp.c_fc.bias", "mlp.c_proj.weight", "mlp.c_proj.bias")
+
+
+class Gpt2Decoder:
+    """The library's static-shape decoder (include/applegpu_b200_ext.h, applegpu_gpt2_decoder_*): a preallocated
+    [B, heads, max_len, 64] KV cache per layer appended in place, and a decode step captured once as a CUDA graph."""
+
+    def __init__(self, model, batch, max_len):
+        import ctypes
+        from . import _lib
+        self._lib = _lib.load()
+        cfg, w = model["config"], model["weights"]
+        names = ["transformer.wte.weight", "transformer.wpe.weight", "transformer.ln_f.weight", "transformer.ln_f.bias"]
+        for i in range(cfg["n_layer"]):
+            names += [f"transformer.h.{i}.{n}" for n in _WEIGHT_ORDER]
+        ids = (ctypes.c_uint64 * len(names))(*[w[n].id for n in names])
+        self.batch, self.max_len = int(batch), int(max_len)
+        self.handle = int(self._lib.applegpu_gpt2_decoder_create(ids, len(names), cfg["n_layer"], cfg["n_head"], cfg["n_embd"], cfg["vocab_size"],
+                                                                 cfg["n_positions"], self.batch, self.max_len))
+        if not self.handle:
+            raise ValueError(gpu._err())
+
+    @staticmethod
+    def supports(model, batch, total_len):
+        cfg = model["config"]
+        return ("int8" not in model and model.get("dtype", "float32") in ("float32", "float16", "bfloat16") and cfg["n_embd"] == 64 * cfg["n_head"]
+                and 1 <= batch <= 16 and total_len <= cfg["n_positions"])
+
+    def prefill(self, kv_cache, first_tokens, prompt_len):
+        import ctypes
+        flat = [t.id for kv in kv_cache for t in kv]
+        arr = (ctypes.c_uint64 * len(flat))(*flat)
+        if self._lib.applegpu_gpt2_decoder_prefill(self.handle, arr, len(flat), first_tokens.id, int(prompt_len)) != 0:
+            raise ValueError(gpu._err())
+
+    def steps(self, n, use_graph=True):
+        """Runs n decode steps; returns the picked tokens as an int32 array [n, batch]."""
+        import ctypes
+        out = np.empty((int(n), self.batch), np.int32)
+        if n > 0 and self._lib.applegpu_gpt2_decoder_steps(self.handle, int(n), out.ctypes.data_as(ctypes.c_void_p), bool(use_graph)) != 0:
+            raise ValueError(gpu._err())
+        return out
+
+    @property
+    def launches_per_step(self):
+        return int(self._lib.applegpu_gpt2_decoder_launches_per_step(self.handle))
+
+    @property
+    def uses_graph(self):
+        return int(self._lib.applegpu_gpt2_decoder_uses_graph(self.handle)) == 1
+
+    def close(self):
+        if self.handle:
+            self._lib.applegpu_gpt2_decoder_destroy(self.handle)
+            self.handle = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def greedy_generate(model, input_ids, max_tokens=50, use_cache=True, compiled=True, engine="auto"):
+    """Greedy decode for a batch of equal-length prompts [B, T]; returns [B, T + max_tokens].
+
+    With the cache and `engine` "auto" or "graph", the prompt runs through gpt2_forward and the decode steps through
+    the library's decoder: a preallocated KV cache appended in place and one captured step replayed per token
+    ("graph"; "direct" issues the same launches one by one). `engine="tape"` keeps the cache the reference's way
+    (concatenation, models/gpt2.py:122-127) and replays an op tape per step (`compiled`), the picked token staying
+    on the device between steps. Models the decoder does not take (int8 weights, head dimension other than 64,
+    more than 16 sequences) use the tape engine."""
     ids = np.asarray(input_ids, dtype=np.int64)
     if ids.ndim == 1:
         ids = ids.reshape(1, -1)
+    if use_cache and max_tokens > 1 and engine in ("auto", "graph", "direct") and Gpt2Decoder.supports(model, ids.shape[0], ids.shape[1] + max_tokens):
+        B, T0 = ids.shape
+        logits, kv = gpt2_forward(model, ids, kv_cache=None, last_only=True)      # prefill of the prompt
+        first = gpu.argmax(logits)
+        del logits
+        dec = Gpt2Decoder(model, B, T0 + max_tokens)
+        try:
+            dec.prefill(kv, first, T0)
+            rest = dec.steps(max_tokens - 1, use_graph=(engine != "direct"))
+            model["_last_decoder_stats"] = {"launches_per_step": dec.launches_per_step, "graph": dec.uses_graph}
+        finally:
+            dec.close()
+        new = np.concatenate([first.to_numpy().astype(np.int64).reshape(B, 1), rest.T.astype(np.int64)], axis=1)
+        return np.concatenate([ids, new], axis=1)
     if not use_cache:
         for _ in range(max_tokens):
             logits, _ = gpt2_forward(model, ids, kv_cache=None, last_only=True)

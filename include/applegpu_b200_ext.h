@@ -213,6 +213,29 @@ APPLEGPU_API int64_t applegpu_profile_report(char* buf, uint64_t cap);
  * Reference: KernelRegistry::resolve_kernel, compute.rs:1478-1567. Returns NULL if unsupported. */
 APPLEGPU_API const char* applegpu_resolve_kernel(const char* base_name, int8_t dtype);
 
+/* ── GPT-2 greedy decoder: preallocated KV cache, one captured step ────────────
+ * Counterpart of the reference's generate loop (python/applegpu_runtime/models/generate.py:83-127 over
+ * models/gpt2.py:47-180), which re-records the forward for every token and grows its KV cache by concat
+ * (gpt2.py:122-127). A decoder owns a [batch, heads, max_len, 64] key and value cache per layer; a step is a fixed
+ * list of kernel launches (the current length and the picked tokens live in device memory), captured once as a
+ * CUDA graph and replayed.
+ *   create:  weight_ids = wte, wpe, ln_f.weight, ln_f.bias, then per layer ln_1.weight, ln_1.bias, c_attn.weight
+ *            [d, 3d], c_attn.bias, attn c_proj.weight [d, d], its bias, ln_2.weight, ln_2.bias, c_fc.weight [d, 4d],
+ *            its bias, mlp c_proj.weight [4d, d], its bias (graph-flavour tensor ids, one float dtype, head
+ *            dimension 64, batch <= 16). Returns a handle, 0 on failure (applegpu_ffi_last_error).
+ *   prefill: kv_ids = k0, v0, k1, v1, ... each [batch, heads, prompt_len, 64] (the cache a prompt forward returned),
+ *            first_tokens_id = int32 [batch], the tokens picked from the prompt's last logits.
+ *   steps:   runs n_steps steps (each consumes the previous token, appends to the cache, picks the next token as the
+ *            first index of the row maximum of the logits) and writes the n_steps x batch picked tokens to
+ *            host_tokens. use_graph = false issues the launches one by one instead of replaying the captured step. */
+APPLEGPU_API uint64_t applegpu_gpt2_decoder_create(const uint64_t* weight_ids, uint32_t n_weights, uint32_t n_layer, uint32_t n_head, uint32_t n_embd,
+                                                  uint32_t vocab, uint32_t n_positions, uint32_t batch, uint32_t max_len);
+APPLEGPU_API int32_t applegpu_gpt2_decoder_prefill(uint64_t decoder, const uint64_t* kv_ids, uint32_t n_kv, uint64_t first_tokens_id, uint32_t prompt_len);
+APPLEGPU_API int32_t applegpu_gpt2_decoder_steps(uint64_t decoder, uint32_t n_steps, int32_t* host_tokens, bool use_graph);
+APPLEGPU_API int32_t applegpu_gpt2_decoder_launches_per_step(uint64_t decoder);
+APPLEGPU_API int32_t applegpu_gpt2_decoder_uses_graph(uint64_t decoder);
+APPLEGPU_API void applegpu_gpt2_decoder_destroy(uint64_t decoder);
+
 /* ── attention without device allocation ───────────────────────────────────────
  * No counterpart in the reference.
  *
