@@ -93,6 +93,7 @@ EXT_SYMBOLS = {
     "applegpu_ffi_tape_begin": (i32, [vp, u32]),
     "applegpu_ffi_tape_end": (u64, [vp, u32]),
     "applegpu_ffi_tape_abort": (None, []),
+    "applegpu_ffi_tape_replay_loop": (i32, [u64p, u32, u32, u32]),
     "applegpu_ffi_tape_replay": (i32, [u64, vp, u32, vp, u32]),
     "applegpu_ffi_from_host": (u64, [vp, u64p, u32, i8]),
     "applegpu_eager_upload": (i32, [u64, vp, u64]),

@@ -561,6 +561,25 @@ int32_t applegpu_ffi_tape_replay(uint64_t tape, const uint64_t* var_inputs, uint
   for (uint64_t v : vals) if (!kept.count(v)) st.rt.free_tensor(v);
   return (int32_t)t.ops.size();
 }
+int32_t applegpu_ffi_tape_replay_loop(const uint64_t* tapes, uint32_t n_tapes, uint32_t iters, uint32_t keep) {
+  // Replays single-output tapes without variable inputs round robin, evaluates every result, and keeps the last
+  // `keep` results alive (so the pool rotates output buffers too). One library call for the whole loop: the host
+  // cost per launch is a few hundred nanoseconds instead of a Python round trip, which is what a kernel of a few
+  // microseconds needs to be timed back to back.
+  if (!ffi_ready("tape_replay_loop")) return -1;
+  if (n_tapes == 0 || keep == 0 || keep > 64) { set_ffi_error("tape_replay_loop failed: need at least one tape and 1..64 kept results"); return -1; }
+  std::vector<uint64_t> ring(keep, 0);
+  int32_t rc = 0;
+  for (uint32_t i = 0; i < iters; i++) {
+    uint64_t out = 0;
+    if (applegpu_ffi_tape_replay(tapes[i % n_tapes], nullptr, 0, &out, 1) < 0 || applegpu_ffi_eval(out) != 0) { rc = -1; if (out) applegpu_ffi_free(out); break; }
+    uint64_t& slot = ring[i % keep];
+    if (slot) applegpu_ffi_free(slot);
+    slot = out;
+  }
+  for (uint64_t id : ring) if (id) applegpu_ffi_free(id);
+  return rc;
+}
 void* applegpu_ffi_device_ptr(uint64_t tensor_id) {
   if (!ffi_ready("device_ptr")) return nullptr;
   LazyState& st = lazy_state();

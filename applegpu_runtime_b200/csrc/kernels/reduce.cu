@@ -7,13 +7,18 @@
 // thread per row over three serial passes; here a warp owns a row, keeps it in registers after
 // a single 16-byte-vectorised read, reduces with shuffles, and writes once.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace ag { namespace k {
 
 // ── layer_norm ──────────────────────────────────────────────────────────────
-// Warp-per-row; ITERS packs per lane cover cols <= 32*ITERS*Pack::N.
+// Warp-per-row; ITERS packs per lane cover cols <= 32*ITERS*Pack::N. A persistent grid (a few CTAs per SM) walks the
+// rows, and a warp keeps TWO rows in flight: the 16-byte loads of its next row are issued before the reductions of
+// the current one, so loads, shuffles and stores of neighbouring rows overlap instead of every warp of the grid
+// reading at the same time and then writing at the same time. Rows stay in registers as raw packs (converted
+// where used), gamma / beta are fetched once per warp.
 template <typename T, int ITERS>
-__global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restrict__ in, const T* __restrict__ gamma, const T* __restrict__ beta,
+__global__ void __launch_bounds__(256) layer_norm_warp_kernel(const T* __restrict__ in, const T* __restrict__ gamma, const T* __restrict__ beta,
                                                                T* __restrict__ out, int64_t rows, int cols, float eps) {
   constexpr int N = Pack<T>::N;
   const int lane = threadIdx.x & 31;
@@ -22,8 +27,6 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
   const float inv_cols = 1.0f / (float)cols;
   pdl_wait();
   pdl_trigger();
-  // gamma / beta do not depend on the row: fetched once, together with the first row's loads, so their
-  // latency is not exposed after the reductions (kept in registers for rows of up to 4 packs per lane)
   constexpr bool kHoist = ITERS <= 4;
   Pack<T> gpk[kHoist ? ITERS : 1], bpk[kHoist ? ITERS : 1];
   if (kHoist) {
@@ -33,34 +36,38 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
       if (pk < packs) { gpk[it] = ld16(gamma + pk * N); bpk[it] = ld16(beta + pk * N); }
     }
   }
-  for (int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * warps_per_block) {
-    const T* x = in + row * cols;
-    float v[ITERS][N];
+  const int64_t stride = (int64_t)gridDim.x * warps_per_block;
+  int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  Pack<T> cur[ITERS], nxt[ITERS];
+  if (row < rows) {
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) { int pk = lane + it * 32; if (pk < packs) cur[it] = ld16_stream(in + row * cols + pk * N); }
+  }
+  for (; row < rows; row += stride) {
+    const int64_t next = row + stride;
+    if (next < rows) {
+#pragma unroll
+      for (int it = 0; it < ITERS; it++) { int pk = lane + it * 32; if (pk < packs) nxt[it] = ld16_stream(in + next * cols + pk * N); }
+    }
     float sum = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
-      int pk = lane + it * 32;
-      if (pk < packs) {
-        Pack<T> p = ld16_stream(x + pk * N);
+      if (lane + it * 32 < packs) {
 #pragma unroll
-        for (int e = 0; e < N; e++) { v[it][e] = Cvt<T>::to(p.v[e]); sum += v[it][e]; }
-      } else {
-#pragma unroll
-        for (int e = 0; e < N; e++) v[it][e] = 0.f;
+        for (int e = 0; e < N; e++) sum += Cvt<T>::to(cur[it].v[e]);
       }
     }
-    float mean = warp_sum(sum) * inv_cols;
+    const float mean = warp_sum(sum) * inv_cols;
     float sq = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
-      int pk = lane + it * 32;
-      if (pk < packs) {
+      if (lane + it * 32 < packs) {
 #pragma unroll
-        for (int e = 0; e < N; e++) { float d = v[it][e] - mean; sq += d * d; }
+        for (int e = 0; e < N; e++) { float d = Cvt<T>::to(cur[it].v[e]) - mean; sq += d * d; }
       }
     }
-    float var = warp_sum(sq) * inv_cols;
-    float inv_std = 1.0f / sqrtf(var + eps);
+    const float var = warp_sum(sq) * inv_cols;
+    const float inv_std = 1.0f / sqrtf(var + eps);
     T* y = out + row * cols;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
@@ -71,11 +78,13 @@ __global__ void __launch_bounds__(128) layer_norm_warp_kernel(const T* __restric
         Pack<T> o;
         float r[N];
 #pragma unroll
-        for (int e = 0; e < N; e++) r[e] = Cvt<T>::to(g.v[e]) * (v[it][e] - mean) * inv_std + Cvt<T>::to(b.v[e]);
+        for (int e = 0; e < N; e++) r[e] = Cvt<T>::to(g.v[e]) * (Cvt<T>::to(cur[it].v[e]) - mean) * inv_std + Cvt<T>::to(b.v[e]);
         pack_from_floats<T>(o, r);
         st16(y + pk * N, o);   // the next kernel (a GEMM) reads this from L2: no evict-first hint
       }
     }
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) cur[it] = nxt[it];
   }
 }
 
@@ -109,8 +118,12 @@ static Status layer_norm_t(cudaStream_t s, const TView& in, const TView& gamma, 
   bool vec = cols % N == 0 && aligned16(x) && aligned16(g) && aligned16(b) && aligned16(y);
   int64_t packs = cols / N;
   if (vec && packs <= 32 * 16) {
-    const int threads = 128, wpb = 4;
-    int grid = grid_for(rows, wpb, 16);
+    // persistent: up to four CTAs of eight warps per SM, every warp walks rows with two in flight
+    const int threads = 256, wpb = 8;
+    // CTAs per SM (APPLEGPU_LN_BPS overrides): measured best on [8192, 768] at 2 for 16-bit rows and 4 for float32
+    static const int bps_env = [] { const char* v = std::getenv("APPLEGPU_LN_BPS"); int n = v ? std::atoi(v) : 0; return n < 0 ? 0 : n > 8 ? 8 : n; }();
+    const int bps = bps_env ? bps_env : (sizeof(T) == 4 ? 4 : 2);
+    int grid = grid_for(rows, wpb, bps);
     int iters = (int)((packs + 31) / 32);
     cudaError_t le = cudaSuccess;
 #define AG_LN(I) le = launch_pdl(layer_norm_warp_kernel<T, I>, dim3(grid), dim3(threads), 0, s, x, g, b, y, rows, (int)cols, eps)

@@ -60,7 +60,7 @@ def _time(fns, iters, warmup=3, single=False):
         return float(np.median(times))
     # The timed loop replays each op from a tape (one library call instead of the Python-side recording), so that
     # the host keeps ahead of kernels of a few microseconds; ops that cannot be taped are issued as above.
-    issue = []
+    tapes = []
     for fn in fns:
         try:
             n = gpu.tape_begin([])
@@ -71,15 +71,25 @@ def _time(fns, iters, warmup=3, single=False):
                 gpu.tape_abort()
                 raise
             out.eval(); keep.append(out)
-            issue.append(lambda tape=tape: tape.replay([])[0])
+            tapes.append(tape)
         except Exception:
-            issue.append(fn)
-    for i in range(len(issue) + 2):
-        o = issue[i % len(issue)](); o.eval(); keep.append(o)
+            tapes = None
+            break
+    if tapes:
+        # the whole timed loop is one library call (applegpu_ffi_tape_replay_loop): the host cost per launch stays far
+        # below the run time of even the smallest kernel here
+        arr = (ctypes.c_uint64 * len(tapes))(*[t.handle for t in tapes])
+        if lib.applegpu_ffi_tape_replay_loop(arr, len(tapes), 2 * len(tapes) + 2, len(tapes)) != 0:
+            raise RuntimeError(lib.applegpu_ffi_last_error())
+        gpu.synchronize()
+        lib.applegpu_timer_start()
+        if lib.applegpu_ffi_tape_replay_loop(arr, len(tapes), iters, len(tapes)) != 0:
+            raise RuntimeError(lib.applegpu_ffi_last_error())
+        return float(lib.applegpu_timer_stop_ms()) / iters
     gpu.synchronize()
     lib.applegpu_timer_start()
     for i in range(iters):
-        o = issue[i % len(issue)](); o.eval(); keep.append(o)
+        o = fns[i % len(fns)](); o.eval(); keep.append(o)
     return float(lib.applegpu_timer_stop_ms()) / iters
 
 

@@ -186,6 +186,9 @@ APPLEGPU_API int32_t applegpu_ffi_tape_begin(const uint64_t* var_inputs, uint32_
 APPLEGPU_API uint64_t applegpu_ffi_tape_end(const uint64_t* outputs, uint32_t n_out);
 APPLEGPU_API void applegpu_ffi_tape_abort(void);
 APPLEGPU_API int32_t applegpu_ffi_tape_replay(uint64_t tape, const uint64_t* var_inputs, uint32_t n_var, uint64_t* out_ids, uint32_t n_out);
+/* Benchmark helper: replays single-output tapes that take no variable inputs round robin `iters` times in one call,
+ * evaluating each result and keeping the last `keep` (1..64) results alive. Returns 0, -1 on error. */
+APPLEGPU_API int32_t applegpu_ffi_tape_replay_loop(const uint64_t* tapes, uint32_t n_tapes, uint32_t iters, uint32_t keep);
 /* Compiled-graph executor: runs a serialized op list on the eager runtime in one call and returns the
  * number of outputs written (-1 on error, text in applegpu_eager_last_error). Replaces
  * applegpu_eager_execute_graph of the reference (crates/core/src/eager_ffi.rs:661-708; wire format and
