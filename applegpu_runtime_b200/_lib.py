@@ -144,6 +144,9 @@ EXT_SYMBOLS = {
     "applegpu_eager_dequantize": (vp, [u64, i8, f32, i32, u64p]),
     "applegpu_eager_attention": (vp, [u64, u64, u64, cbool, u64p]),
     "applegpu_eager_unary": (vp, [u64, cstr, u64p]),
+    "applegpu_eager_view_as": (vp, [u64, i8, u64p, u64p, u32, u64, u64p]),
+    "applegpu_eager_copy": (i32, [u64, u64]),
+    "applegpu_eager_fill": (i32, [u64, u64]),
     "applegpu_eager_linear": (vp, [u64, u64, u64, u64, i32, cbool, u64p]),
     "applegpu_ffi_init_dry": (cbool, []),
     "applegpu_ffi_plan": (i64, [u64, ctypes.c_char_p, u64]),
@@ -176,6 +179,7 @@ EXT_SYMBOLS = {
     "applegpu_flush_l2": (i32, []),
     "applegpu_profile_enable": (None, [cbool]),
     "applegpu_profile_clear": (None, []),
+    "applegpu_profile_filter": (None, [cstr]),
     "applegpu_profile_report": (i64, [ctypes.c_char_p, u64]),
     "applegpu_resolve_kernel": (cstr, [cstr, i8]),
     "applegpu_attention_noalloc": (i32, [vp, vp, vp, vp, i8, u64, u64, u64, u64, u64, cbool, vp]),

@@ -549,11 +549,14 @@ def resolve_kernel(base_name, dtype):
     return r.decode() if r else None
 
 
-def profile(enable=True):
-    """Turns per-kernel CUDA-event timing on or off (clears earlier records when turning on)."""
+def profile(enable=True, only=None):
+    """Turns per-kernel CUDA-event timing on or off (clears earlier records when turning on). `only`: a list of
+    kernel-name prefixes (e.g. ["fused_linear", "matmul"]); just those nodes are bracketed, the rest of the step runs
+    as it normally does."""
     lib = _L()
     if enable:
         lib.applegpu_profile_clear()
+    lib.applegpu_profile_filter(",".join(only).encode() if only else b"")
     lib.applegpu_profile_enable(bool(enable))
 
 

@@ -19,6 +19,7 @@ namespace ag {
 
 std::atomic<uint64_t> g_launch_count{0};
 uint64_t launch_count() { return g_launch_count.load(); }
+void note_launches(uint64_t n) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
 
 // Optional per-kernel timing: CUDA events bracket each launch on the runtime stream and are
 // resolved when the report is read. Off by default (events cost host time, not kernel time).
@@ -34,6 +35,26 @@ void clear() {
   std::lock_guard<std::mutex> g(g_mu);
   for (auto& s : g_spans) { g_free_events.push_back(s.a); g_free_events.push_back(s.b); }
   g_spans.clear();
+}
+// Only nodes whose kernel name starts with one of these prefixes get a span (empty: every node). Bracketing every
+// kernel of a forward makes the host the bottleneck and breaks every programmatic-launch overlap; bracketing one
+// kernel family keeps the rest of the step as it normally runs.
+static std::vector<std::string> g_filter;
+void set_filter(const std::string& csv) {
+  std::lock_guard<std::mutex> g(g_mu);
+  g_filter.clear();
+  size_t i = 0;
+  while (i < csv.size()) {
+    size_t j = csv.find(',', i);
+    if (j == std::string::npos) j = csv.size();
+    if (j > i) g_filter.push_back(csv.substr(i, j - i));
+    i = j + 1;
+  }
+}
+static bool wanted(const std::string& name) {
+  if (g_filter.empty()) return true;
+  for (const std::string& p : g_filter) if (name.compare(0, p.size(), p) == 0) return true;
+  return false;
 }
 static bool take_event(cudaEvent_t* e) {
   if (!g_free_events.empty()) { *e = g_free_events.back(); g_free_events.pop_back(); return true; }
@@ -355,6 +376,7 @@ Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in,
   if (!profile::enabled() || view_only) return execute_node_impl(node, in, out, out_buf);
   std::string name = node.op.kernel_name();
   if (node.op.op == Op::FusedElementwise) name = "fused_elementwise";
+  if (!profile::wanted(name)) return execute_node_impl(node, in, out, out_buf);
   profile::Scope scope(name + dtype_suffix(node.out_dtype), node_work(node, in));
   return execute_node_impl(node, in, out, out_buf);
 }

@@ -18,7 +18,8 @@ namespace ag {
 extern bool g_fused_attention;
 void set_f32_split(bool on);
 uint64_t launch_count();
-namespace profile { void enable(bool on); void clear(); std::string report(); }
+void note_launches(uint64_t n);
+namespace profile { void enable(bool on); void clear(); std::string report(); void set_filter(const std::string& csv); }
 struct Gpt2DecoderCfg { int n_layer, n_head, n_embd, vocab, n_positions, batch, max_len; };
 Status decoder_create(const std::vector<TensorRec>& weights, const Gpt2DecoderCfg& cfg, uint64_t* handle);
 Status decoder_prefill(uint64_t handle, const std::vector<TensorRec>& kvs, const TensorRec& first_tokens, int prompt_len);
@@ -791,6 +792,70 @@ uint8_t* applegpu_eager_create_view(uint64_t base, const uint64_t* shape, const 
   if (out_id) *out_id = id;
   return static_cast<uint8_t*>(p);
 }
+// ── what a frontend with device-resident buffers needs beside the reference's eager ABI ──
+uint8_t* applegpu_eager_view_as(uint64_t base, int8_t dtype, const uint64_t* shape, const uint64_t* strides, uint32_t ndim, uint64_t byte_offset, uint64_t* out_id) {
+  if (!eager_ready()) return nullptr;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  DType dt;
+  if (!dtype_from_wire(dtype, &dt)) { set_eager_error("view_as: unknown dtype code " + std::to_string((int)dtype)); return nullptr; }
+  const TensorRec* b = st.rt.tensor(base);
+  if (!b) { set_eager_error("tensor " + std::to_string(base) + " not found"); return nullptr; }
+  if (ndim > (uint32_t)kMaxDims) { set_eager_error("view_as: too many dimensions"); return nullptr; }
+  TensorRec v = *b;
+  v.dtype = dt; v.shape = to_dims(shape, ndim); v.strides = to_dims(strides, ndim);
+  v.byte_offset = b->byte_offset + (size_t)byte_offset;
+  // the furthest element the view can reach must lie inside the buffer
+  size_t reach = 0;
+  bool empty = false;
+  for (uint32_t i = 0; i < ndim; i++) { if (v.shape[i] == 0) empty = true; else reach += (size_t)(v.shape[i] - 1) * (size_t)v.strides[i]; }
+  if (!empty && b->buf && v.byte_offset + (reach + 1) * dtype_size(dt) > b->buf->capacity) { set_eager_error("view_as: the view reaches past the end of the buffer"); return nullptr; }
+  uint64_t id = st.rt.adopt(v);
+  if (out_id) *out_id = id;
+  return static_cast<uint8_t*>(v.data());
+}
+int32_t applegpu_eager_copy(uint64_t dst, uint64_t src) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec *d, *s0;
+  Status s = st.rt.get(dst, &d);
+  if (s.ok()) s = st.rt.get(src, &s0);
+  if (s.ok() && d->shape != s0->shape) s = Status::invalid("copy: shape mismatch " + dims_str(d->shape) + " vs " + dims_str(s0->shape));
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (s.ok() && ctx.dry) s = Status::compute("no CUDA device (dry-run mode)");
+  if (s.ok() && numel_of(d->shape) > 0) {
+    if (d->dtype == s0->dtype) s = k::copy_strided(ctx.stream, s0->view(), d->view());
+    else if (d->contiguous() && s0->contiguous()) s = k::cast(ctx.stream, s0->view(), d->view());
+    else s = Status::invalid("copy: a converting copy needs contiguous tensors");
+    if (s.ok()) note_launches(1);
+  }
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  return 0;
+}
+int32_t applegpu_eager_fill(uint64_t id, uint64_t bit_pattern) {
+  if (!eager_ready()) return -1;
+  EagerState& st = eager_state();
+  std::lock_guard<std::mutex> g(st.mu);
+  const TensorRec* t;
+  Status s = st.rt.get(id, &t);
+  DeviceCtx& ctx = DeviceCtx::get();
+  if (s.ok() && ctx.dry) s = Status::compute("no CUDA device (dry-run mode)");
+  if (s.ok() && numel_of(t->shape) > 0) {
+    if (t->contiguous()) { s = k::fill(ctx.stream, t->data(), (int)dtype_size(t->dtype), bit_pattern, numel_of(t->shape)); if (s.ok()) note_launches(1); }
+    else {
+      // a strided view: fill a one-element source and broadcast it through the strided copy
+      TensorRec one;
+      one.dtype = t->dtype; one.shape = t->shape; one.strides.assign(t->shape.size(), 0); one.has_meta = true;
+      s = Shared::get().pool.acquire(256, &one.buf);
+      if (s.ok()) s = k::fill(ctx.stream, one.data(), (int)dtype_size(t->dtype), bit_pattern, 1);
+      if (s.ok()) s = k::copy_strided(ctx.stream, one.view(), t->view());
+      if (s.ok()) note_launches(2);
+    }
+  }
+  if (!s.ok()) { set_eager_error(s.to_string()); return -1; }
+  return 0;
+}
 int32_t applegpu_eager_add_scaled_inplace(uint64_t self, uint64_t other, float alpha) {
   if (!eager_ready()) return -1;
   EagerState& st = eager_state();
@@ -1266,6 +1331,7 @@ int32_t applegpu_test_wait_runs_out(int32_t code, uint32_t limit_us) {
 }
 void applegpu_profile_enable(bool on) { ag::profile::enable(on); }
 void applegpu_profile_clear(void) { ag::profile::clear(); }
+void applegpu_profile_filter(const char* prefixes) { ag::profile::set_filter(prefixes ? prefixes : ""); }
 int64_t applegpu_profile_report(char* buf, uint64_t cap) {
   std::string out = ag::profile::report();
   if (buf && cap) { size_t n = out.size() < cap - 1 ? out.size() : (size_t)cap - 1; std::memcpy(buf, out.data(), n); buf[n] = 0; }

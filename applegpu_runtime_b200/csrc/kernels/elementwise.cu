@@ -699,4 +699,28 @@ Status flush_l2(cudaStream_t s, void* scratch, size_t bytes) {
   return Status::OK();
 }
 
+// ── fill ────────────────────────────────────────────────────────────────────
+// out[i] = pattern for a contiguous run of n elements of 1, 2, 4 or 8 bytes (the bit pattern of the value in the
+// tensor's own dtype, prepared by the caller): zero_ / fill_ of a frontend whose buffers live in device memory.
+template <typename E>
+__global__ void __launch_bounds__(256) fill_kernel(E* __restrict__ out, E value, int64_t n) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = value;
+}
+Status fill(cudaStream_t s, void* out, int elem_size, uint64_t pattern, int64_t n) {
+  if (n <= 0) return Status::OK();
+  int grid = grid_for(n, 256 * 4, 8);
+  cudaError_t e;
+  switch (elem_size) {
+    case 1: e = launch_pdl(fill_kernel<uint8_t>, dim3(grid), dim3(256), 0, s, (uint8_t*)out, (uint8_t)pattern, n); break;
+    case 2: e = launch_pdl(fill_kernel<uint16_t>, dim3(grid), dim3(256), 0, s, (uint16_t*)out, (uint16_t)pattern, n); break;
+    case 4: e = launch_pdl(fill_kernel<uint32_t>, dim3(grid), dim3(256), 0, s, (uint32_t*)out, (uint32_t)pattern, n); break;
+    case 8: e = launch_pdl(fill_kernel<unsigned long long>, dim3(grid), dim3(256), 0, s, (unsigned long long*)out, (unsigned long long)pattern, n); break;
+    default: return Status::invalid("fill: element size must be 1, 2, 4 or 8 bytes");
+  }
+  if (e != cudaSuccess) return cuda_status(e, "fill");
+  return Status::OK();
+}
+
 }}  // namespace ag::k

@@ -57,6 +57,8 @@ Status quantize_rows(cudaStream_t s, const TView& w, const TView& q, const TView
 Status cast(cudaStream_t s, const TView& in, const TView& out);
 // Strided gather-copy: dst (any strides) <- src (any strides), same shape and dtype size.
 Status copy_strided(cudaStream_t s, const TView& src, const TView& dst);
+// n contiguous elements of elem_size bytes set to the low bytes of `pattern`
+Status fill(cudaStream_t s, void* out, int elem_size, uint64_t pattern, int64_t n);
 // two strided copies in one launch (the halves of a concat)
 Status copy_strided_pair(cudaStream_t s, const TView& src_a, const TView& dst_a, const TView& src_b, const TView& dst_b);
 

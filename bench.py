@@ -386,15 +386,23 @@ def run_b200(args):
                  "seconds": (t_s1 - t_s0), "median_sm_mhz": sus_clocks["sm_mhz"], "reasons": sus_clocks["reasons"]}
 
     # ── roofline: per-kernel CUDA-event times inside the forward ──
+    # pass 1: every kernel bracketed (the per-kernel table; with an event pair around each of ~90 launches the host
+    # becomes the bottleneck, so these times are upper bounds). pass 2: only the GEMM family bracketed, the rest of the
+    # step runs as it normally does: that pass gives the GEMM launch durations of the roofline.
     gpu.profile(True)
     prof_steps = min(args.steps, 5)
     for i in range(prof_steps):
         step_resident(i)
     rep = gpu.profile_report()
     gpu.profile(False)
+    gpu.profile(True, only=["fused_linear", "matmul"])
+    for i in range(prof_steps):
+        step_resident(i)
+    rep_gemm = gpu.profile_report()
+    gpu.profile(False)
     status = gpu.pipeline_status()
     peaks = measured_peaks()
-    gemm = {k: v for k, v in rep.items() if k.startswith(("fused_linear", "matmul"))}
+    gemm = {k: v for k, v in rep_gemm.items() if k.startswith(("fused_linear", "matmul"))}
     g_ms = sum(v["ms"] for v in gemm.values())
     g_flops = sum(v["work"] for v in gemm.values())
     g_launch = sum(v["launches"] for v in gemm.values())
@@ -409,7 +417,8 @@ def run_b200(args):
                 "peak_sustained": peaks["bf16_tflops_sustained"],
                 "traffic": gemm_traffic_bytes(), "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the GEMM launches of one forward; null = not captured for this revision)",
                 "launches_per_step": g_launch / prof_steps, "avg_launch_ms": g_ms / max(g_launch, 1),
-                "share_of_step": g_ms / total_ms if total_ms else None,
+                "share_of_step": g_ms / prof_steps / (ms / args.steps),
+                "timing": "CUDA events around every GEMM launch of the forward, in situ (other kernels not bracketed); an event pair costs each launch its programmatic-launch overlap with its neighbours",
                 "per_kernel_ms_per_step": {k: round(v["ms"] / prof_steps, 4) for k, v in sorted(rep.items(), key=lambda kv: -kv[1]["ms"])}}
 
     line = {"metric": "gpt2_small_forward_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

@@ -111,6 +111,17 @@ APPLEGPU_API uint8_t* applegpu_eager_unary(uint64_t input_id, const char* op_nam
  * [N,K] when transpose_w. */
 APPLEGPU_API uint8_t* applegpu_eager_linear(uint64_t x_id, uint64_t w_id, uint64_t bias_id, uint64_t residual_id, int32_t act, bool transpose_w, uint64_t* out_id);
 
+/* What a frontend whose buffers live in DEVICE memory needs beside the reference's eager ABI (the reference's C++ shim
+ * memcpy's and memsets through the returned pointers, backend_cpp/applegpu_backend.cpp:267-342, :691-749; these three
+ * calls replace that):
+ *   view_as  a typed, strided view over the buffer of `base` (any dtype, byte offset from the base's first byte);
+ *            shares the buffer, is freed like any other id, fails if it would reach past the end of the buffer;
+ *   copy     dst <- src on the device, both possibly strided, same shape (same dtype, or contiguous with conversion);
+ *   fill     every element of the tensor (contiguous or a view) set to the low bytes of bit_pattern. */
+APPLEGPU_API uint8_t* applegpu_eager_view_as(uint64_t base_id, int8_t dtype, const uint64_t* shape, const uint64_t* strides, uint32_t ndim, uint64_t byte_offset, uint64_t* out_id);
+APPLEGPU_API int32_t applegpu_eager_copy(uint64_t dst_id, uint64_t src_id);
+APPLEGPU_API int32_t applegpu_eager_fill(uint64_t id, uint64_t bit_pattern);
+
 /* ── runtime services ──────────────────────────────────────────────────────── */
 /* Metadata-only mode for hosts without a GPU: ids, shapes, validation, the fusion pass and
  * applegpu_ffi_plan work; anything that would launch a kernel fails. Must be the first init call. */
@@ -211,6 +222,9 @@ APPLEGPU_API int32_t applegpu_flush_l2(void);
  * them. Returns the full length of the report. */
 APPLEGPU_API void applegpu_profile_enable(bool on);
 APPLEGPU_API void applegpu_profile_clear(void);
+/* Restricts the spans to nodes whose kernel name starts with one of the comma-separated prefixes ("" or NULL: all).
+ * Timing one kernel family leaves the rest of the step running as it normally does (no event between its kernels). */
+APPLEGPU_API void applegpu_profile_filter(const char* prefixes);
 APPLEGPU_API int64_t applegpu_profile_report(char* buf, uint64_t cap);
 /* Kernel name the registry resolves for (base name, dtype), e.g. ("matmul", 10) -> "matmul_bf16".
  * Reference: KernelRegistry::resolve_kernel, compute.rs:1478-1567. Returns NULL if unsupported. */
