@@ -192,6 +192,15 @@ class GpuTensor:
 
     # methods named like the reference's pyclass
     def matmul(self, o): return matmul(self, o)
+    def add(self, o): return add(self, o)
+    def sub(self, o): return sub(self, o)
+    def mul(self, o): return mul(self, o)
+    def div(self, o): return div(self, o)
+    def neg(self): return neg(self)
+    def abs(self): return abs(self)
+    def sign(self): return sign(self)
+    def sin(self): return sin(self)
+    def cos(self): return cos(self)
     def relu(self): return relu(self)
     def gelu(self): return gelu(self)
     def gelu_exact(self): return gelu_exact(self)

@@ -127,6 +127,18 @@ def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt):
     return {"op": name, "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
+def bench_w8_linear(rng, dtype, m, n, k, iters, opt):
+    """x [m,k] (16-bit) @ int8 weights [n,k] with per-output-channel scales: matmul_int8, the linear of the int8 models."""
+    e = gpu.dtype_size(dtype)
+    sets = []
+    for _ in range(_nsets(m * k * e + n * k + m * n * e, opt.rotate)):
+        q, scales = gpu.quantize_weight(_tensor(rng, (n, k), "float32", 0.02))
+        sets.append((_tensor(rng, (m, k), dtype), q, scales))
+    ms = _time([lambda x=x, q=q, sc=sc: gpu.matmul_int8(x, q, sc) for x, q, sc in sets], iters, single=opt.single)
+    flops = 2.0 * m * n * k
+    return {"op": "matmul_int8", "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
+
+
 def bench_lm_head(rng, dtype, m, vocab, k, iters, opt):
     a = _tensor(rng, (m, k), dtype)
     wte = _tensor(rng, (vocab, k), dtype, 0.02)
@@ -207,6 +219,8 @@ def main(argv=None):
             rows, d = shape or [131072, 768]
             for (n, k, act, res) in [(3 * d, d, False, False), (d, d, False, True), (4 * d, d, args.act or True, False), (d, 4 * d, False, True)]:
                 out.append(bench_fused_linear(rng, dt, rows, n, k, act, res, args.iters, args))
+        if args.op == "w8_linear" and dt != "float32":
+            out.append(bench_w8_linear(rng, dt, *(shape or [2048, 5120, 1280]), args.iters, args))
         if args.op == "lm_head":
             out.append(bench_lm_head(rng, dt, *(shape or [8192, 50257, 768]), args.iters, args))
         if args.op in ("all", "layer_norm"):

@@ -371,12 +371,13 @@ def run_b200(args):
     t_s0 = time.perf_counter()
     lib.applegpu_timer_start()
     n_sus = 0
+    chunk = 50 if args.sustained_seconds > 0 else max(args.steps, 1)
     while True:
-        for i in range(50):
+        for i in range(chunk):
             step_resident(n_sus + i)
-        n_sus += 50
+        n_sus += chunk
         gpu.synchronize()
-        if time.perf_counter() - t_s0 >= 2.0 or n_sus >= 5000:
+        if time.perf_counter() - t_s0 >= args.sustained_seconds or n_sus >= 5000:
             break
     ms_sus = float(lib.applegpu_timer_stop_ms())
     t_s1 = time.perf_counter()
@@ -589,6 +590,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="headline, e2e, sustained and roofline only (no per-op rows, fp32, decode, strong / tp legs)")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0, help="length of the sustained loop; 0 runs it for --steps steps only (launch lists under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
