@@ -166,6 +166,7 @@ EXT_SYMBOLS = {
     "applegpu_matmul_path": (cstr, [u64, u64, cbool]),
     "applegpu_set_matmul_path": (None, [i32]),
     "applegpu_set_gemm_tile": (None, [i32]),
+    "applegpu_set_sm_margin": (None, [i32]),
     "applegpu_set_f32_split": (None, [ctypes.c_bool]),
     "applegpu_set_host_visible": (i32, [i32]),
     "applegpu_host_visible": (i32, []),

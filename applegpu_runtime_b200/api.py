@@ -535,6 +535,11 @@ def matmul_path(a, b):
     return r.decode()
 
 
+def set_sm_margin(n=0):
+    """Keep `n` SMs out of the persistent kernels' grids (room for a collective on another stream); 0 uses every SM."""
+    _L().applegpu_set_sm_margin(int(n))
+
+
 def set_f32_split(on=True):
     """Large float32 matmuls as a three-term bf16 split on the tensor cores (default) or always on CUDA cores."""
     _L().applegpu_set_f32_split(bool(on))

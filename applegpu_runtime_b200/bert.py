@@ -142,7 +142,19 @@ def bert_forward(model, input_ids, token_type_ids=None, all_reduce=None, compile
 
 
 def _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce):
-    """Issues the ops of one encoder forward."""
+    """Issues the ops of one encoder forward (each all-reduce completes before the ops after it are issued)."""
+    steps = _forward_steps(w, cfg, tok, pos, typ, B, T, all_reduce, None)
+    while True:
+        try:
+            next(steps)
+        except StopIteration as done:
+            return done.value
+
+
+def _forward_steps(w, cfg, tok, pos, typ, B, T, reduce_start, reduce_finish):
+    """The encoder forward as a generator that yields once after starting each all-reduce, so a caller can issue
+    another micro-batch's ops while the collective runs. `reduce_start(t)` returns a handle (or the reduced tensor
+    when `reduce_finish` is None); `reduce_finish(handle)` returns the reduced tensor, ordered after the collective."""
     n_layer, d = cfg["n_layer"], cfg["n_embd"]
     heads = cfg.get("local_heads", cfg["n_head"])
     dh = d // cfg["n_head"]
@@ -152,6 +164,15 @@ def _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce):
     x = gpu.embedding(w["embeddings.word_embeddings.weight"], tok) + gpu.embedding(w["embeddings.position_embeddings.weight"], pos)
     x = x + gpu.embedding(w["embeddings.token_type_embeddings.weight"], typ)
     x = gpu.layer_norm(x, w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)
+
+    def reduced(t):
+        if reduce_start is None:
+            return t
+        handle = reduce_start(t)
+        if reduce_finish is None:
+            return handle
+        yield
+        return reduce_finish(handle)
 
     for i in range(n_layer):
         p = f"encoder.layer.{i}"
@@ -163,13 +184,55 @@ def _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce):
 
         attn = gpu.attention(split(0), split(1), split(2))
         attn = gpu.reshape(gpu.transpose_dims(attn, 1, 2), [rows, dl])
-        attn = _linear(attn, w, f"{p}.attention.output.dense")
-        if all_reduce is not None:
-            attn = all_reduce(attn)
+        attn = yield from reduced(_linear(attn, w, f"{p}.attention.output.dense"))
         x = gpu.layer_norm(x + attn, w[f"{p}.attention.output.LayerNorm.weight"], w[f"{p}.attention.output.LayerNorm.bias"], eps)
         h = gpu.gelu_exact(_linear(x, w, f"{p}.intermediate.dense"))
-        h = _linear(h, w, f"{p}.output.dense")
-        if all_reduce is not None:
-            h = all_reduce(h)
+        h = yield from reduced(_linear(h, w, f"{p}.output.dense"))
         x = gpu.layer_norm(x + h, w[f"{p}.output.LayerNorm.weight"], w[f"{p}.output.LayerNorm.bias"], eps)
     return gpu.reshape(x, [B, T, d])
+
+
+def interleave(generators):
+    """Round-robin over generators until all are exhausted; returns their return values in order."""
+    results = [None] * len(generators)
+    live = list(enumerate(generators))
+    while live:
+        still = []
+        for idx, g in live:
+            try:
+                next(g)
+                still.append((idx, g))
+            except StopIteration as done:
+                results[idx] = done.value
+        live = still
+    return results
+
+
+def bert_forward_overlapped(model, input_ids, tp, micro_batches=4):
+    """Tensor-parallel forward with the all-reduces overlapped with compute: the batch is cut into `micro_batches`
+    groups of sequences whose forwards are issued in lock step, one segment (the ops between two all-reduces) at a
+    time. While one group's partial sums are being added over the ranks on the communication stream, the runtime
+    stream runs the next group's segment; a group's next segment is ordered after its own collective by an event.
+    Nothing in the encoder mixes sequences, so the result equals the unsplit forward. Returns the list of per-group
+    last hidden states [b_i, T, d] in batch order."""
+    w = model["weights"]
+    cfg = model["config"]
+    ids = np.asarray(input_ids, dtype=np.int64)
+    B, T = ids.shape
+    n = max(1, min(int(micro_batches), B))
+    bounds = [B * i // n for i in range(n + 1)]
+    gens = []
+    for lo, hi in zip(bounds[:-1], bounds[1:]):
+        b = hi - lo
+        tok = gpu.from_numpy(np.ascontiguousarray(ids[lo:hi].reshape(-1), dtype=np.int32))
+        pos = gpu.from_numpy(np.tile(np.arange(T, dtype=np.int32), b))
+        typ = gpu.from_numpy(np.zeros(b * T, dtype=np.int32))
+        gens.append(_forward_steps(w, cfg, tok, pos, typ, b, T, tp.all_reduce_start, tp.all_reduce_finish))
+    overlapping = tp.group.world > 1 and tp.sm_margin > 0
+    if overlapping:
+        gpu.set_sm_margin(tp.sm_margin)   # the collective's CTAs need SMs the persistent compute kernels do not hold
+    try:
+        return interleave(gens)
+    finally:
+        if overlapping:
+            gpu.set_sm_margin(0)

@@ -1189,6 +1189,7 @@ int32_t applegpu_set_host_visible(int32_t on) {
 int32_t applegpu_host_visible(void) { return DeviceCtx::get().host_visible ? 1 : 0; }
 void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
 void applegpu_set_gemm_tile(int32_t code) { k::set_gemm_tile(code); }
+void applegpu_set_sm_margin(int32_t n) { k::set_sm_margin(n); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return 0;

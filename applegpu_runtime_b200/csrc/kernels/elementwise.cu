@@ -14,6 +14,7 @@
 namespace ag { namespace k {
 
 static int g_sm_count = 0;
+static int g_sm_margin = 0;   // SMs left free for kernels of other streams (a collective running beside the compute)
 int sm_count() {
   if (g_sm_count == 0) {
     int dev = 0, n = 0;
@@ -21,8 +22,13 @@ int sm_count() {
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) g_sm_count = n;
     else g_sm_count = 148;
   }
-  return g_sm_count;
+  const int usable = g_sm_count - g_sm_margin;
+  return usable < 8 ? 8 : usable;
 }
+// Persistent kernels size their grids from sm_count(): a margin keeps that many SMs out of them, so the CTAs of a
+// collective on another stream find room at once instead of waiting for a persistent kernel to end (and a persistent
+// kernel is not left with fewer SMs than the CTAs it launched).
+void set_sm_margin(int n) { g_sm_margin = n < 0 ? 0 : n; }
 
 static int g_pdl_override = -1;
 void set_pdl_override(int on) { g_pdl_override = on; }

@@ -162,6 +162,7 @@ Status decode_finish(cudaStream_t s, const int32_t* tok, int32_t* history, int32
 Status decode_reset(cudaStream_t s, int* counters, int32_t* pos_ids, int batch, int len);
 // Programmatic dependent launch can be switched off for a region of host code (stream capture of a decode step).
 void set_pdl_override(int on);   // -1 follow the environment, 0 off, 1 on
+void set_sm_margin(int n);       // SMs kept out of the persistent kernels' grids
 
 // Writes more than the L2 capacity so the next timed kernel starts cold.
 Status flush_l2(cudaStream_t s, void* scratch, size_t bytes);

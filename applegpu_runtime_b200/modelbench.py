@@ -131,8 +131,9 @@ def _bert_host_state(cfg, seed=0, std=0.02):
 
 def bench_bert_base_tp(dtype, batch, seq, iters):
     """BERT-base with heads and feed-forward units sharded over the launcher's ranks (torchrun, one rank per
-    GPU): 2 NCCL all-reduces of [batch*seq, 768] per layer on the runtime stream. Rank 0 prints the line;
-    the time is the MAX over ranks of the CUDA-event time."""
+    GPU): 2 NCCL all-reduces of [batch*seq, 768] per layer, timed both serialised on the runtime stream and overlapped
+    with the next micro-batch's compute (bert_forward_overlapped). Rank 0 prints the line; times are the MAX over ranks
+    of the CUDA-event time."""
     from .sharding import RankGroup
     from .tp import TensorParallelGroup, load_bert_shard
     group = RankGroup.from_env()
@@ -140,14 +141,24 @@ def bench_bert_base_tp(dtype, batch, seq, iters):
     model = load_bert_shard(_bert_host_state(BERT_BASE), BERT_BASE, group, dtype=dtype)
     ids = np.random.default_rng(3).integers(0, BERT_BASE["vocab_size"], (batch, seq))
 
-    def step():
+    from .bert import bert_forward_overlapped
+    micro = 4
+
+    def step_serial():
         bert_forward(model, ids, all_reduce=tp.all_reduce).eval()
 
+    def step_overlapped():
+        for out in bert_forward_overlapped(model, ids, tp, micro_batches=micro):
+            out.eval()
+
     group.barrier()
-    ms = group.max(_time(step, iters, 2))
+    ms_serial = group.max(_time(step_serial, iters, 2))
+    group.barrier()
+    ms = group.max(_time(step_overlapped, iters, 2))
     group.barrier()
     payload = batch * seq * BERT_BASE["n_embd"] * gpu.dtype_size(dtype)
-    r = {"config": "bert_base_tp", "dtype": dtype, "batch": batch, "seq": seq, "ranks": group.world, "ms": ms,
+    r = {"config": "bert_base_tp", "dtype": dtype, "batch": batch, "seq": seq, "ranks": group.world, "ms": ms, "micro_batches": micro,
+         "ms_all_reduce_on_runtime_stream": ms_serial,
          "tokens_per_s": batch * seq / ms * 1e3, "all_reduce_bytes": payload, "all_reduces_per_forward": 2 * BERT_BASE["n_layer"]}
     rank = group.rank
     group.close()

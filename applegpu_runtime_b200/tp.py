@@ -10,8 +10,13 @@ layer produce partial sums that are added over the group in place (NCCL all-redu
 own stream: the collective is ordered between the producing GEMM and the consuming layer_norm by
 stream order, no host synchronisation); residual and layer_norm are computed redundantly by every
 rank. Payload per all-reduce: B*T*d elements, 2 per layer.
+
+`bert.bert_forward_overlapped` hides those collectives: the batch is cut into micro-batches whose forwards advance
+in lock step, and each all-reduce runs on a communication stream (all_reduce_start / all_reduce_finish, ordered by
+events) while the runtime stream computes the next micro-batch's segment.
 """
 import ctypes
+import os
 
 import numpy as np
 
@@ -39,9 +44,25 @@ def head_and_ff_ranges(config, rank, world):
 class TensorParallelGroup:
     """all_reduce(t) sums a materialised, contiguous GpuTensor over the ranks of a RankGroup, in place."""
 
-    def __init__(self, group):
+    def __init__(self, group, sm_margin=None):
         self.group = group
         self._stream = None
+        self._comm = None
+        self._pg = None
+        # SMs the compute kernels leave to the collective while the two overlap (all_reduce_start / _finish)
+        self.sm_margin = int(os.environ.get("APPLEGPU_TP_SM_MARGIN", "16")) if sm_margin is None else int(sm_margin)
+
+    def _process_group(self):
+        """A group of its own for the data collectives, with NCCL's stream at high priority: its kernels then take
+        the SMs that fall free between compute kernels instead of queueing behind them."""
+        dist = self.group.dist
+        if self._pg is None:
+            try:
+                opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+                self._pg = dist.new_group(ranks=list(range(self.group.world)), pg_options=opts)
+            except Exception:
+                self._pg = dist.group.WORLD
+        return self._pg
 
     def _torch_stream(self):
         import torch
@@ -50,9 +71,14 @@ class TensorParallelGroup:
             self._stream = torch.cuda.ExternalStream(int(handle or 0))
         return self._stream
 
-    def all_reduce(self, t):
-        if self.group.world == 1 or self.group.dist is None:
-            return t
+    def _comm_stream(self):
+        import torch
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(priority=-1)
+        return self._comm
+
+    def _view(self, t):
+        """The tensor's device memory as a flat torch tensor (evaluates `t`: its kernels are enqueued on the runtime stream)."""
         import torch
         lib = _lib.load()
         ptr = lib.applegpu_ffi_device_ptr(ctypes.c_uint64(t.id))
@@ -62,8 +88,40 @@ class TensorParallelGroup:
         view = torch.as_tensor(_DevMem(ptr, [int(np.prod(t.shape))], _TYPESTR[dt]), device="cuda")
         if dt == "bfloat16":
             view = view.view(torch.bfloat16)   # the interface has no bfloat16 code: same bits, reinterpreted
+        return view
+
+    def all_reduce(self, t):
+        if self.group.world == 1 or self.group.dist is None:
+            return t
+        import torch
+        view = self._view(t)
         with torch.cuda.stream(self._torch_stream()):
-            self.group.dist.all_reduce(view)
+            self.group.dist.all_reduce(view, group=self._process_group())
+        return t
+
+    def all_reduce_start(self, t):
+        """Starts the in-place sum of `t` over the ranks on the communication stream, ordered after the kernels that
+        produce `t`; the runtime stream is not held up. Returns a handle for all_reduce_finish."""
+        if self.group.world == 1 or self.group.dist is None:
+            t.eval()
+            return (t, None, None)
+        import torch
+        view = self._view(t)
+        produced = torch.cuda.Event()
+        produced.record(self._torch_stream())
+        comm = self._comm_stream()
+        comm.wait_event(produced)
+        with torch.cuda.stream(comm):
+            self.group.dist.all_reduce(view, group=self._process_group())
+        done = torch.cuda.Event()
+        done.record(comm)
+        return (t, done, view)
+
+    def all_reduce_finish(self, handle):
+        """Orders the runtime stream after the collective started by all_reduce_start and returns the summed tensor."""
+        t, done, _view = handle
+        if done is not None:
+            self._torch_stream().wait_event(done)
         return t
 
 

@@ -156,6 +156,9 @@ APPLEGPU_API void applegpu_set_matmul_path(int32_t mode);
 /* Tuning override of the tensor-core kernel's tile shape: 0 = chosen per problem by the cost model (default);
  * 1256 / 1128 = CTA-pair tiles of 256 x 256 / 256 x 128; 256 / 192 / 128 = single-CTA tiles of 128 x that width. */
 APPLEGPU_API void applegpu_set_gemm_tile(int32_t code);
+/* Keeps `n` SMs out of the grids of the persistent kernels (GEMM, attention, row kernels), for a collective that runs
+ * on another stream beside them. 0 (default) uses every SM. */
+APPLEGPU_API void applegpu_set_sm_margin(int32_t n);
 /* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
  * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
 APPLEGPU_API void applegpu_set_f32_split(bool on);

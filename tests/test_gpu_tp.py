@@ -31,7 +31,7 @@ def _state(seed):
 
 def _worker(rank, world, port, out_dir):
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank), "MASTER_ADDR": "127.0.0.1",
-                       "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+                       "MASTER_PORT": str(port)})
     import applegpu_runtime_b200 as gpu
     from applegpu_runtime_b200.sharding import RankGroup
     from applegpu_runtime_b200.tp import TensorParallelGroup, load_bert_shard
@@ -43,6 +43,10 @@ def _worker(rank, world, port, out_dir):
     for dtype, tol in (("float32", 2e-4), ("bfloat16", 2e-2)):
         shard = load_bert_shard(state, CFG, group, dtype=dtype)
         got = gpu.bert_forward(shard, ids, all_reduce=tp.all_reduce).to_numpy()
+        # the same forward as micro-batches in lock step with the collectives on the communication stream
+        from applegpu_runtime_b200.bert import bert_forward_overlapped
+        lapped = np.concatenate([o.to_numpy() for o in bert_forward_overlapped(shard, ids, tp, micro_batches=2)], axis=0)
+        assert lapped.shape == got.shape and float(np.max(np.abs(lapped - got))) <= (1e-5 if dtype == "float32" else 2e-2) * float(np.max(np.abs(got)))
         if rank == 0:
             full = gpu.bert_forward(gpu.load_bert_state_dict(state, CFG, dtype="float32"), ids).to_numpy()
             err = float(np.max(np.abs(got - full)) / np.max(np.abs(full)))

@@ -347,3 +347,19 @@ def test_lm_head_argmax_fuses_only_after_the_logits_handle_is_dropped(gpu):
     n32 = gpu.argmax(l32)
     del l32
     assert not any(l.startswith("fused_linear[argmax") for l in n32.plan().splitlines())
+
+
+def test_interleave_advances_generators_in_lock_step():
+    """bert.interleave drives the micro-batch forwards of the overlapped tensor-parallel path: one segment of each in
+    turn, return values in order, exhausted generators dropped."""
+    from applegpu_runtime_b200.bert import interleave
+    log = []
+
+    def steps(tag, n):
+        for i in range(n):
+            log.append((tag, i))
+            yield
+        return tag.upper()
+
+    assert interleave([steps("a", 2), steps("b", 3), steps("c", 0)]) == ["A", "B", "C"]
+    assert log == [("a", 0), ("b", 0), ("a", 1), ("b", 1), ("b", 2)]
