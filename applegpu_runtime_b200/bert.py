@@ -151,19 +151,47 @@ def _record_forward(w, cfg, tok, pos, typ, B, T, all_reduce):
             return done.value
 
 
-def _forward_steps(w, cfg, tok, pos, typ, B, T, reduce_start, reduce_finish):
+def _attention_block(w, cfg, p, x, B, T):
+    """QKV projection, attention and the (row-parallel) output projection of layer `p` on x [rows, d]."""
+    heads = cfg.get("local_heads", cfg["n_head"])
+    dh = cfg["n_embd"] // cfg["n_head"]
+    dl = heads * dh
+    qkv = _linear(x, w, f"{p}.qkv")                                    # [rows, 3*dl]
+
+    def split(j):
+        t = gpu.slice(qkv, dim=1, start=j * dl, end=(j + 1) * dl)
+        return gpu.transpose_dims(gpu.reshape(t, [B, T, heads, dh]), 1, 2)   # [B, heads, T, dh]
+
+    attn = gpu.attention(split(0), split(1), split(2))
+    attn = gpu.reshape(gpu.transpose_dims(attn, 1, 2), [B * T, dl])
+    return _linear(attn, w, f"{p}.attention.output.dense")
+
+
+def _forward_steps(w, cfg, tok, pos, typ, B, T, reduce_start, reduce_finish, tapes=None):
     """The encoder forward as a generator that yields once after starting each all-reduce, so a caller can issue
     another micro-batch's ops while the collective runs. `reduce_start(t)` returns a handle (or the reduced tensor
-    when `reduce_finish` is None); `reduce_finish(handle)` returns the reduced tensor, ordered after the collective."""
+    when `reduce_finish` is None); `reduce_finish(handle)` returns the reduced tensor, ordered after the collective.
+    The forward is cut at the all-reduces into 2 * n_layer + 1 segments; with `tapes` (a dict) every segment is
+    recorded on an op tape the first time it runs for this [B, T] and replayed afterwards: one library call per
+    segment instead of ~20 from Python, which is what lets the host keep ahead of a GPU that has only a slice of
+    the model to compute."""
     n_layer, d = cfg["n_layer"], cfg["n_embd"]
-    heads = cfg.get("local_heads", cfg["n_head"])
-    dh = d // cfg["n_head"]
-    dl = heads * dh
     eps = float(cfg.get("eps", 1e-12))
-    rows = B * T
-    x = gpu.embedding(w["embeddings.word_embeddings.weight"], tok) + gpu.embedding(w["embeddings.position_embeddings.weight"], pos)
-    x = x + gpu.embedding(w["embeddings.token_type_embeddings.weight"], typ)
-    x = gpu.layer_norm(x, w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)
+
+    def run(key, inputs, fn):
+        if tapes is None:
+            return fn(*inputs)
+        tape = tapes.get((key, B, T))
+        if tape is not None:
+            return tape.replay(list(inputs))
+        n = gpu.tape_begin(list(inputs))
+        try:
+            outs = fn(*inputs)
+        except Exception:
+            gpu.tape_abort()
+            raise
+        tapes[(key, B, T)] = gpu.tape_end(n, list(outs))
+        return outs
 
     def reduced(t):
         if reduce_start is None:
@@ -174,22 +202,40 @@ def _forward_steps(w, cfg, tok, pos, typ, B, T, reduce_start, reduce_finish):
         yield
         return reduce_finish(handle)
 
-    for i in range(n_layer):
+    def first(tok, pos, typ):
+        x = gpu.embedding(w["embeddings.word_embeddings.weight"], tok) + gpu.embedding(w["embeddings.position_embeddings.weight"], pos)
+        x = x + gpu.embedding(w["embeddings.token_type_embeddings.weight"], typ)
+        x = gpu.layer_norm(x, w["embeddings.LayerNorm.weight"], w["embeddings.LayerNorm.bias"], eps)
+        return [x, _attention_block(w, cfg, "encoder.layer.0", x, B, T)]
+
+    def mlp(i):
         p = f"encoder.layer.{i}"
-        qkv = _linear(x, w, f"{p}.qkv")                                    # [rows, 3*dl]
 
-        def split(j):
-            t = gpu.slice(qkv, dim=1, start=j * dl, end=(j + 1) * dl)
-            return gpu.transpose_dims(gpu.reshape(t, [B, T, heads, dh]), 1, 2)   # [B, heads, T, dh]
+        def fn(x, attn):
+            x = gpu.layer_norm(x + attn, w[f"{p}.attention.output.LayerNorm.weight"], w[f"{p}.attention.output.LayerNorm.bias"], eps)
+            h = gpu.gelu_exact(_linear(x, w, f"{p}.intermediate.dense"))
+            return [x, _linear(h, w, f"{p}.output.dense")]
+        return fn
 
-        attn = gpu.attention(split(0), split(1), split(2))
-        attn = gpu.reshape(gpu.transpose_dims(attn, 1, 2), [rows, dl])
-        attn = yield from reduced(_linear(attn, w, f"{p}.attention.output.dense"))
-        x = gpu.layer_norm(x + attn, w[f"{p}.attention.output.LayerNorm.weight"], w[f"{p}.attention.output.LayerNorm.bias"], eps)
-        h = gpu.gelu_exact(_linear(x, w, f"{p}.intermediate.dense"))
-        h = yield from reduced(_linear(h, w, f"{p}.output.dense"))
-        x = gpu.layer_norm(x + h, w[f"{p}.output.LayerNorm.weight"], w[f"{p}.output.LayerNorm.bias"], eps)
-    return gpu.reshape(x, [B, T, d])
+    def close_layer(i):
+        p = f"encoder.layer.{i}"
+
+        def fn(x, h):
+            x = gpu.layer_norm(x + h, w[f"{p}.output.LayerNorm.weight"], w[f"{p}.output.LayerNorm.bias"], eps)
+            if i + 1 == n_layer:
+                return [gpu.reshape(x, [B, T, d])]
+            return [x, _attention_block(w, cfg, f"encoder.layer.{i + 1}", x, B, T)]
+        return fn
+
+    x, part = run("first", (tok, pos, typ), first)
+    for i in range(n_layer):
+        attn = yield from reduced(part)
+        x, part = run(("mlp", i), (x, attn), mlp(i))
+        h = yield from reduced(part)
+        outs = run(("close", i), (x, h), close_layer(i))
+        if i + 1 == n_layer:
+            return outs[0]
+        x, part = outs
 
 
 def interleave(generators):
@@ -208,17 +254,19 @@ def interleave(generators):
     return results
 
 
-def bert_forward_overlapped(model, input_ids, tp, micro_batches=4):
+def bert_forward_overlapped(model, input_ids, tp, micro_batches=2, taped=True):
     """Tensor-parallel forward with the all-reduces overlapped with compute: the batch is cut into `micro_batches`
     groups of sequences whose forwards are issued in lock step, one segment (the ops between two all-reduces) at a
     time. While one group's partial sums are being added over the ranks on the communication stream, the runtime
     stream runs the next group's segment; a group's next segment is ordered after its own collective by an event.
-    Nothing in the encoder mixes sequences, so the result equals the unsplit forward. Returns the list of per-group
-    last hidden states [b_i, T, d] in batch order."""
+    Nothing in the encoder mixes sequences, so the result equals the unsplit forward. With `taped` the segments
+    between all-reduces are recorded once per micro-batch shape and replayed. Returns the list of per-group last
+    hidden states [b_i, T, d] in batch order."""
     w = model["weights"]
     cfg = model["config"]
     ids = np.asarray(input_ids, dtype=np.int64)
     B, T = ids.shape
+    tapes = model.setdefault("_segment_tapes", {}) if taped else None
     n = max(1, min(int(micro_batches), B))
     bounds = [B * i // n for i in range(n + 1)]
     gens = []
@@ -227,7 +275,7 @@ def bert_forward_overlapped(model, input_ids, tp, micro_batches=4):
         tok = gpu.from_numpy(np.ascontiguousarray(ids[lo:hi].reshape(-1), dtype=np.int32))
         pos = gpu.from_numpy(np.tile(np.arange(T, dtype=np.int32), b))
         typ = gpu.from_numpy(np.zeros(b * T, dtype=np.int32))
-        gens.append(_forward_steps(w, cfg, tok, pos, typ, b, T, tp.all_reduce_start, tp.all_reduce_finish))
+        gens.append(_forward_steps(w, cfg, tok, pos, typ, b, T, tp.all_reduce_start, tp.all_reduce_finish, tapes=tapes))
     overlapping = tp.group.world > 1 and tp.sm_margin > 0
     if overlapping:
         gpu.set_sm_margin(tp.sm_margin)   # the collective's CTAs need SMs the persistent compute kernels do not hold

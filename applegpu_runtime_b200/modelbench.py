@@ -142,7 +142,7 @@ def bench_bert_base_tp(dtype, batch, seq, iters):
     ids = np.random.default_rng(3).integers(0, BERT_BASE["vocab_size"], (batch, seq))
 
     from .bert import bert_forward_overlapped
-    micro = 4
+    micro = 2
 
     def step_serial():
         bert_forward(model, ids, all_reduce=tp.all_reduce).eval()

@@ -49,6 +49,7 @@ class TensorParallelGroup:
         self._stream = None
         self._comm = None
         self._pg = None
+        self._views = {}
         # SMs the compute kernels leave to the collective while the two overlap (all_reduce_start / _finish)
         self.sm_margin = int(os.environ.get("APPLEGPU_TP_SM_MARGIN", "16")) if sm_margin is None else int(sm_margin)
 
@@ -85,9 +86,16 @@ class TensorParallelGroup:
         if not ptr:
             raise ValueError(lib.applegpu_ffi_last_error().decode())
         dt = t.dtype
-        view = torch.as_tensor(_DevMem(ptr, [int(np.prod(t.shape))], _TYPESTR[dt]), device="cuda")
-        if dt == "bfloat16":
-            view = view.view(torch.bfloat16)   # the interface has no bfloat16 code: same bits, reinterpreted
+        key = (int(ptr), int(np.prod(t.shape)), dt)
+        view = self._views.get(key)
+        if view is None:
+            # pool buffers recur from step to step: the wrapper (it owns nothing) is built once per address and size
+            view = torch.as_tensor(_DevMem(ptr, [key[1]], _TYPESTR[dt]), device="cuda")
+            if dt == "bfloat16":
+                view = view.view(torch.bfloat16)   # the interface has no bfloat16 code: same bits, reinterpreted
+            if len(self._views) >= 512:
+                self._views.clear()
+            self._views[key] = view
         return view
 
     def all_reduce(self, t):

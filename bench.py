@@ -549,8 +549,8 @@ def strong_scaling_leg(gpu, lib, group, model, cfg):
 def tensor_parallel_leg(gpu, lib, group):
     """BERT-base 256 x 512 bf16 with heads and feed-forward units sharded over the ranks (NCCL all-reduce over NVLink,
     two per layer, overlapped with the next micro-batch's compute): ms per forward (MAX over ranks), the same with the
-    collectives serialised on the runtime stream, and, on a small batch, the relative error of rank 0's sharded forward
-    against its own unsharded forward."""
+    collectives serialised on the runtime stream, and, on a small batch, the relative error of the sharded bf16 forward
+    against the unsharded float32 forward on the same GPU (bar: 2e-2, as for every bf16 path)."""
     try:
         from applegpu_runtime_b200 import modelbench as mbm
         from applegpu_runtime_b200.bert import BERT_BASE, bert_forward, bert_forward_overlapped, load_bert_state_dict
@@ -561,7 +561,7 @@ def tensor_parallel_leg(gpu, lib, group):
         rng = np.random.default_rng(3)
         small = rng.integers(0, BERT_BASE["vocab_size"], (4, 512))
         got = np.concatenate([o.to_numpy() for o in bert_forward_overlapped(shard, small, tp, micro_batches=2)], axis=0)
-        full = load_bert_state_dict(state, BERT_BASE, dtype="bfloat16")
+        full = load_bert_state_dict(state, BERT_BASE, dtype="float32")   # the unsharded forward in float32 is the reference
         want = bert_forward(full, small).to_numpy()
         del full
         err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
@@ -581,12 +581,12 @@ def tensor_parallel_leg(gpu, lib, group):
             bert_forward(shard, ids, all_reduce=tp.all_reduce).eval()
 
         def step_overlapped():
-            for out in bert_forward_overlapped(shard, ids, tp, micro_batches=4):
+            for out in bert_forward_overlapped(shard, ids, tp, micro_batches=2):
                 out.eval()
         ms_serial = timed(step_serial)
         ms = timed(step_overlapped)
         return {"workload": "bert-base encoder, batch 256 x seq 512, bf16, head / feed-forward split", "ranks": group.world, "ms_per_forward": ms,
-                "ms_per_forward_all_reduce_on_runtime_stream": ms_serial, "micro_batches": 4,
+                "ms_per_forward_all_reduce_on_runtime_stream": ms_serial, "micro_batches": 2,
                 "tokens_per_s": 256 * 512 / (ms / 1e3), "max_rel_err_vs_unsharded": group.max(err), "all_reduces_per_forward": 24,
                 "overlap": "each all-reduce runs on a communication stream while the runtime stream computes the next micro-batch's segment"}
     except Exception as e:   # the headline line must still be printed

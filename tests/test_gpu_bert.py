@@ -120,3 +120,32 @@ def test_bert_head_and_ff_shards_sum_to_the_full_layer(gpu_dev):
         return gpu.reshape(x, [Bsz, T, d]).to_numpy()
 
     np.testing.assert_allclose(forward_lockstep(), full, atol=2e-4)
+
+
+def test_segment_taped_micro_batched_forward_equals_the_plain_forward(gpu_dev):
+    """bert_forward_overlapped (the tensor-parallel driver: micro-batches in lock step, segments between all-reduces
+    recorded on tapes and replayed) on a single rank, where the collective is the identity. The plain forward adds
+    the residual in the projection's epilogue (one rounding); here the projection is rounded to bf16 first because the
+    all-reduce sits between the two, so the results agree to bf16 rounding, not bit for bit; the replayed passes must
+    reproduce the recording pass's arithmetic exactly."""
+    from applegpu_runtime_b200.bert import bert_forward_overlapped
+    from applegpu_runtime_b200.sharding import RankGroup
+    from applegpu_runtime_b200.tp import TensorParallelGroup
+    import torch  # noqa: F401
+    from oracle import torch_ref
+    cfg = dict(n_layer=3, n_head=4, n_embd=256, d_ff=1024, vocab_size=1003, n_positions=128, type_vocab=2, eps=1e-12)
+    state = {k: v.numpy() for k, v in torch_ref.init_bert_weights(cfg, seed=5).items()}
+    model = gpu_dev.load_bert_state_dict(state, cfg, dtype="bfloat16")
+    tp = TensorParallelGroup(RankGroup())
+    rng = np.random.default_rng(5)
+    for trial in range(3):                      # trial 0 records the tapes, 1 and 2 replay them on other ids
+        ids = rng.integers(0, cfg["vocab_size"], (6, 64))
+        want = gpu_dev.bert_forward(model, ids).to_numpy()
+        parts = bert_forward_overlapped(model, ids, tp, micro_batches=3)
+        got = np.concatenate([p.to_numpy() for p in parts], axis=0)
+        assert got.shape == want.shape
+        assert float(np.max(np.abs(got - want))) <= 1e-2 * float(np.max(np.abs(want))), (trial, float(np.max(np.abs(got - want))))
+        again = np.concatenate([p.to_numpy() for p in bert_forward_overlapped(model, ids, tp, micro_batches=3)], axis=0)
+        assert np.array_equal(again, got), trial
+    assert len(model["_segment_tapes"]) == 2 * cfg["n_layer"] + 1
+    assert gpu_dev.pipeline_status() == 0
