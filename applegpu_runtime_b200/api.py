@@ -435,6 +435,24 @@ def matmul_int8(x, q, scales):
     return _wrap(_L().applegpu_ffi_matmul_int8(x.id, q.id, scales.id), x)
 
 
+_ACT_CODES = {None: 0, "none": 0, "gelu": 1, "gelu_exact": 2, "relu": 3}
+
+
+def linear_fused(x, w, bias=None, residual=None, act=None, ln=None, stats_out=None, stats_zero=None):
+    """act(x @ w + bias) + residual as one tensor-core launch with the epilogue named up front, and layer_norm folded
+    into the product: `ln=(colsum, stats, eps)` makes the result act(rstd * (x @ w - mean * colsum) + bias) with mean and
+    rstd of each row of x taken from `stats` [rows, 2] (int64: sum and sum of squares in 2^-28 fixed point), which equals
+    layer_norm(x) @ w0 + b0 when w = gamma[:, None] * w0, colsum = w.sum(0) and bias = beta @ w0 + b0 (see
+    gpt2.fold_gpt2_layer_norms); `stats_out` [rows, 2] (int64) receives the (sum, sum of squares) of every stored row
+    (added with integer atomics, so the order of addition does not matter; it must hold zeros), `stats_zero` [rows, 2]
+    has those rows cleared. 16-bit dtypes on the tensor-core path only."""
+    colsum, stats, eps = ln if ln is not None else (None, None, 0.0)
+    oid = _L().applegpu_ffi_linear_fused(x.id, w.id, bias.id if bias is not None else 0, residual.id if residual is not None else 0, _ACT_CODES[act],
+                                         colsum.id if colsum is not None else 0, stats.id if stats is not None else 0, float(eps),
+                                         stats_out.id if stats_out is not None else 0, stats_zero.id if stats_zero is not None else 0)
+    return _wrap(oid, x, w, bias, residual, colsum, stats, stats_out, stats_zero)
+
+
 def eval(t):
     t.eval()
 

@@ -544,6 +544,14 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
           if (keep.back().shape != out->shape) return Status::compute("fused residual shape mismatch");
           g.ep.residual = keep.back().data();
         }
+        if (kd.has_ln) {
+          if (!in[idx]->contiguous() || !in[idx + 1]->contiguous()) return Status::compute("linear_fused: column sums and row statistics must be contiguous");
+          g.ep.ln_colsum = static_cast<const float*>(in[idx]->data()); g.ep.ln_stats = static_cast<const long long*>(in[idx + 1]->data());
+          g.ep.ln_eps = kd.f1;
+          idx += 2;
+        }
+        if (kd.has_stats_out) { if (!in[idx]->contiguous()) return Status::compute("linear_fused: row statistics must be contiguous"); g.ep.stats_out = static_cast<long long*>(in[idx++]->data()); }
+        if (kd.has_stats_zero) { if (!in[idx]->contiguous()) return Status::compute("linear_fused: row statistics must be contiguous"); g.ep.stats_zero = static_cast<long long*>(in[idx++]->data()); }
       }
       if (!int8_w && g.dtype == DType::F32 && g.b_dtype == DType::F32 && !dry) {
         bool done = false;

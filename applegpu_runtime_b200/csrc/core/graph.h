@@ -46,8 +46,12 @@ struct OpKind {
   k::FusedProgram prog;
   std::string function_name;         // "fused_<n>" like the reference
   std::string expr;                  // human-readable expression of the chain
-  // FusedLinear epilogue: inputs = [a, b, (bias), (residual)]
+  // FusedLinear epilogue: inputs = [a, b, (bias), (residual), (ln_colsum, ln_stats), (stats_out), (stats_zero)]
   bool has_bias = false, has_residual = false, trans_b = false, causal = false;
+  // layer_norm folded into the product (f1 = eps): has_ln reads per-row (sum, sum of squares) ([rows, 2] int64, fixed
+  // point) and the weight's column sums; has_stats_out adds the stored rows' sums into such a tensor, has_stats_zero
+  // clears another
+  bool has_ln = false, has_stats_out = false, has_stats_zero = false;
   k::Act act = k::Act::None;
 
   // Base kernel name without dtype suffix (graph.rs:168-255).

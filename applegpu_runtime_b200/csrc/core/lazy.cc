@@ -178,6 +178,8 @@ Status LazyRuntime::plan(uint64_t id, std::string* out) {
       if (n->op.has_bias) os << "bias,";
       if (n->op.act == k::Act::GeluTanh) os << "gelu,"; else if (n->op.act == k::Act::GeluErf) os << "gelu_exact,"; else if (n->op.act == k::Act::Relu) os << "relu,";
       if (n->op.has_residual) os << "residual,";
+      if (n->op.has_ln) os << "layer_norm_in,";
+      if (n->op.has_stats_out) os << "row_stats,";
       os << "]";
     }
     if (n->op.op == Op::FusedAttention) os << (n->op.causal ? "[causal" : "[full") << (n->op.i0 == 1 ? ",merge_heads]" : "]");

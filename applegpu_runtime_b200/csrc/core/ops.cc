@@ -122,6 +122,36 @@ Status infer_node(const MetaSource& src, OpNode* node) {
       node->out_shape = bo; node->out_dtype = a;
       return Status::OK();
     }
+    case Op::FusedLinear: {
+      // recorded directly (applegpu_ffi_linear_fused): x [.., M, K] @ w [K, N] with the epilogue inputs that follow
+      size_t want = 2 + (k.has_bias ? 1 : 0) + (k.has_residual ? 1 : 0) + (k.has_ln ? 2 : 0) + (k.has_stats_out ? 1 : 0) + (k.has_stats_zero ? 1 : 0);
+      AG_RETURN_IF_ERROR(need_inputs(*node, want));
+      DType a, w; AG_RETURN_IF_ERROR(dty(0, &a)); AG_RETURN_IF_ERROR(dty(1, &w));
+      AG_RETURN_IF_ERROR(validate_op_dtype(k, a));
+      if (w != a) return Status::invalid(std::string("dtype mismatch: ") + dtype_debug(a) + " vs " + dtype_debug(w));
+      Dims sa, sw; AG_RETURN_IF_ERROR(shp(0, &sa)); AG_RETURN_IF_ERROR(shp(1, &sw));
+      if (sa.size() < 2 || sw.size() != 2) return Status::invalid("linear_fused requires x >= 2D and a 2D [K,N] weight");
+      if (sa.back() != sw[0]) return Status::invalid("matmul inner dim mismatch: " + std::to_string(sa.back()) + " vs " + std::to_string(sw[0]));
+      Dims so = sa; so.back() = sw[1];
+      const int64_t rows = numel_of(so) / (sw[1] ? sw[1] : 1);
+      size_t idx = 2;
+      if (k.has_bias) { Dims sb; AG_RETURN_IF_ERROR(shp(idx++, &sb)); if (sb.size() != 1 || sb[0] != sw[1]) return Status::invalid("linear_fused bias must be [" + std::to_string(sw[1]) + "]"); }
+      if (k.has_residual) { Dims sr; AG_RETURN_IF_ERROR(shp(idx++, &sr)); if (sr != so) return Status::invalid("linear_fused residual shape " + dims_str(sr) + " must be " + dims_str(so)); }
+      auto stats_ok = [&](size_t i, int64_t r) -> Status {
+        Dims ss; DType sd; AG_RETURN_IF_ERROR(shp(i, &ss)); AG_RETURN_IF_ERROR(dty(i, &sd));
+        if (sd != DType::I64 || ss.size() != 2 || ss[0] != r || ss[1] != 2) return Status::invalid("linear_fused row statistics must be Int64 [" + std::to_string(r) + ", 2], got " + dims_str(ss));
+        return Status::OK();
+      };
+      if (k.has_ln) {
+        Dims sc; DType cd; AG_RETURN_IF_ERROR(shp(idx, &sc)); AG_RETURN_IF_ERROR(dty(idx, &cd)); idx++;
+        if (cd != DType::F32 || sc.size() != 1 || sc[0] != sw[1]) return Status::invalid("linear_fused column sums must be Float32 [" + std::to_string(sw[1]) + "]");
+        AG_RETURN_IF_ERROR(stats_ok(idx++, numel_of(sa) / (sa.back() ? sa.back() : 1)));
+      }
+      if (k.has_stats_out) AG_RETURN_IF_ERROR(stats_ok(idx++, rows));
+      if (k.has_stats_zero) AG_RETURN_IF_ERROR(stats_ok(idx++, rows));
+      node->out_shape = so; node->out_dtype = a;
+      return Status::OK();
+    }
     case Op::MatmulInt8: {
       // x [.., M, K] (float) @ dequant(w_q [N, K] int8, scales [N] f32)^T -> [.., M, N]
       AG_RETURN_IF_ERROR(need_inputs(*node, 3));

@@ -369,6 +369,23 @@ uint64_t applegpu_ffi_attention_causal(uint64_t q, uint64_t k, uint64_t v) { ret
 
 uint64_t applegpu_ffi_matmul_int8(uint64_t x, uint64_t q, uint64_t scales) { return record("matmul_int8", mk(Op::MatmulInt8), {x, q, scales}); }
 
+uint64_t applegpu_ffi_linear_fused(uint64_t x, uint64_t w, uint64_t bias, uint64_t residual, int32_t act, uint64_t ln_colsum, uint64_t ln_stats, float ln_eps,
+                                   uint64_t stats_out, uint64_t stats_zero) {
+  OpKind k = mk(Op::FusedLinear);
+  k.f0 = 1.0f; k.f1 = ln_eps;
+  k.act = act == 1 ? k::Act::GeluTanh : act == 2 ? k::Act::GeluErf : act == 3 ? k::Act::Relu : k::Act::None;
+  std::vector<uint64_t> in{x, w};
+  if (bias) { k.has_bias = true; in.push_back(bias); }
+  if (residual) { k.has_residual = true; in.push_back(residual); }
+  if (ln_colsum || ln_stats) {
+    if (!ln_colsum || !ln_stats) { set_ffi_error("linear_fused failed: the folded layer_norm needs both the column sums and the row statistics"); return 0; }
+    k.has_ln = true; in.push_back(ln_colsum); in.push_back(ln_stats);
+  }
+  if (stats_out) { k.has_stats_out = true; in.push_back(stats_out); }
+  if (stats_zero) { k.has_stats_zero = true; in.push_back(stats_zero); }
+  return record("linear_fused", std::move(k), std::move(in));
+}
+
 int32_t applegpu_ffi_quantize_weight(uint64_t weight_id, uint64_t* out_q_id, uint64_t* out_scales_id) {
   if (!ffi_ready("quantize_weight")) return -1;
   LazyState& st = lazy_state();

@@ -50,6 +50,11 @@ struct TcParams {
   int bias_vec;                // bias pointer is 16-byte aligned
   unsigned long long* argmax_keys;   // non-null: merge per-row (value, column) keys instead of storing C
   int c_f32;                         // C, bias and residual are float32 (operands are still 16-bit)
+  const long long* ln_stats;         // folded layer_norm, consumer side: fixed-point (sum, sum of squares) per A row; the float slots hold ln_colsum
+  const float* ln_colsum;
+  float ln_inv_k, ln_eps;
+  long long* stats_out;              // folded layer_norm, producer side: row sums of what is stored (fixed point, integer atomics)
+  long long* stats_zero;             // rows of the other statistics tensor to clear
   int* status;
 #ifdef AG_GEMM_PROBE
   long long* probe;   // per CTA: [0] cycles the MMA thread waited for a free accumulator, [1] cycles in the k loops, [2] k steps, [3] cycles epilogue warp 2 waited for a full accumulator, [4] cycles it spent in the epilogue, [5] tiles, [6] kernel cycles
@@ -133,9 +138,71 @@ __device__ __forceinline__ void load_residual_row(const TcParams& p, const T* R,
 //   p.vec_ok == 1  rows are 16-byte aligned: results are transposed through the warp's staging tile and stored with
 //                  4 lanes per row (64 contiguous bytes per row per instruction)
 //   p.vec_ok == 0  unaligned rows (a dense 50257-wide LM head): staged, 32 consecutive elements per instruction
+// Packed fp32 pipe: two independent operations per instruction on a 64-bit register pair.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+constexpr float kStatsScale = 268435456.0f;          // 2^28: row statistics travel as fixed-point int64 (see emit_row_stats)
+constexpr float kStatsUnscale = 1.0f / 268435456.0f;
+
+// Folded layer_norm, consumer side: mean and 1/std of A row `gm` from the (sum, sum of squares) its producer left.
+__device__ __forceinline__ void ln_row_stats(const TcParams& p, long long gm, float& mean, float& rstd) {
+  if (!p.ln_stats || gm >= p.m) return;
+  const longlong2 raw = __ldg(reinterpret_cast<const longlong2*>(p.ln_stats) + gm);
+  const float2 st = make_float2(__ll2float_rn(raw.x) * kStatsUnscale, __ll2float_rn(raw.y) * kStatsUnscale);
+  const float mu = st.x * p.ln_inv_k;
+  const float var = fmaxf(fmaf(-mu, mu, st.y * p.ln_inv_k), 0.f);
+  rstd = 1.0f / sqrtf(var + p.ln_eps);
+  mean = -mu * rstd;     // handed on as the shift factor: result = acc * rstd + colsum * (-mean * rstd)
+}
+// Folded layer_norm, producer side. A row's (sum, sum of squares) is accumulated from the partial sums of the CTAs
+// that store pieces of it. The partials are converted to 2^-28 fixed point and added with 64-bit integer atomics:
+// integer addition is associative, so the statistics (and everything computed from them) do not depend on the order in
+// which CTAs finish. Range: |sum|, sum of squares < 2^35 per row; resolution 4e-9.
+__device__ __forceinline__ void group_stats(const TcParams& p, const float (&v)[32], int col0, float& row_sum, float& row_sq) {
+  float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
+  if (col0 + 32 <= p.n) {   // uniform: the whole group lies inside the matrix
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) { s0 += v[e]; s1 += v[e + 1]; q0 = fmaf(v[e], v[e], q0); q1 = fmaf(v[e + 1], v[e + 1], q1); }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+      if (col0 + e < p.n) { s0 += v[e]; q0 = fmaf(v[e], v[e], q0); }
+    }
+  }
+  row_sum += s0 + s1; row_sq += q0 + q1;
+}
+// This thread's share of row `gm` (its column groups of one tile) goes into the row's running sums; the rows of the
+// other statistics tensor are cleared by the tile that holds column 0.
+__device__ __forceinline__ void emit_row_stats(const TcParams& p, long long gm, bool clears, float row_sum, float row_sq) {
+  if (gm >= p.m) return;
+  if (p.stats_out) {
+    atomicAdd(reinterpret_cast<unsigned long long*>(p.stats_out) + 2 * gm, (unsigned long long)__float2ll_rn(row_sum * kStatsScale));
+    atomicAdd(reinterpret_cast<unsigned long long*>(p.stats_out) + 2 * gm + 1, (unsigned long long)__float2ll_rn(row_sq * kStatsScale));
+  }
+  if (p.stats_zero && clears) *reinterpret_cast<longlong2*>(p.stats_zero + 2 * gm) = make_longlong2(0, 0);
+}
+
 template <typename T>
 __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint32_t (&rpre)[16],
-                                               long long row0, int col0, int next_col0, long long c_off, int lane, unsigned long long& best_key) {
+                                               long long row0, int col0, int next_col0, long long c_off, int lane, unsigned long long& best_key,
+                                               float ln_mean, float ln_rstd, float& row_sum, float& row_sq) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
   const int sub_row = lane >> 2, sub_chunk = lane & 3;
@@ -238,7 +305,18 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 #pragma unroll
     for (int e = 0; e < 32; e++) v[e] *= p.alpha;
   }
-  if (scale_s) {
+  if (p.ln_stats) {
+    // folded layer_norm: the product ran on the raw rows; this row's mean times the weight's column sums comes off,
+    // then its 1/std scales the rest (the float slots hold the column sums)
+    // two elements per instruction on the packed fp32 pipe: acc * rstd + colsum * shift
+    const uint64_t r2 = pack_f32x2(ln_rstd, ln_rstd), sh2 = pack_f32x2(ln_mean, ln_mean);
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+      const ulonglong2 cs = *reinterpret_cast<const ulonglong2*>(scale_s + g * 4);   // same address in every lane: a broadcast
+      unpack_f32x2(fma_f32x2(pack_f32x2(v[g * 4 + 0], v[g * 4 + 1]), r2, mul_f32x2(cs.x, sh2)), v[g * 4 + 0], v[g * 4 + 1]);
+      unpack_f32x2(fma_f32x2(pack_f32x2(v[g * 4 + 2], v[g * 4 + 3]), r2, mul_f32x2(cs.y, sh2)), v[g * 4 + 2], v[g * 4 + 3]);
+    }
+  } else if (scale_s) {
 #pragma unroll
     for (int g = 0; g < 8; g++) {
       float4 sc = *reinterpret_cast<const float4*>(scale_s + g * 4);   // same address in every lane: a broadcast
@@ -312,6 +390,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
         v[2 * w] += Cvt<T>::to(rv[0]); v[2 * w + 1] += Cvt<T>::to(rv[1]);
       }
     }
+    if (p.stats_out) group_stats(p, v, col0, row_sum, row_sq);
     uint32_t o[16];
 #pragma unroll
     for (int w = 0; w < 16; w++) o[w] = pack2<T>(v[2 * w], v[2 * w + 1]);
@@ -339,6 +418,7 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
       for (int e = 0; e < 8; e++) v[g * 8 + e] += Cvt<T>::to(r.v[e]);
     }
   }
+  if (p.stats_out) group_stats(p, v, col0, row_sum, row_sq);
 #pragma unroll
   for (int g = 0; g < 4; g++) {
     uint4 o;
@@ -519,7 +599,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
       // the float slots hold the int8 per-channel scales, or the float32 bias of a float32-output product
-      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : p.b_scales;
+      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : (p.ln_stats ? p.ln_colsum : p.b_scales);
       if (fsrc) {
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -530,6 +610,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t rpre[16];
       if (p.residual && p.vec_ok == 2 && !p.c_f32 && n0 + pair * 32 < p.n)
         load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0 + lane, n0 + pair * 32, rpre);
+      // folded layer_norm: this row's statistics are fetched (and turned into scale and shift) before the accumulator wait too
+      float ln_mean = 0.f, ln_rstd = 1.f;
+      ln_row_stats(p, row0 + lane, ln_mean, ln_rstd);
       __syncwarp();
 #ifdef AG_GEMM_PROBE
       long long pe0 = clock64();
@@ -542,17 +625,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
       unsigned long long best_key = 0;   // argmax mode: this row's best over the warp's column groups of the tile
+      float row_sum = 0.f, row_sq = 0.f;
 #pragma unroll 1
       for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
         int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
         epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                          c_off, lane, best_key);
+                          c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq);
       }
       if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      emit_row_stats(p, row0 + lane, n0 == 0 && pair == 0, row_sum, row_sq);   // after the accumulator is handed back
 #ifdef AG_GEMM_PROBE
       if (p.probe && warp == 2 && lane == 0) {
         long long pe2 = clock64();
@@ -827,7 +912,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
       float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
       // the float slots hold the int8 per-channel scales, or the float32 bias of a float32-output product
-      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : p.b_scales;
+      const float* fsrc = p.c_f32 ? reinterpret_cast<const float*>(p.bias) : (p.ln_stats ? p.ln_colsum : p.b_scales);
       if (fsrc) {
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -838,6 +923,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t rpre[16];
       if (p.residual && p.vec_ok == 2 && !p.c_f32 && n0 + pair * 32 < p.n)
         load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0 + lane, n0 + pair * 32, rpre);
+      // folded layer_norm: this row's statistics are fetched (and turned into scale and shift) before the accumulator wait too
+      float ln_mean = 0.f, ln_rstd = 1.f;
+      ln_row_stats(p, row0 + lane, ln_mean, ln_rstd);
       __syncwarp();
 #ifdef AG_GEMM_PROBE
       long long pe0 = clock64();
@@ -850,19 +938,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
       unsigned long long best_key = 0;
+      float row_sum = 0.f, row_sq = 0.f;
       if (row0 < p.m) {   // a peer CTA whose rows lie past M has nothing to store
 #pragma unroll 1
         for (int g = pair, gi = 0; g < BN / 32; g += 2, gi++) {
           if (n0 + g * 32 >= p.n) break;
           int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
           epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                            c_off, lane, best_key);
+                            c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq);
         }
-      }
+        }
       if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[acc]), 0));
+      if (row0 < p.m) emit_row_stats(p, row0 + lane, n0 == 0 && pair == 0, row_sum, row_sq);   // after the accumulator is handed back
 #ifdef AG_GEMM_PROBE
       if (p.probe && warp == 2 && lane == 0 && rank == 0) {
         long long pe2 = clock64();
@@ -1175,6 +1265,8 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   p.tiles_m = (int)tiles_m; p.tiles_n = (int)tiles_n; p.status = status_word;
   p.argmax_keys = d.ep.argmax_keys;
   p.c_f32 = d.c_f32 ? 1 : 0;
+  p.ln_stats = d.ep.ln_stats; p.ln_colsum = d.ep.ln_colsum; p.ln_inv_k = d.k ? 1.0f / (float)d.k : 0.f; p.ln_eps = d.ep.ln_eps;
+  p.stats_out = d.ep.stats_out; p.stats_zero = d.ep.stats_zero;
 #ifdef AG_GEMM_PROBE
   p.probe = g_tc_probe;
 #endif
@@ -1261,6 +1353,13 @@ Status matmul(cudaStream_t s, const GemmDesc& d) {
   }
   bool elig = tc_eligible(d);
   if (d.ep.argmax_keys && (!elig || g_force_path == 1)) return Status::invalid("matmul: the row-argmax epilogue needs the tensor-core kernel");
+  if (d.ep.ln_stats || d.ep.stats_out || d.ep.stats_zero) {
+    if (!elig || g_force_path == 1 || d.batch != 1 || d.batch_inner != 1 || d.c_f32 || d.ep.argmax_keys || d.ep.b_scales || (d.ep.ln_stats && !d.ep.ln_colsum))
+      return Status::invalid("matmul: the folded layer_norm epilogue needs an unbatched 16-bit product on the tensor-core kernel");
+    int* st = matmul_status_word();
+    if (!st) return Status::compute("matmul: the kernel workspace is not initialised");
+    return matmul_tc(s, d, st);
+  }
   // a handful of rows against a [K, N] weight: bound by streaming B, spread over every SM
   if (g_force_path == 0 && skinny_eligible(d)) return matmul_skinny(s, d);
   // the same against a [N, K] weight; 16-bit products that large keep the tensor-core kernel (it is as fast there and

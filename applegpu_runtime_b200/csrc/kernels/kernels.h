@@ -72,6 +72,17 @@ struct GemmEpilogue {
   // (value rounded to the storage type, lowest column on ties) is merged into keys[row] with a 64-bit
   // atomic max; C is not written. keys must be zeroed first; argmax_finalize turns them into int32.
   unsigned long long* argmax_keys = nullptr;
+  // layer_norm folded into the product (tensor-core kernels, unbatched, 16-bit C). A consumer whose A rows are the
+  // un-normalised x computes rstd[i] * (acc[i][n] - mean[i] * ln_colsum[n]) before bias / activation, with mean and
+  // rstd from ln_stats[i] = (sum, sum of squares) of row i over K in 2^-28 fixed point (int64); the weight must carry
+  // gamma (W'[k][n] = gamma[k] * W[k][n], ln_colsum[n] = sum_k W'[k][n], bias[n] = sum_k beta[k] * W[k][n] + b[n]).
+  // A producer adds the (sum, sum of squares) of every row it stores into stats_out with 64-bit integer atomics
+  // (associative: the result does not depend on the order in which CTAs finish) and clears the same rows of stats_zero.
+  const long long* ln_stats = nullptr;
+  const float* ln_colsum = nullptr;
+  float ln_eps = 1e-5f;
+  long long* stats_out = nullptr;
+  long long* stats_zero = nullptr;
 };
 struct GemmDesc {
   DType dtype;            // dtype of A and C (f32/f16/bf16)

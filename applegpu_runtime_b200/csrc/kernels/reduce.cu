@@ -148,41 +148,60 @@ Status layer_norm(cudaStream_t s, const TView& in, const TView& gamma, const TVi
 }
 
 // ── softmax / softmax_causal ────────────────────────────────────────────────
-// Warp-per-row with the row in registers. `valid` = number of unmasked leading columns.
+// Warp-per-row with the row in registers; `valid` = number of unmasked leading columns. A persistent grid walks the
+// rows and a warp keeps two rows in flight: the 16-byte loads of its next row are issued before the reductions of the
+// current one (a row's chain load -> max -> exp -> sum -> store is latency-bound on its own). Packs wholly left of the
+// diagonal take a mask-free path, the one pack the diagonal crosses is masked per element, packs right of it are
+// neither read nor computed: zeros are stored.
 template <typename T, int ITERS, bool CAUSAL>
-__global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t total_rows, int rows_per_mat, int cols) {
+__global__ void __launch_bounds__(128, 4) softmax_warp_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t total_rows, int rows_per_mat, int cols) {
   constexpr int N = Pack<T>::N;
   const int lane = threadIdx.x & 31;
   const int wpb = blockDim.x >> 5;
   const int packs = cols / N;
   pdl_wait();
   pdl_trigger();
-  for (int64_t row = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5); row < total_rows; row += (int64_t)gridDim.x * wpb) {
-    int valid = cols;
-    if (CAUSAL) {
-      // 32-bit remainder where the row count allows it: the 64-bit one costs about a fifth of a 1024-column row
-      int r = total_rows <= 0x7fffffff ? (int)((unsigned int)row % (unsigned int)rows_per_mat) : (int)(row % rows_per_mat);
-      valid = r + 1 < cols ? r + 1 : cols;
+  auto valid_of = [&](int64_t row) -> int {
+    if (!CAUSAL) return cols;
+    // 32-bit remainder where the row count allows it: the 64-bit one costs about a fifth of a 1024-column row
+    int r = total_rows <= 0x7fffffff ? (int)((unsigned int)row % (unsigned int)rows_per_mat) : (int)(row % rows_per_mat);
+    return r + 1 < cols ? r + 1 : cols;
+  };
+  const int64_t stride = (int64_t)gridDim.x * wpb;
+  int64_t row = (int64_t)blockIdx.x * wpb + (threadIdx.x >> 5);
+  Pack<T> cur[ITERS], nxt[ITERS];
+  int valid = 0;
+  if (row < total_rows) {
+    valid = valid_of(row);
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) { int pk = lane + it * 32; if (pk < packs && pk * N < valid) cur[it] = ld16_stream(in + row * cols + pk * N); }
+  }
+  for (; row < total_rows; row += stride) {
+    const int64_t next = row + stride;
+    int next_valid = 0;
+    if (next < total_rows) {
+      next_valid = valid_of(next);
+#pragma unroll
+      for (int it = 0; it < ITERS; it++) { int pk = lane + it * 32; if (pk < packs && pk * N < next_valid) nxt[it] = ld16_stream(in + next * cols + pk * N); }
     }
-    const T* x = in + row * cols;
     float v[ITERS][N];
     float m = CAUSAL ? -1e9f : -INFINITY;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
-      int pk = lane + it * 32;
-      int c0 = pk * N;
-      if (pk < packs && c0 < valid) {
-        Pack<T> p = ld16_stream(x + c0);
+      const int c0 = (lane + it * 32) * N;
+      if (lane + it * 32 < packs && c0 < valid) {
+        if (c0 + N <= valid) {
 #pragma unroll
-        for (int e = 0; e < N; e++) {
-          float f = Cvt<T>::to(p.v[e]);
-          bool on = c0 + e < valid;
-          v[it][e] = on ? f : -INFINITY;
-          if (on) m = fmaxf(m, f);
+          for (int e = 0; e < N; e++) { v[it][e] = Cvt<T>::to(cur[it].v[e]); m = fmaxf(m, v[it][e]); }
+        } else {
+#pragma unroll
+          for (int e = 0; e < N; e++) {
+            const float f = Cvt<T>::to(cur[it].v[e]);
+            const bool on = c0 + e < valid;
+            v[it][e] = on ? f : -INFINITY;
+            if (on) m = fmaxf(m, f);
+          }
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < N; e++) v[it][e] = -INFINITY;
       }
     }
     m = warp_max(m);
@@ -190,7 +209,7 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
       // packs entirely right of the diagonal (or past the row) hold only masked slots: skip their math
-      if ((lane + it * 32) * N < valid) {
+      if ((lane + it * 32) * N < valid && lane + it * 32 < packs) {
 #pragma unroll
         for (int e = 0; e < N; e++) {
           // Masked slots hold -inf and contribute exp(-inf) = 0. __expf (hardware exp2) is within
@@ -214,7 +233,7 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
         if (c0 < valid) {
           float r[N];
 #pragma unroll
-          for (int e = 0; e < N; e++) r[e] = (c0 + e < valid) ? v[it][e] * inv : 0.f;
+          for (int e = 0; e < N; e++) r[e] = v[it][e] * inv;     // masked slots hold exp(-inf) = 0: they store 0
           pack_from_floats<T>(o, r);
         } else {
 #pragma unroll
@@ -223,12 +242,15 @@ __global__ void __launch_bounds__(128) softmax_warp_kernel(const T* __restrict__
         st16_stream(y + c0, o);
       }
     }
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) cur[it] = nxt[it];
+    valid = next_valid;
   }
 }
 
 // Block-per-row for long or unaligned rows.
 template <typename T, bool CAUSAL>
-__global__ void __launch_bounds__(256) softmax_block_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t total_rows, int64_t rows_per_mat, int64_t cols) {
+__global__ void __launch_bounds__(256) softmax_block_kernel(const T* in, T* out, int64_t total_rows, int64_t rows_per_mat, int64_t cols) {
   __shared__ float red[33];
   for (int64_t row = blockIdx.x; row < total_rows; row += gridDim.x) {
     int64_t valid = cols;
@@ -261,8 +283,9 @@ static Status softmax_t(cudaStream_t s, const TView& in, const TView& out) {
   int64_t packs = cols / N;
   bool vec = cols % N == 0 && aligned16(x) && aligned16(y) && packs <= 32 * 16 && in.ptr != out.ptr;
   if (vec) {
+    // persistent: four CTAs of four warps per SM (the kernel keeps two rows per warp in registers: ~128 registers)
     const int threads = 128, wpb = 4;
-    int grid = grid_for(total_rows, wpb, 16);
+    int grid = grid_for(total_rows, wpb, 4);
     int iters = (int)((packs + 31) / 32);
     cudaError_t le = cudaSuccess;
 #define AG_SM(I) le = launch_pdl(softmax_warp_kernel<T, I, CAUSAL>, dim3(grid), dim3(threads), 0, s, x, y, total_rows, (int)rows_per_mat, (int)cols)

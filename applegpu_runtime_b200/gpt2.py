@@ -7,6 +7,8 @@ reference lacks: a batch dimension ([B, T] token ids; linears run on [B*T, d], a
 runtime, and the fusion pass folds add_bias / gelu / residual into the GEMM epilogues and the
 five attention ops into one node, so the kernel count per layer is far below the op count.
 """
+import os
+
 import numpy as np
 
 from . import api as gpu
@@ -48,9 +50,11 @@ def init_gpt2_weights(config=None, seed=0, dtype="float32", std=0.02):
     return load_gpt2_state_dict(host, cfg, dtype=dtype)
 
 
-def load_gpt2_state_dict(state, config, dtype="float32"):
+def load_gpt2_state_dict(state, config, dtype="float32", fold_layer_norms=True):
     """Uploads a {name: numpy / torch array} state dict (HF GPT-2 names). Returns the model dict
-    the reference's `load_gpt2_weights` returns: {"weights": {...GpuTensor}, "config": {...}}."""
+    the reference's `load_gpt2_weights` returns: {"weights": {...GpuTensor}, "config": {...}}. 16-bit models also get the
+    layer_norm-folded copies of c_attn / c_fc that the prefill path uses (fold_gpt2_layer_norms; `fold_layer_norms=False`
+    or APPLEGPU_LN_FOLD=0 keeps every layer_norm a kernel)."""
     weights = {}
     for name, arr in state.items():
         if name.endswith(".attn.bias") or name.endswith(".attn.masked_bias") or name == "lm_head.weight":
@@ -62,7 +66,10 @@ def load_gpt2_state_dict(state, config, dtype="float32"):
             t = gpu.cast(t, dtype)
             t.eval()
         weights[name] = t
-    return {"weights": weights, "config": dict(config), "dtype": dtype}
+    model = {"weights": weights, "config": dict(config), "dtype": dtype}
+    if fold_layer_norms and dtype != "float32" and "transformer.h.0.ln_1.weight" in weights and os.environ.get("APPLEGPU_LN_FOLD", "1") != "0":
+        fold_gpt2_layer_norms(model)
+    return model
 
 
 def quantize_gpt2_linears(model):
@@ -76,7 +83,54 @@ def quantize_gpt2_linears(model):
             wt = gpu.reshape(wt, wt.shape)  # materialise [N, K] contiguous
             q[name] = gpu.quantize_weight(wt)
     model["int8"] = q
+    model.pop("ln_fold", None)   # the folded copies are not quantised: the int8 path keeps its layer_norm kernels
     return model
+
+
+def fold_gpt2_layer_norms(model):
+    """Folds ln_1 / ln_2 of every block into the linear that follows it, for the prefill path of 16-bit models.
+
+    layer_norm(x) @ W + b = rstd * (x @ W' - mean * s) + c with W' = gamma[:, None] * W, s = W'.sum(0) and
+    c = beta @ W + b: the product runs on the un-normalised residual stream, the row statistics (sum and sum of squares
+    over the 768 features, accumulated in fixed point with integer atomics so that the order of addition cannot change
+    a bit) come from the epilogue of the GEMM that produced the stream (the attention output projection and the second
+    feed-forward matrix, which add the residual), and the correction is two packed operations per two elements in the
+    consumer's epilogue (api.linear_fused). 23 of the 25 layer_norm launches of a GPT-2-small forward disappear;
+    block 0's ln_1 (its input comes from the embeddings) and ln_f stay kernels. s is summed from the rounded W' the GEMM
+    multiplies with, so mean * s cancels exactly what the product accumulated."""
+    if model.get("dtype", "float32") == "float32" or "int8" in model:
+        return model
+    w = model["weights"]
+    cfg = model["config"]
+    dtype = model["dtype"]
+    fold = {}
+    for i in range(cfg["n_layer"]):
+        p = f"transformer.h.{i}"
+        for ln, lin in ((f"{p}.ln_1", f"{p}.attn.c_attn"), (f"{p}.ln_2", f"{p}.mlp.c_fc")):
+            gamma = w[f"{ln}.weight"].to_numpy().astype(np.float32)
+            beta = w[f"{ln}.bias"].to_numpy().astype(np.float32)
+            w0 = w[f"{lin}.weight"].to_numpy().astype(np.float32)          # [K, N], the values the plain path multiplies with
+            b0 = w[f"{lin}.bias"].to_numpy().astype(np.float32)
+            wf = gpu.cast(gpu.from_numpy(np.ascontiguousarray(gamma[:, None] * w0)), dtype)
+            wf.eval()
+            colsum = gpu.from_numpy(wf.to_numpy().astype(np.float64).sum(0).astype(np.float32))
+            cbias = gpu.cast(gpu.from_numpy((beta.astype(np.float64) @ w0.astype(np.float64) + b0).astype(np.float32)), dtype)
+            cbias.eval()
+            fold[lin] = (wf, colsum, cbias)
+    model["ln_fold"] = fold
+    model["_ln_stats"] = {}
+    return model
+
+
+def _row_stats(model, rows):
+    """Two zeroed [rows, 2] int64 tensors per row count: the running fixed-point (sum, sum of squares) of the residual
+    stream's rows for ln_1 and ln_2. Each is cleared by the GEMM that runs before the one that fills it (stats_zero),
+    and block 0 clears both, so a forward always starts from zeros whatever an interrupted one left behind."""
+    pair = model["_ln_stats"].get(rows)
+    if pair is None:
+        pair = (gpu.from_numpy(np.zeros((rows, 2), np.int64)), gpu.from_numpy(np.zeros((rows, 2), np.int64)))
+        model["_ln_stats"][rows] = pair
+    return pair
 
 
 def _linear(x, w, name, bias):
@@ -104,6 +158,9 @@ def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=No
     w = dict(model["weights"])
     if "int8" in model:
         w["__int8__"] = model["int8"]
+    if "ln_fold" in model and kv_cache is None and np.asarray(input_ids).size >= 64 and "int8" not in model:
+        w["__ln_fold__"] = model["ln_fold"]
+        w["__ln_stats__"] = _row_stats(model, int(np.asarray(input_ids).size))
     cfg = model["config"]
     n_layer, n_head, n_embd = cfg["n_layer"], cfg["n_head"], cfg["n_embd"]
     d_head = n_embd // n_head
@@ -133,7 +190,7 @@ def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=No
 
     tape_key = tape_inputs = None
     if compiled:
-        tape_key = ("gpt2", B, T, use_cache, bool(last_only), batched, "int8" in model)
+        tape_key = ("gpt2", B, T, use_cache, bool(last_only), batched, "int8" in model, "__ln_fold__" in w)
         tape_inputs = [indices, pos_indices] + ([t for kv in kv_cache for t in kv] if use_cache else [])
         tape = model.setdefault("_tapes", {}).get(tape_key)
         if tape is not None:
@@ -161,11 +218,21 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
     pos_emb = gpu.embedding(w["transformer.wpe.weight"], pos_indices)
     x = tok_emb + pos_emb  # [B*T, d]
 
+    fold = w.get("__ln_fold__")
+    stats1, stats2 = w.get("__ln_stats__", (None, None))     # row statistics feeding ln_1 / ln_2
     new_kv_cache = []
     for i in range(n_layer):
         p = f"transformer.h.{i}"
-        x_norm = gpu.layer_norm(x, w[f"{p}.ln_1.weight"], w[f"{p}.ln_1.bias"])
-        qkv = _linear(x_norm, w, f"{p}.attn.c_attn.weight", w[f"{p}.attn.c_attn.bias"])
+        if fold is None:
+            x_norm = gpu.layer_norm(x, w[f"{p}.ln_1.weight"], w[f"{p}.ln_1.bias"])
+            qkv = _linear(x_norm, w, f"{p}.attn.c_attn.weight", w[f"{p}.attn.c_attn.bias"])
+        elif i == 0:
+            # the stream comes from the embeddings here: a layer_norm kernel, and the projection clears ln_2's statistics
+            x_norm = gpu.layer_norm(x, w[f"{p}.ln_1.weight"], w[f"{p}.ln_1.bias"])
+            qkv = gpu.linear_fused(x_norm, w[f"{p}.attn.c_attn.weight"], bias=w[f"{p}.attn.c_attn.bias"], stats_zero=stats2)
+        else:
+            wf, colsum, cbias = fold[f"{p}.attn.c_attn"]
+            qkv = gpu.linear_fused(x, wf, bias=cbias, ln=(colsum, stats1, 1e-5))
 
         q_all = gpu.slice(qkv, dim=1, start=0, end=n_embd)
         k_new = gpu.slice(qkv, dim=1, start=n_embd, end=2 * n_embd)
@@ -186,14 +253,23 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
         attn = gpu.transpose_dims(attn, 1, 2)        # [B, T, n_head, d_head]
         attn = gpu.reshape(attn, [rows, n_embd])
 
-        attn = _linear(attn, w, f"{p}.attn.c_proj.weight", w[f"{p}.attn.c_proj.bias"])
-        x = x + attn
+        if fold is None:
+            attn = _linear(attn, w, f"{p}.attn.c_proj.weight", w[f"{p}.attn.c_proj.bias"])
+            x = x + attn
 
-        x_norm2 = gpu.layer_norm(x, w[f"{p}.ln_2.weight"], w[f"{p}.ln_2.bias"])
-        ffn = _linear(x_norm2, w, f"{p}.mlp.c_fc.weight", w[f"{p}.mlp.c_fc.bias"])
-        ffn = gpu.gelu(ffn)
-        ffn = _linear(ffn, w, f"{p}.mlp.c_proj.weight", w[f"{p}.mlp.c_proj.bias"])
-        x = x + ffn
+            x_norm2 = gpu.layer_norm(x, w[f"{p}.ln_2.weight"], w[f"{p}.ln_2.bias"])
+            ffn = _linear(x_norm2, w, f"{p}.mlp.c_fc.weight", w[f"{p}.mlp.c_fc.bias"])
+            ffn = gpu.gelu(ffn)
+            ffn = _linear(ffn, w, f"{p}.mlp.c_proj.weight", w[f"{p}.mlp.c_proj.bias"])
+            x = x + ffn
+        else:
+            # x += attn @ W + b, and ln_2's row statistics of the new x; ln_1's (already consumed) are cleared
+            x = gpu.linear_fused(attn, w[f"{p}.attn.c_proj.weight"], bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
+            wf, colsum, cbias = fold[f"{p}.mlp.c_fc"]
+            ffn = gpu.linear_fused(x, wf, bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
+            # x += ffn @ W + b, ln_1's statistics for the next block (none after the last: ln_f is a kernel), ln_2's cleared
+            x = gpu.linear_fused(ffn, w[f"{p}.mlp.c_proj.weight"], bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
+                                 stats_out=stats1 if i + 1 < n_layer else None, stats_zero=stats2)
 
     x = gpu.layer_norm(x, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"])
     if last_only:

@@ -91,6 +91,17 @@ APPLEGPU_API uint64_t applegpu_ffi_attention_causal(uint64_t q_id, uint64_t k_id
  * int8-weight matmul as backlog). quantize_weight: w [N,K] float -> *out_q [N,K] int8 and
  * *out_scales [N] f32 with scale[n] = max|w[n,:]|/127, evaluated immediately.
  * matmul_int8: x [..,M,K] @ (q * scale)^T -> [..,M,N], dequantisation fused into the GEMM. */
+/* x [.., M, K] @ w [K, N] with the whole epilogue named up front (0 = absent): bias [N], residual [.., M, N], act
+ * (0 none, 1 tanh-GELU, 2 erf-GELU, 3 ReLU), and layer_norm folded into the product. With ln_colsum [N] (float32) and
+ * ln_stats [M, 2] (int64: sum and sum of squares of each row of x over K, in 2^-28 fixed point) the result is
+ * act(rstd * (x @ w - mean * ln_colsum) + bias), i.e. layer_norm(x) @ w0 + b0 when w = gamma * w0 row-wise,
+ * ln_colsum = column sums of w, bias = beta @ w0 + b0. With stats_out [M, 2] (int64) the (sum, sum of squares) of every
+ * stored row are added into it (64-bit integer atomics on fixed-point values: associative, so the result does not depend
+ * on the order in which CTAs finish; it must hold zeros), in the form a following call takes as ln_stats; with
+ * stats_zero [M, 2] (int64) those rows of it are cleared. One kernel launch; tensor-core path only (16-bit dtypes,
+ * TMA-compatible operands), an error otherwise. No counterpart in the reference. */
+APPLEGPU_API uint64_t applegpu_ffi_linear_fused(uint64_t x_id, uint64_t w_id, uint64_t bias_id, uint64_t residual_id, int32_t act, uint64_t ln_colsum_id,
+                                                uint64_t ln_stats_id, float ln_eps, uint64_t stats_out_id, uint64_t stats_zero_id);
 APPLEGPU_API int32_t applegpu_ffi_quantize_weight(uint64_t weight_id, uint64_t* out_q_id, uint64_t* out_scales_id);
 APPLEGPU_API uint64_t applegpu_ffi_matmul_int8(uint64_t x_id, uint64_t q_id, uint64_t scales_id);
 

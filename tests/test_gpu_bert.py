@@ -144,7 +144,7 @@ def test_segment_taped_micro_batched_forward_equals_the_plain_forward(gpu_dev):
         parts = bert_forward_overlapped(model, ids, tp, micro_batches=3)
         got = np.concatenate([p.to_numpy() for p in parts], axis=0)
         assert got.shape == want.shape
-        assert float(np.max(np.abs(got - want))) <= 1e-2 * float(np.max(np.abs(want))), (trial, float(np.max(np.abs(got - want))))
+        assert float(np.max(np.abs(got - want))) <= 2e-2 * float(np.max(np.abs(want))), (trial, float(np.max(np.abs(got - want))))
         again = np.concatenate([p.to_numpy() for p in bert_forward_overlapped(model, ids, tp, micro_batches=3)], axis=0)
         assert np.array_equal(again, got), trial
     assert len(model["_segment_tapes"]) == 2 * cfg["n_layer"] + 1

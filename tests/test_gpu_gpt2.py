@@ -198,3 +198,43 @@ def test_mlp_config_fp32(gpu_dev):
     y = g.add_bias(g.relu(g.add_bias(gx @ w1, g.from_torch(l1.bias))) @ w2, g.from_torch(l2.bias))
     assert "fused_linear[bias,relu,]" in y.plan()
     np.testing.assert_allclose(y.to_numpy(), ref, atol=1e-5, rtol=1e-5)
+
+
+def test_layer_norm_folded_into_the_linears_matches_the_layer_norm_kernels(gpu_dev):
+    """16-bit prefill with ln_1 / ln_2 folded into c_attn / c_fc (row statistics from the producing GEMM's epilogue,
+    correction in the consuming GEMM's epilogue) against the same model with every layer_norm a kernel, and against the
+    float32 oracle; gains and shifts are random so the folding itself is exercised, and further forwards (direct, taped,
+    replayed) must reproduce the first bit for bit: the row statistics are accumulated in fixed point with integer
+    atomics, whose result does not depend on the order of addition."""
+    rng = np.random.default_rng(11)
+    w = {k: v.numpy() for k, v in torch_ref.init_gpt2_weights(CFG_MID, seed=11).items()}
+    for k in w:
+        if ".ln_" in k and k.endswith(".weight"):
+            w[k] = (1.0 + 0.3 * rng.standard_normal(w[k].shape)).astype(np.float32)
+        elif k.endswith(".bias") and w[k].ndim == 1:
+            w[k] = (0.1 * rng.standard_normal(w[k].shape)).astype(np.float32)
+    ids = rng.integers(0, CFG_MID["vocab_size"], (4, 160))
+    with torch.no_grad():
+        ref = torch_ref.gpt2_forward({k: torch.from_numpy(v) for k, v in w.items()}, CFG_MID, torch.from_numpy(ids))[0].numpy()
+    scale = float(np.max(np.abs(ref)))
+    for dtype in ("bfloat16", "float16"):
+        plain = gpu_dev.load_gpt2_state_dict(w, CFG_MID, dtype=dtype, fold_layer_norms=False)
+        folded = gpu_dev.load_gpt2_state_dict(w, CFG_MID, dtype=dtype)
+        assert "ln_fold" in folded and "ln_fold" not in plain
+        out = gpu_dev.gpt2_forward(folded, ids)[0]
+        plan = out.plan()
+        assert plan.count("layer_norm_in") == 2 * CFG_MID["n_layer"] - 1 and plan.count("row_stats") == 2 * CFG_MID["n_layer"] - 1, plan
+        assert sum(1 for line in plan.splitlines() if line.strip().startswith("layer_norm")) == 2, plan     # block 0's ln_1 and ln_f
+        got = out.to_numpy()
+        base = gpu_dev.gpt2_forward(plain, ids)[0].to_numpy()
+        tol = 2e-2 if dtype == "bfloat16" else 4e-3
+        assert float(np.max(np.abs(got - ref))) <= tol * scale, (dtype, float(np.max(np.abs(got - ref))) / scale)
+        assert float(np.max(np.abs(got - base))) <= tol * scale, (dtype, float(np.max(np.abs(got - base))) / scale)
+        # not worse than the kernel form against the oracle by more than a rounding step
+        assert float(np.max(np.abs(got - ref))) <= 1.5 * float(np.max(np.abs(base - ref))) + 1e-3 * scale
+        again = gpu_dev.gpt2_forward(folded, ids)[0].to_numpy()
+        taped = gpu_dev.gpt2_forward(folded, ids, compiled=True)[0].to_numpy()
+        replayed = gpu_dev.gpt2_forward(folded, ids, compiled=True)[0].to_numpy()
+        for other in (again, taped, replayed):
+            assert np.array_equal(other, got), (dtype, float(np.max(np.abs(other - got))) / scale)
+    assert gpu_dev.pipeline_status() == 0
