@@ -162,14 +162,21 @@ constexpr float kStatsScale = 268435456.0f;          // 2^28: row statistics tra
 constexpr float kStatsUnscale = 1.0f / 268435456.0f;
 
 // Folded layer_norm, consumer side: mean and 1/std of A row `gm` from the (sum, sum of squares) its producer left.
-__device__ __forceinline__ void ln_row_stats(const TcParams& p, long long gm, float& mean, float& rstd) {
-  if (!p.ln_stats || gm >= p.m) return;
-  const longlong2 raw = __ldg(reinterpret_cast<const longlong2*>(p.ln_stats) + gm);
+__device__ __forceinline__ longlong2 ln_stats_fetch(const TcParams& p, long long gm) {
+  if (!p.ln_stats || gm < 0 || gm >= p.m) return make_longlong2(0, 0);
+  return __ldg(reinterpret_cast<const longlong2*>(p.ln_stats) + gm);
+}
+__device__ __forceinline__ void ln_stats_finish(const TcParams& p, const longlong2 raw, float& mean, float& rstd) {
+  if (!p.ln_stats) return;
   const float2 st = make_float2(__ll2float_rn(raw.x) * kStatsUnscale, __ll2float_rn(raw.y) * kStatsUnscale);
   const float mu = st.x * p.ln_inv_k;
   const float var = fmaxf(fmaf(-mu, mu, st.y * p.ln_inv_k), 0.f);
   rstd = 1.0f / sqrtf(var + p.ln_eps);
   mean = -mu * rstd;     // handed on as the shift factor: result = acc * rstd + colsum * (-mean * rstd)
+}
+__device__ __forceinline__ void ln_row_stats(const TcParams& p, long long gm, float& mean, float& rstd) {
+  if (!p.ln_stats || gm >= p.m) return;
+  ln_stats_finish(p, ln_stats_fetch(p, gm), mean, rstd);
 }
 // Folded layer_norm, producer side. A row's (sum, sum of squares) is accumulated from the partial sums of the CTAs
 // that store pieces of it. The partials are converted to 2^-28 fixed point and added with 64-bit integer atomics:
@@ -893,6 +900,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quarter = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
+    // folded layer_norm: a row's statistics are fetched one tile ahead (the load of the next tile's row is in flight
+    // during this tile's epilogue), so their latency is never on the path between two tiles
+    auto tile_row = [&](long long tt) -> long long {
+      if (tt >= num_tiles) return -1;
+      const int rem_ = (int)(tt % tiles_per_batch);
+      return (long long)((rem_ % p.tiles_m) * (2 * BM) + (int)rank * BM) + quarter * 32 + lane;
+    };
+    longlong2 stats_next = ln_stats_fetch(p, tile_row(first_tile));
     for (long long t = first_tile; t < num_tiles && ok; t += tile_step) {
       int batch = (int)(t / tiles_per_batch);
       int rem = (int)(t % tiles_per_batch);
@@ -900,6 +915,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int n0 = (rem / p.tiles_m) * BN;
       const int pair = (warp - 2) >> 2;
       long long row0 = (long long)m0 + quarter * 32;
+      const longlong2 stats_cur = stats_next;
+      stats_next = ln_stats_fetch(p, tile_row(t + tile_step));
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
       if (p.bias && !p.c_f32) {
@@ -925,7 +942,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual) + c_off, row0 + lane, n0 + pair * 32, rpre);
       // folded layer_norm: this row's statistics are fetched (and turned into scale and shift) before the accumulator wait too
       float ln_mean = 0.f, ln_rstd = 1.f;
-      ln_row_stats(p, row0 + lane, ln_mean, ln_rstd);
+      if (row0 + lane < p.m) ln_stats_finish(p, stats_cur, ln_mean, ln_rstd);
       __syncwarp();
 #ifdef AG_GEMM_PROBE
       long long pe0 = clock64();
