@@ -454,8 +454,14 @@ __global__ void __launch_bounds__(256) add_bias_rows_kernel(const T* __restrict_
         }
         break;
       case Act::GeluErf:
+        if (std::is_same<T, __nv_bfloat16>::value) {
+          // the same function as the GEMM epilogue's, so the fused and the unfused linear layer agree
 #pragma unroll
-        for (int i = 0; i < U * N; i++) v[i] = gelu_erf_f(v[i]);
+          for (int i = 0; i < U * N; i++) v[i] = gelu_erf_bf16_f(v[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < U * N; i++) v[i] = gelu_erf_f(v[i]);
+        }
         break;
       case Act::Relu:
 #pragma unroll

@@ -361,8 +361,13 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
       }
       break;
     case Act::GeluErf:
+      if (std::is_same<T, __nv_bfloat16>::value) {
 #pragma unroll
-      for (int e = 0; e < 32; e++) v[e] = gelu_erf_fast_f(v[e]);
+        for (int e = 0; e < 32; e++) v[e] = gelu_erf_bf16_f(v[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++) v[e] = gelu_erf_fast_f(v[e]);
+      }
       break;
     case Act::Relu:
 #pragma unroll

@@ -409,6 +409,12 @@ def run_b200(args):
     g_launch = sum(v["launches"] for v in gemm.values())
     achieved = g_flops / (g_ms / 1e3) / 1e12 if g_ms > 0 else None
     total_ms = sum(v["ms"] for v in rep.values())
+    # second reading: the untimed-by-events step minus the bracketed times of everything that is not a GEMM (attention,
+    # layer_norm, embedding, argmax). Bracketing a launch exposes its launch latency and prologue, so this bound errs the
+    # other way from `achieved`: the GEMM family's true in-pipeline rate lies between the two.
+    other_ms = sum(v["ms"] for k, v in rep.items() if not k.startswith(("fused_linear", "matmul"))) / prof_steps
+    step_ms = ms / args.steps
+    by_sub = g_flops / prof_steps / ((step_ms - other_ms) / 1e3) / 1e12 if step_ms > other_ms > 0 else None
     roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05, all linear layers + LM head)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
@@ -419,6 +425,9 @@ def run_b200(args):
                 "traffic": gemm_traffic_bytes(), "traffic_unit": "bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum, mean over the GEMM launches of one forward; null = not captured for this revision)",
                 "launches_per_step": g_launch / prof_steps, "avg_launch_ms": g_ms / max(g_launch, 1),
                 "share_of_step": g_ms / prof_steps / (ms / args.steps),
+                "achieved_by_subtraction": by_sub, "frac_by_subtraction": (by_sub / peaks["bf16_tflops"]) if by_sub else None,
+                "by_subtraction": "GEMM flops / (device-timed step - event-bracketed time of every non-GEMM kernel): the GEMM launches keep their programmatic overlap, the others lose theirs, so this reads high where `achieved` reads low",
+                "folded_layer_norm": "23 of the 25 layer_norm launches run inside these GEMMs' epilogues (row statistics out of out-proj / FC2, correction in QKV / FC1): their time is counted here, their flops are not",
                 "timing": "CUDA events around every GEMM launch of the forward, in situ (other kernels not bracketed); an event pair costs each launch its programmatic-launch overlap with its neighbours",
                 "per_kernel_ms_per_step": {k: round(v["ms"] / prof_steps, 4) for k, v in sorted(rep.items(), key=lambda kv: -kv[1]["ms"])}}
 
