@@ -553,6 +553,15 @@ def matmul_path(a, b):
     return r.decode()
 
 
+_TILE_CODES = {"auto": 0, "pair256": 1256, "pair192": 1192, "pair128": 1128, "s256": 256, "s192": 192, "s128": 128}
+
+
+def set_gemm_tile(name="auto"):
+    """Pin the tile shape of the tensor-core GEMM (a tuning and test override): CTA-pair tiles 256 x {256, 192, 128}
+    (192 for K-major weights only) or single-CTA tiles 128 x {256, 192, 128}; "auto" picks by modelled cost."""
+    _L().applegpu_set_gemm_tile(_TILE_CODES[name])
+
+
 def set_sm_margin(n=0):
     """Keep `n` SMs out of the persistent kernels' grids (room for a collective on another stream); 0 uses every SM."""
     _L().applegpu_set_sm_margin(int(n))

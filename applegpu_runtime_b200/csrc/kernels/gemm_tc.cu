@@ -686,10 +686,11 @@ template <int BN> struct PairCfg {
   static constexpr int kBBytes = (BN / 2) * BK * 2;         // this CTA's half of B, one k-block
   static constexpr int kKbBytes = kABytes + kBBytes;
   static constexpr int kStageBytes = kPairKbPerStage * kKbBytes;
-  static constexpr int kStages = (BN == 256) ? 3 : 4;
+  static constexpr int kStages = (BN == 128) ? 4 : 3;
   static constexpr int kSmemBytes = kStages * kStageBytes + kStgBytes + bias_bytes(BN) + scale_bytes(BN) + 1024;
   static_assert(kSmemBytes + 512 <= 232448, "dynamic + static shared memory must fit the 227 KB a CTA may use");
-  static constexpr int kTmemCols = 2 * BN;                  // two accumulator buffers
+  static constexpr int kAccStride = (BN == 192) ? 256 : BN; // column distance between the two accumulator buffers
+  static constexpr int kTmemCols = 2 * kAccStride;          // two accumulator buffers (a power of two)
 };
 
 // W8 = the B operand is an int8 [N, K] weight (per-output-channel symmetric quantisation): the dequantisation
@@ -824,7 +825,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef AG_GEMM_PROBE
         long long pc1 = clock64(); pr_wait += pc1 - pc0;
 #endif
-        uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        uint32_t tmem_d = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
         for (int r = 0; r < rounds; r++) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, 3)) { ok = false; break; }
           tc_fence_after_sync();
@@ -957,7 +958,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef AG_GEMM_PROBE
       long long pe1 = clock64();
 #endif
-      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
       uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
       unsigned long long best_key = 0;
       float row_sum = 0.f, row_sq = 0.f;
@@ -1230,18 +1231,22 @@ static bool g_direct_store = [] { const char* v = std::getenv("APPLEGPU_GEMM_DIR
 static int g_tile_override = 0;   // APPLEGPU_GEMM_TILE / set_gemm_tile: 0 auto, else pair*1000 + bn
 static TileChoice choose_tile(const GemmDesc& d, long long nb, int force_path) {
   struct Cand { bool pair; int bn; int step; };
-  // cycles per k-step (64 deep) of one CTA's tile, measured on a B200 with the kernel's own cycle probes
-  static const Cand cands[5] = {{true, 256, 530}, {true, 128, 400}, {false, 256, 780}, {false, 192, 640}, {false, 128, 590}};
+  // cycles per k-step (64 deep) of one CTA's tile, measured on a B200 with the kernel's own cycle probes (pair 192:
+  // interpolated). The 256 x 192 pair tile exists for K-major B only: each CTA loads half of the B tile, and 96 columns
+  // are not a whole number of 64-column swizzle atoms of an N-major operand.
+  static const Cand cands[6] = {{true, 256, 530}, {true, 192, 465}, {true, 128, 400}, {false, 256, 780}, {false, 192, 640}, {false, 128, 590}};
+  const bool b_kmajor = classify_b(d) != 2;
   const long long num_kb = (d.k + BK - 1) / BK;
   const bool pair_ok = d.m > BM && force_path != 3;
   if (g_tile_override) {
     TileChoice t{g_tile_override >= 1000, g_tile_override % 1000};
-    if (!t.pair || pair_ok) return t;
+    if ((!t.pair || pair_ok) && !(t.pair && t.bn == 192 && !b_kmajor)) return t;
   }
   TileChoice best{false, 128};
   long long best_cost = -1;
   for (const Cand& c : cands) {
     if (c.pair && !pair_ok) continue;
+    if (c.pair && c.bn == 192 && !b_kmajor) continue;
     if (!c.pair && force_path == 4 && pair_ok) continue;
     if (c.bn != 128 && d.n <= 128) continue;
     const long long bm = c.pair ? 2 * BM : BM;
@@ -1309,6 +1314,7 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   (d.dtype == DType::BF16 ? launch_tc_pair<BNV, MN, __nv_bfloat16>(s, ma, mb, p, num_tiles) : launch_tc_pair<BNV, MN, __half>(s, ma, mb, p, num_tiles))
   if (use_pair) {
     if (bn == 256) return b_mn ? AG_TCP(256, true) : AG_TCP(256, false);
+    if (bn == 192 && !b_mn) return AG_TCP(192, false);
     return b_mn ? AG_TCP(128, true) : AG_TCP(128, false);
   }
 #undef AG_TCP
@@ -1332,11 +1338,12 @@ static int initial_force_path() {
 }
 static const int g_force_path_init = (g_force_path = initial_force_path());
 void set_matmul_path(int mode) { g_force_path = mode; }
-// APPLEGPU_GEMM_TILE=pair256|pair128|s256|s192|s128 pins the tile shape of the tensor-core kernel (a tuning override).
+// APPLEGPU_GEMM_TILE=pair256|pair192|pair128|s256|s192|s128 pins the tile shape of the tensor-core kernel (a tuning override).
 static int initial_tile_override() {
   const char* v = std::getenv("APPLEGPU_GEMM_TILE");
   if (!v) return 0;
   if (std::strcmp(v, "pair256") == 0) return 1256;
+  if (std::strcmp(v, "pair192") == 0) return 1192;   // K-major B only
   if (std::strcmp(v, "pair128") == 0) return 1128;
   if (std::strcmp(v, "s256") == 0) return 256;
   if (std::strcmp(v, "s192") == 0) return 192;

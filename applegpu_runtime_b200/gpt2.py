@@ -116,10 +116,25 @@ def fold_gpt2_layer_norms(model):
             colsum = gpu.from_numpy(wf.to_numpy().astype(np.float64).sum(0).astype(np.float32))
             cbias = gpu.cast(gpu.from_numpy((beta.astype(np.float64) @ w0.astype(np.float64) + b0).astype(np.float32)), dtype)
             cbias.eval()
+            if lin.endswith(".mlp.c_fc"):
+                wf = _kmajor_copy(wf)          # stored [N, K]; the forward takes the transposed view
             fold[lin] = (wf, colsum, cbias)
+        # the two projections back to the 768-wide stream: N = 768 fills the 74 CTA pairs of the GEMM in 1.73 waves of
+        # 256 x 192 tiles, a shape the kernel has for K-major weights only (see _kmajor_copy)
+        for lin in (f"{p}.attn.c_proj", f"{p}.mlp.c_proj"):
+            fold[lin] = _kmajor_copy(w[f"{lin}.weight"])
     model["ln_fold"] = fold
     model["_ln_stats"] = {}
     return model
+
+
+def _kmajor_copy(w):
+    """A contiguous [N, K] copy of the [K, N] weight `w`: the same values stored K-major (what the tied LM head already
+    is), for which the GEMM has its 256 x 192 CTA-pair tile. The forward multiplies with gpu.transpose(copy), a view."""
+    wt = gpu.transpose(w)
+    wt = gpu.reshape(wt, wt.shape)   # materialise [N, K] contiguous
+    wt.eval()
+    return wt
 
 
 def _row_stats(model, rows):
@@ -264,11 +279,11 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
             x = x + ffn
         else:
             # x += attn @ W + b, and ln_2's row statistics of the new x; ln_1's (already consumed) are cleared
-            x = gpu.linear_fused(attn, w[f"{p}.attn.c_proj.weight"], bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
+            x = gpu.linear_fused(attn, gpu.transpose(fold[f"{p}.attn.c_proj"]), bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
             wf, colsum, cbias = fold[f"{p}.mlp.c_fc"]
-            ffn = gpu.linear_fused(x, wf, bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
+            ffn = gpu.linear_fused(x, gpu.transpose(wf), bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
             # x += ffn @ W + b, ln_1's statistics for the next block (none after the last: ln_f is a kernel), ln_2's cleared
-            x = gpu.linear_fused(ffn, w[f"{p}.mlp.c_proj.weight"], bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
+            x = gpu.linear_fused(ffn, gpu.transpose(fold[f"{p}.mlp.c_proj"]), bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
                                  stats_out=stats1 if i + 1 < n_layer else None, stats_zero=stats2)
 
     x = gpu.layer_norm(x, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"])

@@ -105,12 +105,14 @@ def bench_matmul(rng, dtype, b, m, n, k, iters, opt):
     return {"op": "matmul", "dtype": dtype, "shape": [b, m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
-def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt):
-    """x @ W + b, then GELU or a residual add: one fused_linear launch (the four linears of a GPT-2 layer)."""
+def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt, kmajor=False):
+    """x @ W + b, then GELU or a residual add: one fused_linear launch (the four linears of a GPT-2 layer). `kmajor`:
+    the weight is stored [n, k] and read through a transposed view."""
     e = gpu.dtype_size(dtype)
     sets = []
     for _ in range(_nsets((m * k + k * n + (2 if residual else 1) * m * n) * e, opt.rotate)):
-        sets.append((_tensor(rng, (m, k), dtype), _tensor(rng, (k, n), dtype, 0.02), _tensor(rng, (m, n), dtype) if residual else None))
+        w = gpu.transpose(_tensor(rng, (n, k), dtype, 0.02)) if kmajor else _tensor(rng, (k, n), dtype, 0.02)
+        sets.append((_tensor(rng, (m, k), dtype), w, _tensor(rng, (m, n), dtype) if residual else None))
     bias = _tensor(rng, (n,), dtype)
 
     def make(x, w, r):
@@ -123,7 +125,7 @@ def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt):
 
     ms = _time([make(*t) for t in sets], iters, single=opt.single)
     flops = 2.0 * m * n * k
-    name = "fused_linear[bias" + (",gelu_erf" if act == "erf" else ",gelu" if act else "") + (",residual" if residual else "") + "]"
+    name = "fused_linear[bias" + (",gelu_erf" if act == "erf" else ",gelu" if act else "") + (",residual" if residual else "") + "]" + (" (B K-major)" if kmajor else "")
     return {"op": name, "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
@@ -214,6 +216,10 @@ def main(argv=None):
             for (m, n, k, act, res) in [(8192, 2304, 768, False, False), (8192, 768, 768, False, True), (8192, 3072, 768, True, False),
                                         (8192, 768, 3072, False, True)]:
                 out.append(bench_fused_linear(rng, dt, m, n, k, act, res, args.iters, args))
+        if args.op == "gpt2_linears_kmajor" and dt != "float32":
+            for (m, n, k, act, res) in [(8192, 2304, 768, False, False), (8192, 768, 768, False, True), (8192, 3072, 768, True, False),
+                                        (8192, 768, 3072, False, True)]:
+                out.append(bench_fused_linear(rng, dt, m, n, k, act, res, args.iters, args, kmajor=True))
         if args.op == "linears" and dt != "float32":
             # the four linears of a transformer layer at --shape rows,width (BERT-base: 131072,768 with --act erf)
             rows, d = shape or [131072, 768]

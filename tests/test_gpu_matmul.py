@@ -99,6 +99,32 @@ def test_matmul_cta_pair_tiles(gpu_dev, dtype, m, n, k, kmajor):
     assert rel_err(got, one.astype(np.float64)) <= 1e-3
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m,n,k", [(8192, 768, 768), (2048, 768, 3072), (4100, 776, 200), (300, 200, 64)])
+def test_matmul_cta_pair_192_wide_tiles_kmajor(gpu_dev, dtype, m, n, k):
+    """The 256 x 192 CTA-pair tile (K-major weights: N = 768 fills 74 CTA pairs in 1.73 waves instead of 2.6 or 1.3),
+    pinned; bias and residual in the epilogue, ragged M and N, against fp64 and against the single-CTA kernel."""
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((n, k)).astype(np.float32)
+    bias = rng.standard_normal(n).astype(np.float32)
+    res = rng.standard_normal((m, n)).astype(np.float32)
+    ga, gw, gb, gr = up(gpu_dev, a, dtype), up(gpu_dev, w, dtype), up(gpu_dev, bias, dtype), up(gpu_dev, res, dtype)
+    ref = rounded(a, dtype).astype(np.float64) @ rounded(w, dtype).astype(np.float64).T + rounded(bias, dtype).astype(np.float64) + rounded(res, dtype).astype(np.float64)
+    outs = {}
+    for tile in ("pair192", "s128"):
+        gpu_dev.set_gemm_tile(tile)
+        try:
+            y = gr + gpu_dev.add_bias(ga @ gpu_dev.transpose(gw), gb)
+            assert "fused_linear[bias,residual,]" in y.plan()
+            outs[tile] = y.to_numpy().astype(np.float32)
+        finally:
+            gpu_dev.set_gemm_tile("auto")
+    assert rel_err(outs["pair192"], ref) <= 6e-3
+    assert rel_err(outs["pair192"], outs["s128"].astype(np.float64)) <= 1e-3
+    assert gpu_dev.pipeline_status() == 0
+
+
 @pytest.fixture
 def pair_path(gpu_dev):
     gpu_dev.set_matmul_path("tcgen05_pair")
