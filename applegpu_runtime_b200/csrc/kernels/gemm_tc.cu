@@ -138,6 +138,19 @@ __device__ __forceinline__ void load_residual_row(const TcParams& p, const T* R,
 //   p.vec_ok == 1  rows are 16-byte aligned: results are transposed through the warp's staging tile and stored with
 //                  4 lanes per row (64 contiguous bytes per row per instruction)
 //   p.vec_ok == 0  unaligned rows (a dense 50257-wide LM head): staged, 32 consecutive elements per instruction
+// Two 16-bit floats in one register, for the epilogue paths that work on rounded values pairwise.
+template <typename T> struct Packed2;
+template <> struct Packed2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ type from_floats(float lo, float hi) { return __floats2bfloat162_rn(lo, hi); }
+  static __device__ __forceinline__ float low_to_float(type v) { return __low2float(v); }
+};
+template <> struct Packed2<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ type from_floats(float lo, float hi) { return __floats2half2_rn(lo, hi); }
+  static __device__ __forceinline__ float low_to_float(type v) { return __low2float(v); }
+};
+
 // Packed fp32 pipe: two independent operations per instruction on a 64-bit register pair.
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t r;
@@ -380,6 +393,38 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
     // Key = order-preserving bits of the value in the high word, inverted column in the low word: the
     // larger key is the larger value, or the lower column among equals. NaNs are never selected,
     // except in column 0, which then keeps the row (the serial scan's behaviour).
+    if (col0 > 0 && col0 + 32 <= p.n) {
+      // Whole group inside the matrix and away from column 0: work on the rounded values two at a time. Packed
+      // converts, a tree of packed maxima (a NaN operand loses to a number, as in the scan), then the lowest column
+      // whose rounded value equals the maximum (compared as numbers: +0 and -0 tie, as in the scan): ~90
+      // instructions for 32 columns instead of ~350.
+      using T2 = typename Packed2<T>::type;
+      T2 pk[16];
+#pragma unroll
+      for (int w = 0; w < 16; w++) pk[w] = Packed2<T>::from_floats(v[2 * w], v[2 * w + 1]);
+      T2 mx[8];
+#pragma unroll
+      for (int w = 0; w < 8; w++) mx[w] = __hmax2(pk[w], pk[w + 8]);
+#pragma unroll
+      for (int w = 0; w < 4; w++) mx[w] = __hmax2(mx[w], mx[w + 4]);
+      mx[0] = __hmax2(__hmax2(mx[0], mx[2]), __hmax2(mx[1], mx[3]));
+      const T2 top = __hmax2(mx[0], __lowhigh2highlow(mx[0]));     // both halves: the group's maximum
+      int first = -1;
+#pragma unroll
+      for (int w = 15; w >= 0; w--) {
+        const unsigned eq = __heq2_mask(pk[w], top);                // 0xFFFF per half that equals the maximum
+        if (eq & 0xffff0000u) first = 2 * w + 1;
+        if (eq & 0x0000ffffu) first = 2 * w;
+      }
+      if (first >= 0) {                                             // an all-NaN group has no candidate
+        const float r = Packed2<T>::low_to_float(top);
+        const uint32_t b = __float_as_uint(r);
+        const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+        const unsigned long long key = ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - (uint32_t)(col0 + first));
+        if (key > best_key) best_key = key;
+      }
+      return;
+    }
 #pragma unroll
     for (int e = 0; e < 32; e++) {
       int col = col0 + e;
