@@ -191,6 +191,7 @@ EXT_SYMBOLS = {
     "applegpu_gpt2_decoder_steps": (i32, [u64, u32, vp, cbool]),
     "applegpu_gpt2_decoder_launches_per_step": (i32, [u64]),
     "applegpu_gpt2_decoder_uses_graph": (i32, [u64]),
+    "applegpu_gpt2_decoder_set_engine": (i32, [u64, i32]),
     "applegpu_gpt2_decoder_destroy": (None, [u64]),
     "applegpu_test_wait_runs_out": (i32, [i32, u32]),
 }

@@ -26,7 +26,8 @@ class Gpt2Decoder {
   // weights: wte, wpe, ln_f.weight, ln_f.bias, then per layer ln_1.{weight,bias}, c_attn.{weight,bias}, attn c_proj.{weight,bias},
   // ln_2.{weight,bias}, c_fc.{weight,bias}, mlp c_proj.{weight,bias}
   std::vector<TensorRec> w;
-  std::shared_ptr<Buffer> kv, act, small;
+  std::shared_ptr<Buffer> kv, act, small, layer_table;
+  int engine = 0;                     // 0: one kernel per op (default, faster); 1: the layers as one persistent cooperative kernel
   cudaGraphExec_t exec = nullptr;
   int launches_per_step = 0;
   int prompt_len = 0, steps_done = 0;
@@ -49,8 +50,9 @@ class Gpt2Decoder {
   uint8_t* ff() const { return act_at((size_t)cfg.batch * d() * 7 + 640); }
   uint8_t* logits() const { return act_at((size_t)cfg.batch * d() * 11 + 768); }
   size_t act_bytes() const { return ((size_t)cfg.batch * d() * 11 + 1024) * esz() + (size_t)cfg.batch * cfg.vocab * 4 + 4096; }
-  // small: counters {step, len} | tok [B] | pos_ids [B] | keys u64 [B] | history [max_len, B]
+  // small: counters {step, len} | grid barrier word (offset 128) | tok [B] | pos_ids [B] | keys u64 [B] | history [max_len, B]
   int* counters() const { return static_cast<int*>(small->ptr); }
+  unsigned int* barrier_word() const { return reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(small->ptr) + 128); }
   int32_t* tok() const { return reinterpret_cast<int32_t*>(static_cast<uint8_t*>(small->ptr) + 256); }
   int32_t* pos_ids() const { return reinterpret_cast<int32_t*>(static_cast<uint8_t*>(small->ptr) + 256 + 4 * 1024); }
   unsigned long long* keys() const { return reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(small->ptr) + 256 + 8 * 1024); }
@@ -86,14 +88,38 @@ class Gpt2Decoder {
   TView v2(void* p, int64_t rows, int64_t cols) const { return TView::make(p, dtype, {rows, cols}); }
 
   // One decode step: consumes tok / pos_ids, appends to the caches at *len, leaves the next token in tok.
+  // The device table of per-layer weight and cache pointers the persistent kernel walks (built once).
+  Status ensure_layer_table(cudaStream_t s) {
+    if (layer_table) return Status::OK();
+    const size_t bytes = k::decode_layers_table_bytes(cfg.n_layer);
+    std::vector<uint8_t> host(bytes);
+    for (int l = 0; l < cfg.n_layer; l++) {
+      const void* w12[12];
+      for (int i = 0; i < 12; i++) w12[i] = w[4 + 12 * (size_t)l + i].data();
+      k::decode_layers_fill_entry(host.data(), l, w12, kcache(l), vcache(l));
+    }
+    AG_RETURN_IF_ERROR(Shared::get().pool.acquire(bytes, &layer_table));
+    cudaError_t e = cudaMemcpyAsync(layer_table->ptr, host.data(), bytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);   // `host` goes out of scope
+    if (e != cudaSuccess) { layer_table.reset(); return Status::compute(std::string("decoder: layer table: ") + cudaGetErrorString(e)); }
+    return Status::OK();
+  }
+
   Status enqueue_step(cudaStream_t s) {
     launches_per_step = 0;
     const int B = cfg.batch, D = d();
+    uint8_t* cur = x();
+    uint8_t* other = x2();
+    if (engine == 1) {
+      // embeddings and all layers: one cooperative launch (plus the memset that clears its barrier word)
+      AG_RETURN_IF_ERROR(k::decode_layers(s, dtype, layer_table->ptr, cfg.n_layer, cfg.n_head, D, cfg.max_len, B, w[0].data(), w[1].data(), tok(), pos_ids(),
+                                          counters() + 1, x(), x2(), att(), barrier_word(), k::matmul_status_word()));
+      launches_per_step += 2;
+      return enqueue_head(s, cur);
+    }
     TView tokv = TView::make(tok(), DType::I32, {B}), posv = TView::make(pos_ids(), DType::I32, {B});
     AG_RETURN_IF_ERROR(k::embedding_add(s, w[0].view(), tokv, w[1].view(), posv, v2(x(), B, D)));
     launches_per_step++;
-    uint8_t* cur = x();
-    uint8_t* other = x2();
     const float scale = 1.0f / std::sqrt(64.0f);
     for (int l = 0; l < cfg.n_layer; l++) {
       const TensorRec* lw = &w[4 + 12 * l];
@@ -105,6 +131,12 @@ class Gpt2Decoder {
       AG_RETURN_IF_ERROR(linear(s, ff(), 4 * D, lw[10], lw[11], cur, D, k::Act::None, other));      // x + c_proj(gelu(c_fc))
       launches_per_step += 1;
     }
+    return enqueue_head(s, cur);
+  }
+
+  // ln_f, the tied LM head with the greedy pick, and the step's bookkeeping.
+  Status enqueue_head(cudaStream_t s, uint8_t* cur) {
+    const int B = cfg.batch, D = d();
     AG_RETURN_IF_ERROR(k::layer_norm(s, v2(cur, B, D), w[2].view(), w[3].view(), 1e-5f, v2(xn(), B, D)));
     launches_per_step++;
     // tied LM head: wte [V, d] read as the K-major operand; greedy pick = first index of the row maximum
@@ -213,6 +245,7 @@ Status decoder_steps(uint64_t handle, int n_steps, int32_t* host_tokens, bool us
   DeviceCtx& ctx = DeviceCtx::get();
   AG_RETURN_IF_ERROR(ctx.make_current());
   extern std::atomic<uint64_t> g_launch_count;
+  if (dec->engine == 1) AG_RETURN_IF_ERROR(dec->ensure_layer_table(ctx.stream));
   int first = 0;
   if (use_graph && !dec->exec) {
     // The very first step runs launch by launch (one-time kernel attributes are set outside any capture); then one
@@ -255,6 +288,21 @@ Status decoder_steps(uint64_t handle, int n_steps, int32_t* host_tokens, bool us
   hist.has_meta = true;
   dec->steps_done += n_steps;
   return download(hist, host_tokens, (size_t)n_steps * c.batch * 4, true);   // waits, and reports a timed-out tensor-core wait
+}
+
+// engine 0: one kernel per op; 1: the layers as one persistent cooperative kernel. A captured step of the other engine is dropped.
+Status decoder_set_engine(uint64_t handle, int engine) {
+  std::lock_guard<std::mutex> g(g_dec_mu);
+  Gpt2Decoder* dec = find_decoder(handle);
+  if (!dec) return Status::invalid("decoder: unknown handle");
+  if (engine != 0 && engine != 1) return Status::invalid("decoder: engine must be 0 or 1");
+  if (engine != dec->engine) {
+    DeviceCtx& ctx = DeviceCtx::get();
+    if (ctx.ready && !ctx.dry) cudaStreamSynchronize(ctx.stream);
+    if (dec->exec) { cudaGraphExecDestroy(dec->exec); dec->exec = nullptr; }
+    dec->engine = engine;
+  }
+  return Status::OK();
 }
 
 int decoder_launches_per_step(uint64_t handle) {

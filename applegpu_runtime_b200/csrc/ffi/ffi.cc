@@ -26,6 +26,7 @@ Status decoder_prefill(uint64_t handle, const std::vector<TensorRec>& kvs, const
 Status decoder_steps(uint64_t handle, int n_steps, int32_t* host_tokens, bool use_graph);
 int decoder_launches_per_step(uint64_t handle);
 int decoder_uses_graph(uint64_t handle);
+Status decoder_set_engine(uint64_t handle, int engine);
 void decoder_destroy(uint64_t handle);
 namespace k {
 void set_matmul_path(int mode);
@@ -1338,6 +1339,11 @@ int32_t applegpu_gpt2_decoder_steps(uint64_t decoder, uint32_t n_steps, int32_t*
 }
 int32_t applegpu_gpt2_decoder_launches_per_step(uint64_t decoder) { return decoder_launches_per_step(decoder); }
 int32_t applegpu_gpt2_decoder_uses_graph(uint64_t decoder) { return decoder_uses_graph(decoder); }
+int32_t applegpu_gpt2_decoder_set_engine(uint64_t decoder, int32_t engine) {
+  Status s = decoder_set_engine(decoder, engine);
+  if (!s.ok()) { set_ffi_error("gpt2_decoder_set_engine failed: " + s.to_string()); return -1; }
+  return 0;
+}
 void applegpu_gpt2_decoder_destroy(uint64_t decoder) { decoder_destroy(decoder); }
 
 int32_t applegpu_test_wait_runs_out(int32_t code, uint32_t limit_us) {

@@ -147,6 +147,13 @@ Status attention_f32(cudaStream_t s, const AttnDesc& d);
 // Fixed workspace of the kernel layer (pipeline status word + pinned mirror, skinny-GEMM partials):
 // created once, when the device context is set up, so that no op call allocates.
 Status init_device_workspace(cudaStream_t s);
+int* matmul_status_word();          // the pipeline status word (a bounded wait that gives up records its code there)
+// The layers of a GPT-2 decode step as one cooperative persistent kernel (decode.cu); `layers` is a device table built with
+// decode_layers_fill_entry on the host (12 weight pointers per layer in the decoder's order, then the layer's caches).
+Status decode_layers(cudaStream_t s, DType dt, const void* layers, int n_layer, int heads, int d, int t_max, int batch, const void* wte, const void* wpe,
+                     const int32_t* tok, const int32_t* pos, const int* len_ptr, void* x, void* x2, void* att, unsigned int* bar, int* err);
+size_t decode_layers_table_bytes(int n_layer);
+void decode_layers_fill_entry(void* host_table, int l, const void* const* w12, void* kcache, void* vcache);
 // Pipeline status word of the tcgen05 kernels: a bounded wait that gives up records a code there.
 // status_snapshot enqueues a copy into pinned slot `slot` (0 .. status_slots()-1); once the stream, or
 // an event recorded after the snapshot, has been waited for, status_take returns the value and, when

@@ -81,6 +81,13 @@ class Gpt2Decoder:
             raise ValueError(gpu._err())
         return out
 
+    def set_engine(self, persistent=False):
+        """persistent=False (the default): one kernel per op, chained by programmatic dependent launches; True: the
+        embeddings and all layers of a step run as one cooperative kernel with grid-wide barriers between phases (same
+        arithmetic, same tokens; measured slower, kept as an option)."""
+        if self._lib.applegpu_gpt2_decoder_set_engine(self.handle, 1 if persistent else 0) != 0:
+            raise ValueError(gpu._err())
+
     @property
     def launches_per_step(self):
         return int(self._lib.applegpu_gpt2_decoder_launches_per_step(self.handle))
@@ -106,22 +113,24 @@ def greedy_generate(model, input_ids, max_tokens=50, use_cache=True, compiled=Tr
 
     With the cache and `engine` "auto" or "graph", the prompt runs through gpt2_forward and the decode steps through
     the library's decoder: a preallocated KV cache appended in place and one captured step replayed per token
-    ("graph"; "direct" issues the same launches one by one). `engine="tape"` keeps the cache the reference's way
+    ("graph"; "direct" issues the same launches one by one; "persistent" and "persistent_direct" run the layers of a
+    step as one cooperative kernel instead of one kernel per op). `engine="tape"` keeps the cache the reference's way
     (concatenation, models/gpt2.py:122-127) and replays an op tape per step (`compiled`), the picked token staying
     on the device between steps. Models the decoder does not take (int8 weights, head dimension other than 64,
     more than 16 sequences) use the tape engine."""
     ids = np.asarray(input_ids, dtype=np.int64)
     if ids.ndim == 1:
         ids = ids.reshape(1, -1)
-    if use_cache and max_tokens > 1 and engine in ("auto", "graph", "direct") and Gpt2Decoder.supports(model, ids.shape[0], ids.shape[1] + max_tokens):
+    if use_cache and max_tokens > 1 and engine in ("auto", "graph", "direct", "persistent", "persistent_direct") and Gpt2Decoder.supports(model, ids.shape[0], ids.shape[1] + max_tokens):
         B, T0 = ids.shape
         logits, kv = gpt2_forward(model, ids, kv_cache=None, last_only=True)      # prefill of the prompt
         first = gpu.argmax(logits)
         del logits
         dec = Gpt2Decoder(model, B, T0 + max_tokens)
         try:
+            dec.set_engine(persistent=engine.startswith("persistent"))
             dec.prefill(kv, first, T0)
-            rest = dec.steps(max_tokens - 1, use_graph=(engine != "direct"))
+            rest = dec.steps(max_tokens - 1, use_graph=engine in ("auto", "graph", "persistent"))
             model["_last_decoder_stats"] = {"launches_per_step": dec.launches_per_step, "graph": dec.uses_graph}
         finally:
             dec.close()

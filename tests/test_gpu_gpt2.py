@@ -136,6 +136,10 @@ def test_graph_decoder_matches_the_concat_cache_engine(gpu_dev, dtype):
     direct = gpu_dev.greedy_generate(m, ids, max_tokens=24, use_cache=True, engine="direct")
     assert graph.shape == (5, 33)
     assert stats["graph"] is True and stats["launches_per_step"] <= 7 * CFG_MID["n_layer"] + 8
+    # the layers of a step as one cooperative kernel with grid-wide barriers: the per-op kernels' arithmetic in their order
+    persistent = gpu_dev.greedy_generate(m, ids, max_tokens=24, use_cache=True, engine="persistent")
+    assert m["_last_decoder_stats"]["launches_per_step"] <= 8    # barrier reset + layers kernel, ln_f, LM head, pick, bookkeeping
+    assert graph.tolist() == persistent.tolist()
     if dtype == "float32":
         assert graph.tolist() == tape.tolist() == direct.tolist()
         with torch.no_grad():
