@@ -567,6 +567,16 @@ def set_sm_margin(n=0):
     _L().applegpu_set_sm_margin(int(n))
 
 
+def set_gemm_chain(on=True):
+    """Chained linears: consecutive 16-bit fused linears of one evaluation, each reading the previous one's result, go
+    out as one tensor-core launch (bit-identical results). On by default; APPLEGPU_GEMM_CHAIN=0 starts with it off."""
+    _L().applegpu_set_gemm_chain(bool(on))
+
+
+def gemm_chain_enabled():
+    return bool(_L().applegpu_gemm_chain_enabled())
+
+
 def set_f32_split(on=True):
     """Large float32 matmuls as a three-term bf16 split on the tensor cores (default) or always on CUDA cores."""
     _L().applegpu_set_f32_split(bool(on))

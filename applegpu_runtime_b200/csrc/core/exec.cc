@@ -97,6 +97,80 @@ std::string report() {
 
 #define AG_LAUNCH(expr) do { AG_RETURN_IF_ERROR(expr); g_launch_count.fetch_add(1, std::memory_order_relaxed); } while (0)
 
+// ── chained linears ──────────────────────────────────────────────────────────
+// Inside one evaluation (LazyRuntime::eval opens a ChainScope) a fused linear that the chained tensor-core kernel can take
+// is not launched at once but held back; while the next node is again such a linear that reads the held one's result, it
+// joins. Anything else (another kind of node, a linear that does not follow, four links, the end of the evaluation)
+// launches what is held: one product through k::matmul, several as ONE k::matmul_chain launch. The held products keep
+// their operands and results alive, so the pool cannot hand one of those buffers to a later link.
+namespace chain {
+struct Pending { k::GemmDesc g; std::vector<TensorRec> keep; std::string span; double work; };
+static thread_local int t_scope_depth = 0;
+static thread_local std::vector<Pending> t_pending;
+static thread_local std::string t_span;     // the profile span of the linear being executed (set by execute_node)
+static thread_local double t_work = 0;
+static bool g_enabled = [] { const char* v = std::getenv("APPLEGPU_GEMM_CHAIN"); return !(v && v[0] == '0'); }();   // APPLEGPU_GEMM_CHAIN=0 / set_gemm_chain(false): every linear is its own launch
+static bool active() { return g_enabled && t_scope_depth > 0; }
+
+static Status flush() {
+  if (t_pending.empty()) return Status::OK();
+  std::vector<Pending> p;
+  p.swap(t_pending);
+  cudaStream_t s = DeviceCtx::get().stream;
+  if (p.size() == 1) {
+    if (profile::enabled() && profile::wanted(p[0].span)) {
+      profile::Scope scope(p[0].span, p[0].work);
+      AG_LAUNCH(k::matmul(s, p[0].g));
+    } else {
+      AG_LAUNCH(k::matmul(s, p[0].g));
+    }
+    return Status::OK();
+  }
+  std::vector<k::GemmDesc> descs;
+  double work = 0;
+  for (const Pending& q : p) { descs.push_back(q.g); work += q.work; }
+  // one span for the launch, under the links' own name: a chain of n links counts as one launch doing their work
+  if (profile::enabled() && profile::wanted(p[0].span)) {
+    profile::Scope scope(p[0].span, work);
+    AG_LAUNCH(k::matmul_chain(s, descs.data(), (int)descs.size()));
+  } else {
+    AG_LAUNCH(k::matmul_chain(s, descs.data(), (int)descs.size()));
+  }
+  return Status::OK();
+}
+
+// Holds `g` back, or launches it, as described above. `keep` = every tensor the product touches.
+static Status submit(const k::GemmDesc& g, std::vector<TensorRec> keep) {
+  std::vector<k::GemmDesc> held;
+  for (const Pending& q : t_pending) held.push_back(q.g);
+  if (!t_pending.empty() && !k::matmul_chain_can_append(held.data(), (int)held.size(), g)) AG_RETURN_IF_ERROR(flush());
+  if (!k::matmul_chain_candidate(g)) {
+    AG_RETURN_IF_ERROR(flush());
+    cudaStream_t s = DeviceCtx::get().stream;
+    if (profile::enabled() && profile::wanted(t_span)) {
+      profile::Scope scope(t_span, t_work);
+      AG_LAUNCH(k::matmul(s, g));
+    } else {
+      AG_LAUNCH(k::matmul(s, g));
+    }
+    return Status::OK();
+  }
+  t_pending.push_back(Pending{g, std::move(keep), t_span, t_work});
+  if ((int)t_pending.size() == k::kChainMax) return flush();
+  return Status::OK();
+}
+}  // namespace chain
+
+void set_gemm_chain(bool on) { chain::g_enabled = on; }
+bool gemm_chain_enabled() { return chain::g_enabled; }
+ChainScope::ChainScope() { chain::t_scope_depth++; }
+ChainScope::~ChainScope() {
+  // only non-empty after an error ended the evaluation early: the held products' results are already handed out as
+  // materialised tensors, so they are still launched (best effort)
+  if (--chain::t_scope_depth == 0 && !chain::t_pending.empty()) (void)chain::flush();
+}
+Status ChainScope::finish() { return chain::flush(); }
+
 static Status alloc_out(const Dims& shape, DType dt, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
   out->shape = shape; out->strides = contiguous_strides(shape); out->dtype = dt; out->byte_offset = 0; out->has_meta = true;
   size_t nbytes = (size_t)numel_of(shape) * dtype_size(dt);
@@ -362,6 +436,16 @@ static double node_work(const OpNode& node, const std::vector<const TensorRec*>&
 
 static Status execute_node_impl(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf);
 
+// A fused linear that may be held back for chaining: 16-bit, neither the int8-weight nor the row-argmax form, and every
+// operand contiguous (so that preparing it launches no copy that would have to see a held product's result).
+static bool linear_deferrable(const OpNode& node, const std::vector<const TensorRec*>& in) {
+  if (!chain::active() || node.op.op != Op::FusedLinear || node.op.i1 == 1 || node.op.i2 == 1 || DeviceCtx::get().dry) return false;
+  if (in.size() < 2 || !(in[0]->dtype == DType::BF16 || in[0]->dtype == DType::F16) || in[1]->dtype != in[0]->dtype) return false;
+  if (in[0]->shape.size() != 2) return false;
+  for (size_t i = 0; i < in.size(); i++) if (i != 1 && !in[i]->contiguous()) return false;   // the weight may be a strided view
+  return true;
+}
+
 Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in, TensorRec* out, std::shared_ptr<Buffer> out_buf) {
   {
     // host-visible mode: the host may have read or written any operand since its last use on the device
@@ -373,6 +457,15 @@ Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& in,
   }
   // layout-only ops that return views launch nothing: no span (an event pair around nothing would only add host work)
   const bool view_only = !out_buf && (node.op.op == Op::Transpose || node.op.op == Op::Slice || node.op.op == Op::Reshape);
+  // a held-back linear is launched before any other node runs (view-only nodes launch nothing and touch no data)
+  const bool may_defer = linear_deferrable(node, in);
+  if (!view_only && !may_defer) AG_RETURN_IF_ERROR(chain::flush());
+  if (may_defer) {
+    // its span, if any, is opened where it is launched
+    chain::t_span = node.op.kernel_name() + dtype_suffix(node.out_dtype);
+    chain::t_work = profile::enabled() ? node_work(node, in) : 0.0;
+    return execute_node_impl(node, in, out, out_buf);
+  }
   if (!profile::enabled() || view_only) return execute_node_impl(node, in, out, out_buf);
   std::string name = node.op.kernel_name();
   if (node.op.op == Op::FusedElementwise) name = "fused_elementwise";
@@ -557,6 +650,12 @@ static Status execute_node_impl(const OpNode& node, const std::vector<const Tens
         bool done = false;
         AG_RETURN_IF_ERROR(matmul_f32_split(s, g, &done));
         if (done) return Status::OK();
+      }
+      if (linear_deferrable(node, in)) {
+        // held back for chaining with the linears that follow; everything it touches stays alive until it is launched
+        for (const TensorRec* t : in) keep.push_back(*t);
+        keep.push_back(*out);
+        return chain::submit(g, std::move(keep));
       }
       AG_LAUNCH(k::matmul(s, g));
       return Status::OK();

@@ -117,6 +117,7 @@ Status LazyRuntime::eval(uint64_t id) {
   order = fusion::optimize(graph_, order, keep, &deferred_free_, &minted);
   for (uint64_t m : minted) deferred_free_.insert(m);   // nobody holds a handle: dropped after the last consumer ran
 
+  ChainScope chain_scope;   // consecutive fused linears of this evaluation may go out as one chained launch
   // remaining uses inside this evaluation, to drop dead intermediates early
   for (uint64_t nid : order) {
     const OpNode* np = graph_.get_node(nid);
@@ -148,6 +149,7 @@ Status LazyRuntime::eval(uint64_t id) {
     }
     if (nid != id && deferred_free_.count(nid) && graph_.ref_count(nid) == 0) { deferred_free_.erase(nid); tensors_.erase(nid); }
   }
+  AG_RETURN_IF_ERROR(chain_scope.finish());
   // ids absorbed by the fusion pass no longer exist anywhere
   for (auto it = deferred_free_.begin(); it != deferred_free_.end();) {
     if (!graph_.has_node(*it) && !tensors_.count(*it)) it = deferred_free_.erase(it); else ++it;

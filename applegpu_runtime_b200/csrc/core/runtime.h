@@ -108,6 +108,17 @@ struct Shared {
 // Executes one node: inputs are materialised records, `out` receives the result (a fresh
 // buffer, or a view of an input for layout-only ops). `out_buf`, if set, is a caller-provided
 // destination (the *_out ABI variants).
+// While one is alive on this thread, execute_node may hold fused linears back to launch consecutive ones as one chained
+// kernel (exec.cc). finish() launches what is still held; a scope destroyed without it (an evaluation that failed) drops it.
+void set_gemm_chain(bool on);
+bool gemm_chain_enabled();
+struct ChainScope {
+  ChainScope();
+  ~ChainScope();
+  Status finish();
+  ChainScope(const ChainScope&) = delete;
+  ChainScope& operator=(const ChainScope&) = delete;
+};
 Status execute_node(const OpNode& node, const std::vector<const TensorRec*>& inputs, TensorRec* out,
                     std::shared_ptr<Buffer> out_buf = nullptr);
 Status make_contiguous(const TensorRec& in, TensorRec* out);

@@ -1208,6 +1208,8 @@ int32_t applegpu_host_visible(void) { return DeviceCtx::get().host_visible ? 1 :
 void applegpu_set_attention_path(int32_t mode) { ag::g_fused_attention = (mode != 1); }
 void applegpu_set_gemm_tile(int32_t code) { k::set_gemm_tile(code); }
 void applegpu_set_sm_margin(int32_t n) { k::set_sm_margin(n); }
+void applegpu_set_gemm_chain(bool on) { ag::set_gemm_chain(on); }
+bool applegpu_gemm_chain_enabled(void) { return ag::gemm_chain_enabled(); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return 0;

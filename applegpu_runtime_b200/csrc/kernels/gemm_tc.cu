@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "sm100.cuh"
 #include <cuda.h>
+#include <deque>
 #include <mutex>
 #include <unordered_map>
 #include <cstdlib>
@@ -170,6 +171,20 @@ __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// Two packed 16-bit floats (one 32-bit word, element 0 in the low half) -> two floats in a 64-bit pair, exactly.
+template <typename T> __device__ __forceinline__ uint64_t widen2(uint32_t w);
+template <> __device__ __forceinline__ uint64_t widen2<__nv_bfloat16>(uint32_t w) {
+  return pack_f32x2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));   // bf16 is the upper half of a float
+}
+template <> __device__ __forceinline__ uint64_t widen2<__half>(uint32_t w) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return pack_f32x2(f.x, f.y);
+}
 
 constexpr float kStatsScale = 268435456.0f;          // 2^28: row statistics travel as fixed-point int64 (see emit_row_stats)
 constexpr float kStatsUnscale = 1.0f / 268435456.0f;
@@ -219,10 +234,18 @@ __device__ __forceinline__ void emit_row_stats(const TcParams& p, long long gm, 
   if (p.stats_zero && clears) *reinterpret_cast<longlong2*>(p.stats_zero + 2 * gm) = make_longlong2(0, 0);
 }
 
+#ifdef AG_CHAIN_PROBE
+__device__ long long g_epi_probe[8];   // [0] tmem load + wait, [1] math, [2] stores, [3] groups, [4] residual prologue (CTA 0, warp 2, lane 0)
+#define AG_EPI_T(var) long long var = clock64()
+#define AG_EPI_ADD(slot, a, b) do { if (blockIdx.x == 0 && (threadIdx.x >> 5) == 2 && lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_epi_probe[slot]), (unsigned long long)((b) - (a))); } while (0)
+#else
+#define AG_EPI_T(var)
+#define AG_EPI_ADD(slot, a, b)
+#endif
 template <typename T>
 __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr, uint8_t* stg, const T* bias_s, const float* scale_s, uint32_t (&rpre)[16],
                                                long long row0, int col0, int next_col0, long long c_off, int lane, unsigned long long& best_key,
-                                               float ln_mean, float ln_rstd, float& row_sum, float& row_sq) {
+                                               float ln_mean, float ln_rstd, float& row_sum, float& row_sq, const float* bias_f = nullptr) {
   T* C = reinterpret_cast<T*>(p.c) + c_off;
   const T* R = p.residual ? reinterpret_cast<const T*>(p.residual) + c_off : nullptr;
   const int sub_row = lane >> 2, sub_chunk = lane & 3;
@@ -265,8 +288,11 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 
   // 2. accumulators -> registers
   uint32_t acc[32];
+  AG_EPI_T(t_a);
   tmem_ld_32x32(taddr, acc);
   tmem_ld_wait();
+  AG_EPI_T(t_b);
+  AG_EPI_ADD(0, t_a, t_b);
   float v[32];
 #pragma unroll
   for (int e = 0; e < 32; e++) v[e] = __uint_as_float(acc[e]);
@@ -317,6 +343,121 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
         for (int e = 0; e < 32 && col0 + e < p.n; e++) crow[e] = v[e] + (rrow ? rrow[e] : 0.f);
       }
     }
+    return;
+  }
+
+  // 3a. The common case (16-bit C with 32-byte aligned rows, results stored): the whole chain on the packed fp32 pipe,
+  //     two columns per instruction. The epilogue warps share their schedulers' issue slots with the next tile's main
+  //     loop bookkeeping and with each other, and the K = 768 products of a transformer block are bound by exactly
+  //     these instructions, so every one that goes counts. Same operations in the same order as the scalar code below
+  //     (fma.rn / add.rn / mul.rn on each half), except that the bias rides in the folded layer_norm's FMA and the
+  //     tanh-GELU polynomial is factored as x * (c0 + c1 * x^2).
+  if (direct && !p.argmax_keys && bias_f) {
+    uint64_t vp[16];
+#pragma unroll
+    for (int w = 0; w < 16; w++) vp[w] = pack_f32x2(v[2 * w], v[2 * w + 1]);
+    if (p.alpha != 1.0f) {
+      const uint64_t a2 = pack_f32x2(p.alpha, p.alpha);
+#pragma unroll
+      for (int w = 0; w < 16; w++) vp[w] = mul_f32x2(vp[w], a2);
+    }
+    if (p.ln_stats) {
+      // acc * rstd + (colsum * shift + bias)
+      const uint64_t r2 = pack_f32x2(ln_rstd, ln_rstd), sh2 = pack_f32x2(ln_mean, ln_mean);
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        const ulonglong2 cs = *reinterpret_cast<const ulonglong2*>(scale_s + g * 4);   // same address in every lane: a broadcast
+        const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(bias_f + g * 4);
+        vp[2 * g] = fma_f32x2(vp[2 * g], r2, fma_f32x2(cs.x, sh2, bb.x));
+        vp[2 * g + 1] = fma_f32x2(vp[2 * g + 1], r2, fma_f32x2(cs.y, sh2, bb.y));
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(bias_f + g * 4);
+        if (scale_s) {
+          const ulonglong2 sc = *reinterpret_cast<const ulonglong2*>(scale_s + g * 4);
+          vp[2 * g] = fma_f32x2(vp[2 * g], sc.x, bb.x);
+          vp[2 * g + 1] = fma_f32x2(vp[2 * g + 1], sc.y, bb.y);
+        } else {
+          vp[2 * g] = add_f32x2(vp[2 * g], bb.x);
+          vp[2 * g + 1] = add_f32x2(vp[2 * g + 1], bb.y);
+        }
+      }
+    }
+    if ((Act)p.act == Act::GeluTanh && std::is_same<T, __nv_bfloat16>::value) {
+      // 0.5 x (1 + tanh(x (c0 + c1 x^2))) with the hardware tanh (relative error about 2^-11, a quarter of a bf16 step)
+      const uint64_t c0 = pack_f32x2(0.7978845608f, 0.7978845608f), c1 = pack_f32x2(0.0356774081f, 0.0356774081f), half2v = pack_f32x2(0.5f, 0.5f);
+#pragma unroll
+      for (int w = 0; w < 16; w++) {
+        const uint64_t x = vp[w];
+        const uint64_t u = mul_f32x2(x, fma_f32x2(mul_f32x2(x, x), c1, c0));
+        float u0, u1, t0, t1;
+        unpack_f32x2(u, u0, u1);
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(u0));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(u1));
+        const uint64_t hx = mul_f32x2(x, half2v);
+        vp[w] = fma_f32x2(hx, pack_f32x2(t0, t1), hx);
+      }
+    } else if ((Act)p.act != Act::None) {
+#pragma unroll
+      for (int w = 0; w < 16; w++) {
+        float a, b;
+        unpack_f32x2(vp[w], a, b);
+        switch ((Act)p.act) {
+          case Act::GeluTanh: a = gelu_tanh_f(a); b = gelu_tanh_f(b); break;
+          case Act::GeluErf:
+            if (std::is_same<T, __nv_bfloat16>::value) { a = gelu_erf_bf16_f(a); b = gelu_erf_bf16_f(b); }
+            else { a = gelu_erf_fast_f(a); b = gelu_erf_fast_f(b); }
+            break;
+          case Act::Relu: a = fmaxf(a, 0.f); b = fmaxf(b, 0.f); break;
+          default: break;
+        }
+        vp[w] = pack_f32x2(a, b);
+      }
+    }
+    if (R) {
+#pragma unroll
+      for (int w = 0; w < 16; w++) vp[w] = add_f32x2(vp[w], widen2<T>(rcur[w]));
+    }
+    if (p.stats_out) {
+      if (col0 + 32 <= p.n) {
+        uint64_t s2 = 0, q2 = 0;    // the bit pattern of (0.f, 0.f)
+#pragma unroll
+        for (int w = 0; w < 16; w++) { s2 = add_f32x2(s2, vp[w]); q2 = fma_f32x2(vp[w], vp[w], q2); }
+        float s0, s1, q0, q1;
+        unpack_f32x2(s2, s0, s1); unpack_f32x2(q2, q0, q1);
+        row_sum += s0 + s1; row_sq += q0 + q1;
+      } else {
+#pragma unroll
+        for (int w = 0; w < 16; w++) unpack_f32x2(vp[w], v[2 * w], v[2 * w + 1]);
+        group_stats(p, v, col0, row_sum, row_sq);
+      }
+    }
+    uint32_t o[16];
+#pragma unroll
+    for (int w = 0; w < 16; w++) {
+      float a, b;
+      unpack_f32x2(vp[w], a, b);
+      o[w] = pack2<T>(a, b);
+    }
+    const long long gm = row0 + lane;
+    AG_EPI_T(t_c2);
+    AG_EPI_ADD(1, t_b, t_c2);
+    if (gm < p.m) {
+      T* crow = C + gm * p.c_row + col0;
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        if (col0 + 16 * j + 16 <= p.n) st_global_256(crow + 16 * j, &o[8 * j]);
+        else {
+          const T* tv = reinterpret_cast<const T*>(&o[8 * j]);
+          for (int e = 0; e < 16 && col0 + 16 * j + e < p.n; e++) crow[16 * j + e] = tv[e];
+        }
+      }
+    }
+    AG_EPI_T(t_d2);
+    AG_EPI_ADD(2, t_c2, t_d2);
+    AG_EPI_ADD(3, 0, 1);
     return;
   }
 
@@ -452,6 +593,8 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
 #pragma unroll
     for (int w = 0; w < 16; w++) o[w] = pack2<T>(v[2 * w], v[2 * w + 1]);
     const long long gm = row0 + lane;
+    AG_EPI_T(t_c);
+    AG_EPI_ADD(1, t_b, t_c);
     if (gm < p.m) {
       T* crow = C + gm * p.c_row + col0;
 #pragma unroll
@@ -463,6 +606,9 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
         }
       }
     }
+    AG_EPI_T(t_d);
+    AG_EPI_ADD(2, t_c, t_d);
+    AG_EPI_ADD(3, 0, 1);
     return;
   }
 
@@ -646,7 +792,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       long long row0 = (long long)m0 + quarter * 32;
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
-      if (p.bias && !p.c_f32) {
+      // 16-bit C with 32-byte aligned rows: the packed epilogue takes the bias as floats; they wait in the warp's staging
+      // tile, which that layout leaves unused (zeros when there is no bias)
+      const bool packed_epi = p.vec_ok == 2 && !p.c_f32 && !p.argmax_keys;
+      float* bias_f = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp);
+      if (packed_epi) {
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          bias_f[gi * 32 + lane] = (bias && ci < p.n) ? Cvt<T>::to(__ldg(bias + ci)) : 0.f;
+        }
+      } else if (p.bias && !p.c_f32) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -688,7 +845,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (n0 + g * 32 >= p.n) break;  // uniform across the warp
         int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
         epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                          c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq);
+                          c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq, packed_epi ? bias_f + gi * 32 : nullptr);
       }
       if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
       tc_fence_before_sync();
@@ -970,7 +1127,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       stats_next = ln_stats_fetch(p, tile_row(t + tile_step));
       long long c_off = (long long)(batch / p.batch_inner) * p.c_batch + (long long)(batch % p.batch_inner) * p.c_batch_inner;
       T* bias_s = reinterpret_cast<T*>(smem + STAGES * Cfg::kStageBytes + kStgBytes) + (warp - 2) * epi_slots(BN);
-      if (p.bias && !p.c_f32) {
+      // 16-bit C with 32-byte aligned rows: the packed epilogue takes the bias as floats; they wait in the warp's staging
+      // tile, which that layout leaves unused (zeros when there is no bias)
+      const bool packed_epi = p.vec_ok == 2 && !p.c_f32 && !p.argmax_keys;
+      float* bias_f = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp);
+      if (packed_epi) {
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+#pragma unroll
+        for (int gi = 0; gi < BN / 64; gi++) {
+          int ci = n0 + (pair + 2 * gi) * 32 + lane;
+          bias_f[gi * 32 + lane] = (bias && ci < p.n) ? Cvt<T>::to(__ldg(bias + ci)) : 0.f;
+        }
+      } else if (p.bias && !p.c_f32) {
         const T* bias = reinterpret_cast<const T*>(p.bias);
 #pragma unroll
         for (int gi = 0; gi < BN / 64; gi++) {
@@ -1013,7 +1181,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           if (n0 + g * 32 >= p.n) break;
           int next_col0 = (g + 2 < BN / 32 && n0 + (g + 2) * 32 < p.n) ? n0 + (g + 2) * 32 : -1;
           epilogue_group<T>(p, taddr + (uint32_t)(g * 32), stg, (p.bias && !p.c_f32) ? bias_s + gi * 32 : nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + g * 32, next_col0,
-                            c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq);
+                            c_off, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq, packed_epi ? bias_f + gi * 32 : nullptr);
         }
         }
       if (p.argmax_keys && best_key != 0 && row0 + lane < p.m) atomicMax(p.argmax_keys + row0 + lane, best_key);
@@ -1038,6 +1206,398 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   cluster_sync_all();
   tc_fence_after_sync();
   if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+}
+
+// ── chained products ────────────────────────────────────────────────────────
+// Up to kChainMax products in ONE launch of the CTA-pair kernel's pipeline, where product g + 1 reads product g's result
+// as its A operand (a transformer block's out-projection -> FC1 -> FC2 -> the next block's QKV). Run one after the
+// other, each of these short products pays its own pipeline fill, the exposed epilogue of its last tiles and a partly
+// filled last wave; chained, the tensor pipe only drains once. What makes it possible is that a 256-row block of
+// product g + 1 needs nothing but the same 256 rows of product g:
+//   tiles         every product is cut into 256 x 256 tiles, row block by row block; the host deals the tiles of all
+//                 products, in that order, to the CTA pairs (each tile to the pair with the least work so far) and
+//                 every pair walks its own list, so the roles of a pair need no run-time scheduler
+//   dependencies  when the eight epilogue warps of a CTA have stored their parts of a tile they arrive on a shared-memory
+//                 barrier; the CTA's announcer warp (one thread) waits for it, fences (proxy fence, __threadfence: the
+//                 stores it has observed through the barrier become visible GPU-wide first) and adds 8 to the counter of
+//                 (product, row block), so the fence's latency is not on the epilogue warps' path. The TMA thread of a
+//                 consumer tile waits (bounded) until the producer's row block has all its arrivals (16 per tile), then
+//                 fences the async proxy and loads. A tile only ever waits for tiles earlier in the global order, and every pair takes its
+//                 tiles in that order, so the earliest unfinished tile can always run: no cycle
+//   epilogue      row statistics and residual rows of the next tile are fetched ahead only when its row block is
+//                 already complete (its counter is read one tile earlier); otherwise after the accumulator wait
+//   counters      zero on entry; the last CTA to leave zeroes them again
+// N-major B ([K, N] weights), 16-bit types, unbatched; the epilogue is the pair kernel's (bias, activation, residual,
+// folded layer_norm on either side).
+constexpr int kChainFlagInts = kChainMax * kChainFlagStride;   // + 1 exit counter behind them
+struct ChainParams {
+  TcParams prob[kChainMax];
+  int need[kChainMax];          // arrivals of the previous product's row block a tile of product g waits for (0: none)
+  int count;
+  const int* list_off;          // [clusters + 1] into `list`
+  const int* list;              // product << 24 | tile index within the product (row-block major), in execution order
+  int* flags;                   // [kChainFlagInts + 1]
+#ifdef AG_CHAIN_PROBE
+  long long* probe;             // per CTA, 16 slots: where the roles' cycles go (compile-time diagnostic only)
+#endif
+};
+struct alignas(64) ChainMaps { CUtensorMap a[kChainMax]; CUtensorMap b[kChainMax]; };
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// A look at a counter that orders nothing by itself (an acquire load holds the warp's later memory operations back until
+// it has returned, a full L2 round trip in the middle of an epilogue): only used as a hint, see the epilogue warps.
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+// Bounded like every other wait of these kernels: gives up (recording `code`) after the limit or when another role has.
+__device__ __forceinline__ bool flag_wait(const int* f, int need, int* status, int code) {
+  if (ld_acquire_gpu(f) >= need) return true;
+  unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_gpu(f) >= need) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) { atomicCAS(status, 0, code); return false; }
+    }
+  }
+}
+// Row statistics written earlier in the same launch: read past L1 (the non-coherent path of ln_stats_fetch is for
+// data that is constant for the whole launch).
+__device__ __forceinline__ longlong2 ln_stats_fetch_cg(const TcParams& p, long long gm) {
+  if (!p.ln_stats || gm < 0 || gm >= p.m) return make_longlong2(0, 0);
+  return __ldcg(reinterpret_cast<const longlong2*>(p.ln_stats) + gm);
+}
+
+constexpr int kChainThreads = kTcThreads + 32;    // + the announcer warp
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kChainThreads, 1)
+gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ ChainParams cp) {
+  constexpr int BN = 256;
+  using Cfg = PairCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  constexpr int KBS = kPairKbPerStage;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t tmem_full_bar[2];
+  __shared__ uint64_t tmem_empty_bar[2];
+  __shared__ uint64_t stored_bar[2];        // a tile's results are stored (eight epilogue warps arrive; the announcer waits)
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int s_last;
+  __shared__ TcParams s_prob[kChainMax];
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster = blockIdx.x >> 1;
+
+  {
+    const int* src = reinterpret_cast<const int*>(cp.prob);
+    int* dst = reinterpret_cast<int*>(s_prob);
+    for (int i = threadIdx.x; i < (int)(sizeof(TcParams) / 4) * cp.count; i += blockDim.x) dst[i] = src[i];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps); mbar_init(&stored_bar[a], kEpiWarps); }
+    mbar_fence_init();
+    for (int g = 0; g < cp.count; g++) { prefetch_tmap(&maps.a[g]); prefetch_tmap(&maps.b[g]); }
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_base_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();
+  pdl_trigger();
+  const int li0 = __ldg(cp.list_off + cluster), li1 = __ldg(cp.list_off + cluster + 1);
+  int* const status = s_prob[0].status;
+#ifdef AG_CHAIN_PROBE
+  const long long probe_t0 = clock64();
+#endif
+
+  if (warp == 0) {
+    // ── TMA producer (both CTAs) ──
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int li = li0; li < li1 && ok; li++) {
+        const int e = __ldg(cp.list + li);
+        const int g = e >> 24, lt = e & 0xffffff;
+        const TcParams& p = s_prob[g];
+        const int mi = lt / p.tiles_n, ni = lt - mi * p.tiles_n;
+        const int m0 = mi * (2 * BM) + (int)rank * BM;
+        const int n0 = ni * BN + (int)rank * (BN / 2);
+        const int rounds = ((p.k + BK - 1) / BK + KBS - 1) / KBS;
+        const CUtensorMap* ta = &maps.a[g];
+        const CUtensorMap* tb = &maps.b[g];
+#ifdef AG_CHAIN_PROBE
+        long long q0 = clock64();
+#endif
+        if (cp.need[g] > 0) {
+          // the rows this tile reads are another tile's results: wait for them, then order the generic-proxy view this
+          // thread has just acquired before the async-proxy reads it is about to issue
+          if (!flag_wait(cp.flags + (g - 1) * kChainFlagStride + mi, cp.need[g], status, 6)) { ok = false; break; }
+          fence_proxy_async_global();
+        }
+#ifdef AG_CHAIN_PROBE
+        if (cp.probe) { cp.probe[blockIdx.x * 16 + 0] += clock64() - q0; cp.probe[blockIdx.x * 16 + 8 + g] += clock64() - q0; }
+#endif
+        for (int r = 0; r < rounds; r++) {
+#ifdef AG_CHAIN_PROBE
+          long long q1 = clock64();
+#endif
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, 1)) { ok = false; break; }
+#ifdef AG_CHAIN_PROBE
+          if (cp.probe) cp.probe[blockIdx.x * 16 + 1] += clock64() - q1;
+#endif
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          const uint32_t bar = mapa_u32(smem_u32(&full_bar[stage]), 0);
+#pragma unroll
+          for (int j = 0; j < KBS; j++) {
+            const int kc = (r * KBS + j) * BK;
+            uint8_t* sa = smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes;
+            uint8_t* sb = sa + Cfg::kABytes;
+            tma_load_4d_pair(sa, ta, bar, kc, m0, 0, 0);
+#pragma unroll
+            for (int q = 0; q < BN / 128; q++)
+              tma_load_4d_pair(sb + q * (64 * BK * 2), tb, bar, n0 + q * 64, kc, 0, 0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ── MMA issuer (even CTA only) ──
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(std::is_same<T, __nv_bfloat16>::value ? 1 : 0, 0, 1, 2 * BM, BN);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int li = li0; li < li1 && ok; li++) {
+        const int g = __ldg(cp.list + li) >> 24;
+        const int rounds = ((s_prob[g].k + BK - 1) / BK + KBS - 1) / KBS;
+#ifdef AG_CHAIN_PROBE
+        long long q0 = clock64();
+#endif
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, status, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+#ifdef AG_CHAIN_PROBE
+        if (cp.probe) { cp.probe[blockIdx.x * 16 + 2] += clock64() - q0; cp.probe[blockIdx.x * 16 + 4] += rounds; }
+#endif
+        uint32_t tmem_d = tmem_base + (uint32_t)(acc * Cfg::kAccStride);
+        for (int r = 0; r < rounds; r++) {
+#ifdef AG_CHAIN_PROBE
+          long long q1 = clock64();
+#endif
+          if (!mbar_wait(&full_bar[stage], phase, status, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+#ifdef AG_CHAIN_PROBE
+          if (cp.probe) cp.probe[blockIdx.x * 16 + 3] += clock64() - q1;
+#endif
+#pragma unroll
+          for (int j = 0; j < KBS; j++) {
+            uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes + j * Cfg::kKbBytes);
+            uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; kk++) {
+              uint64_t da = make_smem_desc_sw128(sa + kk * (UMMA_K * 2), 16, 1024);
+              uint64_t db = make_smem_desc_sw128(sb + kk * (UMMA_K * 128), 64 * 128, 1024);
+              mma_f16_ss_pair(tmem_d, da, db, idesc, (r > 0 || j > 0 || kk > 0) ? 1u : 0u);
+            }
+          }
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          mma_commit_pair(mapa_u32(eb, 0));
+          mma_commit_pair(mapa_u32(eb, 1));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t fb = smem_u32(&tmem_full_bar[acc]);
+        mma_commit_pair(mapa_u32(fb, 0));
+        mma_commit_pair(mapa_u32(fb, 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (warp == 2 + kEpiWarps) {
+    // ── announcer (both CTAs): tile by tile, "this CTA's rows of the tile are stored" -> the row block's counter ──
+    if (lane == 0) {
+      int slot = 0; uint32_t parity = 0;
+      for (int li = li0; li < li1; li++) {
+        const int e = __ldg(cp.list + li);
+        const int g = e >> 24, lt = e & 0xffffff;
+        if (!mbar_wait(&stored_bar[slot], parity, status, 8)) break;
+        fence_proxy_async_global();
+        __threadfence();
+        atomicAdd(cp.flags + g * kChainFlagStride + lt / s_prob[g].tiles_n, kEpiWarps);
+        if (++slot == 2) { slot = 0; parity ^= 1; }
+      }
+    }
+  } else {
+    // ── epilogue warps (both CTAs; each reads its own 128 accumulator lanes) ──
+    const int quarter = warp & 3;
+    const int pair = (warp - 2) >> 2;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    bool fetched = false;            // this tile's row statistics and first residual group are already in registers
+    longlong2 stats_raw = make_longlong2(0, 0);
+    uint32_t rpre[16];
+    int e_next = li0 < li1 ? __ldg(cp.list + li0) : -1;
+    int e_next2 = li0 + 1 < li1 ? __ldg(cp.list + li0 + 1) : -1;   // list entries are read two tiles ahead: nothing waits for them
+    T col_bias[BN / 64];                         // the next tile's bias and column sums of this lane's columns, one tile ahead
+    float col_sum[BN / 64];                      // (as loaded: a conversion here would wait for the load)
+    auto fetch_cols = [&](int e_) {
+      const int g_ = e_ >> 24, lt_ = e_ & 0xffffff;
+      const TcParams& q = s_prob[g_];
+      const int n0_ = (lt_ % q.tiles_n) * BN;
+      const T* bias = reinterpret_cast<const T*>(q.bias);
+      const float* cs = q.ln_stats ? q.ln_colsum : nullptr;
+#pragma unroll
+      for (int gi = 0; gi < BN / 64; gi++) {
+        const int ci = n0_ + (pair + 2 * gi) * 32 + lane;
+        col_bias[gi] = (bias && ci < q.n) ? __ldg(bias + ci) : Cvt<T>::from(0.f);
+        col_sum[gi] = (cs && ci < q.n) ? __ldg(cs + ci) : 0.f;
+      }
+    };
+    if (e_next >= 0) fetch_cols(e_next);
+    int fv_next = 0;                 // the dependency counter of the next tile, read one tile ahead
+    if (e_next >= 0 && cp.need[e_next >> 24] > 0) {
+      const int g_ = e_next >> 24, lt_ = e_next & 0xffffff;
+      fv_next = ld_relaxed_gpu(cp.flags + (g_ - 1) * kChainFlagStride + lt_ / s_prob[g_].tiles_n);
+    }
+    for (int li = li0; li < li1 && ok; li++) {
+#ifdef AG_CHAIN_PROBE
+      const long long q_top = clock64();
+#endif
+      const int e = e_next;
+      const int fv = fv_next;
+      const int g = e >> 24, lt = e & 0xffffff;
+      // a copy in registers: fields read through a pointer into shared memory would be loaded again after every
+      // store and tensor-memory load of the epilogue (their asm statements clobber memory)
+      TcParams p;
+      {
+        const TcParams& sp = s_prob[g];
+        p.c = sp.c; p.bias = sp.bias; p.residual = sp.residual; p.b_scales = nullptr; p.alpha = sp.alpha; p.act = sp.act;
+        p.m = sp.m; p.n = sp.n; p.k = sp.k; p.batch = 1; p.batch_inner = 1; p.c_row = sp.c_row; p.c_batch = 0; p.c_batch_inner = 0;
+        p.a_bcast = 0; p.b_bcast = 0; p.tiles_m = sp.tiles_m; p.tiles_n = sp.tiles_n; p.vec_ok = sp.vec_ok; p.bias_vec = sp.bias_vec;
+        p.argmax_keys = nullptr; p.c_f32 = 0; p.ln_stats = sp.ln_stats; p.ln_colsum = sp.ln_colsum; p.ln_inv_k = sp.ln_inv_k; p.ln_eps = sp.ln_eps;
+        p.stats_out = sp.stats_out; p.stats_zero = sp.stats_zero; p.status = status;
+      }
+      const int mi = lt / p.tiles_n, ni = lt - mi * p.tiles_n;
+      const int need = cp.need[g];
+      e_next = e_next2;
+      e_next2 = li + 2 < li1 ? __ldg(cp.list + li + 2) : -1;
+      fv_next = 0;
+      if (e_next >= 0 && cp.need[e_next >> 24] > 0) {
+        const int g_ = e_next >> 24, lt_ = e_next & 0xffffff;
+        fv_next = ld_relaxed_gpu(cp.flags + (g_ - 1) * kChainFlagStride + lt_ / s_prob[g_].tiles_n);
+      }
+      const int m0 = mi * (2 * BM) + (int)rank * BM;
+      const int n0 = ni * BN;
+      const long long row0 = (long long)m0 + quarter * 32;
+      // this tile's bias and column sums were fetched into registers one tile ago; they go to shared memory as floats (the
+      // packed epilogue reads them as broadcasts; the staging tile is unused with 32-byte aligned rows)
+      float* bias_f = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp);
+      float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
+      const float* fsrc = p.ln_stats ? p.ln_colsum : nullptr;
+#pragma unroll
+      for (int gi = 0; gi < BN / 64; gi++) { bias_f[gi * 32 + lane] = Cvt<T>::to(col_bias[gi]); scale_s[gi * 32 + lane] = col_sum[gi]; }
+      if (e_next >= 0) fetch_cols(e_next);
+      const bool res_ahead = p.residual && p.vec_ok == 2 && n0 + pair * 32 < p.n;
+      // `fv` is a relaxed look at the counter taken one tile ago. Seeing it complete, the loads below are issued after
+      // it (they depend on the branch), go to L2 (the statistics) or to lines this SM has not touched in this launch (the
+      // residual rows), and the producer's stores were GPU-visible before the counter moved: they read the final values.
+      if (!fetched && (need == 0 || fv >= need)) {
+        stats_raw = ln_stats_fetch_cg(p, row0 + lane);
+        if (res_ahead) load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual), row0 + lane, n0 + pair * 32, rpre);
+        fetched = true;
+      }
+      __syncwarp();
+#ifdef AG_CHAIN_PROBE
+      long long q0 = clock64();
+      long long q1 = q0;
+#endif
+      if (!__all_sync(0xffffffffu, mbar_wait(&tmem_full_bar[acc], acc_phase, status, 4))) { ok = false; break; }
+      tc_fence_after_sync();
+#ifdef AG_CHAIN_PROBE
+      long long q2 = clock64();
+      if (cp.probe && warp == 2 && lane == 0) { cp.probe[blockIdx.x * 16 + 15] += q0 - q_top; cp.probe[blockIdx.x * 16 + 5] += q1 - q0; cp.probe[blockIdx.x * 16 + 6] += q2 - q1; cp.probe[blockIdx.x * 16 + 12] += fetched ? 0 : 1; }
+#endif
+      if (!fetched) {
+        // This pair's TMA thread acquired the row block's counter before it loaded the tile's operands, and the full
+        // accumulator this warp has just waited for follows those loads through the pipeline's barriers: the producer's
+        // stores are ordered before these reads without another look at the counter.
+        stats_raw = ln_stats_fetch_cg(p, row0 + lane);
+        if (res_ahead) load_residual_row<T>(p, reinterpret_cast<const T*>(p.residual), row0 + lane, n0 + pair * 32, rpre);
+      }
+      fetched = false;
+      float ln_mean = 0.f, ln_rstd = 1.f;
+      if (row0 + lane < p.m) ln_stats_finish(p, stats_raw, ln_mean, ln_rstd);
+      uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
+      uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      unsigned long long best_key = 0;
+      float row_sum = 0.f, row_sq = 0.f;
+      if (row0 < p.m) {
+#pragma unroll 1
+        for (int gg = pair, gi = 0; gg < BN / 32; gg += 2, gi++) {
+          if (n0 + gg * 32 >= p.n) break;
+          int next_col0 = (gg + 2 < BN / 32 && n0 + (gg + 2) * 32 < p.n) ? n0 + (gg + 2) * 32 : -1;
+          epilogue_group<T>(p, taddr + (uint32_t)(gg * 32), stg, nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + gg * 32, next_col0,
+                            0, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq, bias_f + gi * 32);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[acc]), 0));
+      if (row0 < p.m) emit_row_stats(p, row0 + lane, n0 == 0 && pair == 0, row_sum, row_sq);
+      __syncwarp();                                   // every lane's stores and atomics are issued: the announcer takes over
+      if (lane == 0) mbar_arrive(&stored_bar[acc]);
+      // the next tile's statistics and first residual rows, if its row block is known to be complete
+      if (e_next >= 0) {
+        const int gn = e_next >> 24, ltn = e_next & 0xffffff;
+        const TcParams& pn = s_prob[gn];
+        if (cp.need[gn] == 0 || fv_next >= cp.need[gn]) {
+          const int min_ = ltn / pn.tiles_n, nin = ltn - min_ * pn.tiles_n;
+          const long long rown = (long long)(min_ * (2 * BM) + (int)rank * BM) + quarter * 32;
+          stats_raw = ln_stats_fetch_cg(pn, rown + lane);
+          if (pn.residual && pn.vec_ok == 2 && nin * BN + pair * 32 < pn.n)
+            load_residual_row<T>(pn, reinterpret_cast<const T*>(pn.residual), rown + lane, nin * BN + pair * 32, rpre);
+          fetched = true;
+        }
+      }
+#ifdef AG_CHAIN_PROBE
+      if (cp.probe && warp == 2 && lane == 0) { cp.probe[blockIdx.x * 16 + 7] += clock64() - q2; cp.probe[blockIdx.x * 16 + 13] += 1; }
+#endif
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+#ifdef AG_CHAIN_PROBE
+  if (cp.probe && threadIdx.x == 0) cp.probe[blockIdx.x * 16 + 14] += clock64() - probe_t0;
+#endif
+  // the last CTA to get here has seen every other one finish with the counters: it zeroes them for the next launch
+  if (threadIdx.x == 0) { __threadfence(); s_last = atomicAdd(cp.flags + kChainFlagInts, 1) == (int)gridDim.x - 1 ? 1 : 0; }
+  __syncthreads();
+  if (s_last) {
+    for (int i = threadIdx.x; i < cp.count * kChainFlagStride; i += blockDim.x) cp.flags[i] = 0;
+    if (threadIdx.x == 0) cp.flags[kChainFlagInts] = 0;
+  }
 }
 
 // ── host side ───────────────────────────────────────────────────────────────
@@ -1369,6 +1929,223 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
   if (bn == 192) return b_mn ? AG_TC(192, true) : AG_TC(192, false);
   return b_mn ? AG_TC(128, true) : AG_TC(128, false);
 #undef AG_TC
+}
+
+// ── chained products, host side ─────────────────────────────────────────────
+#ifdef AG_CHAIN_PROBE
+long long* g_chain_probe = nullptr;   // set by a probe harness
+void chain_epi_probe(long long* out) { cudaMemcpyFromSymbol(out, g_epi_probe, sizeof(long long) * 8); }
+#endif
+bool matmul_chain_candidate(const GemmDesc& d) {
+  if (g_force_path == 1 || g_force_path == 3 || g_tile_override) return false;
+  if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
+  if (!tc_eligible(d) || classify_b(d) != 2) return false;
+  if (d.batch != 1 || d.batch_inner != 1 || d.c_f32 || d.ep.argmax_keys || d.ep.b_scales || d.ln_gamma) return false;
+  if (d.ep.ln_stats && !d.ep.ln_colsum) return false;
+  if (d.m <= BM || !d.c) return false;
+  // C (and residual) rows 32-byte aligned: the epilogue's one-row-per-lane layout, the only one the chained kernel has
+  auto al32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
+  if (!g_direct_store || !al32(d.c) || d.c_row % 16 != 0 || (d.ep.residual && !al32(d.ep.residual))) return false;
+  const long long tiles_m = (d.m + 2 * BM - 1) / (2 * BM), tiles_n = (d.n + 255) / 256;
+  return tiles_m <= kChainFlagStride && tiles_m * tiles_n < (1 << 24);
+}
+
+namespace {
+// What a product reads and writes, as byte ranges. Row-wise buffers (activations, statistics) may be shared between the
+// products of a chain when they are the SAME rows (same base, pitch and width): row block m of a later product only
+// runs after row block m of every earlier one. Anything else that overlaps a written buffer is refused.
+enum ChainBufKind { kBufA, kBufB, kBufBias, kBufResidual, kBufColsum, kBufLnStats, kBufC, kBufStatsOut, kBufStatsZero };
+struct ChainBuf { const uint8_t* lo; const uint8_t* hi; ChainBufKind kind; int64_t pitch, width; bool written, rowwise; };
+int chain_bufs(const GemmDesc& d, ChainBuf* out) {
+  int n = 0;
+  auto add = [&](const void* p, int64_t bytes, ChainBufKind kind, int64_t pitch, int64_t width, bool written, bool rowwise) {
+    if (!p) return;
+    const uint8_t* lo = static_cast<const uint8_t*>(p);
+    out[n++] = ChainBuf{lo, lo + bytes, kind, pitch, width, written, rowwise};
+  };
+  add(d.a, ((d.m - 1) * d.a_row + d.k) * 2, kBufA, d.a_row, d.k, false, true);
+  add(d.b, ((d.k - 1) * d.b_row + d.n) * 2, kBufB, d.b_row, d.n, false, false);
+  add(d.ep.bias, d.n * 2, kBufBias, 0, d.n, false, false);
+  add(d.ep.residual, ((d.m - 1) * d.c_row + d.n) * 2, kBufResidual, d.c_row, d.n, false, true);
+  add(d.ep.ln_colsum, d.n * 4, kBufColsum, 0, d.n, false, false);
+  add(d.ep.ln_stats, d.m * 16, kBufLnStats, 2, 2, false, true);
+  add(d.c, ((d.m - 1) * d.c_row + d.n) * 2, kBufC, d.c_row, d.n, true, true);
+  add(d.ep.stats_out, d.m * 16, kBufStatsOut, 2, 2, true, true);
+  add(d.ep.stats_zero, d.m * 16, kBufStatsZero, 2, 2, true, true);
+  return n;
+}
+bool chain_same_rows(const ChainBuf& x, const ChainBuf& y) {
+  return x.rowwise && y.rowwise && x.lo == y.lo && x.pitch == y.pitch && x.width == y.width;
+}
+}  // namespace
+
+bool matmul_chain_can_append(const GemmDesc* chain, int count, const GemmDesc& next) {
+  if (count < 1 || count >= kChainMax || !matmul_chain_candidate(next)) return false;
+  const GemmDesc& prev = chain[count - 1];
+  if (next.dtype != chain[0].dtype || next.m != chain[0].m) return false;
+  if (next.a != prev.c || next.a_row != prev.c_row || next.k != prev.n) return false;
+  ChainBuf nb[9], hb[9];
+  const int nn = chain_bufs(next, nb);
+  for (int h = 0; h < count; h++) {
+    const int hn = chain_bufs(chain[h], hb);
+    for (int i = 0; i < nn; i++) {
+      for (int j = 0; j < hn; j++) {
+        const ChainBuf& x = nb[i];
+        const ChainBuf& y = hb[j];
+        if (!(x.written || y.written) || x.hi <= y.lo || y.hi <= x.lo) continue;
+        if (!chain_same_rows(x, y)) return false;
+        if (x.kind == kBufA && !(h == count - 1 && y.kind == kBufC)) return false;   // A is the previous result and nothing else
+        if (x.kind == kBufC && y.kind == kBufC) return false;
+        if (x.kind == kBufStatsOut && (y.kind == kBufStatsOut || y.kind == kBufLnStats)) return false;
+      }
+    }
+  }
+  return true;
+}
+
+namespace {
+struct ChainListKey {
+  int64_t m; int count, clusters; int64_t n[kChainMax], k[kChainMax]; int cost[kChainMax];
+  bool operator==(const ChainListKey& o) const { return std::memcmp(this, &o, sizeof(ChainListKey)) == 0; }
+};
+struct ChainList { ChainListKey key; int off_ints; int total; std::vector<int> host; };
+std::mutex g_chain_mu;
+std::deque<ChainList> g_chain_lists;     // deque: the host copies stay where they are while an upload may still read them
+int g_chain_arena_used = 0;
+
+// Modelled cycles of one tile: the main loop at the tensor rate, or the epilogue where that is longer (K = 768).
+int chain_tile_cost(const GemmDesc& d) {
+  const int num_kb = (int)((d.k + BK - 1) / BK);
+  int epi = 5200;
+  if (d.ep.act != Act::None) epi += 1600;
+  if (d.ep.residual) epi += 400;
+  if (d.ep.ln_stats) epi += 300;
+  if (d.ep.stats_out) epi += 400;
+  const int main_loop = num_kb * 520;
+  return main_loop > epi ? main_loop : epi;
+}
+
+// The tiles of all products in dependency order (product by product, row block by row block), each given to the pair
+// that has the least modelled work so far. Returns the device address of [offsets (clusters + 1) | entries].
+Status chain_list_for(cudaStream_t s, const GemmDesc* chain, int count, int clusters, const int** d_off, const int** d_list) {
+  ChainListKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.m = chain[0].m; key.count = count; key.clusters = clusters;
+  for (int g = 0; g < count; g++) { key.n[g] = chain[g].n; key.k[g] = chain[g].k; key.cost[g] = chain_tile_cost(chain[g]); }
+  int* arena = chain_arena();
+  if (!arena) return Status::compute("matmul: the kernel workspace is not initialised");
+  std::lock_guard<std::mutex> lock(g_chain_mu);
+  for (const ChainList& l : g_chain_lists) {
+    if (l.key == key) { *d_off = arena + l.off_ints; *d_list = arena + l.off_ints + clusters + 1; return Status::OK(); }
+  }
+  const int64_t tiles_m = (chain[0].m + 2 * BM - 1) / (2 * BM);
+  int64_t total = 0;
+  for (int g = 0; g < count; g++) total += tiles_m * ((chain[g].n + 255) / 256);
+  const int64_t ints = clusters + 1 + total;
+  if (ints > kChainArenaInts) return Status::unsupported("matmul: chained products with too many tiles");
+  if (g_chain_arena_used + ints > kChainArenaInts) {
+    // start over; launches that read the old lists are ahead of the upload below in stream order
+    g_chain_lists.clear();
+    g_chain_arena_used = 0;
+  }
+  // Global order = product after product, row block after row block. (A wavefront over groups of row blocks, so that
+  // consumers trail their producers by a step, was measured slower: 123 us per GPT-2-small layer with one group, 141 /
+  // 177 / 258 us with 4 / 8 / 16: with a few tiles per pair and step every step boundary becomes a dependency stall.)
+  std::vector<std::vector<int>> per(clusters);
+  std::vector<long long> load(clusters, 0);
+  for (int g = 0; g < count; g++) {
+    const int64_t tn = (chain[g].n + 255) / 256;
+    for (int64_t t = 0; t < tiles_m * tn; t++) {
+      int best = 0;
+      for (int c = 1; c < clusters; c++) if (load[c] < load[best]) best = c;
+      per[best].push_back((g << 24) | (int)t);
+      load[best] += key.cost[g];
+    }
+  }
+  g_chain_lists.emplace_back();
+  ChainList& l = g_chain_lists.back();
+  l.key = key; l.off_ints = g_chain_arena_used; l.total = (int)total;
+  l.host.reserve((size_t)ints);
+  int run = 0;
+  for (int c = 0; c < clusters; c++) { l.host.push_back(run); run += (int)per[c].size(); }
+  l.host.push_back(run);
+  for (int c = 0; c < clusters; c++) l.host.insert(l.host.end(), per[c].begin(), per[c].end());
+  cudaError_t e = cudaMemcpyAsync(arena + l.off_ints, l.host.data(), (size_t)ints * sizeof(int), cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) { g_chain_lists.pop_back(); return cuda_status(e, "matmul (chained): tile list upload"); }
+  g_chain_arena_used += (int)ints;
+  *d_off = arena + l.off_ints; *d_list = arena + l.off_ints + clusters + 1;
+  return Status::OK();
+}
+
+template <typename T>
+int chain_clusters() {
+  static int cached = -1;
+  if (cached >= 0) return cached;
+  auto kern = gemm_tc_chain_kernel<T>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<256>::kSmemBytes) != cudaSuccess) { cudaGetLastError(); return cached = 0; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * (sm_count() / 2)), 1, 1);
+  cfg.blockDim = dim3(kChainThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg<256>::kSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  return cached = n;
+}
+}  // namespace
+
+Status matmul_chain(cudaStream_t s, const GemmDesc* chain, int count) {
+  if (count < 2 || count > kChainMax) return Status::invalid("matmul (chained): 2.." + std::to_string(kChainMax) + " products");
+  for (int g = 0; g < count; g++) {
+    if (!matmul_chain_candidate(chain[g])) return Status::invalid("matmul (chained): product " + std::to_string(g) + " cannot be chained");
+    if (g > 0 && !matmul_chain_can_append(chain, g, chain[g])) return Status::invalid("matmul (chained): product " + std::to_string(g) + " does not follow the one before");
+  }
+  int* st = matmul_status_word();
+  int* flags = chain_flags();
+  if (!st || !flags) return Status::compute("matmul: the kernel workspace is not initialised");
+  const bool bf16 = chain[0].dtype == DType::BF16;
+  int clusters = bf16 ? chain_clusters<__nv_bfloat16>() : chain_clusters<__half>();
+  if (clusters > sm_count() / 2) clusters = sm_count() / 2;   // sm_count() leaves out the SMs kept free for a collective
+  if (clusters <= 0) return Status::compute("matmul (chained): no resident cluster available");
+  ChainMaps maps;
+  ChainParams cp;
+  std::memset(&cp, 0, sizeof(cp));
+  cp.count = count;
+  cp.flags = flags;
+#ifdef AG_CHAIN_PROBE
+  cp.probe = g_chain_probe;
+#endif
+  const int64_t tiles_m = (chain[0].m + 2 * BM - 1) / (2 * BM);
+  auto al16p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  auto al32p = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31u) == 0; };
+  for (int g = 0; g < count; g++) {
+    const GemmDesc& d = chain[g];
+    AG_RETURN_IF_ERROR(make_map(&maps.a[g], d.dtype, d.a, (uint64_t)d.k, (uint64_t)d.m, 1, 1, (uint64_t)d.a_row, 0, 0, BK, BM));
+    AG_RETURN_IF_ERROR(make_map(&maps.b[g], d.dtype, d.b, (uint64_t)d.n, (uint64_t)d.k, 1, 1, (uint64_t)d.b_row, 0, 0, 64, BK));
+    TcParams& p = cp.prob[g];
+    p.c = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.b_scales = nullptr; p.alpha = d.ep.alpha; p.act = (int)d.ep.act;
+    p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k; p.batch = 1; p.batch_inner = 1;
+    p.c_row = d.c_row; p.c_batch = 0; p.c_batch_inner = 0; p.a_bcast = 0; p.b_bcast = 0;
+    p.tiles_m = (int)tiles_m; p.tiles_n = (int)((d.n + 255) / 256); p.status = st;
+    p.argmax_keys = nullptr; p.c_f32 = 0;
+    p.ln_stats = d.ep.ln_stats; p.ln_colsum = d.ep.ln_colsum; p.ln_inv_k = d.k ? 1.0f / (float)d.k : 0.f; p.ln_eps = d.ep.ln_eps;
+    p.stats_out = d.ep.stats_out; p.stats_zero = d.ep.stats_zero;
+#ifdef AG_GEMM_PROBE
+    p.probe = nullptr;
+#endif
+    p.vec_ok = (al16p(d.c) && d.c_row % 8 == 0 && (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
+    if (p.vec_ok && g_direct_store && al32p(d.c) && d.c_row % 16 == 0 && (!d.ep.residual || al32p(d.ep.residual))) p.vec_ok = 2;
+    p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
+    cp.need[g] = g == 0 ? 0 : 2 * kEpiWarps * cp.prob[g - 1].tiles_n;   // every epilogue warp of both CTAs, every tile of the row block
+  }
+  AG_RETURN_IF_ERROR(chain_list_for(s, chain, count, clusters, &cp.list_off, &cp.list));
+  cudaError_t le = bf16 ? launch_pdl(gemm_tc_chain_kernel<__nv_bfloat16>, dim3(2 * clusters), dim3(kChainThreads), PairCfg<256>::kSmemBytes, s, maps, cp)
+                        : launch_pdl(gemm_tc_chain_kernel<__half>, dim3(2 * clusters), dim3(kChainThreads), PairCfg<256>::kSmemBytes, s, maps, cp);
+  if (le != cudaSuccess) return cuda_status(le, "matmul (tcgen05, chained)");
+  return Status::OK();
 }
 
 // APPLEGPU_MATMUL_PATH=simt|tcgen05|tcgen05_1cta|tcgen05_pair sets the initial value of the path switch.

@@ -106,6 +106,21 @@ struct GemmDesc {
   GemmEpilogue ep;
 };
 Status matmul(cudaStream_t s, const GemmDesc& d);
+// Chained products: up to kChainMax unbatched 16-bit products with [K, N] weights, each reading the previous one's
+// result as its A operand, as ONE launch of the tensor-core kernel (a 256-row block of product g + 1 only needs the same
+// rows of product g, so tiles of consecutive products overlap and the pipeline fills and drains once).
+//   matmul_chain_candidate   d could be a link of a chain
+//   matmul_chain_can_append  `next` may follow chain[0 .. count): it reads chain[count - 1]'s result, and no buffer of
+//                            one product overlaps a buffer another one writes except row block by row block
+//   matmul_chain             launches them (count >= 2; results are those of `matmul` on each in turn, bit for bit)
+constexpr int kChainMax = 4;
+constexpr int kChainFlagStride = 1024;       // row blocks of 256 rows per product
+constexpr int kChainArenaInts = 1 << 18;     // tile lists kept on the device
+bool matmul_chain_candidate(const GemmDesc& d);
+bool matmul_chain_can_append(const GemmDesc* chain, int count, const GemmDesc& next);
+Status matmul_chain(cudaStream_t s, const GemmDesc* chain, int count);
+int* chain_flags();
+int* chain_arena();
 // int8 [N, K] weights against f16 / bf16 activations: true when the tensor-core kernel takes the int8 operand as it
 // lies and widens it in its own prologue (per-channel scales in the epilogue); false when the caller has to hand the
 // kernel a 16-bit copy instead (a single row block, K not a multiple of 16, unaligned operands).

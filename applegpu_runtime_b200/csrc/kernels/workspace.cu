@@ -3,7 +3,8 @@
 // a stream-ordered forward):
 //   * the pipeline status word of the tcgen05 kernels (a bounded wait that gives up records a code
 //     there) with a pinned host mirror, so a synchronisation point can read it with a plain load;
-//   * the partial-sum workspace and the slab counters of the skinny GEMM.
+//   * the partial-sum workspace and the slab counters of the skinny GEMM;
+//   * the arrival counters and the tile lists of the chained tensor-core products.
 // Also holds the test-only kernel that lets a bounded wait run out on purpose: it waits on an mbarrier
 // that nothing arrives at, with a limit of about a millisecond, records its code and returns.
 #include "common.cuh"
@@ -17,6 +18,8 @@ constexpr int kStatusSlots = 128;            // pinned mirror: slot 0 for blocki
 constexpr size_t kStatusRegion = 256;        // the status word sits alone in its 256-byte line
 constexpr size_t kSkCounterBytes = (65536 / 64) * sizeof(unsigned int);
 constexpr size_t kSkPartialBytes = ((size_t)1 << 18) * 16 * sizeof(float);   // k_slabs * n * 16 rows of fp32
+constexpr size_t kChainFlagBytes = ((size_t)kChainMax * kChainFlagStride + 64) * sizeof(int);   // counters + the exit counter
+constexpr size_t kChainArenaBytes = (size_t)kChainArenaInts * sizeof(int);
 
 uint8_t* g_block = nullptr;
 int* g_status_host = nullptr;
@@ -26,11 +29,12 @@ std::mutex g_mu;
 Status init_device_workspace(cudaStream_t s) {
   std::lock_guard<std::mutex> g(g_mu);
   if (g_block) return Status::OK();
-  const size_t total = kStatusRegion + kSkCounterBytes + kSkPartialBytes;
+  // status word | skinny counters | chain counters (these three are cleared) | skinny partials | chain tile lists
+  const size_t total = kStatusRegion + kSkCounterBytes + kChainFlagBytes + kSkPartialBytes + kChainArenaBytes;
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, total);
   if (e != cudaSuccess) return cuda_status(e, "kernel workspace");
-  e = cudaMemsetAsync(p, 0, kStatusRegion + kSkCounterBytes, s);
+  e = cudaMemsetAsync(p, 0, kStatusRegion + kSkCounterBytes + kChainFlagBytes, s);
   if (e != cudaSuccess) { cudaFree(p); return cuda_status(e, "kernel workspace clear"); }
   void* h = nullptr;
   e = cudaMallocHost(&h, kStatusSlots * sizeof(int));
@@ -43,7 +47,9 @@ Status init_device_workspace(cudaStream_t s) {
 
 int* matmul_status_word() { return reinterpret_cast<int*>(g_block); }
 unsigned int* skinny_counters() { return g_block ? reinterpret_cast<unsigned int*>(g_block + kStatusRegion) : nullptr; }
-float* skinny_partials() { return g_block ? reinterpret_cast<float*>(g_block + kStatusRegion + kSkCounterBytes) : nullptr; }
+int* chain_flags() { return g_block ? reinterpret_cast<int*>(g_block + kStatusRegion + kSkCounterBytes) : nullptr; }
+float* skinny_partials() { return g_block ? reinterpret_cast<float*>(g_block + kStatusRegion + kSkCounterBytes + kChainFlagBytes) : nullptr; }
+int* chain_arena() { return g_block ? reinterpret_cast<int*>(g_block + kStatusRegion + kSkCounterBytes + kChainFlagBytes + kSkPartialBytes) : nullptr; }
 int status_slots() { return kStatusSlots; }
 
 // Enqueues a copy of the status word into pinned slot `slot`; the value is defined once the stream

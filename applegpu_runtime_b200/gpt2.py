@@ -104,6 +104,10 @@ def fold_gpt2_layer_norms(model):
     cfg = model["config"]
     dtype = model["dtype"]
     fold = {}
+    # With chained linears (the default; APPLEGPU_GEMM_CHAIN=0 turns them off) out-projection -> FC1 -> FC2 -> the next
+    # block's QKV run as one launch of [K, N] weights and tile shapes stop mattering; without them the separate launches
+    # get K-major copies where that gives the better tile.
+    kmajor = not gpu.gemm_chain_enabled()
     for i in range(cfg["n_layer"]):
         p = f"transformer.h.{i}"
         for ln, lin in ((f"{p}.ln_1", f"{p}.attn.c_attn"), (f"{p}.ln_2", f"{p}.mlp.c_fc")):
@@ -116,13 +120,14 @@ def fold_gpt2_layer_norms(model):
             colsum = gpu.from_numpy(wf.to_numpy().astype(np.float64).sum(0).astype(np.float32))
             cbias = gpu.cast(gpu.from_numpy((beta.astype(np.float64) @ w0.astype(np.float64) + b0).astype(np.float32)), dtype)
             cbias.eval()
-            if lin.endswith(".mlp.c_fc"):
+            if kmajor and lin.endswith(".mlp.c_fc"):
                 wf = _kmajor_copy(wf)          # stored [N, K]; the forward takes the transposed view
             fold[lin] = (wf, colsum, cbias)
         # the two projections back to the 768-wide stream: N = 768 fills the 74 CTA pairs of the GEMM in 1.73 waves of
         # 256 x 192 tiles, a shape the kernel has for K-major weights only (see _kmajor_copy)
         for lin in (f"{p}.attn.c_proj", f"{p}.mlp.c_proj"):
-            fold[lin] = _kmajor_copy(w[f"{lin}.weight"])
+            fold[lin] = _kmajor_copy(w[f"{lin}.weight"]) if kmajor else w[f"{lin}.weight"]
+    fold["kmajor"] = kmajor
     model["ln_fold"] = fold
     model["_ln_stats"] = {}
     return model
@@ -279,11 +284,12 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
             x = x + ffn
         else:
             # x += attn @ W + b, and ln_2's row statistics of the new x; ln_1's (already consumed) are cleared
-            x = gpu.linear_fused(attn, gpu.transpose(fold[f"{p}.attn.c_proj"]), bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
+            as_kn = gpu.transpose if fold["kmajor"] else (lambda t: t)     # K-major copies are stored [N, K]
+            x = gpu.linear_fused(attn, as_kn(fold[f"{p}.attn.c_proj"]), bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
             wf, colsum, cbias = fold[f"{p}.mlp.c_fc"]
-            ffn = gpu.linear_fused(x, gpu.transpose(wf), bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
+            ffn = gpu.linear_fused(x, as_kn(wf), bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
             # x += ffn @ W + b, ln_1's statistics for the next block (none after the last: ln_f is a kernel), ln_2's cleared
-            x = gpu.linear_fused(ffn, gpu.transpose(fold[f"{p}.mlp.c_proj"]), bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
+            x = gpu.linear_fused(ffn, as_kn(fold[f"{p}.mlp.c_proj"]), bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
                                  stats_out=stats1 if i + 1 < n_layer else None, stats_zero=stats2)
 
     x = gpu.layer_norm(x, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"])

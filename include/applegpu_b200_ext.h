@@ -170,6 +170,12 @@ APPLEGPU_API void applegpu_set_gemm_tile(int32_t code);
 /* Keeps `n` SMs out of the grids of the persistent kernels (GEMM, attention, row kernels), for a collective that runs
  * on another stream beside them. 0 (default) uses every SM. */
 APPLEGPU_API void applegpu_set_sm_margin(int32_t n);
+/* Chained linears (default on; APPLEGPU_GEMM_CHAIN=0 sets the initial value to off): inside one evaluation, consecutive
+ * 16-bit fused linears with [K, N] weights where each reads the previous one's result (out-projection -> FC1 -> FC2 -> the
+ * next block's QKV) are launched as ONE tensor-core kernel whose tiles wait, row block by row block, for the tiles that
+ * produce their rows. Results are bit-identical to the separate launches. */
+APPLEGPU_API void applegpu_set_gemm_chain(bool on);
+APPLEGPU_API bool applegpu_gemm_chain_enabled(void);
 /* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
  * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
 APPLEGPU_API void applegpu_set_f32_split(bool on);
