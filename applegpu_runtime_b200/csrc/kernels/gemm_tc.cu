@@ -399,22 +399,52 @@ __device__ __forceinline__ void epilogue_group(const TcParams& p, uint32_t taddr
         const uint64_t hx = mul_f32x2(x, half2v);
         vp[w] = fma_f32x2(hx, pack_f32x2(t0, t1), hx);
       }
-    } else if ((Act)p.act != Act::None) {
+    } else if ((Act)p.act == Act::GeluErf && std::is_same<T, __nv_bfloat16>::value) {
+      // the erf form for bf16 results (common.cuh gelu_erf_bf16_f: an odd polynomial fitted to erf inside one tanh),
+      // clamped per element, the rest two at a time
+      const uint64_t c1 = pack_f32x2(7.97458471e-1f, 7.97458471e-1f), c3 = pack_f32x2(3.70503451e-2f, 3.70503451e-2f),
+                     c5 = pack_f32x2(-3.58732362e-4f, -3.58732362e-4f), half2v = pack_f32x2(0.5f, 0.5f);
 #pragma unroll
       for (int w = 0; w < 16; w++) {
+        const uint64_t x = vp[w];
         float a, b;
-        unpack_f32x2(vp[w], a, b);
-        switch ((Act)p.act) {
-          case Act::GeluTanh: a = gelu_tanh_f(a); b = gelu_tanh_f(b); break;
-          case Act::GeluErf:
-            if (std::is_same<T, __nv_bfloat16>::value) { a = gelu_erf_bf16_f(a); b = gelu_erf_bf16_f(b); }
-            else { a = gelu_erf_fast_f(a); b = gelu_erf_fast_f(b); }
-            break;
-          case Act::Relu: a = fmaxf(a, 0.f); b = fmaxf(b, 0.f); break;
-          default: break;
-        }
-        vp[w] = pack_f32x2(a, b);
+        unpack_f32x2(x, a, b);
+        const uint64_t xc = pack_f32x2(fminf(fmaxf(a, -8.0f), 8.0f), fminf(fmaxf(b, -8.0f), 8.0f));
+        const uint64_t x2 = mul_f32x2(xc, xc);
+        const uint64_t u = mul_f32x2(xc, fma_f32x2(fma_f32x2(c5, x2, c3), x2, c1));
+        float u0, u1, t0, t1;
+        unpack_f32x2(u, u0, u1);
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(u0));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(u1));
+        const uint64_t hx = mul_f32x2(x, half2v);
+        vp[w] = fma_f32x2(hx, pack_f32x2(t0, t1), hx);
       }
+    } else if ((Act)p.act != Act::None) {
+      // the other activations element by element: one uniform test, then a straight loop (as in the scalar path)
+#pragma unroll
+      for (int w = 0; w < 16; w++) unpack_f32x2(vp[w], v[2 * w], v[2 * w + 1]);
+      switch ((Act)p.act) {
+        case Act::GeluTanh:
+#pragma unroll
+          for (int e = 0; e < 32; e++) v[e] = gelu_tanh_f(v[e]);
+          break;
+        case Act::GeluErf:
+          if (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+            for (int e = 0; e < 32; e++) v[e] = gelu_erf_bf16_f(v[e]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++) v[e] = gelu_erf_fast_f(v[e]);
+          }
+          break;
+        case Act::Relu:
+#pragma unroll
+          for (int e = 0; e < 32; e++) v[e] = fmaxf(v[e], 0.f);
+          break;
+        default: break;
+      }
+#pragma unroll
+      for (int w = 0; w < 16; w++) vp[w] = pack_f32x2(v[2 * w], v[2 * w + 1]);
     }
     if (R) {
 #pragma unroll

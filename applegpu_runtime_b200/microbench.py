@@ -129,6 +129,43 @@ def bench_fused_linear(rng, dtype, m, n, k, act, residual, iters, opt, kmajor=Fa
     return {"op": name, "dtype": dtype, "shape": [m, n, k], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
 
 
+def bench_layer_linears(rng, dtype, rows, d, iters, opt, chained=True):
+    """The four linears between two attention kernels of a GPT-2 block with folded layer_norms, as the model issues them
+    (gpt2._record_forward): out-projection (+ residual, row statistics out), FC1 (folded ln_2, GELU), FC2 (+ residual,
+    row statistics out) and the next block's QKV (folded ln_1), [K, N] weights, one evaluation. `chained`: one launch of
+    the chained tensor-core kernel; otherwise four launches."""
+    e = gpu.dtype_size(dtype)
+    was = gpu.gemm_chain_enabled()
+    gpu.set_gemm_chain(bool(chained))
+    try:
+        footprint = (rows * d * 4 + rows * 4 * d + rows * 3 * d + 12 * d * d) * e
+        sets = []
+        for _ in range(_nsets(footprint, opt.rotate)):
+            attn, x = _tensor(rng, (rows, d), dtype), _tensor(rng, (rows, d), dtype)
+            w = [_tensor(rng, (d, d), dtype, 0.02), _tensor(rng, (d, 4 * d), dtype, 0.02), _tensor(rng, (4 * d, d), dtype, 0.02), _tensor(rng, (d, 3 * d), dtype, 0.02)]
+            b = [_tensor(rng, (n,), dtype) for n in (d, 4 * d, d, 3 * d)]
+            cs = [gpu.from_numpy(np.zeros(n, np.float32)) for n in (4 * d, 3 * d)]
+            st = [gpu.from_numpy(np.zeros((rows, 2), np.int64)) for _ in range(2)]
+            for t in cs + st:
+                t.eval()
+            sets.append((attn, x, w, b, cs, st))
+
+        def make(attn, x, w, b, cs, st):
+            def fn():
+                x2 = gpu.linear_fused(attn, w[0], bias=b[0], residual=x, stats_out=st[1], stats_zero=st[0])
+                ff = gpu.linear_fused(x2, w[1], bias=b[1], act="gelu", ln=(cs[0], st[1], 1e-5))
+                x3 = gpu.linear_fused(ff, w[2], bias=b[2], residual=x2, stats_out=st[0], stats_zero=st[1])
+                return gpu.linear_fused(x3, w[3], bias=b[3], ln=(cs[1], st[0], 1e-5))
+            return fn
+
+        ms = _time([make(*t) for t in sets], iters, single=opt.single)
+    finally:
+        gpu.set_gemm_chain(was)
+    flops = 2.0 * rows * d * d * 12
+    name = "gpt2 block linears [out-proj, FC1, FC2, next QKV], " + ("chained: one launch" if chained else "four launches")
+    return {"op": name, "dtype": dtype, "shape": [rows, d], "ms": ms, "work": flops, "rate": flops / ms / 1e9, "unit": "TFLOP/s", "sets": len(sets)}
+
+
 def bench_w8_linear(rng, dtype, m, n, k, iters, opt):
     """x [m,k] (16-bit) @ int8 weights [n,k] with per-output-channel scales: matmul_int8, the linear of the int8 models."""
     e = gpu.dtype_size(dtype)
@@ -225,6 +262,11 @@ def main(argv=None):
             rows, d = shape or [131072, 768]
             for (n, k, act, res) in [(3 * d, d, False, False), (d, d, False, True), (4 * d, d, args.act or True, False), (d, 4 * d, False, True)]:
                 out.append(bench_fused_linear(rng, dt, rows, n, k, act, res, args.iters, args))
+        if args.op in ("all", "layer_linears") and dt != "float32":
+            for chained in (True, False):
+                out.append(bench_layer_linears(rng, dt, *(shape or [8192, 768]), args.iters, args, chained=chained))
+        if args.op == "layer_linears_chained" and dt != "float32":
+            out.append(bench_layer_linears(rng, dt, *(shape or [8192, 768]), args.iters, args, chained=True))
         if args.op == "w8_linear" and dt != "float32":
             out.append(bench_w8_linear(rng, dt, *(shape or [2048, 5120, 1280]), args.iters, args))
         if args.op == "lm_head":
