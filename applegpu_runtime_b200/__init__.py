@@ -17,7 +17,7 @@ from .api import (  # noqa: E402,F401
     add, sub, mul, div, neg, linear_fused, relu, exp, log, sqrt, scalar_mul, reshape, softmax, transpose, transpose_dims, tanh, sin,
     cos, gelu, gelu_exact, sigmoid, layer_norm, embedding, gather, index_select, attention, matmul, slice, concat,
     concat_all, add_bias, softmax_causal, argmax, cast, quantize, dequantize, sum, mean, attention_causal, abs, sign,
-    pool_stats, pool_drain, set_pool_watermark, synchronize, quantize_weight, matmul_int8, set_fusion, set_matmul_path, matmul_path, set_f32_split, set_sm_margin, set_gemm_tile, set_gemm_chain, gemm_chain_enabled, set_attention_path,
+    pool_stats, pool_drain, set_pool_watermark, synchronize, quantize_weight, matmul_int8, set_fusion, set_matmul_path, matmul_path, set_f32_split, set_sm_margin, set_gemm_tile, set_gemm_chain, gemm_chain_enabled, gemm_chain_min_rows, gemm_chain_applies, set_attention_path,
     pipeline_status, launch_count, resolve_kernel, profile, profile_report, Tape, tape_begin, tape_end, tape_abort,
 )
 from .gpt2 import gpt2_forward, init_gpt2_weights, load_gpt2_state_dict, quantize_gpt2_linears, fold_gpt2_layer_norms, GPT2_SMALL, GPT2_LARGE  # noqa: E402,F401

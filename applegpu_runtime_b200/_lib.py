@@ -169,6 +169,8 @@ EXT_SYMBOLS = {
     "applegpu_set_sm_margin": (None, [i32]),
     "applegpu_set_gemm_chain": (None, [ctypes.c_bool]),
     "applegpu_gemm_chain_enabled": (ctypes.c_bool, []),
+    "applegpu_set_gemm_chain_min_rows": (None, [ctypes.c_int64]),
+    "applegpu_gemm_chain_min_rows": (ctypes.c_int64, []),
     "applegpu_ffi_linear_fused": (u64, [u64, u64, u64, u64, i32, u64, u64, ctypes.c_float, u64, u64]),
     "applegpu_set_f32_split": (None, [ctypes.c_bool]),
     "applegpu_set_host_visible": (i32, [i32]),

@@ -567,14 +567,26 @@ def set_sm_margin(n=0):
     _L().applegpu_set_sm_margin(int(n))
 
 
-def set_gemm_chain(on=True):
+def set_gemm_chain(on=True, min_rows=None):
     """Chained linears: consecutive 16-bit fused linears of one evaluation, each reading the previous one's result, go
-    out as one tensor-core launch (bit-identical results). On by default; APPLEGPU_GEMM_CHAIN=0 starts with it off."""
+    out as one tensor-core launch (bit-identical results). On by default; APPLEGPU_GEMM_CHAIN=0 starts with it off.
+    `min_rows`: linears with fewer rows stay separate launches (default 4096, where chaining starts to pay)."""
     _L().applegpu_set_gemm_chain(bool(on))
+    if min_rows is not None:
+        _L().applegpu_set_gemm_chain_min_rows(int(min_rows))
 
 
 def gemm_chain_enabled():
     return bool(_L().applegpu_gemm_chain_enabled())
+
+
+def gemm_chain_min_rows():
+    return int(_L().applegpu_gemm_chain_min_rows())
+
+
+def gemm_chain_applies(rows):
+    """Whether linears of `rows` rows are chained as things stand."""
+    return gemm_chain_enabled() and int(rows) >= gemm_chain_min_rows()
 
 
 def set_f32_split(on=True):

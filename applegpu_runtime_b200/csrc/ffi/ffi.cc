@@ -1210,6 +1210,8 @@ void applegpu_set_gemm_tile(int32_t code) { k::set_gemm_tile(code); }
 void applegpu_set_sm_margin(int32_t n) { k::set_sm_margin(n); }
 void applegpu_set_gemm_chain(bool on) { ag::set_gemm_chain(on); }
 bool applegpu_gemm_chain_enabled(void) { return ag::gemm_chain_enabled(); }
+void applegpu_set_gemm_chain_min_rows(int64_t rows) { k::set_gemm_chain_min_rows(rows); }
+int64_t applegpu_gemm_chain_min_rows(void) { return k::gemm_chain_min_rows(); }
 int32_t applegpu_pipeline_status(void) {
   DeviceCtx& ctx = DeviceCtx::get();
   if (!ctx.ready || ctx.dry) return 0;

@@ -1966,8 +1966,16 @@ Status matmul_tc(cudaStream_t s, const GemmDesc& d, int* status_word) {
 long long* g_chain_probe = nullptr;   // set by a probe harness
 void chain_epi_probe(long long* out) { cudaMemcpyFromSymbol(out, g_epi_probe, sizeof(long long) * 8); }
 #endif
+// Fewer rows than this and the products go out one by one: with a handful of 256-row blocks most tiles wait for the
+// tiles just before them (measured on GPT-2-small's block: chained 66 / 76 / 83 / 114 us against 54 / 72 / 86 / 145 us
+// for four launches at 1024 / 3072 / 4096 / 8192 rows).
+static int64_t g_chain_min_rows = [] { const char* v = std::getenv("APPLEGPU_GEMM_CHAIN_MIN_ROWS"); return v ? (int64_t)std::atoll(v) : (int64_t)4096; }();
+void set_gemm_chain_min_rows(int64_t rows) { g_chain_min_rows = rows < 0 ? 0 : rows; }
+int64_t gemm_chain_min_rows() { return g_chain_min_rows; }
+
 bool matmul_chain_candidate(const GemmDesc& d) {
   if (g_force_path == 1 || g_force_path == 3 || g_tile_override) return false;
+  if (d.m < g_chain_min_rows) return false;
   if (!(d.dtype == DType::BF16 || d.dtype == DType::F16) || d.b_dtype != d.dtype) return false;
   if (!tc_eligible(d) || classify_b(d) != 2) return false;
   if (d.batch != 1 || d.batch_inner != 1 || d.c_f32 || d.ep.argmax_keys || d.ep.b_scales || d.ln_gamma) return false;

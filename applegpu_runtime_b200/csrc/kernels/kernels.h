@@ -116,6 +116,8 @@ Status matmul(cudaStream_t s, const GemmDesc& d);
 constexpr int kChainMax = 4;
 constexpr int kChainFlagStride = 1024;       // row blocks of 256 rows per product
 constexpr int kChainArenaInts = 1 << 18;     // tile lists kept on the device
+void set_gemm_chain_min_rows(int64_t rows);   // products with fewer rows are never chained (default 4096; APPLEGPU_GEMM_CHAIN_MIN_ROWS)
+int64_t gemm_chain_min_rows();
 bool matmul_chain_candidate(const GemmDesc& d);
 bool matmul_chain_can_append(const GemmDesc* chain, int count, const GemmDesc& next);
 Status matmul_chain(cudaStream_t s, const GemmDesc* chain, int count);

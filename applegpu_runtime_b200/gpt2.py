@@ -104,10 +104,9 @@ def fold_gpt2_layer_norms(model):
     cfg = model["config"]
     dtype = model["dtype"]
     fold = {}
-    # With chained linears (the default; APPLEGPU_GEMM_CHAIN=0 turns them off) out-projection -> FC1 -> FC2 -> the next
-    # block's QKV run as one launch of [K, N] weights and tile shapes stop mattering; without them the separate launches
-    # get K-major copies where that gives the better tile.
-    kmajor = not gpu.gemm_chain_enabled()
+    # Both layouts of the three weights whose best tile depends on it are kept (127 MB more for GPT-2-small): [K, N] for the
+    # chained form (out-projection -> FC1 -> FC2 -> the next block's QKV as one launch, where tile shapes stop
+    # mattering), and K-major copies for separate launches (see _kmajor_copy). The forward picks by its row count.
     for i in range(cfg["n_layer"]):
         p = f"transformer.h.{i}"
         for ln, lin in ((f"{p}.ln_1", f"{p}.attn.c_attn"), (f"{p}.ln_2", f"{p}.mlp.c_fc")):
@@ -120,14 +119,14 @@ def fold_gpt2_layer_norms(model):
             colsum = gpu.from_numpy(wf.to_numpy().astype(np.float64).sum(0).astype(np.float32))
             cbias = gpu.cast(gpu.from_numpy((beta.astype(np.float64) @ w0.astype(np.float64) + b0).astype(np.float32)), dtype)
             cbias.eval()
-            if kmajor and lin.endswith(".mlp.c_fc"):
-                wf = _kmajor_copy(wf)          # stored [N, K]; the forward takes the transposed view
             fold[lin] = (wf, colsum, cbias)
+            if lin.endswith(".mlp.c_fc"):
+                fold[lin + ".kmajor"] = _kmajor_copy(wf)          # stored [N, K]; the forward takes the transposed view
         # the two projections back to the 768-wide stream: N = 768 fills the 74 CTA pairs of the GEMM in 1.73 waves of
-        # 256 x 192 tiles, a shape the kernel has for K-major weights only (see _kmajor_copy)
+        # 256 x 192 tiles, a shape the kernel has for K-major weights only
         for lin in (f"{p}.attn.c_proj", f"{p}.mlp.c_proj"):
-            fold[lin] = _kmajor_copy(w[f"{lin}.weight"]) if kmajor else w[f"{lin}.weight"]
-    fold["kmajor"] = kmajor
+            fold[lin] = w[f"{lin}.weight"]
+            fold[lin + ".kmajor"] = _kmajor_copy(w[f"{lin}.weight"])
     model["ln_fold"] = fold
     model["_ln_stats"] = {}
     return model
@@ -210,7 +209,7 @@ def gpt2_forward(model, input_ids, kv_cache=None, last_only=False, device_ids=No
 
     tape_key = tape_inputs = None
     if compiled:
-        tape_key = ("gpt2", B, T, use_cache, bool(last_only), batched, "int8" in model, "__ln_fold__" in w)
+        tape_key = ("gpt2", B, T, use_cache, bool(last_only), batched, "int8" in model, "__ln_fold__" in w, gpu.gemm_chain_applies(B * T))
         tape_inputs = [indices, pos_indices] + ([t for kv in kv_cache for t in kv] if use_cache else [])
         tape = model.setdefault("_tapes", {}).get(tape_key)
         if tape is not None:
@@ -239,6 +238,7 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
     x = tok_emb + pos_emb  # [B*T, d]
 
     fold = w.get("__ln_fold__")
+    chained = gpu.gemm_chain_applies(rows)                   # the block's linears will go out as one launch
     stats1, stats2 = w.get("__ln_stats__", (None, None))     # row statistics feeding ln_1 / ln_2
     new_kv_cache = []
     for i in range(n_layer):
@@ -284,12 +284,15 @@ def _record_forward(w, cfg, indices, pos_indices, kv_cache, B, T, last_only, bat
             x = x + ffn
         else:
             # x += attn @ W + b, and ln_2's row statistics of the new x; ln_1's (already consumed) are cleared
-            as_kn = gpu.transpose if fold["kmajor"] else (lambda t: t)     # K-major copies are stored [N, K]
-            x = gpu.linear_fused(attn, as_kn(fold[f"{p}.attn.c_proj"]), bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
-            wf, colsum, cbias = fold[f"{p}.mlp.c_fc"]
-            ffn = gpu.linear_fused(x, as_kn(wf), bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
+            # chained (enough rows): the [K, N] weights; separate launches: the K-major copies through transposed views
+            def weight(name):
+                return fold[name] if chained else gpu.transpose(fold[name + ".kmajor"])
+            x = gpu.linear_fused(attn, weight(f"{p}.attn.c_proj"), bias=w[f"{p}.attn.c_proj.bias"], residual=x, stats_out=stats2, stats_zero=stats1)
+            _, colsum, cbias = fold[f"{p}.mlp.c_fc"]
+            wf = fold[f"{p}.mlp.c_fc"][0] if chained else gpu.transpose(fold[f"{p}.mlp.c_fc.kmajor"])
+            ffn = gpu.linear_fused(x, wf, bias=cbias, act="gelu", ln=(colsum, stats2, 1e-5))
             # x += ffn @ W + b, ln_1's statistics for the next block (none after the last: ln_f is a kernel), ln_2's cleared
-            x = gpu.linear_fused(ffn, as_kn(fold[f"{p}.mlp.c_proj"]), bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
+            x = gpu.linear_fused(ffn, weight(f"{p}.mlp.c_proj"), bias=w[f"{p}.mlp.c_proj.bias"], residual=x,
                                  stats_out=stats1 if i + 1 < n_layer else None, stats_zero=stats2)
 
     x = gpu.layer_norm(x, w["transformer.ln_f.weight"], w["transformer.ln_f.bias"])

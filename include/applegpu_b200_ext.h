@@ -176,6 +176,10 @@ APPLEGPU_API void applegpu_set_sm_margin(int32_t n);
  * produce their rows. Results are bit-identical to the separate launches. */
 APPLEGPU_API void applegpu_set_gemm_chain(bool on);
 APPLEGPU_API bool applegpu_gemm_chain_enabled(void);
+/* Linears with fewer rows than this are never chained (default 4096, APPLEGPU_GEMM_CHAIN_MIN_ROWS: below about 16 row
+ * blocks of 256 most tiles would wait for the tiles just before them and separate launches are faster). */
+APPLEGPU_API void applegpu_set_gemm_chain_min_rows(int64_t rows);
+APPLEGPU_API int64_t applegpu_gemm_chain_min_rows(void);
 /* float32 matmuls of at least 2 GFLOP run on the tensor cores as a three-term bf16 split with float32
  * accumulation (error ~2^-22 relative); false keeps every float32 product on the CUDA-core kernel. */
 APPLEGPU_API void applegpu_set_f32_split(bool on);

@@ -24,9 +24,10 @@ def rounded(x, dtype):
 
 @pytest.fixture(autouse=True)
 def _restore(gpu_dev):
-    was = gpu_dev.gemm_chain_enabled()
+    was, rows = gpu_dev.gemm_chain_enabled(), gpu_dev.gemm_chain_min_rows()
+    gpu_dev.set_gemm_chain(True, min_rows=0)     # by default only linears of 4096 rows and more are chained
     yield
-    gpu_dev.set_gemm_chain(was)
+    gpu_dev.set_gemm_chain(was, min_rows=rows)
     gpu_dev.set_gemm_tile("auto")
     assert gpu_dev.pipeline_status() == 0, "a bounded wait in the tcgen05 pipeline gave up"
 
@@ -69,11 +70,9 @@ def test_chain_matches_separate_launches(gpu_dev, dtype, rows):
         mids = [o.to_numpy() for o in outs]     # every intermediate is kept alive and read back too
         return mids, gpu.launch_count() - before
 
-    gpu.set_gemm_chain(True)
     chained, launches_chained = run()
     chained_again, _ = run()
-    gpu.set_gemm_chain(False)
-    gpu.set_gemm_tile("pair256")            # the chained kernel's tile shape, one launch per linear
+    gpu.set_gemm_tile("pair256")            # a pinned tile shape (the chained kernel's) also means one launch per linear
     separate, launches_separate = run()
     gpu.set_gemm_tile("auto")
     assert launches_separate == 5
@@ -116,9 +115,7 @@ def test_chain_breaks_where_a_link_does_not_follow(gpu_dev):
         d.eval()
         return [t.to_numpy() for t in (a, b, c, d)]
 
-    gpu.set_gemm_chain(True)
     on = run()
-    gpu.set_gemm_chain(False)
     gpu.set_gemm_tile("pair256")
     off = run()
     for p, q in zip(on, off):
@@ -131,7 +128,6 @@ def test_gpt2_forward_chained_equals_unchained(gpu_dev):
     gpu = gpu_dev
     from applegpu_runtime_b200.gpt2 import init_gpt2_weights, gpt2_forward
     cfg = {"n_layer": 3, "n_head": 4, "n_embd": 256, "vocab_size": 1003, "n_positions": 512}
-    gpu.set_gemm_chain(True)                # the model keeps [K, N] weights for the chained form
     model = init_gpt2_weights(cfg, seed=3, dtype="bfloat16")
     ids = np.random.default_rng(9).integers(0, cfg["vocab_size"], (3, 300))      # 900 rows: a ragged last row block
 
@@ -143,10 +139,26 @@ def test_gpt2_forward_chained_equals_unchained(gpu_dev):
 
     on, launches_on = run()
     on_again, _ = run()
-    gpu.set_gemm_chain(False)
-    gpu.set_gemm_tile("pair256")
+    gpu.set_gemm_tile("pair256")            # same [K, N] weights, one launch per linear
     off, launches_off = run()
     assert np.array_equal(on, off)
     assert np.array_equal(on, on_again)
     assert launches_on < launches_off       # [proj, FC1, FC2, next QKV] went out together
     assert launches_off - launches_on == 3 + 3 + 2   # blocks 0 and 1: proj, FC1, FC2 and the next QKV as one launch instead of four; the last block has three links
+
+
+def test_few_rows_are_not_chained(gpu_dev):
+    """Below the row threshold (default 4096) the linears stay separate launches, where that is faster."""
+    gpu = gpu_dev
+    gpu.set_gemm_chain(True, min_rows=4096)
+    assert gpu.gemm_chain_applies(8192) and not gpu.gemm_chain_applies(2048)
+    rng = np.random.default_rng(2)
+    x = up(gpu, rng.standard_normal((512, 256)).astype(np.float32), "bfloat16")
+    w1 = up(gpu, (rng.standard_normal((256, 512)) / 16).astype(np.float32), "bfloat16")
+    w2 = up(gpu, (rng.standard_normal((512, 256)) / 22).astype(np.float32), "bfloat16")
+    for t in (x, w1, w2):
+        t.eval()
+    before = gpu.launch_count()
+    y = gpu.linear_fused(gpu.linear_fused(x, w1), w2)
+    y.eval()
+    assert gpu.launch_count() - before == 2
