@@ -415,7 +415,7 @@ def run_b200(args):
     other_ms = sum(v["ms"] for k, v in rep.items() if not k.startswith(("fused_linear", "matmul"))) / prof_steps
     step_ms = ms / args.steps
     by_sub = g_flops / prof_steps / ((step_ms - other_ms) / 1e3) / 1e12 if step_ms > other_ms > 0 else None
-    roofline = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05, all linear layers + LM head)",
+    roofline = {"bound": "tensor", "kernel": "gemm_tc_chain_kernel + gemm_tc_pair_kernel (tcgen05: per block one chained launch of out-proj, FC1, FC2 and the next QKV; block 0's QKV; LM head)",
                 "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": (achieved / peaks["bf16_tflops"]) if achieved else None,
                 "peak_source": peaks["source"] + " (burst: the timed region lasts tens of milliseconds at the full SM clock)",
