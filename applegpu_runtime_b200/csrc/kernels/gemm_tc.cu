@@ -2051,15 +2051,21 @@ std::mutex g_chain_mu;
 std::deque<ChainList> g_chain_lists;     // deque: the host copies stay where they are while an upload may still read them
 int g_chain_arena_used = 0;
 
-// Modelled cycles of one tile: the main loop at the tensor rate, or the epilogue where that is longer (K = 768).
+const int g_chain_kstep = [] { const char* v = std::getenv("APPLEGPU_CHAIN_KSTEP"); return v ? std::atoi(v) : 520; }();
+const int g_chain_epi_base = [] { const char* v = std::getenv("APPLEGPU_CHAIN_EPI_BASE"); return v ? std::atoi(v) : 11000; }();
+// Modelled cycles of one tile, for dealing the tiles out evenly: the main loop at the tensor rate, or the epilogue where
+// that is longer (K = 768). Measured on a GPT-2-small block: 123.7 / 121.4 / 117.4 / 117.2 us with an epilogue base of
+// 5 200 / 8 000 / 11 000 / 15 000 cycles (what matters is the weight of the 48-step FC2 tiles against the 12-step ones:
+// about 2 : 1, the epilogue being what bounds the short ones); the k-step cost makes no difference between 420 and 620.
+// APPLEGPU_CHAIN_EPI_BASE / APPLEGPU_CHAIN_KSTEP override the two for tuning.
 int chain_tile_cost(const GemmDesc& d) {
   const int num_kb = (int)((d.k + BK - 1) / BK);
-  int epi = 5200;
-  if (d.ep.act != Act::None) epi += 1600;
-  if (d.ep.residual) epi += 400;
+  int epi = g_chain_epi_base;
+  if (d.ep.act != Act::None) epi += 1500;
+  if (d.ep.residual) epi += 800;
   if (d.ep.ln_stats) epi += 300;
   if (d.ep.stats_out) epi += 400;
-  const int main_loop = num_kb * 520;
+  const int main_loop = num_kb * g_chain_kstep;
   return main_loop > epi ? main_loop : epi;
 }
 
