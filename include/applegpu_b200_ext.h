@@ -199,7 +199,11 @@ APPLEGPU_API void applegpu_set_attention_path(int32_t mode);
  * blocking point of the library (read_bytes / read_f32 / eager_download, applegpu_ffi_synchronize,
  * applegpu_eager_flush_and_wait, applegpu_marker_wait) makes the same check once the stream is idle and
  * reports a non-zero word as an error ("tensor-core pipeline wait timed out (code N)"), so a caller of
- * the reference ABI alone cannot read an undefined result as success. */
+ * the reference ABI alone cannot read an undefined result as success. Codes: 1 a TMA thread waiting for a free pipeline
+ * stage, 2 the MMA thread waiting for a free accumulator, 3 for loaded operands, 4 an epilogue warp waiting for a full
+ * accumulator, 5 an int8 converter warp waiting for raw weights, 6 a TMA thread of the chained kernel waiting for the row
+ * block its tile reads, 8 that kernel's announcer waiting for a tile's stores, 31 the grid barrier of the persistent
+ * decode kernel; the attention kernel uses 10 to 29. */
 APPLEGPU_API int32_t applegpu_pipeline_status(void);
 /* Test hook (no counterpart in the reference): launches one thread that waits, for at most `limit_us`
  * microseconds (capped at 50 ms), on a barrier nothing arrives at, then records `code` in the pipeline
