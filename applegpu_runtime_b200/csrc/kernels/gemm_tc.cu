@@ -1306,7 +1306,12 @@ __device__ __forceinline__ longlong2 ln_stats_fetch_cg(const TcParams& p, long l
   return __ldcg(reinterpret_cast<const longlong2*>(p.ln_stats) + gm);
 }
 
-constexpr int kChainThreads = kTcThreads + 32;    // + the announcer warp
+// Epilogue warps: 8 (two per TMEM lane quarter, alternating column groups, 168 registers each). 4 (one per quarter, every
+// group, 220 registers) was measured at 146 against 112 us per GPT-2-small block: eight groups per tile in series.
+constexpr int kChainEpiWarps = 8;
+constexpr int kChainGroupStep = kChainEpiWarps / 4;           // column groups between two groups of one warp
+constexpr int kChainGroups = 8 / kChainGroupStep;             // 32-column groups of a 256-wide tile per warp
+constexpr int kChainThreads = 64 + kChainEpiWarps * 32 + 32;  // TMA warp, MMA warp, epilogue warps, announcer warp
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kChainThreads, 1)
 gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_constant__ ChainParams cp) {
@@ -1337,7 +1342,7 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps); mbar_init(&stored_bar[a], kEpiWarps); }
+    for (int a = 0; a < 2; a++) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kChainEpiWarps); mbar_init(&stored_bar[a], kChainEpiWarps); }
     mbar_fence_init();
     for (int g = 0; g < cp.count; g++) { prefetch_tmap(&maps.a[g]); prefetch_tmap(&maps.b[g]); }
   }
@@ -1460,7 +1465,7 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else if (warp == 2 + kEpiWarps) {
+  } else if (warp == 2 + kChainEpiWarps) {
     // ── announcer (both CTAs): tile by tile, "this CTA's rows of the tile are stored" -> the row block's counter ──
     if (lane == 0) {
       int slot = 0; uint32_t parity = 0;
@@ -1470,7 +1475,7 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
         if (!mbar_wait(&stored_bar[slot], parity, status, 8)) break;
         fence_proxy_async_global();
         __threadfence();
-        atomicAdd(cp.flags + g * kChainFlagStride + lt / s_prob[g].tiles_n, kEpiWarps);
+        atomicAdd(cp.flags + g * kChainFlagStride + lt / s_prob[g].tiles_n, kChainEpiWarps);
         if (++slot == 2) { slot = 0; parity ^= 1; }
       }
     }
@@ -1485,8 +1490,8 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
     uint32_t rpre[16];
     int e_next = li0 < li1 ? __ldg(cp.list + li0) : -1;
     int e_next2 = li0 + 1 < li1 ? __ldg(cp.list + li0 + 1) : -1;   // list entries are read two tiles ahead: nothing waits for them
-    T col_bias[BN / 64];                         // the next tile's bias and column sums of this lane's columns, one tile ahead
-    float col_sum[BN / 64];                      // (as loaded: a conversion here would wait for the load)
+    T col_bias[kChainGroups];                         // the next tile's bias and column sums of this lane's columns, one tile ahead
+    float col_sum[kChainGroups];                      // (as loaded: a conversion here would wait for the load)
     auto fetch_cols = [&](int e_) {
       const int g_ = e_ >> 24, lt_ = e_ & 0xffffff;
       const TcParams& q = s_prob[g_];
@@ -1494,8 +1499,8 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
       const T* bias = reinterpret_cast<const T*>(q.bias);
       const float* cs = q.ln_stats ? q.ln_colsum : nullptr;
 #pragma unroll
-      for (int gi = 0; gi < BN / 64; gi++) {
-        const int ci = n0_ + (pair + 2 * gi) * 32 + lane;
+      for (int gi = 0; gi < kChainGroups; gi++) {
+        const int ci = n0_ + (pair + kChainGroupStep * gi) * 32 + lane;
         col_bias[gi] = (bias && ci < q.n) ? __ldg(bias + ci) : Cvt<T>::from(0.f);
         col_sum[gi] = (cs && ci < q.n) ? __ldg(cs + ci) : 0.f;
       }
@@ -1538,11 +1543,11 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
       const long long row0 = (long long)m0 + quarter * 32;
       // this tile's bias and column sums were fetched into registers one tile ago; they go to shared memory as floats (the
       // packed epilogue reads them as broadcasts; the staging tile is unused with 32-byte aligned rows)
-      float* bias_f = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp);
-      float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * epi_slots(BN);
+      float* bias_f = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes) + (warp - 2) * (kChainGroups * 32);
+      float* scale_s = reinterpret_cast<float*>(smem + STAGES * Cfg::kStageBytes + kStgBytes + bias_bytes(BN)) + (warp - 2) * (kChainGroups * 32);
       const float* fsrc = p.ln_stats ? p.ln_colsum : nullptr;
 #pragma unroll
-      for (int gi = 0; gi < BN / 64; gi++) { bias_f[gi * 32 + lane] = Cvt<T>::to(col_bias[gi]); scale_s[gi * 32 + lane] = col_sum[gi]; }
+      for (int gi = 0; gi < kChainGroups; gi++) { bias_f[gi * 32 + lane] = Cvt<T>::to(col_bias[gi]); scale_s[gi * 32 + lane] = col_sum[gi]; }
       if (e_next >= 0) fetch_cols(e_next);
       const bool res_ahead = p.residual && p.vec_ok == 2 && n0 + pair * 32 < p.n;
       // `fv` is a relaxed look at the counter taken one tile ago. Seeing it complete, the loads below are issued after
@@ -1575,14 +1580,14 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
       float ln_mean = 0.f, ln_rstd = 1.f;
       if (row0 + lane < p.m) ln_stats_finish(p, stats_raw, ln_mean, ln_rstd);
       uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * Cfg::kAccStride);
-      uint8_t* stg = smem + STAGES * Cfg::kStageBytes + (warp - 2) * kStgBytesPerWarp;
+      uint8_t* stg = nullptr;   // the staged layouts are not used here (rows are 32-byte aligned)
       unsigned long long best_key = 0;
       float row_sum = 0.f, row_sq = 0.f;
       if (row0 < p.m) {
 #pragma unroll 1
-        for (int gg = pair, gi = 0; gg < BN / 32; gg += 2, gi++) {
+        for (int gg = pair, gi = 0; gg < BN / 32; gg += kChainGroupStep, gi++) {
           if (n0 + gg * 32 >= p.n) break;
-          int next_col0 = (gg + 2 < BN / 32 && n0 + (gg + 2) * 32 < p.n) ? n0 + (gg + 2) * 32 : -1;
+          int next_col0 = (gg + kChainGroupStep < BN / 32 && n0 + (gg + kChainGroupStep) * 32 < p.n) ? n0 + (gg + kChainGroupStep) * 32 : -1;
           epilogue_group<T>(p, taddr + (uint32_t)(gg * 32), stg, nullptr, fsrc ? scale_s + gi * 32 : nullptr, rpre, row0, n0 + gg * 32, next_col0,
                             0, lane, best_key, ln_mean, ln_rstd, row_sum, row_sq, bias_f + gi * 32);
         }
@@ -2183,7 +2188,7 @@ Status matmul_chain(cudaStream_t s, const GemmDesc* chain, int count) {
     p.vec_ok = (al16p(d.c) && d.c_row % 8 == 0 && (!d.ep.residual || al16p(d.ep.residual))) ? 1 : 0;
     if (p.vec_ok && g_direct_store && al32p(d.c) && d.c_row % 16 == 0 && (!d.ep.residual || al32p(d.ep.residual))) p.vec_ok = 2;
     p.bias_vec = (d.ep.bias && al16p(d.ep.bias)) ? 1 : 0;
-    cp.need[g] = g == 0 ? 0 : 2 * kEpiWarps * cp.prob[g - 1].tiles_n;   // every epilogue warp of both CTAs, every tile of the row block
+    cp.need[g] = g == 0 ? 0 : 2 * kChainEpiWarps * cp.prob[g - 1].tiles_n;   // every epilogue warp of both CTAs, every tile of the row block
   }
   AG_RETURN_IF_ERROR(chain_list_for(s, chain, count, clusters, &cp.list_off, &cp.list));
   cudaError_t le = bf16 ? launch_pdl(gemm_tc_chain_kernel<__nv_bfloat16>, dim3(2 * clusters), dim3(kChainThreads), PairCfg<256>::kSmemBytes, s, maps, cp)
