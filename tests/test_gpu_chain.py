@@ -162,3 +162,33 @@ def test_few_rows_are_not_chained(gpu_dev):
     y = gpu.linear_fused(gpu.linear_fused(x, w1), w2)
     y.eval()
     assert gpu.launch_count() - before == 2
+
+
+def test_chain_with_sms_kept_free(gpu_dev):
+    """With SMs kept out of the compute grids (room for a collective on another stream) the chained kernel runs on fewer
+    CTA pairs and deals its tiles to those: same results."""
+    gpu = gpu_dev
+    rng = np.random.default_rng(11)
+    x = up(gpu, (rng.standard_normal((1536, 256)) * 0.5).astype(np.float32), "bfloat16")
+    ws = [up(gpu, (rng.standard_normal((256, 768)) / 16).astype(np.float32), "bfloat16"),
+          up(gpu, (rng.standard_normal((768, 256)) / 28).astype(np.float32), "bfloat16"),
+          up(gpu, (rng.standard_normal((256, 512)) / 16).astype(np.float32), "bfloat16")]
+    for t in [x] + ws:
+        t.eval()
+
+    def run():
+        before = gpu.launch_count()
+        h = gpu.linear_fused(x, ws[0], act="gelu")
+        h = gpu.linear_fused(h, ws[1], residual=x)
+        h = gpu.linear_fused(h, ws[2])
+        h.eval()
+        return h.to_numpy(), gpu.launch_count() - before
+
+    full, n_full = run()
+    gpu.set_sm_margin(20)
+    try:
+        fewer, n_fewer = run()
+    finally:
+        gpu.set_sm_margin(0)
+    assert n_full == 1 and n_fewer == 1
+    assert np.array_equal(full, fewer)
