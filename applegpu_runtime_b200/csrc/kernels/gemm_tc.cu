@@ -1525,7 +1525,7 @@ gemm_tc_chain_kernel(const __grid_constant__ ChainMaps maps, const __grid_consta
         const TcParams& sp = s_prob[g];
         p.c = sp.c; p.bias = sp.bias; p.residual = sp.residual; p.b_scales = nullptr; p.alpha = sp.alpha; p.act = sp.act;
         p.m = sp.m; p.n = sp.n; p.k = sp.k; p.batch = 1; p.batch_inner = 1; p.c_row = sp.c_row; p.c_batch = 0; p.c_batch_inner = 0;
-        p.a_bcast = 0; p.b_bcast = 0; p.tiles_m = sp.tiles_m; p.tiles_n = sp.tiles_n; p.vec_ok = sp.vec_ok; p.bias_vec = sp.bias_vec;
+        p.a_bcast = 0; p.b_bcast = 0; p.tiles_m = sp.tiles_m; p.tiles_n = sp.tiles_n; p.vec_ok = 2 /* the only layout a link may have: the others compile out */; p.bias_vec = 0;
         p.argmax_keys = nullptr; p.c_f32 = 0; p.ln_stats = sp.ln_stats; p.ln_colsum = sp.ln_colsum; p.ln_inv_k = sp.ln_inv_k; p.ln_eps = sp.ln_eps;
         p.stats_out = sp.stats_out; p.stats_zero = sp.stats_zero; p.status = status;
       }
