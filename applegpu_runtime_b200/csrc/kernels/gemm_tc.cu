@@ -1307,7 +1307,8 @@ __device__ __forceinline__ longlong2 ln_stats_fetch_cg(const TcParams& p, long l
 }
 
 // Epilogue warps: 8 (two per TMEM lane quarter, alternating column groups, 168 registers each). 4 (one per quarter, every
-// group, 220 registers) was measured at 146 against 112 us per GPT-2-small block: eight groups per tile in series.
+// group, 220 registers) was measured at 146 against 112 us per GPT-2-small block: eight groups per tile in series
+// (121 us with its 255-register budget spent on accumulator loads issued a group ahead).
 constexpr int kChainEpiWarps = 8;
 constexpr int kChainGroupStep = kChainEpiWarps / 4;           // column groups between two groups of one warp
 constexpr int kChainGroups = 8 / kChainGroupStep;             // 32-column groups of a 256-wide tile per warp
