@@ -60,6 +60,64 @@ class Gpt2Decoder {
   size_t small_bytes() const { return 256 + 16 * 1024 + (size_t)cfg.max_len * cfg.batch * 4; }
 
   // c = act(layer_norm?(a) @ w + bias) + residual with w [kdim, ndim] (Conv1D layout)
+  // The split-K linears of a step leave QKV and FC1 unfinished (float partials in their own workspace regions): attention
+  // and FC2 add the partials up themselves, which takes the fence + counter + reload by a last CTA off the tail of two of
+  // a layer's five launches. APPLEGPU_DECODE_DEFER=0 finishes every linear in its own launch.
+  static bool defer_enabled() {
+    static const bool on = [] { const char* v = std::getenv("APPLEGPU_DECODE_DEFER"); return !(v && v[0] == '0'); }();
+    return on;
+  }
+  k::GemmDesc linear_desc(const void* a, int kdim, const TensorRec& wgt, const TensorRec& bias, void* c, int ndim, k::Act act, const void* residual) const {
+    k::GemmDesc g;
+    g.dtype = dtype; g.b_dtype = dtype; g.a = a; g.b = wgt.data(); g.c = c;
+    g.m = cfg.batch; g.n = ndim; g.k = kdim; g.batch = 1; g.batch_inner = 1;
+    g.a_row = kdim; g.a_col = 1; g.a_batch = 0;
+    g.b_row = ndim; g.b_col = 1; g.b_batch = 0;
+    g.c_row = ndim; g.c_batch = 0;
+    g.ep.bias = bias.data(); g.ep.act = act; g.ep.residual = residual;
+    return g;
+  }
+  // A layer with QKV and FC1 left unfinished; false when a shape does not take the split-K kernel (the caller then runs
+  // the layer launch by launch).
+  bool layer_deferrable(const TensorRec* lw) const {
+    const int D = d();
+    if (!defer_enabled() || D / 128 > 8 || cfg.batch > 16) return false;
+    k::GemmDesc q = linear_desc(x(), D, lw[2], lw[3], qkv(), 3 * D, k::Act::None, nullptr);
+    q.ln_gamma = lw[0].data(); q.ln_beta = lw[1].data();
+    k::GemmDesc f = linear_desc(x(), D, lw[8], lw[9], ff(), 4 * D, k::Act::None, nullptr);
+    f.ln_gamma = lw[6].data(); f.ln_beta = lw[7].data();
+    k::GemmDesc f2 = linear_desc(nullptr, 4 * D, lw[10], lw[11], x(), D, k::Act::None, x2());
+    k::GemmDesc pr = linear_desc(att(), D, lw[4], lw[5], x2(), D, k::Act::None, x());
+    return k::decode_linear_eligible(q) && k::decode_linear_eligible(f) && k::decode_linear_eligible(f2) && k::decode_linear_eligible(pr);
+  }
+  Status enqueue_layer_deferred(cudaStream_t s, int l, uint8_t* cur, uint8_t* other, float scale) {
+    const TensorRec* lw = &w[4 + 12 * l];
+    const int D = d(), slabs = (D + 127) / 128;
+    k::DecodeLinearOpts o;
+    // ln_1(x) @ W_qkv: partials only (region 1)
+    k::GemmDesc g = linear_desc(cur, D, lw[2], lw[3], qkv(), 3 * D, k::Act::None, nullptr);
+    g.ln_gamma = lw[0].data(); g.ln_beta = lw[1].data(); g.ln_eps = 1e-5f;
+    o = k::DecodeLinearOpts(); o.region = 1; o.partial_only = true;
+    AG_RETURN_IF_ERROR(k::decode_linear(s, g, o));
+    // attention adds them (+ bias) into q | k | v itself
+    AG_RETURN_IF_ERROR(k::attention_decode(s, dtype, nullptr, kcache(l), vcache(l), att(), counters() + 1, cfg.batch, cfg.n_head, cfg.max_len, scale,
+                                           k::decode_partial_region(1), slabs, lw[3].data()));
+    // x2 = x + att @ W_proj + b (finished in its own launch: the residual stream is read by every CTA of the next one)
+    g = linear_desc(att(), D, lw[4], lw[5], other, D, k::Act::None, cur);
+    AG_RETURN_IF_ERROR(k::decode_linear(s, g));
+    // ln_2(x2) @ W_fc: partials only (region 2)
+    g = linear_desc(other, D, lw[8], lw[9], ff(), 4 * D, k::Act::None, nullptr);
+    g.ln_gamma = lw[6].data(); g.ln_beta = lw[7].data(); g.ln_eps = 1e-5f;
+    o = k::DecodeLinearOpts(); o.region = 2; o.partial_only = true;
+    AG_RETURN_IF_ERROR(k::decode_linear(s, g, o));
+    // x = x2 + gelu(those partials + b_fc) @ W_fc2 + b
+    g = linear_desc(nullptr, 4 * D, lw[10], lw[11], cur, D, k::Act::None, other);
+    o = k::DecodeLinearOpts(); o.xp = k::decode_partial_region(2); o.xp_slabs = slabs; o.xp_bias = lw[9].data(); o.xp_act = k::Act::GeluTanh;
+    AG_RETURN_IF_ERROR(k::decode_linear(s, g, o));
+    launches_per_step += 5;
+    return Status::OK();
+  }
+
   Status linear(cudaStream_t s, const void* a, int kdim, const TensorRec& wgt, const TensorRec& bias, void* c, int ndim, k::Act act, const void* residual,
                 const TensorRec* ln_g = nullptr, const TensorRec* ln_b = nullptr) {
     k::GemmDesc g;
@@ -123,6 +181,7 @@ class Gpt2Decoder {
     const float scale = 1.0f / std::sqrt(64.0f);
     for (int l = 0; l < cfg.n_layer; l++) {
       const TensorRec* lw = &w[4 + 12 * l];
+      if (layer_deferrable(lw)) { AG_RETURN_IF_ERROR(enqueue_layer_deferred(s, l, cur, other, scale)); continue; }
       // ln_1 and ln_2 run in the prologue of the projection that consumes them (the kernel stages its 8..16 rows whole)
       AG_RETURN_IF_ERROR(linear(s, cur, D, lw[2], lw[3], qkv(), 3 * D, k::Act::None, nullptr, &lw[0], &lw[1]));
       AG_RETURN_IF_ERROR(k::attention_decode(s, dtype, qkv(), kcache(l), vcache(l), att(), counters() + 1, B, cfg.n_head, cfg.max_len, scale));

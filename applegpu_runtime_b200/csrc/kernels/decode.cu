@@ -19,6 +19,12 @@ __device__ __forceinline__ unsigned long long globaltimer_ns_dec() {
   return t;
 }
 
+// Geometry of a split-K linear work item of a decode step (see decode_linear_kernel below).
+constexpr int kDlCols = 64;       // columns per CTA
+constexpr int kDlRows = 128;      // K rows per CTA
+constexpr int kDlThreads = 256;
+constexpr int kDlMaxM = 16;
+
 // One (sequence, head) of a decode step's attention, by the first 128 threads of the block (any others only join
 // the barriers and contribute neutral elements to the block reductions, which leaves every sum bit-identical).
 // s_qkv: this head's q | k | v of the new token as floats that hold storage-type values; kc / vc: the head's cache
@@ -75,9 +81,13 @@ __device__ __forceinline__ void attn_decode_item(const float* s_qkv, T* kc, T* v
 
 // grid = B * heads, 128 threads. qkv: [B, 3 * d] rows (q | k | v of the new token); caches: [B, heads, t_max, 64];
 // out: [B, d] (heads merged). *len_ptr = tokens already in the cache; the new token becomes row *len_ptr.
+// `part` non-null: qkv is not materialised; the projection left `slabs` (at most 8) float partials [slab][16][3 * d] and
+// this kernel adds them in K order, adds `bias` and rounds to the storage type, exactly as the projection's own last CTA
+// would have (all loads of a value in flight before the first addition).
 template <typename T>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const T* __restrict__ qkv, T* __restrict__ kcache, T* __restrict__ vcache, T* __restrict__ out,
-                                                               const int* __restrict__ len_ptr, int heads, int t_max, float scale) {
+                                                               const int* __restrict__ len_ptr, int heads, int t_max, float scale,
+                                                               const float* __restrict__ part, int slabs, const T* __restrict__ bias) {
   extern __shared__ float s_scores[];          // [t_max]
   __shared__ AttnDecodeSmem sm;
   __shared__ float s_qkv[192];
@@ -85,8 +95,22 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const T* __restri
   pdl_trigger();
   const int b = blockIdx.x / heads, h = blockIdx.x % heads;
   const int d = heads * 64;
-  const T* row = qkv + (long long)b * 3 * d;
-  for (int i = threadIdx.x; i < 192; i += blockDim.x) s_qkv[i] = Cvt<T>::to(row[(i >> 6) * d + h * 64 + (i & 63)]);
+  if (part) {
+    for (int i = threadIdx.x; i < 192; i += blockDim.x) {
+      const int col = (i >> 6) * d + h * 64 + (i & 63);
+      float v[8];
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) v[ks] = ks < slabs ? __ldcg(part + ((long long)ks * kDlMaxM + b) * 3 * d + col) : 0.f;
+      float t = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) if (ks < slabs) t += v[ks];
+      if (bias) t += Cvt<T>::to(bias[col]);
+      s_qkv[i] = Cvt<T>::to(Cvt<T>::from(t));
+    }
+  } else {
+    const T* row = qkv + (long long)b * 3 * d;
+    for (int i = threadIdx.x; i < 192; i += blockDim.x) s_qkv[i] = Cvt<T>::to(row[(i >> 6) * d + h * 64 + (i & 63)]);
+  }
   __syncthreads();
   T* kc = kcache + ((long long)b * heads + h) * (long long)t_max * 64;
   T* vc = vcache + ((long long)b * heads + h) * (long long)t_max * 64;
@@ -94,14 +118,16 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const T* __restri
 }
 
 Status attention_decode(cudaStream_t s, DType dt, const void* qkv, void* kcache, void* vcache, void* out, const int* len_ptr, int batch, int heads,
-                        int t_max, float scale) {
+                        int t_max, float scale, const float* part, int slabs, const void* bias) {
   if (batch <= 0 || heads <= 0) return Status::OK();
+  if (part && (slabs < 1 || slabs > 8 || batch > kDlMaxM)) return Status::invalid("attention_decode: 1..8 partial slabs of at most 16 rows");
+  if (!part && !qkv) return Status::invalid("attention_decode: no q / k / v");
   if (t_max <= 0 || t_max > 8192) return Status::invalid("attention_decode: cache length must be in 1..8192");
   if (!aligned16(kcache) || !aligned16(vcache)) return Status::compute("attention_decode needs 16-byte aligned caches");
   const size_t smem = (size_t)t_max * sizeof(float);
   cudaError_t le = cudaSuccess;
   AG_DISPATCH_FLOAT(dt, T, (le = launch_pdl(attention_decode_kernel<T>, dim3((unsigned)(batch * heads)), dim3(128), smem, s, (const T*)qkv, (T*)kcache,
-                                             (T*)vcache, (T*)out, len_ptr, heads, t_max, scale)));
+                                             (T*)vcache, (T*)out, len_ptr, heads, t_max, scale, part, slabs, (const T*)bias)));
   if (le != cudaSuccess) return cuda_status(le, "attention_decode");
   return Status::OK();
 }
@@ -119,10 +145,7 @@ Status attention_decode(cudaStream_t s, DType dt, const void* qkv, void* kcache,
 //     way into shared memory, which removes the separate layer_norm launches of the step;
 //   * same deterministic reduction: fp32 partials per K slab in a workspace, the last CTA of a column slab (a
 //     counter) adds them in K order and applies bias / activation / residual.
-constexpr int kDlCols = 64;       // columns per CTA
-constexpr int kDlRows = 128;      // K rows per CTA
-constexpr int kDlThreads = 256;
-constexpr int kDlMaxM = 16;
+
 
 struct DecodeLinearParams {
   const void* x; const void* w; void* y;
@@ -135,6 +158,9 @@ struct DecodeLinearParams {
   // x not materialised: it is act(sum over xp_slabs of xp[slab][m][.] + xp_bias) rounded to the storage type, i.e. the
   // unfinished result of the previous linear of the step (its row length is this linear's k)
   const float* xp = nullptr; int xp_slabs = 0; const void* xp_bias = nullptr; int xp_act = 0;
+  // leave the result unfinished: only the partials are written, and the kernel that consumes them adds them up (no
+  // fence, counter and reload by a last CTA on this launch's tail); y, bias, act and residual are then unused
+  int partial_only = 0;
 };
 
 template <typename T> struct DlVec { using type = uint2; };      // four consecutive 16-bit weights
@@ -217,8 +243,35 @@ __device__ __forceinline__ void dl_partial(const DecodeLinearParams& p, DlSmem& 
 #pragma unroll
     for (int e = 0; e < PER; e++) v[e] = 0.f;
     const int kk = k0 + ch * PER;
-    if (p.xp && m < p.m && kk < p.k) {
-      // the previous linear's partials, added in K order, + bias, activation, rounded as it would have been stored
+    if (p.xp && m < p.m && kk + PER <= p.k && p.xp_slabs <= 8) {
+      // the previous linear's partials, added in K order, + bias, activation, rounded as it would have been stored; all
+      // loads of the (at most eight) slabs are in flight before the first addition
+      float4 q[8][2];
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) {
+        if (ks < p.xp_slabs) {
+          const float4* src = reinterpret_cast<const float4*>(p.xp + ((long long)ks * kDlMaxM + m) * p.k + kk);
+          q[ks][0] = __ldcg(src); q[ks][1] = __ldcg(src + 1);
+        } else {
+          q[ks][0] = make_float4(0.f, 0.f, 0.f, 0.f); q[ks][1] = q[ks][0];
+        }
+      }
+      float t[PER];
+#pragma unroll
+      for (int e = 0; e < PER; e++) t[e] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < 8; ks++) {
+        if (ks < p.xp_slabs) {
+          t[0] += q[ks][0].x; t[1] += q[ks][0].y; t[2] += q[ks][0].z; t[3] += q[ks][0].w;
+          t[4] += q[ks][1].x; t[5] += q[ks][1].y; t[6] += q[ks][1].z; t[7] += q[ks][1].w;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < PER; e++) {
+        if (p.xp_bias) t[e] += Cvt<T>::to(reinterpret_cast<const T*>(p.xp_bias)[kk + e]);
+        v[e] = Cvt<T>::to(Cvt<T>::from(apply_act(t[e], (Act)p.xp_act)));
+      }
+    } else if (p.xp && m < p.m && kk < p.k) {
       for (int e = 0; e < PER; e++) {
         if (kk + e < p.k) {
           float t = 0.f;
@@ -314,6 +367,7 @@ __global__ void __launch_bounds__(kDlThreads) decode_linear_kernel(const DecodeL
   pdl_trigger();
   if (p.ln_gamma) dl_ln_stats<T>(p, sm);
   dl_partial<T>(p, sm, n0, k0, (int)blockIdx.y, wv);
+  if (p.partial_only) return;     // the consumer adds the partials up; the end of this grid orders them before its reads
   const int k_slabs = gridDim.y;
   // the last CTA of this column slab finishes it
   __threadfence();
@@ -345,19 +399,29 @@ bool decode_linear_eligible(const GemmDesc& d) {
   if (d.a_row % n16 != 0 || (reinterpret_cast<uintptr_t>(d.a) & 15u) != 0 || d.k % 8 != 0) return false;   // 16-byte loads of x
   if (d.ln_gamma && (d.k % n16 != 0 || d.k > 256 * n16)) return false;                                     // a row fits the registers of one warp
   const int64_t ks = (d.k + kDlRows - 1) / kDlRows;
-  if (ks > 64 || ks * d.n > (1 << 18)) return false;                                                      // workspace: [k_slabs][16][n] floats
+  if (ks > 64 || ks * kDlMaxM * d.n > (int64_t)kDecodeRegionFloats) return false;                         // one workspace region: [k_slabs][16][n] floats
   return true;
 }
 
-Status decode_linear(cudaStream_t s, const GemmDesc& d) {
+float* decode_partial_region(int region) {
+  float* base = skinny_partials();
+  return base ? base + (size_t)region * kDecodeRegionFloats : nullptr;
+}
+
+Status decode_linear(cudaStream_t s, const GemmDesc& d, const DecodeLinearOpts& o) {
   if (!decode_linear_eligible(d)) return Status::invalid("decode_linear: shape or layout not supported");
-  float* partial = skinny_partials();
+  if (o.region < 0 || o.region >= kDecodeRegions) return Status::invalid("decode_linear: partial region");
+  if (o.xp && (o.xp_slabs < 1 || o.xp_slabs > 64)) return Status::invalid("decode_linear: partial slabs of the input");
+  if (((d.k + kDlRows - 1) / kDlRows) * kDlMaxM * d.n > (int64_t)kDecodeRegionFloats) return Status::invalid("decode_linear: partials exceed a workspace region");
+  float* partial = decode_partial_region(o.region);
   unsigned int* counters = skinny_counters();
   if (!partial || !counters) return Status::compute("decode_linear: the kernel workspace is not initialised");
   DecodeLinearParams p;
   p.x = d.a; p.w = d.b; p.y = d.c; p.bias = d.ep.bias; p.residual = d.ep.residual; p.ln_gamma = d.ln_gamma; p.ln_beta = d.ln_beta; p.ln_eps = d.ln_eps;
   p.act = (int)d.ep.act; p.m = (int)d.m; p.n = (int)d.n; p.k = (int)d.k;
   p.x_row = d.a_row; p.w_row = d.b_row; p.y_row = d.c_row; p.partial = partial; p.counters = counters;
+  p.partial_only = o.partial_only ? 1 : 0;
+  p.xp = o.xp; p.xp_slabs = o.xp_slabs; p.xp_bias = o.xp_bias; p.xp_act = (int)o.xp_act;
   cudaError_t e;
   dim3 grid((unsigned)((d.n + kDlCols - 1) / kDlCols), (unsigned)((d.k + kDlRows - 1) / kDlRows), 1);
   if (d.dtype == DType::BF16) e = launch_pdl(decode_linear_kernel<__nv_bfloat16>, grid, dim3(kDlThreads), 0, s, p);

@@ -185,13 +185,27 @@ Status launch_wait_runs_out(cudaStream_t s, int code, unsigned long long limit_n
 
 // Decode step against a preallocated KV cache [B, heads, t_max, 64]: writes the new token's key / value row at index
 // *len_ptr and attends over rows 0 .. *len_ptr (q, k, v of the new token are the thirds of qkv's [B, 3 * heads * 64] rows).
+// `part` non-null: q / k / v arrive as the `slabs` float partials [slab][16][3 * heads * 64] an unfinished projection left
+// (decode_linear with partial_only); the kernel adds them, adds `bias` and rounds as the projection would have.
 Status attention_decode(cudaStream_t s, DType dt, const void* qkv, void* kcache, void* vcache, void* out, const int* len_ptr, int batch, int heads,
-                        int t_max, float scale);
+                        int t_max, float scale, const float* part = nullptr, int slabs = 0, const void* bias = nullptr);
 // Linear layer of a decode step (at most 16 rows against a [K, N] MODEL WEIGHT, i.e. a matrix no kernel of the step
 // writes: its loads are issued ahead of the programmatic dependency wait); takes the layer_norm prologue of GemmDesc
 // and the bias / activation / residual epilogue.
 bool decode_linear_eligible(const GemmDesc& d);
-Status decode_linear(cudaStream_t s, const GemmDesc& d);
+// The split-K partials live in one of kDecodeRegions regions of the workspace, so that an unfinished result
+// (partial_only: no last-CTA reduction; the consumer adds the partials up) survives until its consumer has run while
+// other linears use another region. xp: the A operand is such an unfinished result, act(sum of xp_slabs partials +
+// xp_bias) rounded to the storage type (d.a is then unused, d.k is the producer's n).
+constexpr int kDecodeRegions = 3;
+constexpr size_t kDecodeRegionFloats = (size_t)1 << 20;     // 4 MB each
+struct DecodeLinearOpts {
+  int region = 0;
+  bool partial_only = false;
+  const float* xp = nullptr; int xp_slabs = 0; const void* xp_bias = nullptr; Act xp_act = Act::None;
+};
+float* decode_partial_region(int region);
+Status decode_linear(cudaStream_t s, const GemmDesc& d, const DecodeLinearOpts& o = DecodeLinearOpts());
 // End of a decode step: history[step] = tok, pos_ids = len + 1, step and len advance (all in device memory).
 Status decode_finish(cudaStream_t s, const int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps);
 Status decode_reset(cudaStream_t s, int* counters, int32_t* pos_ids, int batch, int len);
