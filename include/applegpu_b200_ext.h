@@ -281,7 +281,7 @@ APPLEGPU_API int32_t applegpu_gpt2_decoder_launches_per_step(uint64_t decoder);
 APPLEGPU_API int32_t applegpu_gpt2_decoder_uses_graph(uint64_t decoder);
 /* engine 0 (default): one kernel per op, chained by programmatic dependent launches inside the captured step. engine 1:
  * embeddings and all layers of a step as one persistent cooperative kernel with grid-wide barriers between phases; the
- * same arithmetic in the same order, so the same tokens. Measured slower (0.73 against 0.56 ms per step for GPT-2-small at
+ * same arithmetic in the same order, so the same tokens. Measured slower (0.65 against 0.50 ms per step for GPT-2-small at
  * batch 8: a software grid barrier costs about what a programmatic kernel boundary costs, and the per-op kernels keep
  * more CTAs resident); kept as an option. */
 APPLEGPU_API int32_t applegpu_gpt2_decoder_set_engine(uint64_t decoder, int32_t engine);
