@@ -203,20 +203,21 @@ class Gpt2Decoder {
     g.dtype = dtype; g.b_dtype = dtype; g.a = xn(); g.b = w[0].data();
     g.m = B; g.n = cfg.vocab; g.k = D; g.batch = 1; g.batch_inner = 1;
     g.a_row = D; g.a_col = 1; g.a_batch = 0; g.b_row = 1; g.b_col = D; g.b_batch = 0; g.c_row = cfg.vocab; g.c_batch = 0;
+    unsigned long long* finish_keys = nullptr;
     if (dtype != DType::F32 && std::string(k::matmul_path(g)) == "tcgen05") {
-      cudaError_t ce = cudaMemsetAsync(keys(), 0, (size_t)B * 8, s);
-      if (ce != cudaSuccess) return Status::compute(std::string("decoder: ") + cudaGetErrorString(ce));
+      // the keys are zero here: prefill clears them and every step's last kernel clears them again after reading them
       g.c = nullptr; g.ep.argmax_keys = keys();
       AG_RETURN_IF_ERROR(k::matmul(s, g));
-      AG_RETURN_IF_ERROR(k::argmax_finalize(s, keys(), tok(), B));
+      finish_keys = keys();        // no finalize launch: the step's last kernel turns the keys into tokens
+      launches_per_step += 1;
     } else {
       g.c = logits();
       AG_RETURN_IF_ERROR(k::matmul(s, g));
       TView lg = TView::make(logits(), dtype, {(int64_t)B, (int64_t)cfg.vocab});
       AG_RETURN_IF_ERROR(k::argmax(s, lg, TView::make(tok(), DType::I32, {B})));
+      launches_per_step += 2;
     }
-    launches_per_step += 2;
-    AG_RETURN_IF_ERROR(k::decode_finish(s, tok(), history(), pos_ids(), counters(), counters() + 1, B, cfg.max_len));
+    AG_RETURN_IF_ERROR(k::decode_finish(s, tok(), history(), pos_ids(), counters(), counters() + 1, B, cfg.max_len, finish_keys));
     launches_per_step++;
     return Status::OK();
   }
@@ -288,6 +289,11 @@ Status decoder_prefill(uint64_t handle, const std::vector<TensorRec>& kvs, const
   cudaError_t e = cudaMemcpyAsync(dec->tok(), first_tokens.data(), (size_t)c.batch * 4, cudaMemcpyDeviceToDevice, ctx.stream);
   if (e != cudaSuccess) return Status::compute(std::string("decoder: ") + cudaGetErrorString(e));
   AG_RETURN_IF_ERROR(k::decode_reset(ctx.stream, dec->counters(), dec->pos_ids(), c.batch, prompt_len));
+  {
+    // the row-argmax keys of the LM head start at zero; from then on each step's last kernel clears them after reading them
+    cudaError_t ce = cudaMemsetAsync(dec->keys(), 0, (size_t)c.batch * 8, ctx.stream);
+    if (ce != cudaSuccess) return Status::compute(std::string("decoder: ") + cudaGetErrorString(ce));
+  }
   dec->prompt_len = prompt_len; dec->steps_done = 0; dec->primed = true;
   return Status::OK();
 }

@@ -689,21 +689,34 @@ void decode_layers_fill_entry(void* host_table, int l, const void* const* w12, v
 
 // End of a decode step: the picked tokens go into the history, the next step's position ids are written, and the
 // step and length counters advance. One block; every thread reads the counters before thread 0 changes them.
-__global__ void decode_finish_kernel(const int32_t* __restrict__ tok, int32_t* __restrict__ history, int32_t* __restrict__ pos_ids, int* step_ptr, int* len_ptr,
-                                     int batch, int max_steps) {
+// `keys` non-null: the step's tokens are still the (value, column) keys the LM head's row-argmax epilogue merged; this
+// kernel turns them into token ids itself (what argmax_finalize does: no key and the sticky-NaN key both mean column 0)
+// and clears them for the next step, which saves the step a launch and a memset.
+__global__ void decode_finish_kernel(int32_t* __restrict__ tok, int32_t* __restrict__ history, int32_t* __restrict__ pos_ids, int* step_ptr, int* len_ptr,
+                                     int batch, int max_steps, unsigned long long* __restrict__ keys) {
   pdl_wait();
   pdl_trigger();
   const int step = *step_ptr, len = *len_ptr;
   __syncthreads();
   for (int t = threadIdx.x; t < batch; t += blockDim.x) {
-    if (step < max_steps) history[(long long)step * batch + t] = tok[t];
+    int32_t token;
+    if (keys) {
+      const unsigned long long k = keys[t];
+      token = (k == 0ull || k == 0xffffffffffffffffull) ? 0 : (int32_t)(0xffffffffu - (uint32_t)(k & 0xffffffffu));
+      keys[t] = 0ull;
+      tok[t] = token;
+    } else {
+      token = tok[t];
+    }
+    if (step < max_steps) history[(long long)step * batch + t] = token;
     pos_ids[t] = len + 1;
   }
   if (threadIdx.x == 0) { *step_ptr = step + 1; *len_ptr = len + 1; }
 }
 
-Status decode_finish(cudaStream_t s, const int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps) {
-  cudaError_t le = launch_pdl(decode_finish_kernel, dim3(1), dim3(128), 0, s, tok, history, pos_ids, step_ptr, len_ptr, batch, max_steps);
+Status decode_finish(cudaStream_t s, int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps,
+                     unsigned long long* keys) {
+  cudaError_t le = launch_pdl(decode_finish_kernel, dim3(1), dim3(128), 0, s, tok, history, pos_ids, step_ptr, len_ptr, batch, max_steps, keys);
   if (le != cudaSuccess) return cuda_status(le, "decode_finish");
   return Status::OK();
 }

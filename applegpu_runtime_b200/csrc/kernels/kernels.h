@@ -207,7 +207,9 @@ struct DecodeLinearOpts {
 float* decode_partial_region(int region);
 Status decode_linear(cudaStream_t s, const GemmDesc& d, const DecodeLinearOpts& o = DecodeLinearOpts());
 // End of a decode step: history[step] = tok, pos_ids = len + 1, step and len advance (all in device memory).
-Status decode_finish(cudaStream_t s, const int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps);
+// `keys` non-null: tok is first filled from the row-argmax keys of the LM head (and the keys cleared for the next step).
+Status decode_finish(cudaStream_t s, int32_t* tok, int32_t* history, int32_t* pos_ids, int* step_ptr, int* len_ptr, int batch, int max_steps,
+                     unsigned long long* keys = nullptr);
 Status decode_reset(cudaStream_t s, int* counters, int32_t* pos_ids, int batch, int len);
 // Programmatic dependent launch can be switched off for a region of host code (stream capture of a decode step).
 void set_pdl_override(int on);   // -1 follow the environment, 0 off, 1 on
